@@ -1,0 +1,156 @@
+// Between the QKV projection and attention, in one pass over the packed rows:
+// per-head RMSNorm of q and k, rotary position encoding of q and k, and the write of k and v
+// into the paged cache at this step's slots.
+//
+// It replaces five launches of the reference: `rmsnorm_head_kernel` on q and on k
+// (src/backend/cuda/norm/norm_final.cu:28-45), `rope_kernel` on q and on k
+// (src/backend/cuda/rope/rope_v1.cu:11-45) and `store_kv_kernel`
+// (src/backend/cuda/attention/attention.cu:18-33).  Those fix head_dim = 128 and at most 32
+// heads; here any head_dim up to 512 that is a multiple of 2, any head counts, and a rotary
+// width below the head width (src/module/rope.zig:86-88) are taken.
+//
+// Layouts: qkv[t] = [q heads | k heads | v heads], each head `hd` values, row stride given;
+// q is normalised and rotated in place; cache arrays are [page][kv_head][page_size][hd]
+// (src/memory/page_atten.zig:2) and slot = page * page_size + offset, slot < 0 = do not store.
+// cos/sin tables are float32 [max_positions, rot/2], computed on the host in float64.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+constexpr int MAX_PAIRS = 8;   // rot/2 <= 256 per lane-strided loop of 32
+constexpr int MAX_TAIL = 16;   // hd - rot <= 512
+
+template <typename T>
+__global__ void attn_prep_kernel(T* __restrict__ qkv, long long row_stride, T* __restrict__ kcache,
+                                 T* __restrict__ vcache, const int* __restrict__ positions,
+                                 const int* __restrict__ slots, const float* __restrict__ cos_tab,
+                                 const float* __restrict__ sin_tab, const float* __restrict__ q_gain,
+                                 const float* __restrict__ k_gain, int n_tokens, int nq, int nk, int nkv_cache,
+                                 int hd, int rot, int page_size, float eps, float q_off, float k_off) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    const int heads = nq + 2 * nk;
+    const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads);
+    const int h = (int)(item % heads);
+    T* x = qkv + (size_t)t * row_stride + (size_t)h * hd;
+    const int slot = slots ? slots[t] : -1;
+
+    if (h >= nq + nk) {  // a value head: copy into the cache
+        if (slot < 0 || !vcache) return;
+        const int kvh = h - nq - nk;
+        T* dst = vcache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = x[i];
+        return;
+    }
+    const bool is_q = h < nq;
+    const float* gain = is_q ? q_gain : k_gain;
+    const float goff = is_q ? q_off : k_off;
+    const int half = rot / 2;
+
+    float a[MAX_PAIRS], b[MAX_PAIRS], tail[MAX_TAIL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_PAIRS; ++i) {
+        const int p = lane + 32 * i;
+        if (p < half) {
+            a[i] = to_float(x[p]);
+            b[i] = to_float(x[p + half]);
+            ss += a[i] * a[i] + b[i] * b[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_TAIL; ++i) {
+        const int e = rot + lane + 32 * i;
+        if (e < hd) {
+            tail[i] = to_float(x[e]);
+            ss += tail[i] * tail[i];
+        }
+    }
+    if (gain) {
+        ss = warp_sum(ss);
+        const float rinv = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+        for (int i = 0; i < MAX_PAIRS; ++i) {
+            const int p = lane + 32 * i;
+            if (p < half) {
+                a[i] = a[i] * rinv * (gain[p] + goff);
+                b[i] = b[i] * rinv * (gain[p + half] + goff);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i) {
+            const int e = rot + lane + 32 * i;
+            if (e < hd) tail[i] = tail[i] * rinv * (gain[e] + goff);
+        }
+    }
+    if (cos_tab) {
+        const int pos = positions[t];
+        const float* c = cos_tab + (size_t)pos * half;
+        const float* s = sin_tab + (size_t)pos * half;
+#pragma unroll
+        for (int i = 0; i < MAX_PAIRS; ++i) {
+            const int p = lane + 32 * i;
+            if (p < half) {
+                const float x0 = a[i], x1 = b[i], cs = c[p], sn = s[p];
+                a[i] = x0 * cs - x1 * sn;
+                b[i] = x1 * cs + x0 * sn;
+            }
+        }
+    }
+    T* dst;
+    if (is_q) {
+        dst = x;
+    } else {
+        if (slot < 0 || !kcache) return;
+        const int kvh = h - nq;
+        dst = kcache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd;
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_PAIRS; ++i) {
+        const int p = lane + 32 * i;
+        if (p < half) {
+            dst[p] = from_float<T>(a[i]);
+            dst[p + half] = from_float<T>(b[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_TAIL; ++i) {
+        const int e = rot + lane + 32 * i;
+        if (e < hd) dst[e] = from_float<T>(tail[i]);
+    }
+}
+
+// nk = number of k (and v) heads present in the packed rows: num_kv_heads for a layer that
+// writes its cache, 0 for a layer that only reads another layer's cache.
+LLMK_EXPORT int llmk_attn_prep(void* qkv, long long row_stride, void* kcache, void* vcache, const int* positions,
+                               const int* slots, const float* cos_tab, const float* sin_tab, const float* q_gain,
+                               const float* k_gain, int n_tokens, int nq, int nk, int nkv_cache, int hd, int rot,
+                               int page_size, float eps, float q_off, float k_off, int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (hd <= 0 || hd % 2 != 0 || hd > 512) LLMK_FAIL("attn_prep: head_dim %d must be even and at most 512", hd);
+    if (rot < 0 || rot > hd || rot % 2 != 0) LLMK_FAIL("attn_prep: rotary width %d must be even and at most head_dim %d", rot, hd);
+    if (rot / 2 > 32 * MAX_PAIRS || hd - rot > 32 * MAX_TAIL) LLMK_FAIL("attn_prep: head_dim %d / rotary width %d too large", hd, rot);
+    if (nq < 0 || nk < 0 || nq + nk <= 0) LLMK_FAIL("attn_prep: bad head counts nq=%d nk=%d", nq, nk);
+    if (nk > 0 && (page_size <= 0 || nkv_cache < nk)) LLMK_FAIL("attn_prep: bad cache geometry page_size=%d kv heads=%d", page_size, nkv_cache);
+    if (!cos_tab) rot = 0;
+    if (cos_tab && (!sin_tab || !positions)) LLMK_FAIL("attn_prep: rotary tables need sin and positions");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int warps = 4;
+    const long long items = (long long)n_tokens * (nq + 2 * nk);
+    const long long blocks = (items + warps - 1) / warps;
+    if (blocks > 2147483647LL) LLMK_FAIL("attn_prep: too many rows");
+    if (dtype == LLMK_F32)
+        attn_prep_kernel<float><<<(unsigned)blocks, warps * 32, 0, s>>>(
+            (float*)qkv, row_stride, (float*)kcache, (float*)vcache, positions, slots, cos_tab, sin_tab, q_gain,
+            k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off, k_off);
+    else if (dtype == LLMK_BF16)
+        attn_prep_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, s>>>(
+            (bf16*)qkv, row_stride, (bf16*)kcache, (bf16*)vcache, positions, slots, cos_tab, sin_tab, q_gain, k_gain,
+            n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off, k_off);
+    else
+        LLMK_FAIL("attn_prep: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH("attn_prep");
+    return LLMK_OK;
+}

@@ -1,0 +1,197 @@
+// Row-wise kernels around the matrix products: embedding gather, residual add fused with
+// RMSNorm (optionally on gathered rows), and the gated activation of the feed-forward.
+//
+// What they replace in the reference: `embedding_kernel` (src/backend/cuda/embedding/embedding.cu:3-13),
+// `add_kernel` + `rmsnorm_row_kernel` (src/backend/cuda/arithmetic/add_v1.cu:3-15,
+// src/backend/cuda/norm/norm_final.cu:9-26), `gather_rows_kernel`
+// (src/backend/cuda/memory/memcpy.cu:58-67) and `silu_kernel` + `mul_kernel`
+// (src/backend/cuda/activation/silu_v1.cu:6-18, src/backend/cuda/arithmetic/mul_v1.cu:3-16).
+// The residual stream is float32 here, so the sum x + delta is never rounded to bfloat16.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+// ---------------------------------------------------------------- embedding gather
+// out[t, :] = table[ids[t], :] widened to float32.  An id outside [0, V) gives a zero row and
+// raises *bad (the host checks ids before the step, this is the device-side guard the
+// reference's kernel lacks).
+template <typename T>
+__global__ void embed_rows_kernel(float* __restrict__ out, const T* __restrict__ table,
+                                  const int* __restrict__ ids, int H, int V, int* bad) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0 && bad) atomicAdd(bad, 1);
+    const T* row = table + (size_t)(ok ? id : 0) * H;
+    float* dst = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_float(row[i]) : 0.f;
+}
+
+LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, int n_tokens, int H, int V,
+                                int* bad_flag, int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (H <= 0 || V <= 0) LLMK_FAIL("embed_rows: bad sizes H=%d V=%d", H, V);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == LLMK_F32)
+        embed_rows_kernel<float><<<n_tokens, threads, 0, s>>>(out, (const float*)table, ids, H, V, bad_flag);
+    else if (dtype == LLMK_BF16)
+        embed_rows_kernel<bf16><<<n_tokens, threads, 0, s>>>(out, (const bf16*)table, ids, H, V, bad_flag);
+    else
+        LLMK_FAIL("embed_rows: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH("embed_rows");
+    return LLMK_OK;
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// For output row r, source row s = rows ? rows[r] : r:
+//   v    = resid[s, :] + (delta ? delta[s, :] : 0)          (float32)
+//   resid[s, :] = v                    if write_resid
+//   out[r, :]   = v * (1 / sqrt(mean(v^2) + eps)) * (w + w_offset)      rounded once to T
+// The row is kept in shared memory between the two passes.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ w, T* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps, float w_offset,
+                                   int write_resid) {
+    extern __shared__ float srow[];  // H floats + 33 scratch
+    float* scratch = srow + H;
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* x = resid + (size_t)s * H;
+    const T* d = delta ? delta + (size_t)s * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[i];
+        if (d) v += to_float(d[i]);
+        srow[i] = v;
+        ss += v * v;
+        if (write_resid) x[i] = v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<T>(srow[i] * rinv * (w[i] + w_offset));
+}
+
+LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, const int* rows,
+                                 int n_rows, int H, float eps, float w_offset, int write_resid, int dtype,
+                                 void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    if (H <= 0) LLMK_FAIL("add_rmsnorm: bad width H=%d", H);
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) LLMK_FAIL("add_rmsnorm: width %d needs %zu bytes of shared memory (limit 204800)", H, smem);
+    if (rows && write_resid) LLMK_FAIL("add_rmsnorm: gathered rows cannot be written back");
+    cudaStream_t s = (cudaStream_t)stream;
+    int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define LAUNCH(T)                                                                                            \
+    do {                                                                                                     \
+        if (smem > 48 * 1024) {                                                                              \
+            cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>,                                      \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+            if (e != cudaSuccess) LLMK_FAIL("add_rmsnorm: cannot raise shared memory: %s", cudaGetErrorString(e)); \
+        }                                                                                                    \
+        add_rmsnorm_kernel<T><<<n_rows, threads, smem, s>>>(resid, (const T*)delta, w, (T*)out, rows, H, eps, \
+                                                            w_offset, write_resid);                          \
+    } while (0)
+    if (dtype == LLMK_F32)
+        LAUNCH(float);
+    else if (dtype == LLMK_BF16)
+        LAUNCH(bf16);
+    else
+        LLMK_FAIL("add_rmsnorm: unknown dtype %d", dtype);
+#undef LAUNCH
+    LLMK_CHECK_LAUNCH("add_rmsnorm");
+    return LLMK_OK;
+}
+
+// ------------------------------------------------------------- gated activation
+// in [n, 2F] holds gate in columns [0, F) and up in [F, 2F); out[n, F] = silu(gate) * up with
+// silu(g) = g / (1 + exp(-g)) in float32, rounded once.
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int n, int F, int ld_in) {
+    const size_t total = (size_t)n * F;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(idx / F), col = (int)(idx % F);
+        const float g = to_float(in[(size_t)row * ld_in + col]);
+        const float u = to_float(in[(size_t)row * ld_in + F + col]);
+        out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+template <typename T>
+__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int n, int F, int ld_in) {
+    constexpr int N = Vec16<T>::N;
+    const int fv = F / N;
+    const size_t total = (size_t)n * fv;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(idx / fv), cv = (int)(idx % fv);
+        const T* base = in + (size_t)row * ld_in + (size_t)cv * N;
+        Vec16<T> g, u, o;
+        g.raw = *reinterpret_cast<const decltype(g.raw)*>(base);
+        u.raw = *reinterpret_cast<const decltype(u.raw)*>(base + F);
+        float gf[N], uf[N], of[N];
+        g.unpack(gf);
+        u.unpack(uf);
+#pragma unroll
+        for (int i = 0; i < N; ++i) of[i] = gf[i] / (1.0f + expf(-gf[i])) * uf[i];
+        o.pack(of);
+        *reinterpret_cast<decltype(o.raw)*>(out + (size_t)row * F + (size_t)cv * N) = o.raw;
+    }
+}
+
+template <typename T>
+static int launch_silu_mul(void* out, const void* in, int n, int F, int ld_in, cudaStream_t s) {
+    constexpr int N = Vec16<T>::N;
+    const bool vec = (F % N == 0) && (ld_in % N == 0) && host_aligned16(out) && host_aligned16(in);
+    const size_t work = vec ? (size_t)n * (F / N) : (size_t)n * F;
+    const int threads = 256;
+    size_t blocks = (work + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks == 0) return LLMK_OK;
+    if (vec)
+        silu_mul_vec_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in);
+    else
+        silu_mul_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in);
+    return LLMK_OK;
+}
+
+LLMK_EXPORT int llmk_silu_mul(void* out, const void* in, int n_rows, int F, int ld_in, int dtype, void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    if (F <= 0 || ld_in < 2 * F) LLMK_FAIL("silu_mul: bad sizes F=%d ld_in=%d", F, ld_in);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == LLMK_F32)
+        launch_silu_mul<float>(out, in, n_rows, F, ld_in, s);
+    else if (dtype == LLMK_BF16)
+        launch_silu_mul<bf16>(out, in, n_rows, F, ld_in, s);
+    else
+        LLMK_FAIL("silu_mul: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH("silu_mul");
+    return LLMK_OK;
+}
+
+// --------------------------------------------------------- convert rows to float32
+// out[n, W] float32 = in[n, W] of type T (used to hand bfloat16 logits out as float32).
+template <typename T>
+__global__ void widen_kernel(float* __restrict__ out, const T* __restrict__ in, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = to_float(in[idx]);
+}
+
+LLMK_EXPORT int llmk_widen(float* out, const void* in, long long total, int dtype, void* stream) {
+    if (total <= 0) return LLMK_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == LLMK_F32)
+        widen_kernel<float><<<(int)blocks, 256, 0, s>>>(out, (const float*)in, (size_t)total);
+    else if (dtype == LLMK_BF16)
+        widen_kernel<bf16><<<(int)blocks, 256, 0, s>>>(out, (const bf16*)in, (size_t)total);
+    else
+        LLMK_FAIL("widen: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH("widen");
+    return LLMK_OK;
+}

@@ -1,0 +1,462 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+One `Executor.step(entries)` runs exactly the tokens it is given, as one batch, against the
+cache that earlier steps left: portions of prompts beside single decoded tokens, cut
+anywhere.  It is the reference's `Executor.forward(entries)` (src/executor.zig:530-590) with
+two differences: the caller may pass token ids directly (replay) and gets float32 logits at the
+rows it names (the reference returns only sampled ids, src/executor.zig:669-677).
+
+Host work per step: fill one pinned metadata buffer (`StepMetaBuilder`), ONE host-to-device
+copy, the launches (or one graph replay for a pure-decode step), one device-to-host copy of
+the sampled ids.  A step with more tokens than `max_step_tokens` is cut into passes
+(src/executor.zig:986-1043).
+
+Pages must have been reserved for every position the step writes (`reserve`); the scheduler
+or the replay program does that, as the reference's scheduler calls `ensure`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheError, CacheManager
+from ..cache.storage import CacheStorage, bytes_per_page, plan_groups
+from ..kernels import ops
+from .context import GroupView, StepContext, StepMetaBuilder, Workspace
+from .model import DecoderModel
+
+SEED_STRIDE = 0x9E3779B97F4A7C15
+DEFAULT_SEED = 0x5EED
+MASK64 = (1 << 64) - 1
+
+
+class StepError(ValueError):
+    pass
+
+
+@dataclass
+class EngineLimits:
+    """Engine-side limits (command-line options in the reference, src/cli.zig:33-62)."""
+    max_num_seqs: int = 256          # sequences per step
+    max_model_len: int = 4096        # longest sequence; width of the block tables
+    max_step_tokens: int = 8192      # tokens per forward pass (`--pass-tokens`)
+    page_size: int = 16              # tokens per cache page (`--block-size`)
+    num_pages: Optional[int] = None  # pages per group (`--kv-blocks`); None: from free memory
+    gpu_util: float = 0.9            # share of device memory the process may use
+
+    def __post_init__(self):
+        if self.max_num_seqs <= 0 or self.max_model_len <= 0 or self.page_size <= 0:
+            raise StepError("engine limits must be positive")
+        self.max_step_tokens = max(self.max_step_tokens, self.max_num_seqs)
+
+
+@dataclass
+class StepEntry:
+    req: Hashable
+    tokens: Sequence[int]
+    start: int                              # position of tokens[0] in its sequence
+    want: Sequence[int] = ()                # indices into `tokens` whose logits are wanted
+    temperature: float = 0.0                # for sampled ids
+
+
+@dataclass
+class StepOutput:
+    logits: Optional[torch.Tensor] = None   # float32 [wanted, vocab], device
+    token_ids: Optional[List[int]] = None   # one per wanted row, host
+
+
+class Executor:
+    def __init__(self, model: DecoderModel, limits: EngineLimits, seed: int = DEFAULT_SEED,
+                 eager: bool = False, sync_each: bool = False):
+        self.model = model
+        self.limits = limits
+        self.device = model.device
+        self.dtype = model.dtype
+        self.eager = eager or sync_each
+        self.sync_each = sync_each
+        self.step_seed = seed & MASK64
+        self.n_graph_steps = 0
+        self.n_eager_steps = 0
+        self.launch_count = 0
+        if limits.max_model_len > model.max_positions():
+            raise StepError(f"max_model_len {limits.max_model_len} exceeds the model's "
+                            f"{model.max_positions()} positions")
+        self.max_blocks = (limits.max_model_len + limits.page_size - 1) // limits.page_size
+
+        # caches: one request per cache number of the run list
+        kv_requests, state_requests = {}, {}
+        for item in model.spec.run_order:
+            if item.cache is None:
+                continue
+            mixer = model.layers[item.layer].mixer
+            kv = mixer.cache_request()
+            st = mixer.state_request()
+            for table, req in ((kv_requests, kv), (state_requests, st)):
+                if req is None:
+                    continue
+                if item.cache in table and table[item.cache] != req:
+                    raise StepError(f"run items sharing cache {item.cache} ask for different geometries")
+                table[item.cache] = req
+        self.kv_requests, self.state_requests = kv_requests, state_requests
+        self.group_specs, self.group_index = plan_groups(kv_requests)
+        pages = self._pages_per_group()
+        self.cache = CacheManager(self.group_specs, pages, limits.page_size, limits.max_num_seqs)
+        self.storage = CacheStorage(kv_requests, state_requests, self.group_index, pages, limits.page_size,
+                                    limits.max_num_seqs, self.dtype, self.device)
+        self.layer_caches = [self.storage.layer_cache(item.cache, item.writes_cache) for item in model.spec.run_order]
+        self._unique_mixers = []
+        for layer in model.layers:
+            m = getattr(layer, "mixer", None)
+            if m is not None and hasattr(m, "prepare_step"):
+                self._unique_mixers.append(m)
+
+        self.workspace = Workspace(self.device, limits.max_step_tokens)
+        Tm, Sm, G = limits.max_step_tokens, limits.max_num_seqs, len(self.group_specs)
+        words = 64 + 10 * Tm + 10 * Sm + G * (Tm + Sm * self.max_blocks + 8)
+        self.meta_host = [torch.empty(words, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.meta_events = [None, None]
+        self.meta_dev = torch.zeros(words, dtype=torch.int32, device=self.device)
+        self._meta_turn = 0
+        self.sample_scratch = torch.empty(ops.sample_scratch_bytes(max(Sm, 64)) // 4, dtype=torch.float32,
+                                          device=self.device)
+        self.ids_host = torch.empty(max(Tm, Sm), dtype=torch.int32).pin_memory()
+        self.graphs: Dict[int, dict] = {}
+
+    # ------------------------------------------------------------------ sizing
+    def _pages_per_group(self) -> List[int]:
+        lim = self.limits
+        if lim.num_pages is not None:
+            if lim.num_pages * lim.page_size < lim.max_model_len:
+                raise StepError(f"{lim.num_pages} pages of {lim.page_size} tokens cannot hold one sequence of "
+                                f"max_model_len {lim.max_model_len}")
+            return [lim.num_pages] * len(self.group_specs)
+        # From free memory, as the reference does (src/graph/scheduler.zig:386-403):
+        # (total * util - used - activations reserve) / bytes per page over all layers.
+        free, total = torch.cuda.mem_get_info(self.device)
+        used = total - free
+        budget = int(total * lim.gpu_util) - used - self._activation_reserve()
+        per_page = sum(bytes_per_page(self.kv_requests, self.group_index, g, lim.page_size, self.dtype)
+                       for g in range(len(self.group_specs)))
+        if per_page == 0:
+            return [0] * len(self.group_specs)
+        n = budget // per_page
+        cap = lim.max_num_seqs * self.max_blocks   # more than every sequence at full length is never used
+        n = int(min(n, cap))
+        if n * lim.page_size < lim.max_model_len:
+            raise StepError(f"the memory budget leaves {max(n, 0)} pages, fewer than one sequence of "
+                            f"max_model_len {lim.max_model_len} needs")
+        return [n] * len(self.group_specs)
+
+    def _activation_reserve(self) -> int:
+        spec = self.model.spec
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        widest = 0
+        for ls in spec.layers:
+            ffn = getattr(ls, "ffn", None)
+            widest = max(widest, 3 * getattr(ffn, "intermediate_size", 0) + 6 * spec.hidden_size)
+        return self.limits.max_step_tokens * (widest * elem + spec.hidden_size * 4) \
+            + 2 * 64 * spec.vocab_size * 4 + (64 << 20)
+
+    # ------------------------------------------------------------------ cache front
+    def admit(self, req: Hashable) -> bool:
+        slot = self.cache.admit(req)
+        if self.cache.fresh_state:
+            self.storage.reset_state(self.cache.fresh_state)
+            self.cache.fresh_state.clear()
+        return slot is not None
+
+    def reserve(self, req: Hashable, start: int, end: int) -> bool:
+        return self.cache.reserve(req, start, end)
+
+    def can_reserve(self, req: Hashable, start: int, end: int) -> bool:
+        return self.cache.can_reserve(req, start, end)
+
+    def release(self, req: Hashable) -> None:
+        self.cache.release(req)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry], sample: bool = False, return_logits: bool = True) -> StepOutput:
+        """Run the entries' tokens as one batch.  Logits rows (and sampled ids) come in the order
+        of the entries and, inside an entry, of its `want` list."""
+        entries = [e for e in entries]
+        self._validate(entries)
+        n_tokens = sum(len(e.tokens) for e in entries)
+        if n_tokens == 0:
+            return StepOutput(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+                              if return_logits else None, [] if sample else None)
+        pure_decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if pure_decode and sample and not return_logits and not self.eager:
+            return self._graph_step(entries)
+        passes = self._passes(entries)
+        logits_parts, ids_parts, order = [], [], []
+        for sub, keys in passes:
+            out = self._eager_pass(sub, sample, return_logits or len(passes) > 1)
+            if return_logits or len(passes) > 1:
+                logits_parts.append(out.logits)
+            if sample:
+                ids_parts += out.token_ids
+            order += keys
+        self.n_eager_steps += 1
+        result = StepOutput()
+        # restore the order (entry, k-th want) when passes or want lists permuted it
+        wanted = [(i, k) for i, e in enumerate(entries) for k in range(len(e.want))]
+        perm = None
+        if order != wanted:
+            where = {key: r for r, key in enumerate(order)}
+            perm = [where[key] for key in wanted]
+        if return_logits:
+            logits = logits_parts[0] if len(logits_parts) == 1 else torch.cat(logits_parts, dim=0)
+            if perm is not None:
+                logits = logits.index_select(0, torch.as_tensor(perm, dtype=torch.long, device=self.device))
+            result.logits = logits
+        if sample:
+            result.token_ids = [ids_parts[r] for r in perm] if perm is not None else ids_parts
+        return result
+
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        lim = self.limits
+        V = self.model.spec.vocab_size
+        if len(entries) > lim.max_num_seqs:
+            raise StepError(f"{len(entries)} sequences in one step, the limit is {lim.max_num_seqs}")
+        seen = set()
+        for e in entries:
+            if e.req in seen:
+                raise StepError(f"request {e.req!r} appears twice in one step")
+            seen.add(e.req)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.req!r} brings no tokens")
+            if e.start < 0 or e.start + n > lim.max_model_len:
+                raise StepError(f"request {e.req!r}: positions [{e.start}, {e.start + n}) exceed max_model_len "
+                                f"{lim.max_model_len}")
+            toks = np.asarray(e.tokens)
+            if toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= V:
+                bad = [int(t) for t in toks.tolist() if not (isinstance(t, int) and 0 <= t < V)][:1]
+                raise StepError(f"request {e.req!r}: token id {bad[0] if bad else '?'} outside the vocabulary [0, {V})")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.req!r}: wanted place {w} outside its {n} tokens")
+            if not self.cache.is_admitted(e.req):
+                raise StepError(f"request {e.req!r} was not admitted")
+            for g in self.cache.groups:
+                table = g.table(e.req)
+                last_page = (e.start + n - 1) // lim.page_size
+                first_live = g.first_needed_position(e.start) // lim.page_size
+                if last_page >= len(table) or any(table[i] < 0 for i in range(first_live, last_page + 1)):
+                    raise StepError(f"request {e.req!r}: no pages reserved for positions up to {e.start + n - 1}")
+
+    def _passes(self, entries: Sequence[StepEntry]):
+        """Cut the entries into passes of at most `max_step_tokens` tokens.  Each pass is a list of
+        entries plus the (entry index, k-th want) key of each of its wanted rows, in row order."""
+        cap = self.limits.max_step_tokens
+        passes, cur, keys, room = [], [], [], cap
+        for i, e in enumerate(entries):
+            off = 0
+            n = len(e.tokens)
+            while off < n:
+                take = min(n - off, room)
+                want_here = [(k, w - off) for k, w in enumerate(e.want) if off <= w < off + take]
+                cur.append(StepEntry(e.req, e.tokens[off:off + take], e.start + off, [w for _, w in want_here],
+                                     e.temperature))
+                keys += [(i, k) for k, _ in want_here]
+                off += take
+                room -= take
+                if room == 0:
+                    passes.append((cur, keys))
+                    cur, keys, room = [], [], cap
+        if cur:
+            passes.append((cur, keys))
+        return passes
+
+    # -- metadata
+    def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0):
+        """Fill and upload the step's metadata; returns (StepContext, want rows view, temps view,
+        seed view, number of wanted rows)."""
+        lim = self.limits
+        ps = lim.page_size
+        S_real = len(entries)
+        S = max(S_real, pad_to)
+        q_lens = [len(e.tokens) for e in entries] + [1] * (S - S_real)
+        starts = [e.start for e in entries] + [0] * (S - S_real)
+        T = sum(q_lens)
+        pure_decode = all(n == 1 for n in q_lens)
+        b = StepMetaBuilder(q_lens, starts, pure_decode)
+        self.step_seed = (self.step_seed + SEED_STRIDE) & MASK64
+        b.add("seed", np.array([self.step_seed], dtype=np.uint64).view(np.int32))
+        ids = np.zeros(T, dtype=np.int32)
+        pos = np.zeros(T, dtype=np.int32)
+        seq_of = np.zeros(T, dtype=np.int32)
+        cu_q = np.zeros(S + 1, dtype=np.int32)
+        ctx_len = np.zeros(S, dtype=np.int32)
+        state_slots = np.full(S, -1, dtype=np.int32)
+        want_rows, temps = [], []
+        t = 0
+        for s, e in enumerate(entries):
+            n = q_lens[s]
+            ids[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos[t:t + n] = np.arange(e.start, e.start + n, dtype=np.int32)
+            seq_of[t:t + n] = s
+            ctx_len[s] = e.start + n
+            state_slots[s] = self.cache.state.slot(e.req)
+            want_rows += [t + w for w in e.want]
+            temps += [e.temperature] * len(e.want)
+            t += n
+            cu_q[s + 1] = t
+        for s in range(S_real, S):          # padding rows: one token, no keys, written nowhere
+            seq_of[t] = s
+            t += 1
+            cu_q[s + 1] = t
+            want_rows.append(t - 1)
+            temps.append(0.0)
+        b.add("ids", ids)
+        b.add("positions", pos)
+        b.add("seq_of_token", seq_of)
+        b.add("cu_q", cu_q)
+        b.add("ctx_len", ctx_len)
+        b.add("state_slots", state_slots)
+        b.add("want_rows", np.asarray(want_rows, dtype=np.int32))
+        b.add("temps", np.asarray(temps, dtype=np.float32), dtype=np.float32)
+        for gi, g in enumerate(self.cache.groups):
+            slots = np.full(T, -1, dtype=np.int32)
+            bt = np.zeros((S, self.max_blocks), dtype=np.int32)
+            t = 0
+            for s, e in enumerate(entries):
+                table = g.table(e.req)
+                n = q_lens[s]
+                tab = np.asarray(table, dtype=np.int32)
+                bt[s, :len(table)] = tab
+                p = np.arange(e.start, e.start + n)
+                slots[t:t + n] = tab[p // ps] * ps + p % ps
+                t += n
+            b.add(f"slots_{gi}", slots)
+            b.add(f"block_tables_{gi}", bt)
+        for m in self._unique_mixers:
+            m.prepare_step(b)
+
+        turn = self._meta_turn
+        self._meta_turn ^= 1
+        if self.meta_events[turn] is not None:
+            self.meta_events[turn].synchronize()
+        layout, total = b.pack_into(self.meta_host[turn])
+        self.meta_dev[:total].copy_(self.meta_host[turn][:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.meta_events[turn] = ev
+
+        def view(name):
+            off, size, dt = layout[name]
+            v = self.meta_dev[off:off + size]
+            return v.view(torch.float32) if dt == np.float32 else v
+
+        ctx = StepContext(
+            n_tokens=T, n_seqs=S, dtype=self.dtype, device=self.device, workspace=self.workspace,
+            requests=[e.req for e in entries], starts=starts, q_lens=q_lens, pure_decode=pure_decode,
+            max_ctx=int(ctx_len.max()) if S else 0, max_ctx_bound=lim.max_model_len,
+            ids=view("ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_len=view("ctx_len"),
+            state_slots=view("state_slots"), seq_of_token=view("seq_of_token"),
+            groups=[GroupView(view(f"slots_{gi}"), view(f"block_tables_{gi}"), self.max_blocks)
+                    for gi in range(len(self.cache.groups))],
+            extra={n: view(n) for n in layout})
+        return ctx, view("want_rows"), view("temps"), view("seed"), len(want_rows)
+
+    def _maybe_sync(self):
+        if self.sync_each:
+            torch.cuda.synchronize(self.device)
+
+    def _eager_pass(self, entries: Sequence[StepEntry], sample: bool, return_logits: bool) -> StepOutput:
+        ctx, want_rows, temps, seed, n_want = self._build_meta(entries)
+        out = StepOutput()
+        if n_want == 0:
+            self.model.hidden_states(ctx, self.layer_caches)
+            if return_logits:
+                out.logits = torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+            if sample:
+                out.token_ids = []
+            return out
+        logits = self.model.forward(ctx, self.layer_caches, want_rows, n_want)
+        if sample:
+            ids_dev = self.workspace.flat("sampled_ids", max(n_want, self.limits.max_num_seqs), torch.int32)[:n_want]
+            if n_want * ops.SAMPLE_SPLIT * 2 > self.sample_scratch.numel():
+                self.sample_scratch = torch.empty(n_want * ops.SAMPLE_SPLIT * 2, dtype=torch.float32, device=self.device)
+            ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
+            host = self.ids_host[:n_want] if n_want <= self.ids_host.numel() else torch.empty(n_want, dtype=torch.int32).pin_memory()
+            host.copy_(ids_dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            out.token_ids = host.tolist()
+        if return_logits:
+            out.logits = logits
+        return out
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def buckets(self) -> List[int]:
+        """Batch sizes with a captured graph: 1, 2, 4, 8, 16, then steps of 16, and max_num_seqs
+        (src/executor.zig:613-626)."""
+        top = self.limits.max_num_seqs
+        out = [b for b in (1, 2, 4, 8, 16) if b <= top]
+        out += list(range(32, top + 1, 16))
+        if top not in out:
+            out.append(top)
+        return out
+
+    def _bucket_for(self, n: int) -> int:
+        for b in self.buckets():
+            if b >= n:
+                return b
+        raise StepError(f"{n} sequences exceed max_num_seqs {self.limits.max_num_seqs}")
+
+    def _capture(self, bucket: int) -> dict:
+        """Warm up once with an all-padding batch (loads kernels, lets the library pick its
+        algorithms, creates the workspaces), then record the same launches into a graph
+        (src/executor.zig:609-660)."""
+        V = self.model.spec.vocab_size
+        logits = torch.empty((bucket, V), dtype=torch.float32, device=self.device)
+        ids_dev = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+
+        def run():
+            ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket)
+            ctx.fixed_shapes = True
+            self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
+            ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
+
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            run()
+            run()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        # the metadata upload stays outside the graph: build it first, then capture the launches
+        ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket)
+        ctx.fixed_shapes = True
+        torch.cuda.synchronize(self.device)
+        self.workspace.frozen = True
+        try:
+            with torch.cuda.graph(graph, stream=stream):
+                self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
+                ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
+        finally:
+            self.workspace.frozen = False
+        entry = {"graph": graph, "ids": ids_dev, "logits": logits}
+        self.graphs[bucket] = entry
+        return entry
+
+    def capture_all(self) -> None:
+        for b in self.buckets():
+            if b not in self.graphs:
+                self._capture(b)
+
+    def _graph_step(self, entries: Sequence[StepEntry]) -> StepOutput:
+        bucket = self._bucket_for(len(entries))
+        g = self.graphs.get(bucket) or self._capture(bucket)
+        self._build_meta(entries, pad_to=bucket)
+        g["graph"].replay()
+        n = len(entries)
+        host = self.ids_host[:n]
+        host.copy_(g["ids"][:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.n_graph_steps += 1
+        return StepOutput(None, host.tolist())

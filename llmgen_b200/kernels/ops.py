@@ -1,0 +1,204 @@
+"""Python bindings of the CUDA kernels: thin functions from torch tensors to the C ABI.
+
+torch is used as the allocator and for stream handles only; every function launches on
+`torch.cuda.current_stream()`, allocates nothing and never synchronises, so a sequence of
+calls can be captured into a CUDA graph.  There is no CPU path: a tensor that is not on a
+CUDA device raises `KernelError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 storage, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernel arguments must live on a CUDA device (there is no CPU path)")
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.llmk_last_error().decode("utf-8", "replace"))
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    if t.dim() < 2:
+        return t.shape[-1] if t.dim() == 1 else 1
+    if t.stride(-1) != 1:
+        raise KernelError("kernel operands must be contiguous in their last dimension")
+    return t.stride(-2)
+
+
+# ---------------------------------------------------------------------------- elementwise
+def embed_rows(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tensor] = None) -> None:
+    """out[t] (float32 [n, H]) = table[ids[t]]; ids int32 on the device."""
+    lib = build.load("elementwise")
+    n, H = out.shape
+    _check(lib, lib.llmk_embed_rows(_ptr(out), _ptr(table), _ptr(ids), c_int(n), c_int(H), c_int(table.shape[0]),
+                                    _ptr(bad_flag), c_int(dtype_code(table.dtype)), _stream()))
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, weight_offset: float = 0.0, rows: Optional[torch.Tensor] = None,
+                write_resid: bool = True) -> None:
+    """resid (float32 [n, H]) += delta; out = rmsnorm(resid) * (weight + offset).
+
+    With `rows` (int32 [m]) output row r is computed from source row rows[r] and the
+    residual is left untouched."""
+    lib = build.load("elementwise")
+    H = resid.shape[-1]
+    n_rows = out.shape[0]
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: residual and gain must be float32")
+    if delta is not None and (delta.dtype != out.dtype or not delta.is_contiguous()):
+        raise KernelError("add_rmsnorm: delta must be contiguous and of the output's dtype")
+    if rows is not None:
+        write_resid = False
+    _check(lib, lib.llmk_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), c_int(n_rows),
+                                     c_int(H), c_float(eps), c_float(weight_offset), c_int(1 if write_resid else 0),
+                                     c_int(dtype_code(out.dtype)), _stream()))
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out[n, F] = silu(gate_up[:, :F]) * gate_up[:, F:2F]."""
+    lib = build.load("elementwise")
+    n, F = out.shape
+    _check(lib, lib.llmk_silu_mul(_ptr(out), _ptr(gate_up), c_int(n), c_int(F), c_int(_row_stride(gate_up)),
+                                  c_int(dtype_code(out.dtype)), _stream()))
+
+
+def widen(out: torch.Tensor, src: torch.Tensor) -> None:
+    """out (float32) = src, element by element (both contiguous)."""
+    lib = build.load("elementwise")
+    _check(lib, lib.llmk_widen(_ptr(out), _ptr(src), c_longlong(src.numel()), c_int(dtype_code(src.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------------ attn_prep
+def attn_prep(qkv: torch.Tensor, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+              positions: Optional[torch.Tensor], slots: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+              sin: Optional[torch.Tensor], q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
+              nq: int, nk: int, hd: int, rot: int, page_size: int, eps: float,
+              q_offset: float = 0.0, k_offset: float = 0.0) -> None:
+    """Per-head norm and rotary encoding of q (in place) and k, and the cache write of k, v."""
+    lib = build.load("attn_prep")
+    n = qkv.shape[0]
+    nkv_cache = kcache.shape[1] if kcache is not None else 0
+    _check(lib, lib.llmk_attn_prep(_ptr(qkv), c_longlong(_row_stride(qkv)), _ptr(kcache), _ptr(vcache),
+                                   _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(q_gain), _ptr(k_gain),
+                                   c_int(n), c_int(nq), c_int(nk), c_int(nkv_cache), c_int(hd), c_int(rot),
+                                   c_int(page_size), c_float(eps), c_float(q_offset), c_float(k_offset),
+                                   c_int(dtype_code(qkv.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------- matrix products
+def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores (float32 multiply-add, fixed k order)."""
+    lib = build.load("gemm_simt")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm: shapes a{list(a.shape)} w{list(w.shape)} out{list(out.shape)} do not fit")
+    if a.dtype != w.dtype:
+        raise KernelError("gemm: a and w must share a dtype")
+    _check(lib, lib.llmk_gemm_simt(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
+                                   c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(_row_stride(out)),
+                                   c_int(1 if accumulate else 0), c_int(dtype_code(a.dtype)),
+                                   c_int(dtype_code(out.dtype)), _stream()))
+
+
+GEMV_MAX_ROWS = 4
+
+
+def gemv_bf16(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 4 in bfloat16, float32 accumulation."""
+    lib = build.load("gemv")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemv: shapes a{list(a.shape)} w{list(w.shape)} out{list(out.shape)} do not fit")
+    _check(lib, lib.llmk_gemv_bf16(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
+                                   c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(_row_stride(out)),
+                                   c_int(1 if accumulate else 0), c_int(dtype_code(out.dtype)), _stream()))
+
+
+def gemv_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= GEMV_MAX_ROWS and a.shape[1] % 8 == 0
+            and _row_stride(a) % 8 == 0 and _row_stride(w) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+# ------------------------------------------------------------------------------ attention
+def attention_tile_queries(nq: int, nkv: int) -> int:
+    """Queries per tile of `paged_attention` for this group size."""
+    lib = build.load("attention")
+    return int(lib.llmk_attention_tile_queries(c_int(nq), c_int(nkv)))
+
+
+def attention_scratch_floats(n_tokens: int, nq: int, hd: int, num_parts: int) -> int:
+    return 0 if num_parts <= 1 else n_tokens * nq * num_parts * (hd + 2)
+
+
+def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                    block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
+                    tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, n_tokens: int, nq: int, nkv: int,
+                    hd: int, page_size: int, window: int, scale: float, num_parts: int = 1, part_size: int = 0,
+                    scratch: Optional[torch.Tensor] = None) -> None:
+    """out[t, nq*hd] = causal GQA of q[t] over the paged cache (see csrc/attention.cu)."""
+    lib = build.load("attention")
+    if num_parts > 1:
+        need = attention_scratch_floats(n_tokens, nq, hd, num_parts)
+        if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"paged_attention: split into {num_parts} parts needs {need} float32 of scratch")
+    _check(lib, lib.llmk_paged_attention(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(q_stride),
+                                         _ptr(kcache), _ptr(vcache), _ptr(block_tables), c_int(max_blocks),
+                                         _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq), _ptr(tile_q0), c_int(n_tiles),
+                                         c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
+                                         c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
+                                         _ptr(scratch), c_int(dtype_code(q.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------------- sampling
+SAMPLE_SPLIT = 32
+
+
+def sample_scratch_bytes(max_rows: int) -> int:
+    return max_rows * SAMPLE_SPLIT * 8
+
+
+def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, seed: torch.Tensor,
+           scratch: torch.Tensor) -> None:
+    """out_ids[s] (int32) = argmax or Gumbel-max draw of logits[s] (float32 [n, V])."""
+    lib = build.load("sampling")
+    n, V = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    if scratch.numel() * scratch.element_size() < sample_scratch_bytes(n):
+        raise KernelError("sample: scratch too small")
+    _check(lib, lib.llmk_sample(_ptr(out_ids), _ptr(logits), c_longlong(_row_stride(logits)), _ptr(temps),
+                                _ptr(seed), c_int(n), c_int(V), _ptr(scratch), _stream()))

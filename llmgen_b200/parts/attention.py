@@ -1,0 +1,134 @@
+"""Causal grouped-query attention over the paged cache, as a mixer."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import FULL, WINDOW
+from ..kernels import ops
+from .base import KVRequest, LayerCache, Mixer
+from .linear import linear
+from .registry import build_position, norm_class, register_mixer
+from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
+
+NUM_SMS = 148
+
+
+class GQAAttention(Mixer):
+    """q, k, v projections (packed into one [(nq + 2 nkv) hd, H] matrix at load) -> per-head
+    RMSNorm of q and k, rotary encoding, cache write (one kernel) -> attention over the block
+    table -> output projection.
+
+    Order and formulas: src/models/qwen3.zig:192-207 (q/k norm before RoPE, norm weights
+    shared by all heads), src/module/attention.zig:85-92, src/backend/cpu/attention.zig:64-118.
+    A run item with `writes=False` projects q only and reads the cache another item wrote."""
+
+    @staticmethod
+    def weight_decls(spec: AttentionSpec):
+        qd, kd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        decls = [WeightDecl(spec.q_proj, (qd, spec.hidden_size)), WeightDecl(spec.k_proj, (kd, spec.hidden_size)),
+                 WeightDecl(spec.v_proj, (kd, spec.hidden_size)), WeightDecl(spec.o_proj, (spec.hidden_size, qd))]
+        for n in (spec.q_norm, spec.k_norm):
+            if n is not None:
+                decls += norm_class(n).weight_decls(n)
+        return decls
+
+    @staticmethod
+    def kernel_modules(spec):
+        return ("attn_prep", "attention", "gemm_simt", "gemv")
+
+    def __init__(self, spec: AttentionSpec, weights, dtype, device):
+        if spec.num_heads % spec.num_kv_heads != 0:
+            raise ValueError(f"attention: {spec.num_heads} heads are not a multiple of {spec.num_kv_heads} kv heads")
+        if spec.head_dim % 8 != 0 or spec.head_dim > 512:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 8, at most 512")
+        for n in (spec.q_norm, spec.k_norm):
+            if n is not None and (n.kind != "rmsnorm" or n.dim != spec.head_dim):
+                raise ValueError("attention: per-head norms must be RMSNorm over head_dim")
+        self.spec = spec
+        self.dtype = dtype
+        self.nq, self.nkv, self.hd = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        self.w_qkv = torch.cat([weights.host_tensor(spec.q_proj), weights.host_tensor(spec.k_proj),
+                                weights.host_tensor(spec.v_proj)], dim=0).to(device=device, dtype=dtype).contiguous()
+        self.w_q = self.w_qkv[: self.nq * self.hd]
+        self.w_o = weights.device_tensor(spec.o_proj, dtype, device)
+        self.q_gain = weights.device_tensor(spec.q_norm.weight, dtype, device) if spec.q_norm else None
+        self.k_gain = weights.device_tensor(spec.k_norm.weight, dtype, device) if spec.k_norm else None
+        self.norm_eps = float((spec.q_norm or spec.k_norm).eps) if (spec.q_norm or spec.k_norm) else 0.0
+        if spec.q_norm and spec.k_norm and spec.q_norm.eps != spec.k_norm.eps:
+            raise ValueError("attention: q and k norms must share eps")
+        self.q_off = float(spec.q_norm.weight_offset) if spec.q_norm else 0.0
+        self.k_off = float(spec.k_norm.weight_offset) if spec.k_norm else 0.0
+        self.position = build_position(spec.position, weights, dtype, device) if spec.position is not None else None
+        self.window = int(spec.window or 0)
+        self.bq = ops.attention_tile_queries(self.nq, self.nkv)
+        self.tiles_name = f"attention_tiles_bq{self.bq}"
+
+    # -- what the engine asks
+    def cache_request(self) -> KVRequest:
+        return KVRequest(WINDOW if self.window else FULL, self.window, self.nkv, self.hd)
+
+    def max_positions(self):
+        return self.position.max_positions if self.position is not None else None
+
+    def prepare_step(self, builder) -> None:
+        """Tiles of `bq` queries: (sequence, first query of the tile) pairs."""
+        if builder.has(self.tiles_name + "_seq"):
+            return
+        seq, q0 = [], []
+        for s, n in enumerate(builder.q_lens):
+            for start in range(0, max(n, 1), self.bq):
+                seq.append(s)
+                q0.append(start)
+        builder.add(self.tiles_name + "_seq", seq)
+        builder.add(self.tiles_name + "_q0", q0)
+
+    def _split(self, ctx):
+        """(num_parts, part_size) for flash-decoding; only pure-decode steps are split."""
+        if not ctx.pure_decode:
+            return 1, 0
+        G = self.nq // self.nkv
+        chunks = (G + 15) // 16
+        blocks = max(1, ctx.n_seqs * self.nkv * chunks)
+        longest = ctx.max_ctx_bound if ctx.fixed_shapes else ctx.max_ctx
+        if self.window:
+            longest = min(longest, self.window)
+        by_sms = (2 * NUM_SMS + blocks - 1) // blocks
+        by_len = max(1, longest // 128)
+        parts = max(1, min(by_sms, by_len, 64))
+        if self.window:
+            # parts are ranges of absolute key positions: a window far into a long context
+            # would leave most of an even split empty, so windowed layers are not split
+            return 1, 0
+        return parts, 0
+
+    def forward(self, ctx, x: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        T = ctx.n_tokens
+        ws = ctx.workspace
+        group = ctx.groups[cache.group]
+        nk = self.nkv if cache.writes else 0
+        width = (self.nq + 2 * nk) * self.hd
+        qkv = ws.buffer("attn_qkv", T, (self.nq + 2 * self.nkv) * self.hd, self.dtype)
+        if cache.writes:
+            linear(x, self.w_qkv, qkv)
+            packed = qkv
+        else:
+            packed = qkv[:, :width]
+            linear(x, self.w_q, packed)
+        cos, sin = self.position.tables() if self.position is not None else (None, None)
+        rot = self.position.rotary_dim if self.position is not None else 0
+        ops.attn_prep(packed, cache.k, cache.v, ctx.positions, group.slots, cos, sin, self.q_gain, self.k_gain,
+                      self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off)
+        o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
+        tile_seq = ctx.array(self.tiles_name + "_seq")
+        tile_q0 = ctx.array(self.tiles_name + "_q0")
+        parts, part_size = self._split(ctx)
+        scratch = None
+        if parts > 1:
+            scratch = ws.flat("attn_split", ops.attention_scratch_floats(T, self.nq, self.hd, parts), torch.float32)
+        ops.paged_attention(o, packed, packed.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks,
+                            ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
+                            self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch)
+        return linear(o, self.w_o, ws.buffer("mixer_out", T, self.spec.hidden_size, self.dtype))
+
+
+register_mixer("attention", GQAAttention)

@@ -1,0 +1,91 @@
+"""What each kind of part must offer.  These classes are documentation with defaults; a part
+need not inherit from them as long as it has the same methods.
+
+All parts:
+    weight_decls(spec) -> [WeightDecl]        static; tensors read from the model file
+    kernel_modules(spec) -> (str, ...)        static; CUDA modules to build before first use
+    __init__(spec, weights, dtype, device)    take tensors from the `WeightStore`
+
+Norm:
+    add_norm(resid, delta, out, rows=None)    resid(float32) += delta; out = norm(resid);
+                                              with `rows`: output row r from source row rows[r],
+                                              resid untouched
+Position encoding:
+    tables()                                  whatever its mixer's kernel needs (cos, sin)
+Mixer:
+    cache_request() -> KVRequest | None       pages it needs (group kind, kv heads, head width)
+    state_request() -> StateRequest | None    fixed-size per-request state (shape, dtype)
+    prepare_step(builder)                     optional: add int32 arrays to the step's metadata
+    forward(ctx, x, cache) -> tensor [T, H]   x is the normed input; `cache` is this run
+                                              item's `LayerCache`
+Feed-forward:
+    forward(ctx, x) -> tensor [T, H]
+Block:
+    mixer                                     the block's mixer (the engine asks it for cache)
+    forward(ctx, resid, delta, cache) -> delta_out
+                                              `delta` is the previous block's output not yet
+                                              added to the residual (None for the first block);
+                                              the block adds it inside its first norm
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class KVRequest:
+    """Paged keys and values: which group's pages, and the geometry of one token's entry."""
+    group_kind: str          # cache.manager.FULL or WINDOW
+    window: int              # 0 for FULL
+    num_kv_heads: int
+    head_dim: int
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """One array of `shape` and `dtype` per request, zero when the request starts."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """What a run item hands to its mixer."""
+    k: Optional[torch.Tensor] = None        # [pages, kv_heads, page_size, head_dim]
+    v: Optional[torch.Tensor] = None
+    group: int = 0                          # index into ctx.groups
+    page_size: int = 0
+    writes: bool = True                     # False: read what another run item wrote
+    state: Optional[torch.Tensor] = None    # [slots, *shape]
+
+
+class Part:
+    @staticmethod
+    def weight_decls(spec):
+        return []
+
+    @staticmethod
+    def kernel_modules(spec):
+        return ()
+
+
+class Mixer(Part):
+    def cache_request(self) -> Optional[KVRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def prepare_step(self, builder) -> None:
+        pass
+
+    def forward(self, ctx, x, cache: LayerCache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x):
+        raise NotImplementedError

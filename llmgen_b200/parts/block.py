@@ -1,0 +1,52 @@
+"""The arrangement of a layer's parts."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .base import LayerCache, Part
+from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward_class, mixer_class, norm_class,
+                       register_block)
+from .spec import PreNormBlockSpec
+
+
+class PreNormBlock(Part):
+    """x1 = x + mixer(norm(x)); x2 = x1 + ffn(norm(x1))  (src/models/qwen3.zig:224-236).
+
+    The residual stream is float32 and lives in one buffer.  Each sum is folded into the norm
+    that follows it: the block receives the previous block's output as `delta`, adds it in its
+    first norm, adds the mixer's output in its second norm and returns the feed-forward's
+    output as the next `delta`."""
+
+    @staticmethod
+    def weight_decls(spec: PreNormBlockSpec):
+        return (norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm)
+                + mixer_class(spec.mixer).weight_decls(spec.mixer)
+                + norm_class(spec.ffn_norm).weight_decls(spec.ffn_norm)
+                + feed_forward_class(spec.ffn).weight_decls(spec.ffn))
+
+    @staticmethod
+    def kernel_modules(spec: PreNormBlockSpec):
+        return (tuple(norm_class(spec.mixer_norm).kernel_modules(spec.mixer_norm))
+                + tuple(mixer_class(spec.mixer).kernel_modules(spec.mixer))
+                + tuple(feed_forward_class(spec.ffn).kernel_modules(spec.ffn)))
+
+    def __init__(self, spec: PreNormBlockSpec, weights, dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer_norm = build_norm(spec.mixer_norm, weights, dtype, device)
+        self.mixer = build_mixer(spec.mixer, weights, dtype, device)
+        self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device)
+        self.ffn = build_feed_forward(spec.ffn, weights, dtype, device)
+
+    def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], cache: LayerCache) -> torch.Tensor:
+        T, H = resid.shape
+        normed = ctx.workspace.buffer("block_normed", T, H, self.dtype)
+        self.mixer_norm.add_norm(resid, delta, normed)
+        mixed = self.mixer.forward(ctx, normed, cache)
+        self.ffn_norm.add_norm(resid, mixed, normed)
+        return self.ffn.forward(ctx, normed)
+
+
+register_block("prenorm", PreNormBlock)
