@@ -1,0 +1,211 @@
+"""Command line in the reference's manner (src/cli.zig:1-125, src/llmgen.zig:35-492):
+
+    python -m llmgen_b200 chat  [prompt] [max_new] [options]   generate and print `token ids: ...`
+    python -m llmgen_b200 bench <workload.json>    [options]   run a workload, print a JSON summary
+
+Options keep the reference's names and meanings:
+    --model <dir>  --temp <f>  --max-model-len <n>  --max-num-seqs <n>  --max-batched-tokens <n>
+    --pass-tokens <n>  --block-size <n>  --gpu-util <f>  --kv-blocks <n>
+    --policy prefill_first|chunked  --chunk <n>  --out <path>  --dup <n>  --eager  --sync-each
+Added: --dtype bfloat16|float32, --seed <n>, --random <config.json> (random weights drawn from
+--seed instead of a model folder).  The model is a folder with config.json and model.safetensors
+(default: environment variable LLMGEN_MODEL).
+
+There is no tokenizer here (the engine's contract is token ids in, token ids out): the chat
+prompt is a list of token ids, "12,7,99" or "12 7 99", or @file with a JSON list.  The
+reference's REPL, --single and --no-kv-cache belong to its text edge and its legacy path and
+are not offered.
+
+Workload format (src/bench/workload.zig:6-16):
+    {"name": ..., "rounds": [[{"prompt_ids": [...], "max_tokens": n, "temperature": 0.6,
+                               "ignore_eos": true}, ...], ...]}
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import resource
+import statistics
+import sys
+import time
+from typing import List
+
+from .engine.scheduler import CHUNKED, PREFILL_FIRST
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="llmgen_b200", description="Single-GPU inference engine for sm_100a")
+    ap.add_argument("cmd", choices=["chat", "bench"])
+    ap.add_argument("arg0", nargs="?", help="chat: prompt token ids; bench: workload.json")
+    ap.add_argument("max_new", nargs="?", type=int, default=2000, help="chat: most tokens to generate")
+    ap.add_argument("--model", default=os.environ.get("LLMGEN_MODEL"))
+    ap.add_argument("--random", metavar="CONFIG_JSON", help="draw random weights for this config.json instead of --model")
+    ap.add_argument("--seed", type=int, default=0x5EED)
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    ap.add_argument("--temp", type=float, default=0.0)
+    ap.add_argument("--max-model-len", type=int, default=4096)
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-batched-tokens", type=int, default=16384)
+    ap.add_argument("--pass-tokens", type=int, default=8192)
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--gpu-util", type=float, default=0.9)
+    ap.add_argument("--kv-blocks", type=int, default=0)
+    ap.add_argument("--policy", choices=[PREFILL_FIRST, CHUNKED], default=PREFILL_FIRST)
+    ap.add_argument("--chunk", type=int, default=2048)
+    ap.add_argument("--out")
+    ap.add_argument("--dup", type=int, default=1)
+    ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--sync-each", action="store_true")
+    return ap
+
+
+def parse_prompt(text: str) -> List[int]:
+    if text.startswith("@"):
+        with open(text[1:], "r", encoding="utf-8") as f:
+            return [int(t) for t in json.load(f)]
+    return [int(t) for t in text.replace(",", " ").split()]
+
+
+def make_llm(args):
+    from .engine.api import LLM, random_model
+    if args.random:
+        with open(args.random, "r", encoding="utf-8") as f:
+            model = random_model(json.load(f), args.seed, args.dtype)
+    elif args.model:
+        model = args.model
+    else:
+        raise SystemExit("no model: give --model <dir>, set LLMGEN_MODEL, or use --random <config.json>")
+    return LLM(model, dtype=args.dtype, seed=args.seed, max_num_seqs=args.max_num_seqs,
+               max_model_len=args.max_model_len, max_batched_tokens=args.max_batched_tokens,
+               pass_tokens=args.pass_tokens, block_size=args.block_size, gpu_util=args.gpu_util,
+               kv_blocks=args.kv_blocks, policy=args.policy, chunk=args.chunk, eager=args.eager,
+               sync_each=args.sync_each)
+
+
+def chat(args) -> int:
+    from .sampling import SamplingParams
+    if not args.arg0:
+        raise SystemExit("chat needs a prompt: token ids such as \"12,7,99\" or @ids.json")
+    prompt = parse_prompt(args.arg0)
+    llm = make_llm(args)
+    print(f"[load] {llm.load_seconds:.2f} s", file=sys.stderr)
+    room = args.max_model_len - len(prompt)
+    params = SamplingParams(temperature=args.temp, max_tokens=max(1, min(args.max_new, room)), ignore_eos=False)
+    t0 = time.perf_counter()
+    requests = [llm.engine.add_request(prompt, params) for _ in range(max(1, args.dup))]
+    first = None
+    while not llm.engine.is_finished():
+        llm.engine.step()
+        for r, tok in llm.engine.last_emitted:
+            if r is requests[0]:
+                if first is None:
+                    first = time.perf_counter()
+                print(tok, end=" ", flush=True)
+    t1 = time.perf_counter()
+    print()
+    ids = requests[0].completion
+    n = len(ids)
+    if first is not None:
+        per = (t1 - first) / max(1, n - 1) * 1e3
+        print(f"[chat] TTFT {(first - t0) * 1e3:.1f} ms, {per:.2f} ms/token, {n} tokens", file=sys.stderr)
+    print("token ids: " + " ".join(str(t) for t in ids))
+    if args.dup > 1:
+        # the reference's batch-consistency check: copies of one prompt must agree (greedy)
+        if any(r.completion != ids for r in requests[1:]):
+            print("error: outputs of duplicated requests differ", file=sys.stderr)
+            return 1
+        print(f"[chat] {args.dup} duplicated requests agree", file=sys.stderr)
+    return 0
+
+
+def percentiles(values: List[float]) -> dict:
+    """numpy-style linear percentiles (src/bench/recorder.zig:5-40)."""
+    if not values:
+        return {"mean": 0.0, "p50": 0.0, "p90": 0.0, "p99": 0.0, "max": 0.0}
+    v = sorted(values)
+
+    def pct(p):
+        k = (len(v) - 1) * p / 100.0
+        lo = int(k)
+        hi = min(lo + 1, len(v) - 1)
+        return v[lo] + (v[hi] - v[lo]) * (k - lo)
+    return {"mean": sum(v) / len(v), "p50": pct(50), "p90": pct(90), "p99": pct(99), "max": v[-1]}
+
+
+def run_round(llm, reqs, ttft_ms, itl_ms) -> tuple:
+    from .sampling import SamplingParams
+    t0 = time.perf_counter()
+    handles = [llm.engine.add_request(r["prompt_ids"], SamplingParams(
+        temperature=float(r.get("temperature", 0.6)), max_tokens=int(r["max_tokens"]),
+        ignore_eos=bool(r.get("ignore_eos", True)))) for r in reqs]
+    steps = 0
+    while not llm.engine.is_finished():
+        llm.engine.step()
+        steps += 1
+    wall = time.perf_counter() - t0
+    for h in handles:
+        ttft_ms.append((h.first_token_time - h.arrival_time) * 1e3)
+        itl_ms += [(b - a) * 1e3 for a, b in zip(h.token_times, h.token_times[1:])]
+    llm.engine.release_finished()
+    return wall, steps, sum(len(h.completion) for h in handles)
+
+
+def bench(args) -> int:
+    import torch
+    from .sampling import SamplingParams
+    if not args.arg0:
+        raise SystemExit("bench needs a workload.json")
+    with open(args.arg0, "r", encoding="utf-8") as f:
+        wl = json.load(f)
+    rounds = wl.get("rounds") or []
+    if not rounds or not rounds[0]:
+        raise SystemExit("empty workload")
+    llm = make_llm(args)
+    reqs0 = rounds[0]
+    in_tok = sum(len(r["prompt_ids"]) for r in reqs0)
+    print(f"[bench] {wl.get('name', '?')}: {len(reqs0)} requests x {len(rounds)} rounds, input {in_tok} tokens", file=sys.stderr)
+    # warm-up, as the reference does: the first ids of request 0, 64 tokens at temperature 1
+    warm = min(64, max(1, args.max_model_len - 8))
+    llm.generate([reqs0[0]["prompt_ids"][:8]], SamplingParams(temperature=1.0, max_tokens=warm, ignore_eos=True))
+    ex = llm.executor
+    pre0, graph0, eager0 = llm.engine.scheduler.num_preemptions, ex.n_graph_steps, ex.n_eager_steps
+    ttft_ms, itl_ms, walls, steps, out_tok = [], [], [], 0, 0
+    for i, reqs in enumerate(rounds):
+        wall, n, produced = run_round(llm, reqs, ttft_ms, itl_ms)
+        walls.append(wall)
+        steps += n
+        if i == 0:
+            out_tok = produced
+        print(f"[bench] round {i + 1}: {wall:.3f} s, {produced / wall:.1f} tok/s", file=sys.stderr)
+    leak = not ex.cache.all_free()
+    if leak:
+        print(f"[bench] cache pages leaked: free {ex.cache.num_free_pages()}", file=sys.stderr)
+    wall = statistics.median(walls)
+    free, total = torch.cuda.mem_get_info()
+    pages = ex.cache.groups[0].pool.num_pages
+    summary = {
+        "engine": "llmgen_b200", "workload": wl.get("name", "?"), "n_requests": len(reqs0), "repeat": len(rounds),
+        "input_tokens": in_tok, "output_tokens": out_tok, "wall_s": wall,
+        "throughput_out": out_tok / wall, "throughput_total": (out_tok + in_tok) / wall,
+        "ttft_ms": percentiles(ttft_ms), "itl_ms": percentiles(itl_ms),
+        "peak_rss_mb": resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 1024.0,
+        "device_used_mb": (total - free) / 2 ** 20, "weights_mb": llm.model.weight_bytes() / 2 ** 20,
+        "kv_cache_mb": ex.storage.bytes_held() / 2 ** 20, "kv_tokens": pages * ex.limits.page_size,
+        "load_s": llm.load_seconds, "preemptions": llm.engine.scheduler.num_preemptions - pre0, "steps": steps,
+        "graph_steps": ex.n_graph_steps - graph0, "eager_steps": ex.n_eager_steps - eager0,
+        "policy": args.policy, "dtype": args.dtype, "kv_leak": leak,
+    }
+    text = json.dumps(summary, indent=2)
+    print(text)
+    if args.out:
+        with open(args.out, "w", encoding="utf-8") as f:
+            f.write(text + "\n")
+    return 0
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    if args.sync_each:
+        args.eager = True
+    return chat(args) if args.cmd == "chat" else bench(args)

@@ -17,7 +17,7 @@ from typing import List, Sequence, Tuple
 
 from ..sampling.params import SamplingParams
 from .executor import Executor, StepEntry
-from .scheduler import FINISHED, BatchScheduler, Request, Scheduled, SchedulerConfig, SchedulerError
+from .scheduler import FINISHED, PREFILL_FIRST, BatchScheduler, Request, Scheduled, SchedulerConfig, SchedulerError
 
 
 class EngineError(RuntimeError):
@@ -38,6 +38,12 @@ class Engine:
     def __init__(self, executor: Executor, config: SchedulerConfig):
         self.executor = executor
         config.max_num_seqs = min(config.max_num_seqs, executor.limits.max_num_seqs)
+        if config.policy == PREFILL_FIRST and config.max_num_batched_tokens < executor.limits.max_model_len:
+            # whole prompts only: a preempted sequence is computed again in one portion, so the
+            # token budget must admit the longest sequence or it could never come back
+            raise EngineError(f"policy prefill_first needs max_batched_tokens ({config.max_num_batched_tokens}) "
+                              f">= max_model_len ({executor.limits.max_model_len}); use --policy chunked "
+                              f"for a smaller budget")
         self.scheduler = BatchScheduler(executor, config)
         self.requests: List[Request] = []
         self.next_id = 0

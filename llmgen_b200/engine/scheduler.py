@@ -114,7 +114,8 @@ class BatchScheduler:
         """State slot and pages for positions [0, upto) of a waiting request, or nothing."""
         if len(self.running) >= self.config.max_num_seqs:
             return False
-        if not self.cache.admit(request.id):
+        admitted = self.cache.admit(request.id)     # a slot number (0 counts) or True; None / False: full
+        if admitted is None or admitted is False:
             return False
         if not self.cache.reserve(request.id, 0, upto):
             self.cache.release(request.id)

@@ -1,0 +1,155 @@
+"""Generation through the Python entry point and the command line: greedy ids against the plain
+implementation, both scheduling policies, preemption when pages run out, CUDA-graph replay
+against eager steps, temperature sampling."""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+import torch
+
+from tests.plain.qwen3_plain import PlainQwen3
+from tests.util import ROOT, TINY, make_folder, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tmp():
+    with tempfile.TemporaryDirectory() as d:
+        yield d
+
+
+def greedy_reference(path, prompts, n_new):
+    m = PlainQwen3(path)
+    return [m.greedy(p, n_new) for p in prompts]
+
+
+@pytest.mark.parametrize("name,policy,eager", [("A", "prefill_first", False), ("A", "chunked", True),
+                                               ("B", "chunked", False), ("C", "prefill_first", True)])
+def test_greedy_generation_matches_plain(tmp, name, policy, eager):
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, name)
+    vocab = TINY[name][0]["vocab_size"]
+    prompts = [random_ids(n, vocab, 40 + i) for i, n in enumerate((5, 17, 33))]
+    ref = greedy_reference(path, prompts, 16)
+    llm = LLM(path, dtype="float32", max_model_len=128, max_num_seqs=4, max_batched_tokens=128, pass_tokens=64,
+              block_size=TINY[name][5], kv_blocks=24, policy=policy, chunk=8, eager=eager)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    assert [o["token_ids"] for o in outs] == ref
+    assert llm.executor.cache.all_free()
+    if not eager:
+        assert llm.executor.n_graph_steps > 0
+
+
+def test_bfloat16_generation_runs_and_agrees_mostly(tmp):
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "A")
+    prompts = [random_ids(n, 256, 50 + i) for i, n in enumerate((9, 40))]
+    ref = greedy_reference(path, prompts, 8)
+    llm = LLM(path, dtype="bfloat16", max_model_len=128, max_num_seqs=4, max_batched_tokens=128, kv_blocks=16)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    for o, r in zip(outs, ref):
+        assert len(o["token_ids"]) == 8 and o["token_ids"][0] == r[0]
+
+
+def test_preemption_recomputes_and_gives_the_same_ids(tmp):
+    """Configuration B's workload: five prompts, four sequences at a time, twelve pages of 32
+    tokens: pages run out, the last running sequence is preempted and later computed again."""
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "B")
+    prompts = [random_ids(n, 384, 60 + i) for i, n in enumerate((1, 9, 40, 64, 100))]
+    ref = greedy_reference(path, prompts, 24)
+    for policy in ("chunked", "prefill_first"):
+        llm = LLM(path, dtype="float32", max_model_len=256, max_num_seqs=4, max_batched_tokens=256, pass_tokens=256,
+                  block_size=32, kv_blocks=12, policy=policy, chunk=16)
+        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+        assert llm.engine.scheduler.num_preemptions > 0
+        assert [o["token_ids"] for o in outs] == ref
+        assert llm.executor.cache.all_free()
+
+
+def test_graph_replay_equals_eager_and_duplicates_agree(tmp):
+    """The reference's `--dup` check (src/llmgen.zig:229-240): copies of one prompt in one batch
+    give identical ids; and graph replay gives what eager steps give."""
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "C")
+    prompt = random_ids(21, 301, 70)
+    outs = {}
+    for eager in (False, True):
+        llm = LLM(path, dtype="bfloat16", max_model_len=128, max_num_seqs=8, max_batched_tokens=128, kv_blocks=64,
+                  eager=eager)
+        res = llm.generate([prompt] * 5, SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True))
+        assert all(r["token_ids"] == res[0]["token_ids"] for r in res)
+        outs[eager] = res[0]["token_ids"]
+        assert (llm.executor.n_graph_steps > 0) == (not eager)
+    assert outs[False] == outs[True]
+
+
+def test_temperature_sampling_is_seeded(tmp):
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "B")
+    prompts = [random_ids(n, 384, 80 + i) for i, n in enumerate((9, 40))]
+    runs = []
+    for seed in (7, 7, 8):
+        llm = LLM(path, dtype="float32", seed=seed, max_model_len=256, max_num_seqs=4, max_batched_tokens=256,
+                  block_size=32, kv_blocks=16, policy="chunked", chunk=16)
+        runs.append([o["token_ids"] for o in llm.generate(prompts, SamplingParams(temperature=0.7, max_tokens=20, ignore_eos=True))])
+    assert runs[0] == runs[1] and runs[0] != runs[2]
+    greedy = greedy_reference(path, prompts, 20)
+    assert runs[0] != greedy
+
+
+def test_eos_ends_a_request(tmp):
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "A")
+    prompt = random_ids(12, 256, 90)
+    ref = greedy_reference(path, [prompt], 10)[0]
+    llm = LLM(path, dtype="float32", max_model_len=64, max_num_seqs=2, max_batched_tokens=64, kv_blocks=8)
+    llm.engine.scheduler.config.eos_token_ids = (ref[4],)
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=10))[0]["token_ids"]
+    stop = ref.index(ref[4])
+    assert out == ref[:stop + 1]
+
+
+def test_requests_that_cannot_be_served_are_refused(tmp):
+    from llmgen_b200 import LLM, SamplingParams
+    from llmgen_b200.engine.engine import EngineError
+    path = make_folder(tmp, "A")
+    llm = LLM(path, dtype="float32", max_model_len=64, max_num_seqs=2, max_batched_tokens=64, kv_blocks=4)
+    with pytest.raises(EngineError, match="too long"):
+        llm.engine.add_request([1] * 60, SamplingParams(max_tokens=10))
+    with pytest.raises(EngineError, match="empty"):
+        llm.engine.add_request([], SamplingParams(max_tokens=10))
+    with pytest.raises(EngineError, match="vocabulary"):
+        llm.engine.add_request([1, 256], SamplingParams(max_tokens=1))
+    with pytest.raises(Exception, match="max_model_len"):
+        LLM(path, dtype="float32", max_model_len=4096)            # beyond the model's positions
+
+
+def test_command_line_chat_and_bench(tmp):
+    path = make_folder(tmp, "A")
+    prompt = random_ids(11, 256, 95)
+    ref = greedy_reference(path, [prompt], 6)[0]
+    cmd = [sys.executable, "-m", "llmgen_b200", "chat", ",".join(map(str, prompt)), "6", "--model", path,
+           "--dtype", "float32", "--max-model-len", "64", "--kv-blocks", "8", "--max-num-seqs", "4",
+           "--max-batched-tokens", "64", "--dup", "3"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("token ids:")][0]
+    assert [int(x) for x in line.split(":")[1].split()] == ref
+    workload = {"name": "tiny", "rounds": [[{"prompt_ids": random_ids(20, 256, 96 + i), "max_tokens": 8} for i in range(3)]] * 2}
+    wl = os.path.join(tmp, "workload.json")
+    with open(wl, "w") as f:
+        json.dump(workload, f)
+    out_json = os.path.join(tmp, "bench_out.json")
+    cmd = [sys.executable, "-m", "llmgen_b200", "bench", wl, "--model", path, "--max-model-len", "128",
+           "--kv-blocks", "32", "--max-num-seqs", "4", "--max-batched-tokens", "128", "--policy", "chunked",
+           "--chunk", "16", "--out", out_json]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    summary = json.load(open(out_json))
+    assert summary["n_requests"] == 3 and summary["output_tokens"] == 24 and summary["throughput_out"] > 0
+    assert summary["policy"] == "chunked" and summary["kv_leak"] is False

@@ -1,0 +1,398 @@
+"""Each CUDA kernel alone against a plain float32 reference, at sizes other than the engine's
+test models use (odd widths, head sizes in steps of 16, groups of 1 to 8, vocabularies that
+are no power of two)."""
+import math
+import random
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 2e-2) * scale
+
+
+def dev(t, dtype=None):
+    return t.to(device="cuda", dtype=dtype or t.dtype).contiguous()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llmgen_b200.kernels import ops as o
+    return o
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_rows(ops, dtype):
+    torch.manual_seed(0)
+    V, H = 100, 72
+    table = torch.randn(V, H).to(dtype)
+    ids = torch.tensor([3, 99, 0, 57, 3], dtype=torch.int32)
+    out = torch.empty(5, H, dtype=torch.float32, device="cuda")
+    bad = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_rows(out, dev(table), dev(ids), bad)
+    assert torch.equal(out.cpu(), plain.embedding(ids.tolist(), table.float()))
+    assert int(bad.item()) == 0
+    ops.embed_rows(out, dev(table), dev(torch.tensor([1, 100, -1, 2, 5], dtype=torch.int32)), bad)
+    assert int(bad.item()) == 2 and float(out[1].abs().sum()) == 0.0 and float(out[2].abs().sum()) == 0.0
+    assert torch.equal(out[3].cpu(), table[2].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [100, 1032, 5120])
+def test_add_rmsnorm(ops, dtype, H):
+    torch.manual_seed(1)
+    n, eps = 7, 3e-5
+    resid = torch.randn(n, H) * 2
+    delta = torch.randn(n, H).to(dtype)
+    w = 1 + 0.2 * torch.randn(H)
+    r = dev(resid)
+    out = torch.empty(n, H, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r, dev(delta), dev(w), out, eps, 0.0)
+    summed = resid + delta.float()
+    assert torch.allclose(r.cpu(), summed, atol=1e-6)          # the sum stays float32
+    ref = plain.rmsnorm(summed, w, eps)
+    assert float((out.float().cpu() - ref).abs().max()) < tol(dtype, 6)
+    # no delta, a weight offset, gathered rows, residual untouched
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32)
+    out2 = torch.empty(3, H, dtype=dtype, device="cuda")
+    before = r.clone()
+    ops.add_rmsnorm(r, None, dev(w), out2, eps, 1.0, rows=dev(rows))
+    assert torch.equal(r, before)
+    ref2 = plain.rmsnorm(summed[rows.long()], w, eps, weight_offset=1.0)
+    assert float((out2.float().cpu() - ref2).abs().max()) < tol(dtype, 10)
+    # gathered rows with a pending delta
+    r3 = dev(resid)
+    ops.add_rmsnorm(r3, dev(delta), dev(w), out2, eps, 0.0, rows=dev(rows))
+    assert torch.equal(r3.cpu(), resid)
+    assert float((out2.float().cpu() - ref[rows.long()]).abs().max()) < tol(dtype, 6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("F", [50, 64, 176])
+def test_silu_mul(ops, dtype, F):
+    torch.manual_seed(2)
+    x = (torch.randn(9, 2 * F) * 3).to(dtype)
+    out = torch.empty(9, F, dtype=dtype, device="cuda")
+    ops.silu_mul(out, dev(x))
+    g, u = x.float()[:, :F], x.float()[:, F:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.float().cpu() - ref).abs().max()) < tol(dtype, 10)
+
+
+# ------------------------------------------------------------------ attn_prep
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot", [(5, 1, 48, 48), (4, 2, 16, 16), (3, 3, 64, 32), (16, 8, 128, 128), (2, 1, 256, 256)])
+def test_attn_prep(ops, dtype, nq, nkv, hd, rot):
+    torch.manual_seed(3)
+    T, page, pages, eps = 6, 8, 5, 1e-5
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(dtype)
+    positions = [3, 17, 0, 42, 9, 41]
+    slots = [5, 17, -1, 0, 39, 16]                      # page * 8 + offset; -1: do not store
+    qg, kg = 1 + 0.3 * torch.randn(hd), 1 + 0.3 * torch.randn(hd)
+    cos64, sin64 = plain.rope_tables(64, rot, 10000.0)
+    kc = torch.full((pages, nkv, page, hd), 7.0, dtype=dtype, device="cuda")
+    vc = torch.full((pages, nkv, page, hd), 7.0, dtype=dtype, device="cuda")
+    x = dev(qkv)
+    ops.attn_prep(x, kc, vc, dev(torch.tensor(positions, dtype=torch.int32)), dev(torch.tensor(slots, dtype=torch.int32)),
+                  dev(cos64.float()), dev(sin64.float()), dev(qg), dev(kg), nq, nkv, hd, rot, page, eps)
+    f = qkv.float()
+    q = f[:, :nq * hd].view(T, nq, hd)
+    k = f[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
+    v = f[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    q_ref = plain.apply_rope(plain.rmsnorm(q, qg, eps), positions, cos64, sin64, rot)
+    k_ref = plain.apply_rope(plain.rmsnorm(k, kg, eps), positions, cos64, sin64, rot)
+    got_q = x.float().cpu()[:, :nq * hd].view(T, nq, hd)
+    assert float((got_q - q_ref).abs().max()) < tol(dtype, 6)
+    kc_ref = torch.full((pages, nkv, page, hd), 7.0)
+    vc_ref = torch.full((pages, nkv, page, hd), 7.0)
+    for t, s in enumerate(slots):
+        if s >= 0:
+            kc_ref[s // page, :, s % page] = k_ref[t]
+            vc_ref[s // page, :, s % page] = v[t]
+    assert float((kc.float().cpu() - kc_ref).abs().max()) < tol(dtype, 6)
+    assert torch.equal(vc.float().cpu(), vc_ref)                       # values are copied bit for bit
+    # the k and v columns of the packed rows are left as they were
+    assert torch.equal(x.cpu()[:, nq * hd:], qkv[:, nq * hd:])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attn_prep_without_norm_or_rope_and_q_only(ops, dtype):
+    torch.manual_seed(4)
+    T, nq, nkv, hd = 3, 2, 1, 32
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(dtype)
+    kc = torch.zeros(2, nkv, 4, hd, dtype=dtype, device="cuda")
+    vc = torch.zeros_like(kc)
+    x = dev(qkv)
+    ops.attn_prep(x, kc, vc, None, dev(torch.tensor([0, 5, 2], dtype=torch.int32)), None, None, None, None,
+                  nq, nkv, hd, 0, 4, 0.0)
+    assert torch.equal(x.cpu(), qkv)
+    assert torch.equal(kc.cpu()[1, 0, 1], qkv[1, nq * hd:(nq + 1) * hd])
+    # a layer that reads another layer's cache: only q heads are present, nothing is stored
+    q_only = dev(qkv[:, :nq * hd].contiguous())
+    kc.zero_()
+    g = 1 + 0.1 * torch.randn(hd)
+    ops.attn_prep(q_only, kc, vc, None, dev(torch.tensor([0, 5, 2], dtype=torch.int32)), None, None, dev(g), dev(g),
+                  nq, 0, hd, 0, 4, 1e-6)
+    assert float(kc.abs().sum()) == 0.0
+    ref = plain.rmsnorm(qkv.float()[:, :nq * hd].view(T, nq, hd), g, 1e-6)
+    assert float((q_only.float().cpu().view(T, nq, hd) - ref).abs().max()) < tol(dtype, 6)
+
+
+def test_attn_prep_refuses_what_it_cannot_do(ops):
+    x = torch.zeros(1, 3 * 18, dtype=torch.float32, device="cuda")
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        ops.attn_prep(x, None, None, None, None, None, None, None, None, 1, 1, 17, 0, 4, 0.0)
+    with pytest.raises(ops.KernelError, match="CUDA device"):
+        ops.attn_prep(torch.zeros(1, 48), None, None, None, None, None, None, None, None, 1, 1, 16, 0, 4, 0.0)
+
+
+# ------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 33, 70])
+def test_gemm_simt(ops, dtype, M):
+    torch.manual_seed(5)
+    N, K = 130, 77
+    a = torch.randn(M, K).to(dtype)
+    w = (torch.randn(N, K) * 0.2).to(dtype)
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    ops.gemm_simt(out, dev(a), dev(w))
+    ref = a.double() @ w.double().t()
+    assert float((out.double().cpu() - ref).abs().max()) < tol(dtype, 4)
+    if dtype == torch.bfloat16:                     # float32 output of a bfloat16 product
+        out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        ops.gemm_simt(out32, dev(a), dev(w))
+        assert float((out32.double().cpu() - ref).abs().max()) < 1e-4
+    # strided operands and accumulate
+    big = torch.zeros(M, N + 6, dtype=dtype, device="cuda")
+    view = big[:, 3:3 + N]
+    ops.gemm_simt(view, dev(a), dev(w))
+    ops.gemm_simt(view, dev(a), dev(w), accumulate=True)
+    assert float((view.double().cpu() - 2 * ref).abs().max()) < tol(dtype, 12)
+    assert float(big[:, :3].abs().sum()) == 0.0 and float(big[:, 3 + N:].abs().sum()) == 0.0
+
+
+def test_gemm_simt_row_does_not_depend_on_the_batch(ops):
+    """float32: a row's result is bit-identical whatever else is in the batch."""
+    torch.manual_seed(6)
+    a = dev(torch.randn(70, 333))
+    w = dev(torch.randn(50, 333))
+    full = torch.empty(70, 50, device="cuda")
+    ops.gemm_simt(full, a, w)
+    for rows in ([0], [69], list(range(10, 27))):
+        part = torch.empty(len(rows), 50, device="cuda")
+        ops.gemm_simt(part, a[rows].contiguous(), w)
+        assert torch.equal(part, full[rows])
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemv_bf16(ops, M, out_dtype):
+    torch.manual_seed(7)
+    N, K = 131, 520
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=out_dtype, device="cuda")
+    assert ops.gemv_usable(dev(a), dev(w))
+    ops.gemv_bf16(out, dev(a), dev(w))
+    ref = a.double() @ w.double().t()
+    assert float((out.double().cpu() - ref).abs().max()) < (1e-4 if out_dtype == torch.float32 else 3e-2)
+    assert not ops.gemv_usable(dev(torch.zeros(5, K, dtype=torch.bfloat16)), dev(w))
+    assert not ops.gemv_usable(dev(torch.zeros(2, 12, dtype=torch.bfloat16)), dev(torch.zeros(4, 12, dtype=torch.bfloat16)))
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemv_bf16(torch.empty(1, 4, dtype=out_dtype, device="cuda"), dev(torch.zeros(1, 12, dtype=torch.bfloat16)),
+                      dev(torch.zeros(4, 12, dtype=torch.bfloat16)))
+
+
+# ------------------------------------------------------------------ attention
+def paged_case(seqs, nq, nkv, hd, page, dtype, seed, sharpen=None):
+    """seqs: [(ctx, q_len)].  Builds a shuffled paged cache and q; returns tensors and the plain result."""
+    g = torch.Generator().manual_seed(seed)
+    max_blocks = max((c + page - 1) // page for c, _ in seqs) + 1
+    n_pages = sum((c + page - 1) // page for c, _ in seqs) + 3
+    order = list(range(n_pages))
+    random.Random(seed).shuffle(order)
+    kc = torch.randn(n_pages, nkv, page, hd, generator=g).to(dtype)      # unused slots hold noise
+    vc = torch.randn(n_pages, nkv, page, hd, generator=g).to(dtype)
+    bt = torch.zeros(len(seqs), max_blocks, dtype=torch.int32)
+    T = sum(q for _, q in seqs)
+    q = torch.randn(T, nq, hd, generator=g).to(dtype)
+    ref = torch.zeros(T, nq, hd)
+    cu, ctxs, t = [0], [], 0
+    for s, (ctx, q_len) in enumerate(seqs):
+        nb = (ctx + page - 1) // page
+        pages = [order.pop() for _ in range(nb)]
+        bt[s, :nb] = torch.tensor(pages, dtype=torch.int32)
+        ctxs.append(ctx)
+        if ctx >= q_len and ctx > 0:
+            k_seq = torch.stack([kc[pages[p // page], :, p % page] for p in range(ctx)]).float()
+            v_seq = torch.stack([vc[pages[p // page], :, p % page] for p in range(ctx)]).float()
+            if sharpen is not None:
+                sharpen(s, ctx, q_len, q, t, k_seq, kc, pages, page)
+            q_full = torch.zeros(ctx, nq, hd)
+            q_full[ctx - q_len:] = q[t:t + q_len].float()
+            ref[t:t + q_len] = plain.causal_attention(q_full, k_seq, v_seq, 1.0 / math.sqrt(hd), sharpen.window if sharpen is not None and hasattr(sharpen, "window") else None)[ctx - q_len:]
+        t += q_len
+        cu.append(t)
+    return q, kc, vc, bt, torch.tensor(ctxs, dtype=torch.int32), torch.tensor(cu, dtype=torch.int32), ref, max_blocks
+
+
+def run_attention(ops, q, kc, vc, bt, ctxs, cu, max_blocks, nq, nkv, hd, page, window=0, parts=1, part_size=0):
+    T = q.shape[0]
+    bq = ops.attention_tile_queries(nq, nkv)
+    seq, q0 = [], []
+    for s in range(len(ctxs)):
+        n = int(cu[s + 1] - cu[s])
+        for start in range(0, max(n, 1), bq):
+            seq.append(s)
+            q0.append(start)
+    out = torch.full((T, nq * hd), 9.0, dtype=q.dtype, device="cuda")
+    scratch = None
+    if parts > 1:
+        scratch = torch.empty(ops.attention_scratch_floats(T, nq, hd, parts), dtype=torch.float32, device="cuda")
+    qd = dev(q.view(T, nq * hd))
+    ops.paged_attention(out, qd, nq * hd, dev(kc), dev(vc), dev(bt), max_blocks, dev(ctxs), dev(cu),
+                        dev(torch.tensor(seq, dtype=torch.int32)), dev(torch.tensor(q0, dtype=torch.int32)), len(seq), T,
+                        nq, nkv, hd, page, window, 1.0 / math.sqrt(hd), parts, part_size, scratch)
+    return out.float().cpu().view(T, nq, hd)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page", [(4, 2, 64, 16), (8, 1, 32, 32), (6, 2, 48, 16), (16, 8, 128, 16),
+                                            (3, 3, 16, 8), (40, 2, 16, 16), (2, 2, 256, 64)])
+def test_paged_attention_mixed_batch(ops, dtype, nq, nkv, hd, page):
+    # the reference's own mixed case (src/backend/cpu/attention.zig:188-251): the tail of a
+    # prompt (ctx 70, 30 queries), a decoded token (ctx 41), a padding row (ctx 0); plus a whole
+    # prompt that ends on a page's edge and a single first token
+    seqs = [(70, 30), (41, 1), (0, 1), (4 * page, 4 * page), (1, 1), (150, 100)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 11)
+    got = run_attention(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
+    assert float((got - ref).abs().max()) < tol(dtype, 3)
+    assert float(got[31].abs().max()) == 0.0        # the padding row gives zeros
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("parts,part_size", [(1, 0), (3, 64), (2, 128), (5, 0), (16, 0), (2, 512)])
+def test_flash_decoding_split(ops, dtype, parts, part_size):
+    nq, nkv, hd, page = 4, 2, 128, 16
+    seqs = [(150, 1), (1, 1), (0, 1), (333, 1), (64, 1), (65, 1)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 12)
+    got = run_attention(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, parts=parts, part_size=part_size)
+    assert float((got - ref).abs().max()) < tol(dtype, 3)
+    assert float(got[2].abs().max()) == 0.0
+
+
+class FarKey:
+    """Scales one key (and the queries) so that a single far score stands out: if that key is
+    missed (a page's edge, a part's boundary, the first key) the output is visibly wrong."""
+    def __init__(self, where):
+        self.where = where
+
+    def __call__(self, s, ctx, q_len, q, t, k_seq, kc, pages, page):
+        j = self.where(ctx)
+        if not 0 <= j < ctx:
+            return
+        direction = q[t + q_len - 1, 0].float()
+        boost = (6.0 * direction / direction.norm()).to(kc.dtype)
+        kc[pages[j // page], :, j % page] = boost
+        k_seq[j] = boost.float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("where", [lambda c: 0, lambda c: 15, lambda c: 16, lambda c: c - 1, lambda c: 255, lambda c: 256,
+                                   lambda c: c // 2])
+def test_far_key_among_hundreds(ops, dtype, where):
+    nq, nkv, hd, page = 2, 1, 64, 16
+    seqs = [(700, 1), (513, 3)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 13, sharpen=FarKey(where))
+    for parts, part_size in ((1, 0), (4, 0), (3, 256)):
+        if parts > 1:       # split runs are for single-token rows
+            seqs1 = [(700, 1)]
+            q1, kc1, vc1, bt1, ctxs1, cu1, ref1, mb1 = paged_case(seqs1, nq, nkv, hd, page, dtype, 13, sharpen=FarKey(where))
+            got = run_attention(ops, q1, kc1, vc1, bt1, ctxs1, cu1, mb1, nq, nkv, hd, page, parts=parts, part_size=part_size)
+            assert float((got - ref1).abs().max()) < tol(dtype, 3)
+        else:
+            got = run_attention(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
+            assert float((got - ref).abs().max()) < tol(dtype, 3)
+
+
+class WindowEdge(FarKey):
+    def __init__(self, window, offset):
+        super().__init__(lambda ctx: ctx - 1 - window + offset)   # offset 0: just outside; 1: just inside
+        self.window = window
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 16, 40, 100])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_window_edge(ops, dtype, window, offset):
+    """The key one place outside the window must not be seen, the one just inside must."""
+    nq, nkv, hd, page = 6, 2, 48, 16
+    seqs = [(130, 1), (97, 33), (40, 40), (0, 1)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 14, sharpen=WindowEdge(window, offset))
+    got = run_attention(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, window=window)
+    assert float((got - ref).abs().max()) < tol(dtype, 3)
+
+
+def test_attention_refuses_what_it_cannot_do(ops):
+    z = torch.zeros(1, 20, device="cuda")
+    zi = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        ops.paged_attention(z, z, 20, z, z, zi, 1, zi, zi, zi, zi, 1, 1, 1, 1, 20, 16, 0, 1.0)
+    with pytest.raises(ops.KernelError, match="multiple"):
+        ops.paged_attention(z, z, 48, z, z, zi, 1, zi, zi, zi, zi, 1, 1, 3, 2, 16, 16, 0, 1.0)
+
+
+# ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("V", [1000, 301, 151936])
+def test_sample_greedy_finds_the_peak_in_every_segment(ops, V):
+    torch.manual_seed(8)
+    peaks = [0, 1, V // 32, V // 2 + 3, V - 2, V - 1]
+    logits = torch.randn(len(peaks), V)
+    for r, p in enumerate(peaks):
+        logits[r, p] = 50.0
+    logits[1, 7] = 50.0       # a tie: the smaller id wins
+    out = torch.zeros(len(peaks), dtype=torch.int32, device="cuda")
+    scratch = torch.empty(ops.sample_scratch_bytes(len(peaks)) // 4, dtype=torch.float32, device="cuda")
+    seed = torch.tensor([1234], dtype=torch.int64, device="cuda")
+    ops.sample(out, dev(logits), dev(torch.zeros(len(peaks))), seed, scratch)
+    assert out.cpu().tolist() == peaks
+
+
+def test_sample_temperature_matches_the_plain_sampler(ops):
+    torch.manual_seed(9)
+    V, S = 301, 6
+    logits = torch.randn(S, V) * 2
+    temps = torch.tensor([0.7, 0.0, 1.0, 0.3, 2.5, 0.7])
+    step_seed = 0x5EED + 0x9E3779B97F4A7C15
+    out = torch.zeros(S, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(ops.sample_scratch_bytes(S) // 4, dtype=torch.float32, device="cuda")
+    seed = torch.tensor([step_seed - (1 << 64) if step_seed >= (1 << 63) else step_seed], dtype=torch.int64, device="cuda")
+    ops.sample(out, dev(logits), dev(temps), seed, scratch)
+    got = out.cpu().tolist()
+    for row in range(S):
+        if temps[row] <= 0:
+            assert got[row] == int(logits[row].argmax())
+            continue
+        scores = plain.gumbel_scores(logits[row], float(temps[row]), step_seed, row)
+        # the chosen id's perturbed score is the largest, up to the rounding of log on the two sides
+        assert float(scores.max() - scores[got[row]]) < 1e-4
+    out2 = torch.zeros_like(out)
+    ops.sample(out2, dev(logits), dev(temps), seed, scratch)
+    assert torch.equal(out, out2)                                  # same seed, same draw
+    seed2 = torch.tensor([99], dtype=torch.int64, device="cuda")
+    draws = []
+    flat = torch.zeros(1, V)
+    for s in range(300):
+        seed2.fill_(s * 7919 + 1)
+        one = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.sample(one, dev(flat), dev(torch.ones(1)), seed2, scratch)
+        draws.append(int(one.item()))
+    assert len(set(draws)) > 150                                   # uniform logits: draws spread over the vocabulary

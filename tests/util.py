@@ -85,3 +85,51 @@ class Driver:
             self.executor.release(rid)
             del self.positions[rid]
         return out.logits.float().cpu()
+
+
+FP32_TOL = 1e-4          # max abs difference of float32 logits (logits here are O(1))
+
+
+def bf16_tol(ref: torch.Tensor) -> float:
+    """bfloat16 keeps 8 bits of mantissa: logits may differ by a few percent of their scale."""
+    return 4e-2 * max(1.0, float(ref.abs().max()))
+
+
+def logits_close(got: torch.Tensor, ref: torch.Tensor, dtype: str) -> float:
+    diff = float((got.float() - ref.float()).abs().max())
+    limit = FP32_TOL if dtype == "float32" else bf16_tol(ref)
+    assert diff <= limit, f"max |diff| {diff:.3e} above {limit:.3e} ({dtype})"
+    return diff
+
+
+def manual_context(q_lens, starts, tables, page_size, dtype, mixers=(), max_step_tokens=4096, state_slots=None):
+    """A StepContext built by hand (one cache group), for tests that run a single part.
+    `tables[s]` is the block table of sequence s."""
+    import numpy as np
+    from llmgen_b200.engine.context import GroupView, StepContext, StepMetaBuilder, Workspace
+    S, T = len(q_lens), sum(q_lens)
+    max_blocks = max(len(t) for t in tables)
+    b = StepMetaBuilder(q_lens, starts, all(n == 1 for n in q_lens))
+    pos, seq_of, slots = [], [], []
+    cu = [0]
+    for s, (n, st) in enumerate(zip(q_lens, starts)):
+        for p in range(st, st + n):
+            pos.append(p)
+            seq_of.append(s)
+            slots.append(tables[s][p // page_size] * page_size + p % page_size)
+        cu.append(cu[-1] + n)
+    bt = np.zeros((S, max_blocks), dtype=np.int32)
+    for s, t in enumerate(tables):
+        bt[s, :len(t)] = t
+    for m in mixers:
+        m.prepare_step(b)
+    dev = lambda a, dt=torch.int32: torch.as_tensor(np.asarray(a), dtype=dt).cuda()
+    ctx = StepContext(
+        n_tokens=T, n_seqs=S, dtype=dtype, device=torch.device("cuda:0"), workspace=Workspace(torch.device("cuda:0"), max_step_tokens),
+        requests=list(range(S)), starts=list(starts), q_lens=list(q_lens), pure_decode=b.pure_decode,
+        max_ctx=max(s + n for s, n in zip(starts, q_lens)), max_ctx_bound=max_blocks * page_size,
+        ids=dev([0] * T), positions=dev(pos), cu_q=dev(cu), ctx_len=dev([s + n for s, n in zip(starts, q_lens)]),
+        state_slots=dev(state_slots if state_slots is not None else list(range(S))), seq_of_token=dev(seq_of),
+        groups=[GroupView(dev(slots), dev(bt.reshape(-1)), max_blocks)],
+        extra={name: dev(arr) for name, arr in b.arrays.items()})
+    return ctx
