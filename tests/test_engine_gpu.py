@@ -56,16 +56,16 @@ def test_bfloat16_generation_runs_and_agrees_mostly(tmp):
 
 
 def test_preemption_recomputes_and_gives_the_same_ids(tmp):
-    """Configuration B's workload: five prompts, four sequences at a time, twelve pages of 32
-    tokens: pages run out, the last running sequence is preempted and later computed again."""
+    """Five prompts, four sequences at a time, eight pages of 32 tokens: pages run out while
+    decoding, the last running sequence is preempted and later computed again from position 0."""
     from llmgen_b200 import LLM, SamplingParams
     path = make_folder(tmp, "B")
     prompts = [random_ids(n, 384, 60 + i) for i, n in enumerate((1, 9, 40, 64, 100))]
-    ref = greedy_reference(path, prompts, 24)
+    ref = greedy_reference(path, prompts, 40)
     for policy in ("chunked", "prefill_first"):
         llm = LLM(path, dtype="float32", max_model_len=256, max_num_seqs=4, max_batched_tokens=256, pass_tokens=256,
-                  block_size=32, kv_blocks=12, policy=policy, chunk=16)
-        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+                  block_size=32, kv_blocks=8, policy=policy, chunk=16)
+        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
         assert llm.engine.scheduler.num_preemptions > 0
         assert [o["token_ids"] for o in outs] == ref
         assert llm.executor.cache.all_free()

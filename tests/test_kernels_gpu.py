@@ -84,7 +84,7 @@ def test_silu_mul(ops, dtype, F):
     ops.silu_mul(out, dev(x))
     g, u = x.float()[:, :F], x.float()[:, F:]
     ref = g / (1 + torch.exp(-g)) * u
-    assert float((out.float().cpu() - ref).abs().max()) < tol(dtype, 10)
+    assert torch.allclose(out.float().cpu(), ref, rtol=1e-5 if dtype == torch.float32 else 1e-2, atol=tol(dtype))
 
 
 # ------------------------------------------------------------------ attn_prep
@@ -279,8 +279,9 @@ def test_paged_attention_mixed_batch(ops, dtype, nq, nkv, hd, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("parts,part_size", [(1, 0), (3, 64), (2, 128), (5, 0), (16, 0), (2, 512)])
+@pytest.mark.parametrize("parts,part_size", [(1, 0), (6, 64), (3, 128), (5, 0), (16, 0), (2, 512)])
 def test_flash_decoding_split(ops, dtype, parts, part_size):
+    # a fixed part_size must cover the longest context (parts * part_size >= 333); 0 splits evenly
     nq, nkv, hd, page = 4, 2, 128, 16
     seqs = [(150, 1), (1, 1), (0, 1), (333, 1), (64, 1), (65, 1)]
     q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 12)

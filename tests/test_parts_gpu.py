@@ -123,7 +123,7 @@ def test_attention_part_whole_then_in_portions(dtype, nq, nkv, hd, H, window, wi
         outs, start = [], 0
         for n in cuts:
             ctx = manual_context([n], [start], [table], page, dtype, mixers=[part])
-            outs.append(part.forward(ctx, x[start:start + n].cuda()).float().cpu().clone())
+            outs.append(part.forward(ctx, x[start:start + n].cuda(), cache).float().cpu().clone())
             start += n
         got = torch.cat(outs)
         assert float((got - ref).abs().max()) < tol(dtype, 30), cuts

@@ -45,7 +45,9 @@ def case(tmp, name, sharp=False):
 
 def sharpen(path, tmp, name):
     """A copy of the model whose q/k norm gains are 3x: scores grow 9x, attention becomes
-    peaked, and a single missed or misplaced key shows in the logits."""
+    peaked, and a single missed or misplaced key shows in the logits.  Run in float32 only: in
+    bfloat16 the rounding of q and k is magnified 9x in the scores as well, so a comparison with
+    float32 arithmetic would measure that and not the cache."""
     from safetensors.torch import load_file, save_file
     out = os.path.join(tmp, f"sharp_{name}")
     if not os.path.isdir(out):
@@ -139,7 +141,7 @@ def mixed_trace(reqs, seed, max_live=4):
     return steps, peak
 
 
-@pytest.mark.parametrize("name,dtype", CASES + [("C-sharp", "float32"), ("C-sharp", "bfloat16"), ("A-sharp", "float32")])
+@pytest.mark.parametrize("name,dtype", CASES + [("C-sharp", "float32"), ("B-sharp", "float32"), ("A-sharp", "float32")])
 def test_mixed_with_pages_used_again(tmp, name, dtype):
     sharp = name.endswith("-sharp")
     name = name[0]
