@@ -1,0 +1,316 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine's decode step and prefill on one B200, at the Qwen3-0.6B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+Prints ONE JSON line.  A "step" is one decode step of `--batch` sequences (default 8) whose
+prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
+
+  value     decoded tokens per second, timed on the device with CUDA events over exactly K
+            graph-replayed decode steps (metadata upload + captured forward + sampling), after W
+            warm-up steps.  Contexts grow from 512 + W upward.
+  e2e       the same through the Python entry point (`Engine.step`): every step copies its
+            metadata from pinned host memory to the device and reads the sampled ids back.
+  prefill   one 2,048-token prompt through one step: tokens/s, ms, and flops / time / the measured
+            bf16 peak.
+  roofline  the decode step against HBM: bytes it has to read (every weight once, the cache of the
+            live requests) / its time / the measured copy bandwidth.
+  points    decode tokens/s at batch 1 and 64.
+
+Inputs are larger than L2 (1.19 GB of weights per step against 126 MB), so nothing is flushed
+between timed iterations.  The reference (Zig + CUDA for sm_86) cannot be built or installed
+here, so `--impl reference` reports that it is unavailable.
+"""
+import argparse
+import json
+import os
+import re
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: "Qwen3-0.6B shape ... 28 layers, hidden 1024, 16 q heads, 8 kv heads,
+# head_dim 128, intermediate 3072 SwiGLU, vocab 151936, rope_theta 1,000,000, rms_eps 1e-6,
+# q/k RMSNorm, tied embeddings, full attention", benchmarked at max_model_len 4096.
+QWEN3_0_6B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 3072, "vocab_size": 151936, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 40960, "hidden_act": "silu",
+}
+CONTEXT = 4096
+PROMPT_TOKENS = 512
+PREFILL_TOKENS = 2048
+SEED = 2
+PUBLISHED_B8 = 1666.0      # s4, 8 requests, RTX 3090 (the nearest published figure)
+
+
+def check_against_baseline_json():
+    """The sizes above are those BASELINE.json names; fail loudly if the file says otherwise."""
+    path = os.path.join(ROOT, "BASELINE.json")
+    if not os.path.isfile(path):
+        return
+    text = json.load(open(path))["configs"][2]
+    pats = {"num_hidden_layers": r"(\d+) layers", "hidden_size": r"hidden (\d+)", "num_attention_heads": r"(\d+) q heads",
+            "num_key_value_heads": r"(\d+) kv heads", "head_dim": r"head_dim (\d+)", "intermediate_size": r"intermediate (\d+)",
+            "vocab_size": r"vocab (\d+)"}
+    for key, pat in pats.items():
+        m = re.search(pat, text)
+        if m and int(m.group(1)) != QWEN3_0_6B[key]:
+            raise SystemExit(f"bench.py: BASELINE.json configs[2] gives {key}={m.group(1)}, bench has {QWEN3_0_6B[key]}")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def mark(self):
+        return time.perf_counter()
+
+    def stop(self, windows):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.lines:
+            if not any(a <= t <= b + 0.15 for a, b in windows):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, f[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:      # the timed regions were shorter than a sampling period: use every sample
+            for t, line in self.lines:
+                f = [x.strip() for x in line.split(",")]
+                try:
+                    sm.append(float(f[0]))
+                    mx.append(float(f[1]))
+                except (ValueError, IndexError):
+                    pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, n_layers):
+    """Bytes and flops of the model as executed (bfloat16)."""
+    H, hd, nq, nkv = cfg["hidden_size"], cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    F, V = cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = (nq + 2 * nkv) * hd * H + H * nq * hd + 3 * F * H
+    mm_params = n_layers * per_layer
+    norm_params = n_layers * (2 * H + 2 * hd) + H
+    weight_bytes = 2 * (mm_params + V * H) + 4 * norm_params     # lm_head = the tied table, read whole once
+    kv_bytes_per_token = n_layers * 2 * nkv * hd * 2
+    return {"mm_params": mm_params, "weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token,
+            "per_layer_params": per_layer}
+
+
+def prefill_flops(cfg, n_layers, P):
+    nums = model_numbers(cfg, n_layers)
+    gemm = 2 * nums["mm_params"] * P + 2 * cfg["vocab_size"] * cfg["hidden_size"]      # lm_head on one row
+    attn = 4 * n_layers * cfg["num_attention_heads"] * cfg["head_dim"] * P * (P + 1) // 2
+    return gemm + attn
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "AIxSpace/llmgen is a Zig 0.15 + CUDA (sm_86) program: no Zig "
+                          "compiler is installed and pip reports 'Neither setup.py nor pyproject.toml found', so it "
+                          "cannot be installed or run here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    check_against_baseline_json()
+    warmup = max(3, args.warmup)
+    K = max(1, args.steps)
+
+    import numpy as np
+    import torch
+    from llmgen_b200.engine.api import LLM, random_model
+    from llmgen_b200.engine.executor import StepEntry
+    from llmgen_b200.kernels import ops
+    from llmgen_b200.sampling import SamplingParams
+
+    cfg = dict(QWEN3_0_6B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    n_layers = cfg["num_hidden_layers"]
+    pk = peaks()
+    nums = model_numbers(cfg, n_layers)
+    rng = np.random.default_rng(SEED)
+    model = random_model(cfg, SEED, "bfloat16")
+    llm = LLM(model, max_num_seqs=64, max_model_len=CONTEXT, max_batched_tokens=16384, pass_tokens=8192,
+              block_size=args.block_size, gpu_util=0.5, seed=SEED)
+    ex = llm.executor
+    V = cfg["vocab_size"]
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+
+    def device_decode(batch, warm, steps):
+        """K graph-replayed decode steps timed with CUDA events; returns (ms per step, mean context)."""
+        reqs = [f"dev{batch}_{i}" for i in range(batch)]
+        total = PROMPT_TOKENS + warm + steps + 1
+        prompts = [rng.integers(0, V, PROMPT_TOKENS).tolist() for _ in range(batch)]
+        for r in reqs:
+            assert ex.admit(r) and ex.reserve(r, 0, total)
+        ex.step([StepEntry(r, p, 0, [PROMPT_TOKENS - 1], 0.6) for r, p in zip(reqs, prompts)], sample=True, return_logits=False)
+        bucket = ex._bucket_for(batch)
+        g = ex.graphs.get(bucket) or ex._capture(bucket)
+        toks = rng.integers(0, V, batch).tolist()
+        pos = PROMPT_TOKENS
+
+        def one(pos):
+            ex._build_meta([StepEntry(r, [t], pos, [0], 0.6) for r, t in zip(reqs, toks)], pad_to=bucket)
+            g["graph"].replay()
+        for _ in range(warm):
+            one(pos)
+            pos += 1
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = sampler.mark()
+        start.record()
+        first = pos
+        for _ in range(steps):
+            one(pos)
+            pos += 1
+        end.record()
+        torch.cuda.synchronize()
+        windows.append((w0, sampler.mark()))
+        ms = start.elapsed_time(end) / steps
+        for r in reqs:
+            ex.release(r)
+        return ms, (first + 1 + pos) / 2.0, g["launches"]
+
+    # ---- prefill: one 2,048-token prompt, one step
+    def prefill_once():
+        ids = rng.integers(0, V, PREFILL_TOKENS).tolist()
+        assert ex.admit("prefill") and ex.reserve("prefill", 0, PREFILL_TOKENS)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        w0 = sampler.mark()
+        start.record()
+        ex.step([StepEntry("prefill", ids, 0, [PREFILL_TOKENS - 1], 0.6)], sample=True, return_logits=False)
+        end.record()
+        torch.cuda.synchronize()
+        windows.append((w0, sampler.mark()))
+        ex.release("prefill")
+        return start.elapsed_time(end)
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = statistics.median(prefill_once() for _ in range(5))
+    pf = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+    prefill = {"value": PREFILL_TOKENS / (prefill_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": prefill_ms,
+               "frac": pf / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---- the decode step on the device
+    launches0 = ops.launches()
+    ms_step, mean_ctx, launches_per_step = device_decode(args.batch, warmup, K)
+    value = args.batch / (ms_step / 1e3)
+    step_bytes = nums["weight_bytes"] + args.batch * mean_ctx * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]}
+
+    # ---- end to end through the entry point: host token ids in, host token ids out, every step
+    prompts = [rng.integers(0, V, PROMPT_TOKENS).tolist() for _ in range(args.batch)]
+    params = SamplingParams(temperature=0.6, max_tokens=warmup + K + 2, ignore_eos=True)
+    for p in prompts:
+        llm.engine.add_request(p, params)
+    llm.engine.step()                       # the prompts
+    for _ in range(warmup):
+        llm.engine.step()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = sampler.mark()
+    t0 = time.perf_counter()
+    start.record()
+    emitted = 0
+    for _ in range(K):
+        llm.engine.step()
+        emitted += len(llm.engine.last_emitted)
+    end.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    windows.append((w0, sampler.mark()))
+    e2e_ms = max(start.elapsed_time(end), wall * 1e3)
+    llm.engine.run_until_done()
+    llm.engine.release_finished()
+    meta_words = 2 + 3 * args.batch + (args.batch + 1) + 4 * args.batch + 2 * args.batch + args.batch + args.batch * ex.max_blocks
+    e2e = {"value": emitted / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_words,
+           "d2h_bytes_per_step": 4 * args.batch}
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ms_b, _, _ = device_decode(b, warmup, K)
+            points[f"decode_b{b}"] = b / (ms_b / 1e3)
+    clocks = sampler.stop(windows)
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-0.6B shape, bf16, random weights, 512-token prompts)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8, "dtype": "bf16",
+        "data": "synthetic: seeded uniform-random token ids, random-init weights (seed 2)",
+        "config": {"model": "Qwen3-0.6B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+                   "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
+                   "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": V, "tied_embeddings": True,
+                   "prompt_tokens": PROMPT_TOKENS, "mean_context": mean_ctx, "page_size": args.block_size,
+                   "l2": "inputs larger than L2 (1.19 GB of weights per step), no flush", "peaks": pk["source"]},
+        "e2e": e2e, "gpu_launches": launches_per_step * K, "prefill": prefill, "roofline": roofline, "points": points,
+        "clocks": clocks, "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -434,13 +434,14 @@ class Executor:
         ctx.fixed_shapes = True
         torch.cuda.synchronize(self.device)
         self.workspace.frozen = True
+        launches_before = ops.launches()
         try:
             with torch.cuda.graph(graph, stream=stream):
                 self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
                 ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
         finally:
             self.workspace.frozen = False
-        entry = {"graph": graph, "ids": ids_dev, "logits": logits}
+        entry = {"graph": graph, "ids": ids_dev, "logits": logits, "launches": ops.launches() - launches_before}
         self.graphs[bucket] = entry
         return entry
 
@@ -454,6 +455,7 @@ class Executor:
         g = self.graphs.get(bucket) or self._capture(bucket)
         self._build_meta(entries, pad_to=bucket)
         g["graph"].replay()
+        self.launch_count += g["launches"]
         n = len(entries)
         host = self.ids_host[:n]
         host.copy_(g["ids"][:n], non_blocking=True)

@@ -42,9 +42,19 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(lib, rc: int) -> None:
+class _Counter:
+    """How many kernels of this package were launched (a claim for benchmarks' records)."""
+    launches = 0
+
+
+def launches() -> int:
+    return _Counter.launches
+
+
+def _check(lib, rc: int, n_kernels: int = 1) -> None:
     if rc != 0:
         raise KernelError(lib.llmk_last_error().decode("utf-8", "replace"))
+    _Counter.launches += n_kernels
 
 
 def _row_stride(t: torch.Tensor) -> int:
@@ -180,7 +190,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                                          _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq), _ptr(tile_q0), c_int(n_tiles),
                                          c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
                                          c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
-                                         _ptr(scratch), c_int(dtype_code(q.dtype)), _stream()))
+                                         _ptr(scratch), c_int(dtype_code(q.dtype)), _stream()),
+           2 if num_parts > 1 else 1)
 
 
 # ------------------------------------------------------------------------------- sampling
@@ -201,4 +212,4 @@ def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, see
     if scratch.numel() * scratch.element_size() < sample_scratch_bytes(n):
         raise KernelError("sample: scratch too small")
     _check(lib, lib.llmk_sample(_ptr(out_ids), _ptr(logits), c_longlong(_row_stride(logits)), _ptr(temps),
-                                _ptr(seed), c_int(n), c_int(V), _ptr(scratch), _stream()))
+                                _ptr(seed), c_int(n), c_int(V), _ptr(scratch), _stream()), 2)
