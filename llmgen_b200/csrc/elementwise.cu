@@ -106,66 +106,72 @@ LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w
 }
 
 // ------------------------------------------------------------- gated activation
-// in [n, 2F] holds gate in columns [0, F) and up in [F, 2F); out[n, F] = silu(gate) * up with
-// silu(g) = g / (1 + exp(-g)) in float32, rounded once.
+// in [n, 2F] alternates `group` gate columns and `group` up columns (group = F: gate in columns
+// [0, F), up in [F, 2F)); out[n, F] = silu(gate) * up with silu(g) = g / (1 + exp(-g)) in float32,
+// rounded once.  Output column j reads gate column 2 * group * (j / group) + j % group and the up
+// column `group` further.
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int n, int F, int ld_in) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, int n, int F, int ld_in, int group) {
     const size_t total = (size_t)n * F;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const int row = (int)(idx / F), col = (int)(idx % F);
-        const float g = to_float(in[(size_t)row * ld_in + col]);
-        const float u = to_float(in[(size_t)row * ld_in + F + col]);
+        const int gcol = 2 * group * (col / group) + col % group;
+        const float g = to_float(in[(size_t)row * ld_in + gcol]);
+        const float u = to_float(in[(size_t)row * ld_in + gcol + group]);
         out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
 template <typename T>
-__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int n, int F, int ld_in) {
+__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int n, int F, int ld_in, int group) {
     constexpr int N = Vec16<T>::N;
     const int fv = F / N;
     const size_t total = (size_t)n * fv;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
-        const int row = (int)(idx / fv), cv = (int)(idx % fv);
-        const T* base = in + (size_t)row * ld_in + (size_t)cv * N;
+        const int row = (int)(idx / fv), col = (int)(idx % fv) * N;
+        const int gcol = 2 * group * (col / group) + col % group;
+        const T* base = in + (size_t)row * ld_in + gcol;
         Vec16<T> g, u, o;
         g.raw = *reinterpret_cast<const decltype(g.raw)*>(base);
-        u.raw = *reinterpret_cast<const decltype(u.raw)*>(base + F);
+        u.raw = *reinterpret_cast<const decltype(u.raw)*>(base + group);
         float gf[N], uf[N], of[N];
         g.unpack(gf);
         u.unpack(uf);
 #pragma unroll
         for (int i = 0; i < N; ++i) of[i] = gf[i] / (1.0f + expf(-gf[i])) * uf[i];
         o.pack(of);
-        *reinterpret_cast<decltype(o.raw)*>(out + (size_t)row * F + (size_t)cv * N) = o.raw;
+        *reinterpret_cast<decltype(o.raw)*>(out + (size_t)row * F + col) = o.raw;
     }
 }
 
 template <typename T>
-static int launch_silu_mul(void* out, const void* in, int n, int F, int ld_in, cudaStream_t s) {
+static int launch_silu_mul(void* out, const void* in, int n, int F, int ld_in, int group, cudaStream_t s) {
     constexpr int N = Vec16<T>::N;
-    const bool vec = (F % N == 0) && (ld_in % N == 0) && host_aligned16(out) && host_aligned16(in);
+    const bool vec = (F % N == 0) && (group % N == 0) && (ld_in % N == 0) && host_aligned16(out) && host_aligned16(in);
     const size_t work = vec ? (size_t)n * (F / N) : (size_t)n * F;
     const int threads = 256;
     size_t blocks = (work + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks == 0) return LLMK_OK;
     if (vec)
-        silu_mul_vec_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in);
+        silu_mul_vec_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in, group);
     else
-        silu_mul_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in);
+        silu_mul_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in, group);
     return LLMK_OK;
 }
 
-LLMK_EXPORT int llmk_silu_mul(void* out, const void* in, int n_rows, int F, int ld_in, int dtype, void* stream) {
+LLMK_EXPORT int llmk_silu_mul(void* out, const void* in, int n_rows, int F, int ld_in, int group, int dtype,
+                              void* stream) {
     if (n_rows <= 0) return LLMK_OK;
     if (F <= 0 || ld_in < 2 * F) LLMK_FAIL("silu_mul: bad sizes F=%d ld_in=%d", F, ld_in);
+    if (group <= 0 || F % group != 0) LLMK_FAIL("silu_mul: group %d must divide F=%d", group, F);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == LLMK_F32)
-        launch_silu_mul<float>(out, in, n_rows, F, ld_in, s);
+        launch_silu_mul<float>(out, in, n_rows, F, ld_in, group, s);
     else if (dtype == LLMK_BF16)
-        launch_silu_mul<bf16>(out, in, n_rows, F, ld_in, s);
+        launch_silu_mul<bf16>(out, in, n_rows, F, ld_in, group, s);
     else
         LLMK_FAIL("silu_mul: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH("silu_mul");

@@ -17,6 +17,7 @@ import torch
 from ..kernels import build as kernel_build
 from ..kernels import ops
 from ..parts.base import LayerCache
+from ..parts.linear import _FORCE as _FORCE_GEMM
 from ..parts.linear import linear
 from ..parts.registry import build_block, build_norm, model_kernel_modules
 from ..parts.spec import ModelSpec
@@ -94,7 +95,7 @@ class DecoderModel:
         self.final_norm.add_norm(resid, delta, normed, rows=rows)
         if out is None:
             out = torch.empty((n_rows, V), dtype=torch.float32, device=self.device)
-        if self.dtype == torch.float32 or ops.gemv_usable(normed, self.lm_head):
+        if self.dtype == torch.float32 or ops.gemv_usable(normed, self.lm_head) or _FORCE_GEMM != "lib":
             linear(normed, self.lm_head, out)
         else:
             # the library product writes bfloat16; widen afterwards

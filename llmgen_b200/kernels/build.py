@@ -42,6 +42,7 @@ MODULES: Dict[str, List[str]] = {
     "attn_prep": [],
     "gemm_simt": [],
     "gemv": [],
+    "gemm_tc": [],
     "attention": [],
     "sampling": [],
 }

@@ -95,12 +95,13 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
                                      c_int(dtype_code(out.dtype)), _stream()))
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
-    """out[n, F] = silu(gate_up[:, :F]) * gate_up[:, F:2F]."""
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, group: int = 0) -> None:
+    """out[n, F] = silu(gate) * up, where gate_up[n, 2F] alternates `group` gate columns and `group`
+    up columns (group 0 or F: gate in columns [0, F), up in [F, 2F))."""
     lib = build.load("elementwise")
     n, F = out.shape
     _check(lib, lib.llmk_silu_mul(_ptr(out), _ptr(gate_up), c_int(n), c_int(F), c_int(_row_stride(gate_up)),
-                                  c_int(dtype_code(out.dtype)), _stream()))
+                                  c_int(group if group else F), c_int(dtype_code(out.dtype)), _stream()))
 
 
 def widen(out: torch.Tensor, src: torch.Tensor) -> None:
@@ -161,6 +162,53 @@ def gemv_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[0] <= GEMV_MAX_ROWS and a.shape[1] % 8 == 0
             and _row_stride(a) % 8 == 0 and _row_stride(w) % 8 == 0
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """True when the tensor-core product takes these operands: bfloat16, rows starting on 16-byte
+    boundaries (what its TMA loads need)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and _row_stride(a) % 8 == 0 and _row_stride(w) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+_tc_error_flags = {}
+
+
+def tc_error_flag(device) -> torch.Tensor:
+    """Device int that a tensor-core kernel raises when one of its bounded waits gave up."""
+    key = str(device)
+    flag = _tc_error_flags.get(key)
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        _tc_error_flags[key] = flag
+    return flag
+
+
+def check_tc_errors(device) -> None:
+    """Raise if a tensor-core kernel reported a wait that ran out (synchronises)."""
+    flag = _tc_error_flags.get(str(device))
+    if flag is not None and int(flag.item()) != 0:
+        flag.zero_()
+        raise KernelError("a tensor-core kernel gave up waiting on a barrier (results of that step are invalid)")
+
+
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pdl: bool = False) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tensor cores (tcgen05), bfloat16 operands, float32
+    accumulation; `out` is bfloat16 or float32.  With `gated`, w interleaves gate and up rows in
+    groups of 16 and out[M, N/2] = silu(gate) * up."""
+    lib = build.load("gemm_tc")
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if gated else N
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != n_out:
+        raise KernelError(f"gemm_tc: shapes a{list(a.shape)} w{list(w.shape)} out{list(out.shape)} do not fit")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: operands must be bfloat16")
+    _check(lib, lib.llmk_gemm_tc(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
+                                 c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(_row_stride(out)),
+                                 c_int(1 if gated else 0), c_int(dtype_code(out.dtype)), _ptr(tc_error_flag(a.device)),
+                                 c_int(1 if pdl else 0), _stream()))
 
 
 # ------------------------------------------------------------------------------ attention

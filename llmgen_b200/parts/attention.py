@@ -6,7 +6,7 @@ import torch
 from ..cache.manager import FULL, WINDOW
 from ..kernels import ops
 from .base import KVRequest, LayerCache, Mixer
-from .linear import linear
+from .linear import GEMM_MODULES, linear
 from .registry import build_position, norm_class, register_mixer
 from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
 
@@ -34,7 +34,7 @@ class GQAAttention(Mixer):
 
     @staticmethod
     def kernel_modules(spec):
-        return ("attn_prep", "attention", "gemm_simt", "gemv")
+        return ("attn_prep", "attention") + GEMM_MODULES
 
     def __init__(self, spec: AttentionSpec, weights, dtype, device):
         if spec.num_heads % spec.num_kv_heads != 0:

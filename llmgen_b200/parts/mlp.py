@@ -5,17 +5,31 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward
-from .linear import linear
+from .linear import GEMM_MODULES, gated_product_usable, linear
 from .registry import register_feed_forward
 from .spec import GatedMLPSpec, WeightDecl
 
 
+GATE_UP_GROUP = 16   # rows of gate, then rows of up, alternating: what the gated epilogue expects
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, group: int = GATE_UP_GROUP) -> torch.Tensor:
+    """[2F, H]: rows [2 g k, 2 g k + g) are gate rows [g k, g k + g), the next g rows the same up
+    rows (values untouched)."""
+    F, H = w_gate.shape
+    if F % group != 0:
+        raise ValueError(f"intermediate size {F} is not a multiple of {group}")
+    return torch.stack([w_gate.view(F // group, group, H), w_up.view(F // group, group, H)], dim=1).reshape(2 * F, H)
+
+
 class GatedMLP(FeedForward):
-    """down( silu(x Wg^T) * (x Wu^T) ).  Gate and up are packed row-wise into one [2F, H]
-    matrix at load (values untouched) so that one product yields both, and the activation is
-    one pass over the packed result.  The reference runs gate, up, silu and mul as four
-    nodes, each rounded to bfloat16 (src/models/qwen3.zig:153-162); here act * up is rounded
-    once."""
+    """down( silu(x Wg^T) * (x Wu^T) ).  Gate and up are packed into one [2F, H] matrix at load
+    (values untouched) so that one product yields both.  In bfloat16 the rows alternate in groups
+    of 16 and the tensor-core product applies the activation in its epilogue, so the [T, 2F]
+    intermediate is never written; for a handful of rows (weight-streaming product) and in float32
+    the activation is one pass over the packed result.  The reference runs gate, up, silu and mul
+    as four nodes, each rounded to bfloat16 (src/models/qwen3.zig:153-162); here act * up is
+    rounded once."""
 
     @staticmethod
     def weight_decls(spec: GatedMLPSpec):
@@ -25,24 +39,34 @@ class GatedMLP(FeedForward):
 
     @staticmethod
     def kernel_modules(spec):
-        return ("elementwise", "gemm_simt", "gemv")
+        return ("elementwise",) + GEMM_MODULES
 
     def __init__(self, spec: GatedMLPSpec, weights, dtype, device):
         if spec.activation != "silu":
             raise ValueError(f"gated feed-forward: activation {spec.activation!r} is not supported")
         self.spec = spec
         self.dtype = dtype
-        self.w_gate_up = torch.cat([weights.host_tensor(spec.gate_proj), weights.host_tensor(spec.up_proj)], dim=0) \
-            .to(device=device, dtype=dtype).contiguous()
+        F = spec.intermediate_size
+        w_gate, w_up = weights.host_tensor(spec.gate_proj), weights.host_tensor(spec.up_proj)
+        if dtype == torch.bfloat16 and F % GATE_UP_GROUP == 0:
+            self.group = GATE_UP_GROUP
+            packed = interleave_gate_up(w_gate, w_up)
+        else:
+            self.group = F
+            packed = torch.cat([w_gate, w_up], dim=0)
+        self.w_gate_up = packed.to(device=device, dtype=dtype).contiguous()
         self.w_down = weights.device_tensor(spec.down_proj, dtype, device)
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
-        gate_up = linear(x, self.w_gate_up, ws.buffer("ffn_gate_up", T, 2 * F, self.dtype))
         act = ws.buffer("ffn_act", T, F, self.dtype)
-        ops.silu_mul(act, gate_up)
+        if self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up):
+            ops.gemm_tc(act, x, self.w_gate_up, gated=True)
+        else:
+            gate_up = linear(x, self.w_gate_up, ws.buffer("ffn_gate_up", T, 2 * F, self.dtype))
+            ops.silu_mul(act, gate_up, group=self.group)
         return linear(act, self.w_down, ws.buffer("ffn_out", T, H, self.dtype))
 
 

@@ -116,7 +116,7 @@ def model_weight_decls(model_spec) -> List[WeightDecl]:
 def model_kernel_modules(model_spec) -> List[str]:
     """Names of the CUDA modules a model's parts launch (what its first call compiles)."""
     _ensure_builtin()
-    mods = ["elementwise", "gemm_simt", "gemv", "sampling"]
+    mods = ["elementwise", "gemm_simt", "gemv", "gemm_tc", "sampling"]
     for layer in model_spec.layers:
         mods += list(block_class(layer).kernel_modules(layer))
     return list(dict.fromkeys(mods))

@@ -85,6 +85,11 @@ def test_silu_mul(ops, dtype, F):
     g, u = x.float()[:, :F], x.float()[:, F:]
     ref = g / (1 + torch.exp(-g)) * u
     assert torch.allclose(out.float().cpu(), ref, rtol=1e-5 if dtype == torch.float32 else 1e-2, atol=tol(dtype))
+    if F % 16 == 0:        # gate and up alternating in groups of 16 columns
+        mixed = torch.stack([x[:, :F].reshape(9, F // 16, 16), x[:, F:].reshape(9, F // 16, 16)], dim=2).reshape(9, 2 * F)
+        out2 = torch.empty(9, F, dtype=dtype, device="cuda")
+        ops.silu_mul(out2, dev(mixed), group=16)
+        assert torch.equal(out2, out)
 
 
 # ------------------------------------------------------------------ attn_prep
@@ -190,6 +195,65 @@ def test_gemm_simt_row_does_not_depend_on_the_batch(ops):
         part = torch.empty(len(rows), 50, device="cuda")
         ops.gemm_simt(part, a[rows].contiguous(), w)
         assert torch.equal(part, full[rows])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 72, 136), (33, 384, 512), (128, 128, 64), (200, 1000, 1032),
+                                   (257, 4096, 1024), (64, 130, 2048), (2048, 1024, 3072), (300, 50, 40)])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemm_tc(ops, M, N, K, out_dtype):
+    """The tcgen05 product against a float64 reference of the same bfloat16 operands: every tile
+    width, tails in M, N and K, float32 and bfloat16 results."""
+    torch.manual_seed(50 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    # one entry that only the last k-slice sees, and one that only the last rows see
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+    ops.gemm_tc(out, dev(a), dev(w))
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    ref = a.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err < (2e-5 if out_dtype == torch.float32 else 6e-3) * scale, (err, scale)
+
+
+def test_gemm_tc_strided_operands_and_untouched_neighbours(ops):
+    torch.manual_seed(60)
+    M, N, K = 70, 96, 200
+    a_big = torch.randn(M, K + 16).to(torch.bfloat16).cuda()
+    w_big = torch.randn(N, K + 8).to(torch.bfloat16).cuda()
+    a, w = a_big[:, 8:8 + K], w_big[:, :K]
+    big = torch.zeros(M + 2, N + 16, dtype=torch.bfloat16, device="cuda")
+    view = big[1:M + 1, 8:8 + N]
+    assert ops.gemm_tc_usable(a, w)
+    ops.gemm_tc(view, a, w)
+    ref = a.double().cpu() @ w.double().cpu().t()
+    assert float((view.double().cpu() - ref).abs().max()) < 6e-3 * float(ref.abs().max())
+    assert float(big[0].abs().sum()) == 0 and float(big[M + 1].abs().sum()) == 0
+    assert float(big[:, :8].abs().sum()) == 0 and float(big[:, 8 + N:].abs().sum()) == 0
+    # rows that do not start on 16-byte boundaries are refused, not mis-computed
+    assert not ops.gemm_tc_usable(a_big[:, 1:1 + K], w)
+    with pytest.raises(ops.KernelError, match="usable"):
+        ops.gemm_tc(view, a_big[:, 1:1 + K], w)
+
+
+@pytest.mark.parametrize("M,F,K", [(3, 48, 64), (130, 176, 80), (2048, 3072, 1024)])
+def test_gemm_tc_gated(ops, M, F, K):
+    """Gate and up rows interleaved in groups of 16: the epilogue returns silu(gate) * up."""
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    torch.manual_seed(70)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    wg = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    packed = interleave_gate_up(wg, wu)
+    out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tc(out, dev(a), dev(packed), gated=True)
+    g = a.double() @ wg.double().t()
+    u = a.double() @ wu.double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4])
