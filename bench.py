@@ -157,6 +157,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
+    ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -244,12 +246,14 @@ def main():
         windows.append((w0, sampler.mark()))
         ex.release("prefill")
         return start.elapsed_time(end)
-    for _ in range(3):
-        prefill_once()
-    prefill_ms = statistics.median(prefill_once() for _ in range(5))
-    pf = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
-    prefill = {"value": PREFILL_TOKENS / (prefill_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": prefill_ms,
-               "frac": pf / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+    prefill = None
+    if not args.skip_prefill:
+        for _ in range(3):
+            prefill_once()
+        prefill_ms = statistics.median(prefill_once() for _ in range(5))
+        pf = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+        prefill = {"value": PREFILL_TOKENS / (prefill_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": prefill_ms,
+                   "frac": pf / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
 
     # ---- the decode step on the device
     launches0 = ops.launches()
@@ -260,32 +264,34 @@ def main():
     roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]}
 
     # ---- end to end through the entry point: host token ids in, host token ids out, every step
-    prompts = [rng.integers(0, V, PROMPT_TOKENS).tolist() for _ in range(args.batch)]
-    params = SamplingParams(temperature=0.6, max_tokens=warmup + K + 2, ignore_eos=True)
-    for p in prompts:
-        llm.engine.add_request(p, params)
-    llm.engine.step()                       # the prompts
-    for _ in range(warmup):
-        llm.engine.step()
-    torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    w0 = sampler.mark()
-    t0 = time.perf_counter()
-    start.record()
-    emitted = 0
-    for _ in range(K):
-        llm.engine.step()
-        emitted += len(llm.engine.last_emitted)
-    end.record()
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    windows.append((w0, sampler.mark()))
-    e2e_ms = max(start.elapsed_time(end), wall * 1e3)
-    llm.engine.run_until_done()
-    llm.engine.release_finished()
-    meta_words = 2 + 3 * args.batch + (args.batch + 1) + 4 * args.batch + 2 * args.batch + args.batch + args.batch * ex.max_blocks
-    e2e = {"value": emitted / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_words,
-           "d2h_bytes_per_step": 4 * args.batch}
+    e2e = None
+    if not args.skip_e2e:
+        prompts = [rng.integers(0, V, PROMPT_TOKENS).tolist() for _ in range(args.batch)]
+        params = SamplingParams(temperature=0.6, max_tokens=warmup + K + 2, ignore_eos=True)
+        for p in prompts:
+            llm.engine.add_request(p, params)
+        llm.engine.step()                       # the prompts
+        for _ in range(warmup):
+            llm.engine.step()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = sampler.mark()
+        t0 = time.perf_counter()
+        start.record()
+        emitted = 0
+        for _ in range(K):
+            llm.engine.step()
+            emitted += len(llm.engine.last_emitted)
+        end.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        windows.append((w0, sampler.mark()))
+        e2e_ms = max(start.elapsed_time(end), wall * 1e3)
+        llm.engine.run_until_done()
+        llm.engine.release_finished()
+        meta_words = 2 + 3 * args.batch + (args.batch + 1) + 4 * args.batch + 2 * args.batch + args.batch + args.batch * ex.max_blocks
+        e2e = {"value": emitted / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_words,
+               "d2h_bytes_per_step": 4 * args.batch}
 
     points = {}
     if not args.skip_points:
