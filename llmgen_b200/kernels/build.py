@@ -146,9 +146,23 @@ def _compile(module: str, verbose_ptxas: bool = False) -> str:
             pass
         raise KernelBuildError(f"nvcc failed for {module}.cu:\n{' '.join(cmd)}\n{proc.stdout}")
     os.replace(tmp_out, out)
+    _prune_stale(module, out)
     if verbose_ptxas:
         _log(proc.stdout)
     return out
+
+
+def _prune_stale(module: str, keep: str) -> None:
+    """Remove libraries of `module` built from older sources (same folder, other hash)."""
+    folder = os.path.dirname(keep)
+    prefix = module + "_"
+    for name in os.listdir(folder):
+        stem = name[len(prefix):-3] if name.startswith(prefix) and name.endswith(".so") else ""
+        if len(stem) == 16 and all(c in "0123456789abcdef" for c in stem) and os.path.join(folder, name) != keep:
+            try:
+                os.remove(os.path.join(folder, name))
+            except OSError:
+                pass
 
 
 def ensure_built(modules: Iterable[str], verbose_ptxas: bool = False) -> Dict[str, str]:
