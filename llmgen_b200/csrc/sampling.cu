@@ -105,3 +105,67 @@ LLMK_EXPORT int llmk_sample(int* out, const float* logits, long long ld, const f
     LLMK_CHECK_LAUNCH("sample_final");
     return LLMK_OK;
 }
+
+// ------------------------------------------------------------------ sampling without an allocator
+// `llmk_sample_static` (declared in llmk_sample_static.h) is `llmk_sample` for callers that cannot
+// hand over scratch memory because they cannot allocate any: code running where cudaMalloc is off
+// limits, such as a host that embeds this library beside a runtime owning all device memory, or a
+// callback that must not call into an allocator.  The candidates of the first stage go to a
+// file-scope device array instead of a caller's buffer.  Every GPU that loads this library holds
+// the array (LLMK_SAMPLE_STATIC_MAX_ROWS * 32 * 8 bytes = 64 KiB) until the process exits.
+//
+// In host code `g_sample_static_scratch` is only a handle for the runtime, not a device address;
+// the address is asked for once per device with cudaGetSymbolAddress, with that device current,
+// on the first call made on that device.  That first call should therefore come before any stream
+// capture.  Both stages overwrite every slot they read, so nothing has to be cleared between calls;
+// but all calls share the one array, so two calls that overlap on the GPU (different streams) race.
+#include "llmk_sample_static.h"
+
+#include <mutex>
+
+static __device__ __align__(256) unsigned char g_sample_static_scratch[LLMK_SAMPLE_STATIC_MAX_ROWS * SPLIT * 8];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_lock;
+void* g_static_ptr[MAX_DEVICES] = {};
+}  // namespace
+
+LLMK_EXPORT int llmk_sample_static_max_rows() { return LLMK_SAMPLE_STATIC_MAX_ROWS; }
+
+LLMK_EXPORT int llmk_sample_static(int* out, const float* logits, long long ld, const float* temps,
+                                   const unsigned long long* seed, int n_rows, int V, void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    if (n_rows > LLMK_SAMPLE_STATIC_MAX_ROWS)
+        LLMK_FAIL("sample_static: %d rows exceed the built-in scratch of %d rows; use llmk_sample with scratch of your own",
+                  n_rows, LLMK_SAMPLE_STATIC_MAX_ROWS);
+    if (V <= 0 || ld < V) LLMK_FAIL("sample_static: bad sizes V=%d ld=%lld", V, ld);
+    if (!out || !logits || !seed || !temps) LLMK_FAIL("sample_static: out, logits, seed and temperatures are required");
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        LLMK_FAIL("sample_static: no usable current device (%s, device %d)", cudaGetErrorString(e), dev);
+    void* base = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(g_static_lock);
+        if (!g_static_ptr[dev]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_sample_static_scratch);
+            if (e != cudaSuccess || !p) {
+                snprintf(g_llmk_error, sizeof(g_llmk_error), "sample_static: cudaGetSymbolAddress failed on device %d: %s",
+                         dev, cudaGetErrorString(e));
+                return LLMK_CUDA_ERROR;
+            }
+            g_static_ptr[dev] = p;
+        }
+        base = g_static_ptr[dev];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    float* pv = (float*)base;
+    int* pi = (int*)(pv + (size_t)n_rows * SPLIT);
+    sample_partial_kernel<<<dim3(n_rows, SPLIT), THREADS, 0, s>>>(pv, pi, logits, ld, temps, seed, V);
+    LLMK_CHECK_LAUNCH("sample_static (first stage)");
+    sample_final_kernel<<<n_rows, 32, 0, s>>>(out, pv, pi);
+    LLMK_CHECK_LAUNCH("sample_static (second stage)");
+    return LLMK_OK;
+}
