@@ -1,0 +1,414 @@
+// Attention of single decoded tokens over the paged cache in bfloat16, shaped for memory bandwidth:
+// flash-decoding with the merge of the key parts fused into the same kernel.
+//
+// Grid (parts, kv heads x head chunks, sequences), 128 threads.  A block owns one sequence, one kv
+// head, up to GC query heads of its group (they share every K and V row that is read) and one part
+// of the visible keys [lo, ctx), where lo = max(0, ctx - window) for a windowed layer: the visible
+// range is cut evenly into `parts` pieces, so the launch shape does not depend on the context
+// lengths (a CUDA graph replays it).
+//   stream   every warp takes 8 of each 32 keys and brings their K and V rows into shared memory
+//            through a cp.async ring of its own (4 stages; keys past the part's end are zero-filled),
+//            so the loop has no block-wide barrier.  It keeps a running (m, l, acc): scores with 4
+//            lanes per key (float32 dot products against q, which sits in shared memory pre-multiplied
+//            by scale), maximum and sum over the 8 keys by shuffles, then P V with every lane owning
+//            head_dim / 32 output values for all GC heads.  The four warps' states are merged at the end.
+//   merge    with parts > 1 the block writes its un-normalised sums and (m, l) to scratch and takes
+//            a ticket from a per-(sequence, head chunk) counter; the block that draws the last ticket
+//            merges all parts in part order, sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p, writes
+//            the output row and resets the counter.  The result does not depend on which block
+//            merges.  Counters must be zero before the first launch and are left zero.
+// A sequence with ctx <= 0 (a padding row of a captured batch) gets zeros.
+//
+// Same algorithm as the reference's `attn_decode_kernel<G>` + `attn_decode_reduce_kernel`
+// (src/backend/cuda/attention/attention.cu:51-207): one block per (kv head, sequence, part), the
+// group's heads share K/V reads, three phases, partial (m, l, o) merged afterwards; here the merge
+// needs no second launch, any group size is taken (chunks of up to 8 heads), head_dim is 64 or
+// 128, and a window is cut into parts too.  Other head sizes use csrc/attention.cu.
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int WARPS = THREADS / 32;
+constexpr int KPW = 8;        // keys a warp takes per step
+constexpr int STAGES = 4;     // depth of each warp's cp.async ring
+
+struct DecodeParams {
+    const bf16* q;
+    const bf16* kcache;
+    const bf16* vcache;
+    bf16* out;
+    const int* block_tables;
+    const int* ctx_len;
+    const int* cu_q;
+    float* part_o;       // [tokens][nq][parts][hd]
+    float* part_ml;      // [tokens][nq][parts][2]
+    int* counters;       // [sequences][gridDim.y]
+    long long q_stride, o_stride;
+    int max_blocks, nq, nkv, log2_page, window, chunks, page_cap;
+    float scale;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;     // 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int HD, int GC>
+struct DecodeSmem {
+    static constexpr int ROW = HD * 2;                        // bytes of one key's K or V row
+    static constexpr int STAGE = 2 * KPW * ROW;               // one warp's stage: KPW rows of K, then of V
+    static constexpr int KV_OFF = 0;                          // [WARPS][STAGES][STAGE]
+    static constexpr int Q_OFF = KV_OFF + WARPS * STAGES * STAGE;   // float [GC][HD]
+    static constexpr int MRG_OFF = Q_OFF + GC * HD * 4;       // float [WARPS][GC][HD + 2]
+    static constexpr int PAGES_OFF = MRG_OFF + WARPS * GC * (HD + 2) * 4;
+    static size_t bytes(int page_cap) { return (size_t)PAGES_OFF + (size_t)page_cap * 4; }
+};
+
+template <int HD, int GC>
+__global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeParams p) {
+    using L = DecodeSmem<HD, GC>;
+    constexpr int DPL = HD / 32;        // output values per lane
+    constexpr int CH = HD / 32;         // 16-byte chunks of a K row per lane (4 lanes per key)
+    constexpr int CPR = HD / 8;         // 16-byte chunks per row
+    constexpr int CPL = KPW * CPR / 32; // chunks of K (and of V) a lane copies per stage
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* q_s = reinterpret_cast<float*>(smem + L::Q_OFF);
+    float* mrg = reinterpret_cast<float*>(smem + L::MRG_OFF);
+    int* pages_s = reinterpret_cast<int*>(smem + L::PAGES_OFF);
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int part = blockIdx.x, parts = gridDim.x;
+    const int kvh = blockIdx.y / p.chunks, chunk = blockIdx.y % p.chunks;
+    const int s = blockIdx.z;
+    const int G = p.nq / p.nkv;
+    const int g0 = chunk * GC;                      // first head of the chunk inside the group
+    const int n_heads = min(GC, G - g0);
+    pdl_launch_dependents();
+    pdl_wait();
+    const int ctx = p.ctx_len[s];
+    const int t = p.cu_q[s];
+    if (ctx <= 0) {
+        if (part == 0)
+            for (int i = tid; i < n_heads * HD; i += THREADS)
+                p.out[(size_t)t * p.o_stride + (size_t)(kvh * G + g0) * HD + i] = from_float<bf16>(0.f);
+        return;
+    }
+    const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int part_len = ceil_div(ceil_div(ctx - lo, parts), 8) * 8;
+    const int k_beg = lo + part * part_len;
+    const int k_end = min(ctx, k_beg + part_len);
+    const int n_keys = max(0, k_end - k_beg);
+    const int lps = p.log2_page, ps_mask = (1 << p.log2_page) - 1;
+    const int page_base = k_beg >> lps;
+    const int n_pages = n_keys > 0 ? ((k_end - 1) >> lps) - page_base + 1 : 0;
+    const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+
+    // The part's page ids and q (float32, pre-multiplied by scale; zeros for heads beyond the group).
+    for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = bt[page_base + i];
+    for (int i = tid; i < GC * HD; i += THREADS) {
+        const int g = i / HD;
+        q_s[i] = g < n_heads ? to_float(p.q[(size_t)t * p.q_stride + (size_t)(kvh * G + g0 + g) * HD + i % HD]) * p.scale : 0.f;
+    }
+    __syncthreads();
+
+    // Each warp streams the keys it is given (KPW of every WARPS * KPW) through a cp.async ring of
+    // its own, so the loop needs no block-wide barrier.  K rows are stored with their 16-byte chunks
+    // swizzled by the key's parity: the four lanes of two neighbouring keys then read eight different
+    // bank groups.  Keys past the part's end are zero-filled.
+    const int n_steps = ceil_div(n_keys, WARPS * KPW);
+    unsigned char* ring = smem + L::KV_OFF + warp * STAGES * L::STAGE;
+    auto issue = [&](int step, int stage) {
+        unsigned char* dst = ring + stage * L::STAGE;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+            const int c = lane + 32 * i;
+            const int key = c / CPR, l = c % CPR;
+            const int kidx = step * (WARPS * KPW) + warp * KPW + key;
+            const bool valid = kidx < n_keys;
+            const int kpos = k_beg + (valid ? kidx : 0);
+            const int page = pages_s[(kpos >> lps) - page_base];
+            const size_t off = ((((size_t)page * p.nkv + kvh) << lps) + (kpos & ps_mask)) * HD + l * 8;
+            cp_async_16(dst + key * L::ROW + ((l ^ ((key & 1) << 2)) << 4), p.kcache + off, valid);
+            cp_async_16(dst + KPW * L::ROW + key * L::ROW + (l << 4), p.vcache + off, valid);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < n_steps) issue(st, st); else cp_async_commit();
+    }
+
+    const int grp = lane >> 2, j = lane & 3;
+    float m[GC], l[GC], acc[GC][DPL];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
+    }
+    for (int step = 0; step < n_steps; ++step) {
+        const int stage = step % STAGES;
+        // the ring slot freed by the previous step takes the load of step + STAGES - 1
+        if (step + STAGES - 1 < n_steps) issue(step + STAGES - 1, (step + STAGES - 1) % STAGES); else cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        const unsigned char* Ks = ring + stage * L::STAGE;
+        const unsigned char* Vs = Ks + KPW * L::ROW;
+        const int key = grp;
+        const bool valid = step * (WARPS * KPW) + warp * KPW + key < n_keys;
+        float dot[GC];
+#pragma unroll
+        for (int g = 0; g < GC; ++g) dot[g] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int lc = c * 4 + j;
+            Vec16<bf16> v;
+            v.raw = *reinterpret_cast<const uint4*>(Ks + key * L::ROW + ((lc ^ ((key & 1) << 2)) << 4));
+            float kf[8];
+            v.unpack(kf);
+#pragma unroll
+            for (int g = 0; g < GC; ++g) {
+                const float4* qa = reinterpret_cast<const float4*>(q_s + g * HD + lc * 8);
+                const float4 a = qa[0], b = qa[1];
+                dot[g] = fmaf(a.x, kf[0], dot[g]); dot[g] = fmaf(a.y, kf[1], dot[g]);
+                dot[g] = fmaf(a.z, kf[2], dot[g]); dot[g] = fmaf(a.w, kf[3], dot[g]);
+                dot[g] = fmaf(b.x, kf[4], dot[g]); dot[g] = fmaf(b.y, kf[5], dot[g]);
+                dot[g] = fmaf(b.z, kf[6], dot[g]); dot[g] = fmaf(b.w, kf[7], dot[g]);
+            }
+        }
+        float pr[GC];
+#pragma unroll
+        for (int g = 0; g < GC; ++g) {
+            float d = dot[g];
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            const float sv = valid ? d : -INFINITY;
+            float mx = sv;
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m[g], mx);
+            const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
+            pr[g] = valid ? __expf(sv - m_new) : 0.f;
+            float sum = pr[g];
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+            l[g] = l[g] * alpha + sum;
+            m[g] = m_new;
+#pragma unroll
+            for (int dd = 0; dd < DPL; ++dd) acc[g][dd] *= alpha;
+        }
+#pragma unroll
+        for (int kk = 0; kk < KPW; ++kk) {
+            const unsigned char* vr = Vs + kk * L::ROW + lane * DPL * 2;
+            float vf[DPL];
+            if constexpr (DPL == 4) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
+            } else {
+                const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+                vf[0] = a.x; vf[1] = a.y;
+            }
+#pragma unroll
+            for (int g = 0; g < GC; ++g) {
+                const float pk = __shfl_sync(0xffffffffu, pr[g], kk * 4);
+#pragma unroll
+                for (int dd = 0; dd < DPL; ++dd) acc[g][dd] = fmaf(pk, vf[dd], acc[g][dd]);
+            }
+        }
+        __syncwarp();    // every lane has read the stage before it is refilled
+    }
+    cp_async_wait<0>();
+
+    // Merge the warps' states: M = max m_w, o = sum_w e^{m_w - M} acc_w, L = sum_w e^{m_w - M} l_w.
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+        float* row = mrg + (warp * GC + g) * (HD + 2);
+#pragma unroll
+        for (int dd = 0; dd < DPL; ++dd) row[lane * DPL + dd] = acc[g][dd];
+        if (lane == 0) {
+            row[HD] = m[g];
+            row[HD + 1] = l[g];
+        }
+    }
+    __syncthreads();
+    auto merged = [&](int g, int d, float& M, float& Lsum) -> float {
+        M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, mrg[(w * GC + g) * (HD + 2) + HD]);
+        float o = 0.f;
+        Lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float* row = mrg + (w * GC + g) * (HD + 2);
+            const float e = row[HD] == -INFINITY ? 0.f : __expf(row[HD] - M);
+            o += e * row[d];
+            Lsum += e * row[HD + 1];
+        }
+        return o;
+    };
+
+    // ---- the block's result
+    if (parts == 1) {
+        for (int i = tid; i < n_heads * HD; i += THREADS) {
+            float M, Ls;
+            const float o = merged(i / HD, i % HD, M, Ls);
+            p.out[(size_t)t * p.o_stride + (size_t)(kvh * G + g0) * HD + i] = from_float<bf16>(Ls > 0.f ? o / Ls : 0.f);
+        }
+        return;
+    }
+    for (int i = tid; i < n_heads * HD; i += THREADS) {
+        const int g = i / HD, d = i % HD;
+        float M, Ls;
+        const float o = merged(g, d, M, Ls);
+        const size_t row = ((size_t)t * p.nq + kvh * G + g0 + g) * parts + part;
+        p.part_o[row * HD + d] = o;
+        if (d == 0) {
+            p.part_ml[row * 2] = M;
+            p.part_ml[row * 2 + 1] = Ls;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* counter = p.counters + (size_t)s * gridDim.y + blockIdx.y;
+        const int ticket = atomicAdd(counter, 1);
+        is_last = ticket == parts - 1;
+        if (is_last) *counter = 0;     // every other block of this (sequence, chunk) has already drawn
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // (m, l) of every part of the chunk's heads into shared memory, then each thread merges one
+    // output value with independent loads of the parts' sums, in part order.
+    float* ml_s = mrg;      // [n_heads][parts][2], fits: parts <= 128
+    for (int i = tid; i < n_heads * parts * 2; i += THREADS) {
+        const int g = i / (parts * 2);
+        ml_s[i] = __ldcg(p.part_ml + ((size_t)t * p.nq + kvh * G + g0 + g) * parts * 2 + i % (parts * 2));
+    }
+    __syncthreads();
+    for (int i = tid; i < n_heads * HD; i += THREADS) {
+        const int g = i / HD, d = i % HD;
+        const float* ml = ml_s + g * parts * 2;
+        const float* po = p.part_o + ((size_t)t * p.nq + kvh * G + g0 + g) * parts * HD + d;
+        float M = -INFINITY;
+        for (int pt = 0; pt < parts; ++pt)
+            if (ml[2 * pt + 1] > 0.f) M = fmaxf(M, ml[2 * pt]);
+        float denom = 0.f, v = 0.f;
+        for (int pt0 = 0; pt0 < parts; pt0 += 8) {
+            float o[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) o[u] = pt0 + u < parts ? __ldcg(po + (size_t)(pt0 + u) * HD) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (pt0 + u < parts) {
+                    const float lp = ml[2 * (pt0 + u) + 1];
+                    if (lp > 0.f) {
+                        const float e = __expf(ml[2 * (pt0 + u)] - M);
+                        denom += e * lp;
+                        v += e * o[u];
+                    }
+                }
+            }
+        }
+        p.out[(size_t)t * p.o_stride + (size_t)(kvh * G + g0) * HD + i] = from_float<bf16>(denom > 0.f ? v / denom : 0.f);
+    }
+}
+
+template <int HD, int GC>
+int launch(const DecodeParams& p, dim3 grid, size_t smem, cudaStream_t s) {
+    auto kernel = attention_decode_kernel<HD, GC>;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LLMK_FAIL("attention_decode: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+        configured = smem;
+    }
+    LLMK_CHECK_LAUNCH_RC("attention_decode", llmk_launch(kernel, grid, dim3(THREADS), smem, s, true, p));
+    return LLMK_OK;
+}
+
+template <int HD>
+int dispatch_group(int gc, const DecodeParams& p, dim3 grid, cudaStream_t s) {
+    switch (gc) {
+        case 1: return launch<HD, 1>(p, grid, DecodeSmem<HD, 1>::bytes(p.page_cap), s);
+        case 2: return launch<HD, 2>(p, grid, DecodeSmem<HD, 2>::bytes(p.page_cap), s);
+        case 4: return launch<HD, 4>(p, grid, DecodeSmem<HD, 4>::bytes(p.page_cap), s);
+        default: return launch<HD, 8>(p, grid, DecodeSmem<HD, 8>::bytes(p.page_cap), s);
+    }
+}
+
+int chunk_heads(int G) { return G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8; }
+
+}  // namespace
+
+// 1 if the kernel takes these sizes.
+LLMK_EXPORT int llmk_attention_decode_usable(int nq, int nkv, int hd, int page_size) {
+    if (nkv <= 0 || nq <= 0 || nq % nkv != 0 || page_size <= 0) return 0;
+    if ((page_size & (page_size - 1)) != 0) return 0;       // page and offset of a key by shift and mask
+    return (hd == 64 || hd == 128) ? 1 : 0;
+}
+
+// Floats of scratch for `n_seqs` sequences cut into `parts`: partial outputs, then (m, l) pairs.
+LLMK_EXPORT long long llmk_attention_decode_scratch_floats(int n_seqs, int nq, int hd, int parts) {
+    return parts <= 1 ? 0 : (long long)n_seqs * nq * parts * (hd + 2);
+}
+
+// Ints of counters for `n_seqs` sequences (zero them once; every launch leaves them zero).
+LLMK_EXPORT long long llmk_attention_decode_counters(int n_seqs, int nq, int nkv) {
+    if (nkv <= 0) return 0;
+    const int G = nq / nkv;
+    return (long long)n_seqs * nkv * ceil_div(G, chunk_heads(G));
+}
+
+// out[t, nq*hd] for the single token t = cu_q[s] of each of n_seqs sequences.  `max_ctx` bounds every
+// ctx_len[s] of this launch (it sizes the shared-memory copy of a part's page ids).
+LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void* q, long long q_stride,
+                                      const void* kcache, const void* vcache, const int* block_tables,
+                                      int max_blocks, const int* ctx_len, const int* cu_q, int n_seqs, int nq,
+                                      int nkv, int hd, int page_size, int window, float scale, int parts,
+                                      int max_ctx, float* scratch, int* counters, void* stream) {
+    if (n_seqs <= 0) return LLMK_OK;
+    if (!llmk_attention_decode_usable(nq, nkv, hd, page_size))
+        LLMK_FAIL("attention_decode: not taken (heads %d/%d, head_dim %d must be 64 or 128, page size %d must be a power of two)", nq, nkv, hd, page_size);
+    if (parts < 1 || parts > 128 || (parts > 1 && (!scratch || !counters)))
+        LLMK_FAIL("attention_decode: bad split (%d parts, scratch %p, counters %p)", parts, (void*)scratch, (void*)counters);
+    if (n_seqs > 65535) LLMK_FAIL("attention_decode: %d sequences exceed the grid", n_seqs);
+    if (!host_aligned16(q) || !host_aligned16(kcache) || !host_aligned16(vcache) || q_stride % 8 != 0)
+        LLMK_FAIL("attention_decode: q and the cache must start on 16-byte boundaries");
+    DecodeParams p;
+    const int G = nq / nkv;
+    const int gc = chunk_heads(G);
+    p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;
+    p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
+    p.part_o = scratch;
+    p.part_ml = parts > 1 ? scratch + (size_t)n_seqs * nq * parts * hd : nullptr;
+    p.counters = counters;
+    p.q_stride = q_stride; p.o_stride = o_stride; p.max_blocks = max_blocks;
+    p.nq = nq; p.nkv = nkv; p.window = window;
+    p.log2_page = 0;
+    while ((1 << p.log2_page) < page_size) ++p.log2_page;
+    p.chunks = ceil_div(G, gc);
+    const int visible = window > 0 ? min(window, max_ctx) : max_ctx;
+    const int part_cap = ceil_div(ceil_div(max(visible, 1), parts), 8) * 8;
+    p.page_cap = part_cap / page_size + 2;       // page ids of one part, kept in shared memory
+    p.scale = scale;
+    if ((size_t)p.page_cap * 4 > 64 * 1024)
+        LLMK_FAIL("attention_decode: %d keys per part in pages of %d need too much shared memory; use more parts", part_cap, page_size);
+    dim3 grid(parts, nkv * p.chunks, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    return hd == 128 ? dispatch_group<128>(gc, p, grid, s) : dispatch_group<64>(gc, p, grid, s);
+}

@@ -1,0 +1,437 @@
+// Causal grouped-query attention over the paged cache for prompts and prompt portions in bfloat16,
+// on the 5th-generation tensor cores of sm_100a: S = Q K^T and O = P V are `tcgen05.mma`
+// instructions with their accumulators in tensor memory; K and V pages arrive through TMA.
+//
+// Block = one tile of 128 rows of one (sequence, kv head): 128 / gc queries x gc query heads of the
+// kv head's group (gc = the largest power of two dividing the group size, at most 16), so a K/V
+// tile is read once for gc heads.  192 threads:
+//   warp 0     TMA producer: the Q tile once (a 3-D box [queries, gc heads, 64] per half of the head),
+//              then per tile of 128 keys the K pages and the V pages of the block table into a ring
+//              of two stages.
+//   warp 1     owns tensor memory (S0 | S1 | O: 128 + 128 + head_dim columns) and issues the MMAs:
+//              S[j] = Q K_j^T (K-major operands), O_j = P_j V_j (V read MN-major: keys are V's rows
+//              in shared memory).  S is double-buffered so that Q K_{j+1}^T runs under the softmax of
+//              tile j.
+//   warps 2-5  softmax: one thread per row.  Pass 1 reads S from tensor memory and finds the row
+//              maximum (causal and window mask on the tiles that need it); then the previous tile's
+//              O_j is read back and added to the float32 accumulator in registers, rescaled by
+//              exp(m_old - m_new); pass 2 writes P = exp2((s - m) * scale * log2 e) as bfloat16 into
+//              shared memory in the swizzled K-major layout the second MMA reads.
+// Statistics (m, l), the accumulator and the final division are float32.
+//
+// Tiles follow the reference's prefill kernel in spirit (src/backend/cuda/attention/attention.cu:300-466:
+// 64-query tiles, `mma.sync`, K/V through `cp.async`, group sizes 1 and 2 only); semantics follow its
+// CPU attention (src/backend/cpu/attention.zig:64-118): query j of a portion sits at position
+// ctx - q_len + j and sees keys 0..position (or the last `window` of them); a row with ctx < q_len
+// gives zeros.
+//
+// Taken: head_dim 64 or 128, page sizes 16, 32, 64, 128, any group size.  Everything else is refused
+// with an error and the caller uses the CUDA-core kernel (csrc/attention.cu).  The cache arrays must
+// hold finite values everywhere (slots never written are zero): masked keys enter the second MMA
+// with weight 0.  Every wait is bounded; a wait that gives up raises `*error_flag`.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int BM = 128;     // rows of a tile
+constexpr int BN = 128;     // keys per tile
+constexpr int THREADS = 192;
+constexpr int MAX_PAGES_PER_TILE = 8;   // page size >= 16
+
+struct Params {
+    bf16* out;
+    long long o_stride;
+    const int* block_tables;
+    const int* ctx_len;
+    const int* cu_q;
+    const int* tile_seq;
+    const int* tile_q0;
+    int* error_flag;
+    int max_blocks, nq, nkv, page_size, window, gc, bq, chunks;
+    float scale_log2;
+    unsigned v_lbo, v_sbo;
+};
+
+template <int HD>
+struct Smem {
+    static constexpr int Q_BYTES = BM * HD * 2;
+    static constexpr int KV_BYTES = BN * HD * 2;       // one K or V tile
+    static constexpr int P_BYTES = BM * BN * 2;
+    static constexpr int Q_OFF = 0;
+    static constexpr int K_OFF = Q_OFF + Q_BYTES;       // 2 stages
+    static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;  // 2 stages
+    static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
+    static constexpr int BAR_OFF = P_OFF + P_BYTES;
+    static constexpr int NUM_BARS = 13;
+    static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const Params p) {
+    using L = Smem<HD>;
+    constexpr int HB = HD / 64;                 // 64-wide blocks of the head
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t S_COL0 = 0, S_COL1 = BN, O_COL = 2 * BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    uint64_t* q_full = bars;            // 1
+    uint64_t* k_full = bars + 1;        // 2
+    uint64_t* v_full = bars + 3;        // 2
+    uint64_t* k_empty = bars + 5;       // 2
+    uint64_t* v_empty = bars + 7;       // 2
+    uint64_t* s_full = bars + 9;        // 2
+    uint64_t* p_full = bars + 11;       // 1, 128 arrivals
+    uint64_t* o_full = bars + 12;       // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = p.nq / p.nkv;
+    const int kvh = blockIdx.y / p.chunks;
+    const int chunk = blockIdx.y % p.chunks;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < L::NUM_BARS; ++i) tc::mbar_init(tc::smem_u32(&bars[i]), i == 11 ? 128 : 1);
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&map_q);
+        tc::prefetch_tensormap(&map_k);
+        tc::prefetch_tensormap(&map_v);
+        pdl_launch_dependents();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();   // q, the cache and the step's arrays come from earlier work of the stream
+
+    const int s = p.tile_seq[blockIdx.x];
+    const int q0 = p.tile_q0[blockIdx.x];
+    const int q_beg = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - q_beg;
+    const int ctx = p.ctx_len[s];
+    const int nq_tile = min(p.bq, q_len - q0);
+    const bool padding = ctx < q_len || nq_tile <= 0;
+    const int first_pos = ctx - q_len + q0;
+    int kt0 = 0, n_tiles = 0;
+    if (!padding) {
+        const int k_end = first_pos + nq_tile;
+        const int k_beg = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+        kt0 = (k_beg / BN) * BN;
+        n_tiles = (k_end - kt0 + BN - 1) / BN;
+    }
+    const int head0 = kvh * G + chunk * p.gc;
+
+    if (warp == 0) {
+        if (lane == 0 && n_tiles > 0) {
+            const uint32_t qbar = tc::smem_u32(q_full);
+            tc::mbar_expect_tx(qbar, L::Q_BYTES);
+#pragma unroll
+            for (int h = 0; h < HB; ++h)
+                tc::tma_load_3d(tc::smem_u32(smem + L::Q_OFF + h * BM * 128), &map_q, qbar, h * 64, head0, q_beg + q0);
+            const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+            const int ps = p.page_size;
+            const int pages_per_tile = BN / ps;
+            const int last_page = (ctx - 1) / ps;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j & 1;
+                const uint32_t round = j >> 1;
+                int rows[MAX_PAGES_PER_TILE];
+                const int page0 = (kt0 + j * BN) / ps;
+#pragma unroll
+                for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg) {
+                    if (pg < pages_per_tile) {
+                        int page = __ldg(bt + min(page0 + pg, last_page));
+                        if (page < 0) page = __ldg(bt + last_page);   // a page the window has passed: masked anyway
+                        rows[pg] = (page * p.nkv + kvh) * ps;
+                    }
+                }
+                if (!tc::mbar_wait(tc::smem_u32(&k_empty[st]), (round & 1) ^ 1, abort_flag)) break;
+                uint32_t bar = tc::smem_u32(&k_full[st]);
+                tc::mbar_expect_tx(bar, L::KV_BYTES);
+                uint32_t dst = tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
+#pragma unroll
+                for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg)
+                    if (pg < pages_per_tile)
+#pragma unroll
+                        for (int h = 0; h < HB; ++h)
+                            tc::tma_load_2d(dst + h * BN * 128 + pg * ps * 128, &map_k, bar, h * 64, rows[pg]);
+                if (!tc::mbar_wait(tc::smem_u32(&v_empty[st]), (round & 1) ^ 1, abort_flag)) break;
+                bar = tc::smem_u32(&v_full[st]);
+                tc::mbar_expect_tx(bar, L::KV_BYTES);
+                dst = tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+#pragma unroll
+                for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg)
+                    if (pg < pages_per_tile)
+#pragma unroll
+                        for (int h = 0; h < HB; ++h)
+                            tc::tma_load_2d(dst + h * BN * 128 + pg * ps * 128, &map_v, bar, h * 64, rows[pg]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t idesc_s = tc::idesc_bf16_f32(BM, BN);
+            constexpr uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(BM, HD);
+            const uint32_t q_addr = tc::smem_u32(smem + L::Q_OFF);
+            const uint32_t p_addr = tc::smem_u32(smem + L::P_OFF);
+            auto issue_qk = [&](int j) -> bool {
+                const int st = j & 1;
+                if (!tc::mbar_wait(tc::smem_u32(&k_full[st]), (j >> 1) & 1, abort_flag)) return false;
+                tc::tc_fence_after_sync();
+                const uint32_t k_addr = tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32;
+                    tc::mma_bf16_ss(tmem_base + (st ? S_COL1 : S_COL0), tc::smem_desc_sw128(q_addr + off),
+                                    tc::smem_desc_sw128(k_addr + off), idesc_s, k != 0);
+                }
+                tc::mma_commit(tc::smem_u32(&s_full[st]));
+                tc::mma_commit(tc::smem_u32(&k_empty[st]));
+                return true;
+            };
+            bool ok = tc::mbar_wait(tc::smem_u32(q_full), 0, abort_flag);
+            if (ok) tc::tc_fence_after_sync();
+            ok = ok && issue_qk(0);
+            if (ok && n_tiles > 1) ok = issue_qk(1);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int st = j & 1;
+                ok = tc::mbar_wait(tc::smem_u32(p_full), j & 1, abort_flag) &&
+                     tc::mbar_wait(tc::smem_u32(&v_full[st]), (j >> 1) & 1, abort_flag);
+                if (!ok) break;
+                tc::tc_fence_after_sync();
+                const uint32_t v_addr = tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t da = tc::smem_desc_sw128(p_addr + (kk / 4) * (BM * 128) + (kk % 4) * 32);
+                    const uint64_t db = tc::smem_desc_sw128_mn(v_addr + kk * 16 * 128, p.v_lbo, p.v_sbo);
+                    tc::mma_bf16_ss(tmem_base + O_COL, da, db, idesc_o, kk != 0);
+                }
+                tc::mma_commit(tc::smem_u32(o_full));
+                tc::mma_commit(tc::smem_u32(&v_empty[st]));
+                if (j + 2 < n_tiles) ok = issue_qk(j + 2);
+            }
+        }
+    } else {
+        // Softmax and accumulation: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int qi = r / p.gc;
+        const int head = head0 + r % p.gc;
+        const bool row_valid = !padding && qi < nq_tile && (chunk * p.gc + r % p.gc) < G;
+        const int qpos = first_pos + qi;
+        const int lo = p.window > 0 ? qpos - p.window : -1;   // keys at positions > lo are visible
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float sl2 = p.scale_log2;
+        float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
+        float acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+        uint8_t* p_row = smem + L::P_OFF + r * 128;
+        bool ok = true;
+
+        auto accumulate = [&](float alpha) {
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o[32];
+                tc::tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(o[i]));
+            }
+        };
+
+        for (int j = 0; j < n_tiles; ++j) {
+            const int st = j & 1;
+            const int k0 = kt0 + j * BN;
+            ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag));
+            if (!ok) break;
+            tc::tc_fence_after_sync();
+            const uint32_t s_addr = tmem_base + lane_addr + (st ? S_COL1 : S_COL0);
+            const bool need_mask = (k0 + BN - 1 > qpos) || (k0 <= lo);
+            // pass 1: the row maximum
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tc::tmem_ld_32x32(s_addr + c * 32, v);
+                tc::tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int kpos = k0 + c * 32 + i;
+                        if (kpos <= qpos && kpos > lo) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * sl2);
+            // the previous tile's P V, now that its MMA has had pass 1 to finish
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(o_full), (j - 1) & 1, abort_flag));
+                if (!ok) break;
+                tc::tc_fence_after_sync();
+                accumulate(alpha_pending);
+            }
+            alpha_pending = alpha;
+            // pass 2: P into shared memory, row sum
+            const float mb = (m_new == -INFINITY) ? 0.f : m_new * sl2;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tc::tmem_ld_32x32(s_addr + c * 32, v);
+                tc::tmem_ld_wait();
+                float pv[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int kpos = k0 + c * 32 + i;
+                    const bool vis = !need_mask || (kpos <= qpos && kpos > lo);
+                    pv[i] = vis ? fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -mb)) : 0.f;
+                    sum += pv[i];
+                }
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {
+                    Vec16<bf16> pk;
+                    pk.pack(pv + q8 * 8);
+                    const int col = c * 32 + q8 * 8;
+                    const int chunk16 = (col % 64) / 8;
+                    *reinterpret_cast<uint4*>(p_row + (col / 64) * (BM * 128) + ((chunk16 ^ (r & 7)) << 4)) = pk.raw;
+                }
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            tc::fence_proxy_async();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(tc::smem_u32(p_full));
+        }
+        if (ok && n_tiles > 0) {
+            ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(o_full), (n_tiles - 1) & 1, abort_flag));
+            if (ok) {
+                tc::tc_fence_after_sync();
+                accumulate(alpha_pending);
+            }
+        }
+        if (ok && qi < max(nq_tile, 0) && (chunk * p.gc + r % p.gc) < G) {
+            const float inv = (row_valid && l > 0.f) ? 1.0f / l : 0.f;
+            bf16* o = p.out + (size_t)(q_beg + q0 + qi) * p.o_stride + (size_t)head * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = acc[i + e] * inv;
+                Vec16<bf16> pk;
+                pk.pack(f);
+                *reinterpret_cast<uint4*>(o + i) = pk.raw;
+            }
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
+int group_chunk(int G) {
+    int gc = 1;
+    while (gc < 16 && G % (gc * 2) == 0) gc *= 2;
+    return gc;
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, dim3 grid,
+           cudaStream_t s) {
+    using L = Smem<HD>;
+    auto kernel = attention_tc_kernel<HD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) LLMK_FAIL("attention_tc: cannot raise shared memory to %d: %s", L::TOTAL, cudaGetErrorString(e));
+        configured = true;
+    }
+    LLMK_CHECK_LAUNCH_RC("attention_tc", llmk_launch(kernel, grid, dim3(THREADS), L::TOTAL, s, true, mq, mk, mv, p));
+    return LLMK_OK;
+}
+
+}  // namespace
+
+// Queries per tile for this group size (0: the kernel does not take these sizes).
+LLMK_EXPORT int llmk_attention_tc_tile_queries(int nq, int nkv, int hd, int page_size) {
+    if (nkv <= 0 || nq <= 0 || nq % nkv != 0) return 0;
+    if (hd != 64 && hd != 128) return 0;
+    if (page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return 0;
+    return BM / group_chunk(nq / nkv);
+}
+
+// out[t, nq*hd] = attention of q[t] (bfloat16, row stride q_stride) over the paged cache
+// [num_pages, nkv, page_size, hd].  tile_seq / tile_q0 list tiles of `llmk_attention_tc_tile_queries`
+// queries each.  v_lbo / v_sbo: 0 for the defaults (descriptor strides of the V operand).
+LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, long long q_stride, int n_tokens,
+                                  const void* kcache, const void* vcache, long long num_pages,
+                                  const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,
+                                  const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd,
+                                  int page_size, int window, float scale, int* error_flag, unsigned v_lbo,
+                                  unsigned v_sbo, void* stream) {
+    if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
+    const int bq = llmk_attention_tc_tile_queries(nq, nkv, hd, page_size);
+    if (bq == 0)
+        LLMK_FAIL("attention_tc: not taken (heads %d/%d, head_dim %d must be 64 or 128, page size %d must be 16, 32, 64 or 128)",
+                  nq, nkv, hd, page_size);
+    if (q_stride % 8 != 0 || o_stride % 8 != 0 || !host_aligned16(q) || !host_aligned16(out) || !host_aligned16(kcache) ||
+        !host_aligned16(vcache))
+        LLMK_FAIL("attention_tc: q, out and the cache must start on 16-byte boundaries with row strides that are multiples of 8");
+    if (nkv > 65535) LLMK_FAIL("attention_tc: grid too large");
+    Params p;
+    const int G = nq / nkv;
+    p.gc = group_chunk(G);
+    p.bq = bq;
+    p.chunks = G / p.gc;
+    p.out = (bf16*)out;
+    p.o_stride = o_stride;
+    p.block_tables = block_tables;
+    p.ctx_len = ctx_len;
+    p.cu_q = cu_q;
+    p.tile_seq = tile_seq;
+    p.tile_q0 = tile_q0;
+    p.error_flag = error_flag;
+    p.max_blocks = max_blocks;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.page_size = page_size;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.v_lbo = v_lbo ? v_lbo : (unsigned)(BN * 128);
+    p.v_sbo = v_sbo ? v_sbo : 1024u;
+    CUtensorMap mq, mk, mv;
+    if (!tc_host::make_map_bf16_3d(&mq, q, hd, nq, n_tokens, hd, q_stride, p.gc, p.bq))
+        LLMK_FAIL("attention_tc: cuTensorMapEncodeTiled failed for q");
+    const uint64_t rows = (uint64_t)num_pages * nkv * page_size;
+    if (!tc_host::cached_map_bf16_2d(&mk, kcache, rows, hd, hd, page_size) ||
+        !tc_host::cached_map_bf16_2d(&mv, vcache, rows, hd, hd, page_size))
+        LLMK_FAIL("attention_tc: cuTensorMapEncodeTiled failed for the cache");
+    dim3 grid(n_tiles, nkv * p.chunks);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 128) return launch<128>(mq, mk, mv, p, grid, s);
+    return launch<64>(mq, mk, mv, p, grid, s);
+}

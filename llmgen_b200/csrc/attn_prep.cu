@@ -10,7 +10,10 @@
 // width below the head width (src/module/rope.zig:86-88) are taken.
 //
 // Layouts: qkv[t] = [q heads | k heads | v heads], each head `hd` values, row stride given;
-// q is normalised and rotated in place; cache arrays are [page][kv_head][page_size][hd]
+// q is normalised and rotated into `q_out` (which may be the packed rows themselves).  The packed
+// rows are of the storage type T, or (splits > 0) `splits` float32 slices [splits][n][row_stride],
+// `split_stride` floats apart, added in slice order: the partial sums of a projection cut along K.
+// Cache arrays are [page][kv_head][page_size][hd]
 // (src/memory/page_atten.zig:2) and slot = page * page_size + offset, slot < 0 = do not store.
 // cos/sin tables are float32 [max_positions, rot/2], computed on the host in float64.
 #include "common.cuh"
@@ -21,7 +24,22 @@ constexpr int MAX_PAIRS = 8;   // rot/2 <= 256 per lane-strided loop of 32
 constexpr int MAX_TAIL = 16;   // hd - rot <= 512
 
 template <typename T>
-__global__ void attn_prep_kernel(T* __restrict__ qkv, long long row_stride, T* __restrict__ kcache,
+struct PackedRow {
+    const T* x;
+    const float* p;
+    int splits;
+    long long split_stride;
+    __device__ __forceinline__ float operator[](int e) const {
+        if (splits == 0) return to_float(x[e]);
+        float acc = p[e];
+        for (int sp = 1; sp < splits; ++sp) acc += p[(size_t)sp * split_stride + e];
+        return acc;
+    }
+};
+
+template <typename T>
+__global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_stride, int splits, long long split_stride,
+                                 T* __restrict__ q_out, long long q_stride, T* __restrict__ kcache,
                                  T* __restrict__ vcache, const int* __restrict__ positions,
                                  const int* __restrict__ slots, const float* __restrict__ cos_tab,
                                  const float* __restrict__ sin_tab, const float* __restrict__ q_gain,
@@ -34,14 +52,36 @@ __global__ void attn_prep_kernel(T* __restrict__ qkv, long long row_stride, T* _
     if (item >= (long long)n_tokens * heads) return;
     const int t = (int)(item / heads);
     const int h = (int)(item % heads);
-    T* x = qkv + (size_t)t * row_stride + (size_t)h * hd;
+    pdl_launch_dependents();
+    pdl_wait();
+    PackedRow<T> x;
+    x.x = static_cast<const T*>(qkv) + (size_t)t * row_stride + (size_t)h * hd;
+    x.p = static_cast<const float*>(qkv) + (size_t)t * row_stride + (size_t)h * hd;
+    x.splits = splits;
+    x.split_stride = split_stride;
     const int slot = slots ? slots[t] : -1;
 
     if (h >= nq + nk) {  // a value head: copy into the cache
         if (slot < 0 || !vcache) return;
         const int kvh = h - nq - nk;
         T* dst = vcache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd;
-        for (int i = lane; i < hd; i += 32) dst[i] = x[i];
+        if (splits == 0) {
+            for (int i = lane; i < hd; i += 32) dst[i] = x.x[i];
+            return;
+        }
+        float vv[MAX_TAIL];
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i) vv[i] = 0.f;
+#pragma unroll 4
+        for (int sp = 0; sp < splits; ++sp) {
+            const float* ps = x.p + (size_t)sp * split_stride;
+#pragma unroll
+            for (int i = 0; i < MAX_TAIL; ++i)
+                if (lane + 32 * i < hd) vv[i] += __ldcg(ps + lane + 32 * i);
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i)
+            if (lane + 32 * i < hd) dst[lane + 32 * i] = from_float<T>(vv[i]);
         return;
     }
     const bool is_q = h < nq;
@@ -51,23 +91,50 @@ __global__ void attn_prep_kernel(T* __restrict__ qkv, long long row_stride, T* _
 
     float a[MAX_PAIRS], b[MAX_PAIRS], tail[MAX_TAIL];
     float ss = 0.f;
+    if (splits == 0) {
 #pragma unroll
-    for (int i = 0; i < MAX_PAIRS; ++i) {
-        const int p = lane + 32 * i;
-        if (p < half) {
-            a[i] = to_float(x[p]);
-            b[i] = to_float(x[p + half]);
-            ss += a[i] * a[i] + b[i] * b[i];
+        for (int i = 0; i < MAX_PAIRS; ++i) {
+            const int p = lane + 32 * i;
+            if (p < half) {
+                a[i] = to_float(x.x[p]);
+                b[i] = to_float(x.x[p + half]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i) {
+            const int e = rot + lane + 32 * i;
+            if (e < hd) tail[i] = to_float(x.x[e]);
+        }
+    } else {
+        // partial sums: the loads of one slice are independent, slices are added in order
+#pragma unroll
+        for (int i = 0; i < MAX_PAIRS; ++i) a[i] = b[i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i) tail[i] = 0.f;
+#pragma unroll 4
+        for (int sp = 0; sp < splits; ++sp) {
+            const float* ps = x.p + (size_t)sp * split_stride;
+#pragma unroll
+            for (int i = 0; i < MAX_PAIRS; ++i) {
+                const int p = lane + 32 * i;
+                if (p < half) {
+                    a[i] += __ldcg(ps + p);
+                    b[i] += __ldcg(ps + p + half);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < MAX_TAIL; ++i) {
+                const int e = rot + lane + 32 * i;
+                if (e < hd) tail[i] += __ldcg(ps + e);
+            }
         }
     }
 #pragma unroll
-    for (int i = 0; i < MAX_TAIL; ++i) {
-        const int e = rot + lane + 32 * i;
-        if (e < hd) {
-            tail[i] = to_float(x[e]);
-            ss += tail[i] * tail[i];
-        }
-    }
+    for (int i = 0; i < MAX_PAIRS; ++i)
+        if (lane + 32 * i < half) ss += a[i] * a[i] + b[i] * b[i];
+#pragma unroll
+    for (int i = 0; i < MAX_TAIL; ++i)
+        if (rot + lane + 32 * i < hd) ss += tail[i] * tail[i];
     if (gain) {
         ss = warp_sum(ss);
         const float rinv = 1.0f / sqrtf(ss / (float)hd + eps);
@@ -101,7 +168,7 @@ __global__ void attn_prep_kernel(T* __restrict__ qkv, long long row_stride, T* _
     }
     T* dst;
     if (is_q) {
-        dst = x;
+        dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
     } else {
         if (slot < 0 || !kcache) return;
         const int kvh = h - nq;
@@ -124,7 +191,8 @@ __global__ void attn_prep_kernel(T* __restrict__ qkv, long long row_stride, T* _
 
 // nk = number of k (and v) heads present in the packed rows: num_kv_heads for a layer that
 // writes its cache, 0 for a layer that only reads another layer's cache.
-LLMK_EXPORT int llmk_attn_prep(void* qkv, long long row_stride, void* kcache, void* vcache, const int* positions,
+LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits, long long split_stride, void* q_out,
+                               long long q_stride, void* kcache, void* vcache, const int* positions,
                                const int* slots, const float* cos_tab, const float* sin_tab, const float* q_gain,
                                const float* k_gain, int n_tokens, int nq, int nk, int nkv_cache, int hd, int rot,
                                int page_size, float eps, float q_off, float k_off, int dtype, void* stream) {
@@ -134,6 +202,8 @@ LLMK_EXPORT int llmk_attn_prep(void* qkv, long long row_stride, void* kcache, vo
     if (rot / 2 > 32 * MAX_PAIRS || hd - rot > 32 * MAX_TAIL) LLMK_FAIL("attn_prep: head_dim %d / rotary width %d too large", hd, rot);
     if (nq < 0 || nk < 0 || nq + nk <= 0) LLMK_FAIL("attn_prep: bad head counts nq=%d nk=%d", nq, nk);
     if (nk > 0 && (page_size <= 0 || nkv_cache < nk)) LLMK_FAIL("attn_prep: bad cache geometry page_size=%d kv heads=%d", page_size, nkv_cache);
+    if (splits < 0 || (splits > 0 && split_stride <= 0)) LLMK_FAIL("attn_prep: bad partial sums (%d slices)", splits);
+    if (!q_out && nq > 0) LLMK_FAIL("attn_prep: no place for q");
     if (!cos_tab) rot = 0;
     if (cos_tab && (!sin_tab || !positions)) LLMK_FAIL("attn_prep: rotary tables need sin and positions");
     cudaStream_t s = (cudaStream_t)stream;
@@ -141,16 +211,19 @@ LLMK_EXPORT int llmk_attn_prep(void* qkv, long long row_stride, void* kcache, vo
     const long long items = (long long)n_tokens * (nq + 2 * nk);
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 2147483647LL) LLMK_FAIL("attn_prep: too many rows");
+    cudaError_t e;
     if (dtype == LLMK_F32)
-        attn_prep_kernel<float><<<(unsigned)blocks, warps * 32, 0, s>>>(
-            (float*)qkv, row_stride, (float*)kcache, (float*)vcache, positions, slots, cos_tab, sin_tab, q_gain,
-            k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off, k_off);
+        e = llmk_launch(attn_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
+                        splits, split_stride, (float*)q_out, q_stride, (float*)kcache, (float*)vcache, positions, slots,
+                        cos_tab, sin_tab, q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off,
+                        k_off);
     else if (dtype == LLMK_BF16)
-        attn_prep_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, s>>>(
-            (bf16*)qkv, row_stride, (bf16*)kcache, (bf16*)vcache, positions, slots, cos_tab, sin_tab, q_gain, k_gain,
-            n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off, k_off);
+        e = llmk_launch(attn_prep_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
+                        splits, split_stride, (bf16*)q_out, q_stride, (bf16*)kcache, (bf16*)vcache, positions, slots,
+                        cos_tab, sin_tab, q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off,
+                        k_off);
     else
         LLMK_FAIL("attn_prep: unknown dtype %d", dtype);
-    LLMK_CHECK_LAUNCH("attn_prep");
+    LLMK_CHECK_LAUNCH_RC("attn_prep", e);
     return LLMK_OK;
 }

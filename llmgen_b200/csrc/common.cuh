@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+#include <utility>
 
 #define LLMK_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -107,3 +109,47 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     __syncthreads();
     return scratch[32];
 }
+
+// ------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with `llmk_launch(..., pdl = true)` may start while the kernel before it in
+// the stream is still draining.  Such a kernel must call `pdl_wait()` before it reads anything an
+// earlier kernel wrote or writes anything an earlier kernel may still read; what comes before the
+// wait (barrier set-up, loads of weights) overlaps the predecessor's tail.  `pdl_launch_dependents()`
+// lets the next kernel begin its own prologue.  Both are no-ops in a plain launch.  LLMGEN_PDL=0 in
+// the environment turns the attribute off everywhere.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool llmk_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("LLMGEN_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t llmk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl && llmk_pdl_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+#define LLMK_CHECK_LAUNCH_RC(what, rc__)                                                           \
+    do {                                                                                           \
+        cudaError_t e__ = (rc__);                                                                  \
+        if (e__ != cudaSuccess) {                                                                  \
+            snprintf(g_llmk_error, sizeof(g_llmk_error), "%s: %s", what, cudaGetErrorString(e__)); \
+            return LLMK_CUDA_ERROR;                                                                \
+        }                                                                                          \
+    } while (0)

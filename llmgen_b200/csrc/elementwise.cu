@@ -19,6 +19,8 @@ template <typename T>
 __global__ void embed_rows_kernel(float* __restrict__ out, const T* __restrict__ table,
                                   const int* __restrict__ ids, int H, int V, int* bad) {
     const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
     if (!ok && threadIdx.x == 0 && bad) atomicAdd(bad, 1);
@@ -33,40 +35,75 @@ LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, i
     if (H <= 0 || V <= 0) LLMK_FAIL("embed_rows: bad sizes H=%d V=%d", H, V);
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
+    cudaError_t e;
     if (dtype == LLMK_F32)
-        embed_rows_kernel<float><<<n_tokens, threads, 0, s>>>(out, (const float*)table, ids, H, V, bad_flag);
+        e = llmk_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const float*)table, ids, H, V, bad_flag);
     else if (dtype == LLMK_BF16)
-        embed_rows_kernel<bf16><<<n_tokens, threads, 0, s>>>(out, (const bf16*)table, ids, H, V, bad_flag);
+        e = llmk_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const bf16*)table, ids, H, V, bad_flag);
     else
         LLMK_FAIL("embed_rows: unknown dtype %d", dtype);
-    LLMK_CHECK_LAUNCH("embed_rows");
+    LLMK_CHECK_LAUNCH_RC("embed_rows", e);
     return LLMK_OK;
 }
 
 // ------------------------------------------------------- residual add + RMSNorm
 // For output row r, source row s = rows ? rows[r] : r:
 //   v    = resid[s, :] + (delta ? delta[s, :] : 0)          (float32)
+//          where delta is a [n, H] array of T, or (splits > 0) `splits` float32 slices
+//          [splits][n_src][H], `split_stride` floats apart, added in slice order: the partial sums
+//          of a matrix product cut along K
 //   resid[s, :] = v                    if write_resid
 //   out[r, :]   = v * (1 / sqrt(mean(v^2) + eps)) * (w + w_offset)      rounded once to T
 // The row is kept in shared memory between the two passes.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __restrict__ delta,
                                    const float* __restrict__ w, T* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps, float w_offset,
-                                   int write_resid) {
+                                   int write_resid, int splits, long long split_stride) {
     extern __shared__ float srow[];  // H floats + 33 scratch
     float* scratch = srow + H;
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int s = rows ? rows[r] : r;
     float* x = resid + (size_t)s * H;
-    const T* d = delta ? delta + (size_t)s * H : nullptr;
+    const T* d = (delta && splits == 0) ? static_cast<const T*>(delta) + (size_t)s * H : nullptr;
+    const float* dp = (delta && splits > 0) ? static_cast<const float*>(delta) + (size_t)s * H : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = x[i];
-        if (d) v += to_float(d[i]);
-        srow[i] = v;
-        ss += v * v;
-        if (write_resid) x[i] = v;
+    if (dp && (H & 3) == 0 && (split_stride & 3) == 0 && aligned16(dp) && aligned16(x)) {
+        // Partial sums: 16-byte loads, eight slices in flight at a time, added in slice order.
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(x + i);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp0 = 0; sp0 < splits; sp0 += 8) {
+                float4 t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    t[u] = sp0 + u < splits ? __ldcg(reinterpret_cast<const float4*>(dp + (size_t)(sp0 + u) * split_stride + i))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w;
+                }
+            }
+            v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+            *reinterpret_cast<float4*>(srow + i) = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            if (write_resid) *reinterpret_cast<float4*>(x + i) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = x[i];
+            if (d) v += to_float(d[i]);
+            if (dp) {
+                float acc = dp[i];
+                for (int sp = 1; sp < splits; ++sp) acc += dp[(size_t)sp * split_stride + i];
+                v += acc;
+            }
+            srow[i] = v;
+            ss += v * v;
+            if (write_resid) x[i] = v;
+        }
     }
     ss = block_sum(ss, scratch);
     const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
@@ -75,13 +112,14 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
 }
 
 LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, const int* rows,
-                                 int n_rows, int H, float eps, float w_offset, int write_resid, int dtype,
-                                 void* stream) {
+                                 int n_rows, int H, float eps, float w_offset, int write_resid, int splits,
+                                 long long split_stride, int dtype, void* stream) {
     if (n_rows <= 0) return LLMK_OK;
     if (H <= 0) LLMK_FAIL("add_rmsnorm: bad width H=%d", H);
     const size_t smem = (size_t)(H + 33) * sizeof(float);
     if (smem > 200 * 1024) LLMK_FAIL("add_rmsnorm: width %d needs %zu bytes of shared memory (limit 204800)", H, smem);
     if (rows && write_resid) LLMK_FAIL("add_rmsnorm: gathered rows cannot be written back");
+    if (splits < 0 || (splits > 0 && split_stride < H)) LLMK_FAIL("add_rmsnorm: bad partial sums (%d slices, stride %lld)", splits, split_stride);
     cudaStream_t s = (cudaStream_t)stream;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
 #define LAUNCH(T)                                                                                            \
@@ -91,9 +129,10 @@ LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
             if (e != cudaSuccess) LLMK_FAIL("add_rmsnorm: cannot raise shared memory: %s", cudaGetErrorString(e)); \
         }                                                                                                    \
-        add_rmsnorm_kernel<T><<<n_rows, threads, smem, s>>>(resid, (const T*)delta, w, (T*)out, rows, H, eps, \
-                                                            w_offset, write_resid);                          \
+        launch_rc = llmk_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, true, resid, delta, w, \
+                                (T*)out, rows, H, eps, w_offset, write_resid, splits, split_stride);         \
     } while (0)
+    cudaError_t launch_rc = cudaSuccess;
     if (dtype == LLMK_F32)
         LAUNCH(float);
     else if (dtype == LLMK_BF16)
@@ -101,7 +140,7 @@ LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w
     else
         LLMK_FAIL("add_rmsnorm: unknown dtype %d", dtype);
 #undef LAUNCH
-    LLMK_CHECK_LAUNCH("add_rmsnorm");
+    LLMK_CHECK_LAUNCH_RC("add_rmsnorm", launch_rc);
     return LLMK_OK;
 }
 
@@ -146,6 +185,28 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ i
     }
 }
 
+// The same from the float32 partial sums of a product cut along K: in is [splits][n][ld_in] with
+// slices `split_stride` floats apart, added in slice order before the activation.
+template <typename T>
+__global__ void silu_mul_partials_kernel(T* __restrict__ out, const float* __restrict__ in, int n, int F, int ld_in,
+                                         int group, int splits, long long split_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = (size_t)n * F;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(idx / F), col = (int)(idx % F);
+        const int gcol = 2 * group * (col / group) + col % group;
+        const float* base = in + (size_t)row * ld_in + gcol;
+        float g = base[0], u = base[group];
+        for (int sp = 1; sp < splits; ++sp) {
+            g += base[(size_t)sp * split_stride];
+            u += base[(size_t)sp * split_stride + group];
+        }
+        out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
 template <typename T>
 static int launch_silu_mul(void* out, const void* in, int n, int F, int ld_in, int group, cudaStream_t s) {
     constexpr int N = Vec16<T>::N;
@@ -162,12 +223,28 @@ static int launch_silu_mul(void* out, const void* in, int n, int F, int ld_in, i
     return LLMK_OK;
 }
 
-LLMK_EXPORT int llmk_silu_mul(void* out, const void* in, int n_rows, int F, int ld_in, int group, int dtype,
-                              void* stream) {
+LLMK_EXPORT int llmk_silu_mul(void* out, const void* in, int n_rows, int F, int ld_in, int group, int splits,
+                              long long split_stride, int dtype, void* stream) {
     if (n_rows <= 0) return LLMK_OK;
     if (F <= 0 || ld_in < 2 * F) LLMK_FAIL("silu_mul: bad sizes F=%d ld_in=%d", F, ld_in);
     if (group <= 0 || F % group != 0) LLMK_FAIL("silu_mul: group %d must divide F=%d", group, F);
     cudaStream_t s = (cudaStream_t)stream;
+    if (splits > 0) {
+        const size_t work = (size_t)n_rows * F;
+        size_t blocks = (work + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        cudaError_t e;
+        if (dtype == LLMK_F32)
+            e = llmk_launch(silu_mul_partials_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out,
+                            (const float*)in, n_rows, F, ld_in, group, splits, split_stride);
+        else if (dtype == LLMK_BF16)
+            e = llmk_launch(silu_mul_partials_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)out,
+                            (const float*)in, n_rows, F, ld_in, group, splits, split_stride);
+        else
+            LLMK_FAIL("silu_mul: unknown dtype %d", dtype);
+        LLMK_CHECK_LAUNCH_RC("silu_mul", e);
+        return LLMK_OK;
+    }
     if (dtype == LLMK_F32)
         launch_silu_mul<float>(out, in, n_rows, F, ld_in, group, s);
     else if (dtype == LLMK_BF16)

@@ -88,7 +88,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            tc::pdl_wait();   // A was written by the kernel before this one
+            pdl_wait();   // A was written by the kernel before this one
             int issued = 0;
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
@@ -101,7 +101,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc::tma_load_2d(a_dst + L::A_BYTES, &map_w, bar, kb * BK, n0);
                 issued = kb + 1;
             }
-            tc::pdl_launch_dependents();
+            pdl_launch_dependents();
             if (*abort_flag) {
                 // Let the copies that are in flight land before the block's memory is given up.
                 for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {

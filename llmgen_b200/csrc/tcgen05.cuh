@@ -14,6 +14,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <unordered_map>
+
 namespace tc {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
@@ -124,13 +127,6 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
     return p;
 }
 
-// ------------------------------------------------------------- programmatic dependent launch
-// `pdl_wait` blocks until the kernels this one depends on have completed and their writes are
-// visible; everything before it may overlap their tail.  `pdl_launch_dependents` lets the next
-// kernel of the stream start its own prologue.  Both are no-ops for a plain launch.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // --------------------------------------------------------------------------- tensor memory
 // Allocate `cols` columns (a power of two >= 32) of the SM's tensor memory; the base address is
 // written to shared memory at `slot`.  One whole warp executes this.
@@ -211,6 +207,21 @@ __host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N) {
            | ((uint32_t)(N >> 3) << 17)  // N / 8
            | ((uint32_t)(M >> 4) << 24); // M / 16
 }
+// The same with B read MN-major: B's rows (the N of the product) are contiguous in shared memory
+// and its K steps from row to row, as a [K, N] tile loaded row by row.
+__host__ __device__ constexpr uint32_t idesc_bf16_f32_b_mn(int M, int N) { return idesc_bf16_f32(M, N) | (1u << 16); }
+// Shared-memory matrix descriptor of an MN-major operand in the 128-byte swizzle: every K index owns
+// one 128-byte row of 64 contiguous MN elements; 8 such rows form a 1024-byte group; `sbo_bytes`
+// separates groups of 8 K indices, `lbo_bytes` separates blocks of 64 MN elements.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes (64 bfloat16)
 // in the 128-byte swizzle that a TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes: 8-row groups are
 // 1024 bytes apart.  The tile must start on a 1024-byte boundary; advancing along K inside the
@@ -261,6 +272,60 @@ inline bool make_map_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, 
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A bfloat16 array addressed as [d2][d1][d0] (d0 contiguous) with element strides s1, s2 between
+// steps of d1 and d2, loaded in boxes of [b2, b1, 64] elements with the 128-byte swizzle.
+inline bool make_map_bf16_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
+                             uint64_t s2, uint32_t b1, uint32_t b2) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {s1 * 2, s2 * 2};
+    cuuint32_t box[3] = {64, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor maps are encoded once per (base, shape, stride, box) and kept: weights and the engine's
+// workspaces do not move, so a step encodes nothing.
+struct MapKey {
+    const void* base;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows, box_cols;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+               box_cols == o.box_cols;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.base);
+        h = h * 1000003u ^ k.rows;
+        h = h * 1000003u ^ k.cols;
+        h = h * 1000003u ^ k.ld;
+        h = h * 1000003u ^ k.box_rows;
+        return h * 1000003u ^ k.box_cols;
+    }
+};
+
+inline bool cached_map_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                               uint32_t box_rows, uint32_t box_cols = 64) {
+    static std::mutex lock;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+    MapKey key{base, rows, cols, ld, box_rows, box_cols};
+    std::lock_guard<std::mutex> guard(lock);
+    auto it = maps.find(key);
+    if (it != maps.end()) {
+        *out = it->second;
+        return true;
+    }
+    if (!make_map_bf16_2d(out, base, rows, cols, ld, box_rows, box_cols)) return false;
+    if (maps.size() > 4096) maps.clear();
+    maps.emplace(key, *out);
+    return true;
 }
 
 }  // namespace tc_host

@@ -33,6 +33,7 @@ class Workspace:
         self.device = device
         self.default_rows = default_rows
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._retired: List[torch.Tensor] = []   # replaced buffers stay alive: captured graphs still use them
         self.frozen = False   # set while a graph is being captured: no new allocations
 
     def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, capacity_rows: Optional[int] = None) -> torch.Tensor:
@@ -43,17 +44,22 @@ class Workspace:
             if self.frozen:
                 raise RuntimeError(f"workspace {key!r} must exist before graph capture")
             cap = max(cap, rows)
+            if buf is not None:
+                self._retired.append(buf)
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:rows]
 
-    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    def flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A 1-D buffer; with `zero` it is cleared when created (not on later calls)."""
         key = f"{name}:flat:{dtype}"
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < numel:
             if self.frozen:
                 raise RuntimeError(f"workspace {key!r} must exist (and be large enough) before graph capture")
-            buf = torch.empty((max(numel, 1),), dtype=dtype, device=self.device)
+            if buf is not None:
+                self._retired.append(buf)
+            buf = (torch.zeros if zero else torch.empty)((max(numel, 1),), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:numel]
 
@@ -66,7 +72,8 @@ class StepMetaBuilder:
 
     ALIGN = 4  # words: every array starts on a 16-byte boundary
 
-    def __init__(self, q_lens: Sequence[int] = (), starts: Sequence[int] = (), pure_decode: bool = False):
+    def __init__(self, q_lens: Sequence[int] = (), starts: Sequence[int] = (), pure_decode: bool = False,
+                 page_size: int = 0):
         self.names: List[str] = []
         self.arrays: Dict[str, np.ndarray] = {}
         # the batch, for parts that derive arrays of their own from it
@@ -75,6 +82,7 @@ class StepMetaBuilder:
         self.n_seqs = len(self.q_lens)
         self.n_tokens = sum(self.q_lens)
         self.pure_decode = pure_decode
+        self.page_size = page_size
 
     def add(self, name: str, values, dtype=np.int32) -> None:
         if name in self.arrays:
@@ -141,6 +149,10 @@ class StepContext:
     groups: List[GroupView] = field(default_factory=list)
     extra: Dict[str, torch.Tensor] = field(default_factory=dict)
     fixed_shapes: bool = False   # True inside graph capture/replay: choose launch shapes from bounds
+    max_seqs_bound: int = 0      # most sequences any step of this engine has
 
     def array(self, name: str) -> torch.Tensor:
         return self.extra[name]
+
+    def has_array(self, name: str) -> bool:
+        return name in self.extra

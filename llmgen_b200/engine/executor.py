@@ -283,7 +283,7 @@ class Executor:
         starts = [e.start for e in entries] + [0] * (S - S_real)
         T = sum(q_lens)
         pure_decode = all(n == 1 for n in q_lens)
-        b = StepMetaBuilder(q_lens, starts, pure_decode)
+        b = StepMetaBuilder(q_lens, starts, pure_decode, lim.page_size)
         self.step_seed = (self.step_seed + SEED_STRIDE) & MASK64
         b.add("seed", np.array([self.step_seed], dtype=np.uint64).view(np.int32))
         ids = np.zeros(T, dtype=np.int32)
@@ -355,6 +355,7 @@ class Executor:
             n_tokens=T, n_seqs=S, dtype=self.dtype, device=self.device, workspace=self.workspace,
             requests=[e.req for e in entries], starts=starts, q_lens=q_lens, pure_decode=pure_decode,
             max_ctx=int(ctx_len.max()) if S else 0, max_ctx_bound=lim.max_model_len,
+            max_seqs_bound=lim.max_num_seqs,
             ids=view("ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_len=view("ctx_len"),
             state_slots=view("state_slots"), seq_of_token=view("seq_of_token"),
             groups=[GroupView(view(f"slots_{gi}"), view(f"block_tables_{gi}"), self.max_blocks)

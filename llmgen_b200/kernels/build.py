@@ -43,7 +43,10 @@ MODULES: Dict[str, List[str]] = {
     "gemm_simt": [],
     "gemv": [],
     "gemm_tc": [],
+    "gemm_skinny": [],
     "attention": [],
+    "attention_decode": [],
+    "attention_tc": [],
     "sampling": [],
 }
 

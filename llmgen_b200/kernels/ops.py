@@ -65,6 +65,26 @@ def _row_stride(t: torch.Tensor) -> int:
     return t.stride(-2)
 
 
+class Partials:
+    """The result of a matrix product cut along K: float32 slices [splits, rows, cols] whose sum, in
+    slice order, is the product.  The kernels that consume a product (`add_rmsnorm`, `attn_prep`,
+    `silu_mul`) take a `Partials` in place of the finished array and do the sum themselves."""
+
+    def __init__(self, tensor: torch.Tensor):
+        if tensor.dim() != 3 or tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError("partial sums are a contiguous float32 [splits, rows, cols] array")
+        self.tensor = tensor
+        self.splits, self.rows, self.cols = tensor.shape
+
+    @property
+    def split_stride(self) -> int:
+        return self.rows * self.cols
+
+    def sum(self) -> torch.Tensor:
+        """The finished product (float32), for callers that have no kernel taking slices."""
+        return self.tensor.sum(dim=0)
+
+
 # ---------------------------------------------------------------------------- elementwise
 def embed_rows(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tensor] = None) -> None:
     """out[t] (float32 [n, H]) = table[ids[t]]; ids int32 on the device."""
@@ -74,10 +94,11 @@ def embed_rows(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, bad_fl
                                     _ptr(bad_flag), c_int(dtype_code(table.dtype)), _stream()))
 
 
-def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Tensor,
                 eps: float, weight_offset: float = 0.0, rows: Optional[torch.Tensor] = None,
                 write_resid: bool = True) -> None:
-    """resid (float32 [n, H]) += delta; out = rmsnorm(resid) * (weight + offset).
+    """resid (float32 [n, H]) += delta; out = rmsnorm(resid) * (weight + offset).  `delta` is an
+    array of the output's dtype, a `Partials`, or None.
 
     With `rows` (int32 [m]) output row r is computed from source row rows[r] and the
     residual is left untouched."""
@@ -86,22 +107,34 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     n_rows = out.shape[0]
     if resid.dtype != torch.float32 or weight.dtype != torch.float32:
         raise KernelError("add_rmsnorm: residual and gain must be float32")
-    if delta is not None and (delta.dtype != out.dtype or not delta.is_contiguous()):
+    splits, split_stride = 0, 0
+    if isinstance(delta, Partials):
+        if delta.cols != H or delta.rows != resid.shape[0]:
+            raise KernelError("add_rmsnorm: partial sums do not have the residual's shape")
+        splits, split_stride, delta = delta.splits, delta.split_stride, delta.tensor
+    elif delta is not None and (delta.dtype != out.dtype or not delta.is_contiguous()):
         raise KernelError("add_rmsnorm: delta must be contiguous and of the output's dtype")
     if rows is not None:
         write_resid = False
     _check(lib, lib.llmk_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), c_int(n_rows),
                                      c_int(H), c_float(eps), c_float(weight_offset), c_int(1 if write_resid else 0),
-                                     c_int(dtype_code(out.dtype)), _stream()))
+                                     c_int(splits), c_longlong(split_stride), c_int(dtype_code(out.dtype)), _stream()))
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, group: int = 0) -> None:
-    """out[n, F] = silu(gate) * up, where gate_up[n, 2F] alternates `group` gate columns and `group`
-    up columns (group 0 or F: gate in columns [0, F), up in [F, 2F))."""
+def silu_mul(out: torch.Tensor, gate_up, group: int = 0) -> None:
+    """out[n, F] = silu(gate) * up, where gate_up[n, 2F] (an array or a `Partials`) alternates `group`
+    gate columns and `group` up columns (group 0 or F: gate in columns [0, F), up in [F, 2F))."""
     lib = build.load("elementwise")
     n, F = out.shape
-    _check(lib, lib.llmk_silu_mul(_ptr(out), _ptr(gate_up), c_int(n), c_int(F), c_int(_row_stride(gate_up)),
-                                  c_int(group if group else F), c_int(dtype_code(out.dtype)), _stream()))
+    splits, split_stride = 0, 0
+    if isinstance(gate_up, Partials):
+        splits, split_stride, ld = gate_up.splits, gate_up.split_stride, gate_up.cols
+        gate_up = gate_up.tensor
+    else:
+        ld = _row_stride(gate_up)
+    _check(lib, lib.llmk_silu_mul(_ptr(out), _ptr(gate_up), c_int(n), c_int(F), c_int(ld),
+                                  c_int(group if group else F), c_int(splits), c_longlong(split_stride),
+                                  c_int(dtype_code(out.dtype)), _stream()))
 
 
 def widen(out: torch.Tensor, src: torch.Tensor) -> None:
@@ -111,20 +144,36 @@ def widen(out: torch.Tensor, src: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------ attn_prep
-def attn_prep(qkv: torch.Tensor, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+def attn_prep(qkv, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
               positions: Optional[torch.Tensor], slots: Optional[torch.Tensor], cos: Optional[torch.Tensor],
               sin: Optional[torch.Tensor], q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
               nq: int, nk: int, hd: int, rot: int, page_size: int, eps: float,
-              q_offset: float = 0.0, k_offset: float = 0.0) -> None:
-    """Per-head norm and rotary encoding of q (in place) and k, and the cache write of k, v."""
+              q_offset: float = 0.0, k_offset: float = 0.0, q_out: Optional[torch.Tensor] = None) -> None:
+    """Per-head norm and rotary encoding of q and k, and the cache write of k, v.  `qkv` holds the
+    packed rows [n, (nq + 2 nk) hd] as an array (q is then rewritten in place unless `q_out` is
+    given) or as a `Partials` (q goes to `q_out`, which gives the storage dtype)."""
     lib = build.load("attn_prep")
-    n = qkv.shape[0]
     nkv_cache = kcache.shape[1] if kcache is not None else 0
-    _check(lib, lib.llmk_attn_prep(_ptr(qkv), c_longlong(_row_stride(qkv)), _ptr(kcache), _ptr(vcache),
+    splits, split_stride = 0, 0
+    if isinstance(qkv, Partials):
+        if q_out is None:
+            raise KernelError("attn_prep: partial sums need a place for q")
+        n, stride, src = qkv.rows, qkv.cols, qkv.tensor
+        splits, split_stride = qkv.splits, qkv.split_stride
+        dtype = q_out.dtype
+    else:
+        n, stride, src = qkv.shape[0], _row_stride(qkv), qkv
+        dtype = qkv.dtype
+        if q_out is None:
+            q_out = qkv
+    if q_out.dtype != dtype:
+        raise KernelError("attn_prep: q_out must have the storage dtype")
+    _check(lib, lib.llmk_attn_prep(_ptr(src), c_longlong(stride), c_int(splits), c_longlong(split_stride),
+                                   _ptr(q_out), c_longlong(_row_stride(q_out)), _ptr(kcache), _ptr(vcache),
                                    _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(q_gain), _ptr(k_gain),
                                    c_int(n), c_int(nq), c_int(nk), c_int(nkv_cache), c_int(hd), c_int(rot),
                                    c_int(page_size), c_float(eps), c_float(q_offset), c_float(k_offset),
-                                   c_int(dtype_code(qkv.dtype)), _stream()))
+                                   c_int(dtype_code(dtype)), _stream()))
 
 
 # ------------------------------------------------------------------------- matrix products
@@ -211,6 +260,49 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
                                  c_int(1 if pdl else 0), _stream()))
 
 
+SKINNY_MAX_ROWS = 256
+SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED = 0, 1, 2
+_skinny_plans = {}
+
+
+def gemm_skinny_splits(M: int, N: int, K: int) -> int:
+    """Into how many slices of K the few-rows product cuts [M, K] x [N, K]^T (1: no cut)."""
+    key = (M, N, K)
+    v = _skinny_plans.get(key)
+    if v is None:
+        v = int(build.load("gemm_skinny").llmk_gemm_skinny_splits(c_int(M), c_int(N), c_int(K)))
+        _skinny_plans[key] = v
+    return v
+
+
+def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int = SKINNY_DIRECT) -> None:
+    """The weight-streaming tensor-core product for M <= 256 rows (csrc/gemm_skinny.cu).
+    SKINNY_DIRECT: out[M, N]; SKINNY_GATED: out[M, N/2] = silu(gate) * up; SKINNY_PARTIAL: out is
+    float32 [splits, M, N] and receives the partial sums of `splits` slices of K."""
+    lib = build.load("gemm_skinny")
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError(f"gemm_skinny: operands a{list(a.shape)} {a.dtype} w{list(w.shape)} {w.dtype} do not fit")
+    if mode == SKINNY_PARTIAL:
+        if out.dim() != 3 or out.shape[1] != M or out.shape[2] != N or out.dtype != torch.float32 or not out.is_contiguous():
+            raise KernelError("gemm_skinny: partial sums go to a contiguous float32 [splits, M, N] array")
+        splits, ldc = out.shape[0], N
+    else:
+        n_out = N // 2 if mode == SKINNY_GATED else N
+        if out.shape[0] != M or out.shape[1] != n_out:
+            raise KernelError(f"gemm_skinny: out{list(out.shape)} does not fit [{M}, {n_out}]")
+        splits, ldc = 1, _row_stride(out)
+    _check(lib, lib.llmk_gemm_skinny(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
+                                     c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(ldc),
+                                     c_int(splits), c_int(mode), c_int(dtype_code(out.dtype)),
+                                     _ptr(tc_error_flag(a.device)), _stream()))
+
+
+def gemm_skinny_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return a.shape[0] <= SKINNY_MAX_ROWS and gemm_tc_usable(a, w)
+
+
 # ------------------------------------------------------------------------------ attention
 def attention_tile_queries(nq: int, nkv: int) -> int:
     """Queries per tile of `paged_attention` for this group size."""
@@ -240,6 +332,63 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                                          c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
                                          _ptr(scratch), c_int(dtype_code(q.dtype)), _stream()),
            2 if num_parts > 1 else 1)
+
+
+def attention_decode_usable(nq: int, nkv: int, hd: int, page_size: int) -> bool:
+    return bool(build.load("attention_decode").llmk_attention_decode_usable(c_int(nq), c_int(nkv), c_int(hd), c_int(page_size)))
+
+
+def attention_decode_scratch_floats(n_seqs: int, nq: int, hd: int, parts: int) -> int:
+    return 0 if parts <= 1 else n_seqs * nq * parts * (hd + 2)
+
+
+def attention_decode_counters(n_seqs: int, nq: int, nkv: int) -> int:
+    lib = build.load("attention_decode")
+    lib.llmk_attention_decode_counters.restype = c_longlong
+    return int(lib.llmk_attention_decode_counters(c_int(n_seqs), c_int(nq), c_int(nkv)))
+
+
+def attention_decode(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                     block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
+                     n_seqs: int, nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
+                     parts: int, max_ctx: int, scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor]) -> None:
+    """out[t] = attention of the single token of each sequence over the paged cache, bfloat16
+    (csrc/attention_decode.cu).  `counters` (int32) must be zero before the first call."""
+    lib = build.load("attention_decode")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: bfloat16 only")
+    if parts > 1:
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < attention_decode_scratch_floats(n_seqs, nq, hd, parts):
+            raise KernelError("attention_decode: scratch too small")
+        if counters is None or counters.dtype != torch.int32 or counters.numel() < attention_decode_counters(n_seqs, nq, nkv):
+            raise KernelError("attention_decode: counters too small")
+    _check(lib, lib.llmk_attention_decode(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(q_stride),
+                                          _ptr(kcache), _ptr(vcache), _ptr(block_tables), c_int(max_blocks),
+                                          _ptr(ctx_len), _ptr(cu_q), c_int(n_seqs), c_int(nq), c_int(nkv), c_int(hd),
+                                          c_int(page_size), c_int(window), c_float(scale), c_int(parts), c_int(max_ctx),
+                                          _ptr(scratch), _ptr(counters), _stream()))
+
+
+def attention_tc_tile_queries(nq: int, nkv: int, hd: int, page_size: int) -> int:
+    """Queries per tile of the tensor-core attention; 0 when it does not take these sizes."""
+    return int(build.load("attention_tc").llmk_attention_tc_tile_queries(c_int(nq), c_int(nkv), c_int(hd), c_int(page_size)))
+
+
+def attention_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                 block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
+                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, n_tokens: int, nq: int, nkv: int,
+                 hd: int, page_size: int, window: int, scale: float, v_lbo: int = 0, v_sbo: int = 0) -> None:
+    """out[t, nq*hd] = causal GQA of q[t] over the paged cache on the tensor cores, bfloat16
+    (csrc/attention_tc.cu).  q is [n_tokens, >= nq*hd] with row stride q_stride."""
+    lib = build.load("attention_tc")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_tc: bfloat16 only")
+    _check(lib, lib.llmk_attention_tc(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(q_stride),
+                                      c_int(n_tokens), _ptr(kcache), _ptr(vcache), c_longlong(kcache.shape[0]),
+                                      _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len), _ptr(cu_q),
+                                      _ptr(tile_seq), _ptr(tile_q0), c_int(n_tiles), c_int(nq), c_int(nkv), c_int(hd),
+                                      c_int(page_size), c_int(window), c_float(scale), _ptr(tc_error_flag(q.device)),
+                                      ctypes.c_uint(v_lbo), ctypes.c_uint(v_sbo), _stream()))
 
 
 # ------------------------------------------------------------------------------- sampling

@@ -1,22 +1,30 @@
 """Causal grouped-query attention over the paged cache, as a mixer."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..cache.manager import FULL, WINDOW
 from ..kernels import ops
 from .base import KVRequest, LayerCache, Mixer
-from .linear import GEMM_MODULES, linear
+from .linear import GEMM_MODULES, linear, linear_sliced
 from .registry import build_position, norm_class, register_mixer
 from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
 
 NUM_SMS = 148
+_FORCE_ATTN = os.environ.get("LLMGEN_ATTN", "")      # "simt": the CUDA-core kernel everywhere
 
 
 class GQAAttention(Mixer):
     """q, k, v projections (packed into one [(nq + 2 nkv) hd, H] matrix at load) -> per-head
     RMSNorm of q and k, rotary encoding, cache write (one kernel) -> attention over the block
     table -> output projection.
+
+    Attention kernels: in bfloat16 a step of single decoded tokens runs the bandwidth-shaped
+    flash-decoding kernel (csrc/attention_decode.cu), any other step the tensor-core kernel
+    (csrc/attention_tc.cu); float32, and sizes those two refuse, run the general CUDA-core kernel
+    (csrc/attention.cu).
 
     Order and formulas: src/models/qwen3.zig:192-207 (q/k norm before RoPE, norm weights
     shared by all heads), src/module/attention.zig:85-92, src/backend/cpu/attention.zig:64-118.
@@ -34,7 +42,7 @@ class GQAAttention(Mixer):
 
     @staticmethod
     def kernel_modules(spec):
-        return ("attn_prep", "attention") + GEMM_MODULES
+        return ("attn_prep", "attention", "attention_decode", "attention_tc") + GEMM_MODULES
 
     def __init__(self, spec: AttentionSpec, weights, dtype, device):
         if spec.num_heads % spec.num_kv_heads != 0:
@@ -62,6 +70,7 @@ class GQAAttention(Mixer):
         self.window = int(spec.window or 0)
         self.bq = ops.attention_tile_queries(self.nq, self.nkv)
         self.tiles_name = f"attention_tiles_bq{self.bq}"
+        self._tc_bq = {}       # page size -> queries per tile of the tensor-core kernel (0: not taken)
 
     # -- what the engine asks
     def cache_request(self) -> KVRequest:
@@ -70,17 +79,32 @@ class GQAAttention(Mixer):
     def max_positions(self):
         return self.position.max_positions if self.position is not None else None
 
-    def prepare_step(self, builder) -> None:
-        """Tiles of `bq` queries: (sequence, first query of the tile) pairs."""
-        if builder.has(self.tiles_name + "_seq"):
+    def _tiles(self, builder, bq: int) -> None:
+        name = f"attention_tiles_bq{bq}"
+        if builder.has(name + "_seq"):
             return
         seq, q0 = [], []
         for s, n in enumerate(builder.q_lens):
-            for start in range(0, max(n, 1), self.bq):
+            for start in range(0, max(n, 1), bq):
                 seq.append(s)
                 q0.append(start)
-        builder.add(self.tiles_name + "_seq", seq)
-        builder.add(self.tiles_name + "_q0", q0)
+        builder.add(name + "_seq", seq)
+        builder.add(name + "_q0", q0)
+
+    def tc_tile_queries(self, page_size: int) -> int:
+        if self.dtype != torch.bfloat16 or _FORCE_ATTN == "simt":
+            return 0
+        if page_size not in self._tc_bq:
+            self._tc_bq[page_size] = ops.attention_tc_tile_queries(self.nq, self.nkv, self.hd, page_size)
+        return self._tc_bq[page_size]
+
+    def prepare_step(self, builder) -> None:
+        """Tiles of queries, (sequence, first query of the tile) pairs, for the kernel this step
+        will run: none for a step of single decoded tokens in bfloat16."""
+        self._tiles(builder, self.bq)
+        page_size = getattr(builder, "page_size", 0)
+        if not builder.pure_decode and page_size and self.tc_tile_queries(page_size):
+            self._tiles(builder, self.tc_tile_queries(page_size))
 
     def _split(self, ctx):
         """(num_parts, part_size) for flash-decoding; only pure-decode steps are split."""
@@ -106,19 +130,28 @@ class GQAAttention(Mixer):
         ws = ctx.workspace
         group = ctx.groups[cache.group]
         nk = self.nkv if cache.writes else 0
-        width = (self.nq + 2 * nk) * self.hd
-        qkv = ws.buffer("attn_qkv", T, (self.nq + 2 * self.nkv) * self.hd, self.dtype)
-        if cache.writes:
-            linear(x, self.w_qkv, qkv)
-            packed = qkv
-        else:
-            packed = qkv[:, :width]
-            linear(x, self.w_q, packed)
+        packed = linear_sliced(ws, "attn_qkv" if cache.writes else "attn_q_only", x,
+                               self.w_qkv if cache.writes else self.w_q, self.dtype)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rot = self.position.rotary_dim if self.position is not None else 0
+        q = ws.buffer("attn_q", T, self.nq * self.hd, self.dtype) if isinstance(packed, ops.Partials) else packed
         ops.attn_prep(packed, cache.k, cache.v, ctx.positions, group.slots, cos, sin, self.q_gain, self.k_gain,
-                      self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off)
+                      self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q)
+        packed = q
         o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
+        scale = float(self.spec.scale)
+        if (self.dtype == torch.bfloat16 and ctx.pure_decode and _FORCE_ATTN != "simt"
+                and ops.attention_decode_usable(self.nq, self.nkv, self.hd, cache.page_size)):
+            self._decode(ctx, o, packed, cache, group, scale)
+            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+        tc_bq = 0 if ctx.pure_decode else self.tc_tile_queries(cache.page_size)
+        if tc_bq and ctx.has_array(f"attention_tiles_bq{tc_bq}_seq"):
+            tile_seq = ctx.array(f"attention_tiles_bq{tc_bq}_seq")
+            tile_q0 = ctx.array(f"attention_tiles_bq{tc_bq}_q0")
+            ops.attention_tc(o, packed, packed.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks,
+                             ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
+                             self.hd, cache.page_size, self.window, scale)
+            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         tile_seq = ctx.array(self.tiles_name + "_seq")
         tile_q0 = ctx.array(self.tiles_name + "_q0")
         parts, part_size = self._split(ctx)
@@ -128,7 +161,30 @@ class GQAAttention(Mixer):
         ops.paged_attention(o, packed, packed.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks,
                             ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
                             self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch)
-        return linear(o, self.w_o, ws.buffer("mixer_out", T, self.spec.hidden_size, self.dtype))
+        return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+
+
+    def _decode(self, ctx, o, q, cache, group, scale) -> None:
+        """Single decoded tokens: as many key parts as fill the SMs about twice, at least 64 keys
+        a part; under graph capture the bound on the context length decides, not the lengths."""
+        ws = ctx.workspace
+        S = ctx.n_seqs
+        G = self.nq // self.nkv
+        chunks = (G + 7) // 8
+        bound = ctx.max_ctx_bound if ctx.fixed_shapes else max(ctx.max_ctx, 1)
+        visible = min(bound, self.window) if self.window else bound
+        blocks = max(1, S * self.nkv * chunks)
+        parts = max(1, min((2 * NUM_SMS + blocks - 1) // blocks, visible // 64, 64))
+        parts = max(parts, (visible + 4095) // 4096)          # shared memory holds a part's scores
+        scratch = counters = None
+        if parts > 1:
+            scratch = ws.flat("attn_decode_split", ops.attention_decode_scratch_floats(S, self.nq, self.hd, parts),
+                              torch.float32)
+            counters = ws.flat("attn_decode_counters", ops.attention_decode_counters(max(ctx.max_seqs_bound, S), self.nq, self.nkv),
+                               torch.int32, zero=True)
+        ops.attention_decode(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len,
+                             ctx.cu_q, S, self.nq, self.nkv, self.hd, cache.page_size, self.window, scale, parts,
+                             bound, scratch, counters)
 
 
 register_mixer("attention", GQAAttention)

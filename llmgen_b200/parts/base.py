@@ -9,17 +9,21 @@ All parts:
 Norm:
     add_norm(resid, delta, out, rows=None)    resid(float32) += delta; out = norm(resid);
                                               with `rows`: output row r from source row rows[r],
-                                              resid untouched
+                                              resid untouched.  `delta` is None, an array [T, H]
+                                              of the compute dtype, or a `kernels.ops.Partials`
+                                              (float32 slices to be added up), whichever the
+                                              part before it returned
 Position encoding:
     tables()                                  whatever its mixer's kernel needs (cos, sin)
 Mixer:
     cache_request() -> KVRequest | None       pages it needs (group kind, kv heads, head width)
     state_request() -> StateRequest | None    fixed-size per-request state (shape, dtype)
     prepare_step(builder)                     optional: add int32 arrays to the step's metadata
-    forward(ctx, x, cache) -> tensor [T, H]   x is the normed input; `cache` is this run
-                                              item's `LayerCache`
+    forward(ctx, x, cache) -> [T, H]          x is the normed input; `cache` is this run
+                                              item's `LayerCache`; returns an array or a
+                                              `Partials` (see `parts.linear.linear_sliced`)
 Feed-forward:
-    forward(ctx, x) -> tensor [T, H]
+    forward(ctx, x) -> [T, H]                 an array or a `Partials`
 Block:
     mixer                                     the block's mixer (the engine asks it for cache)
     forward(ctx, resid, delta, cache) -> delta_out

@@ -1,10 +1,13 @@
 """y = x W^T: the one place that chooses a matrix-product kernel.
 
     float32 engine   CUDA-core kernel with a fixed summation order (csrc/gemm_simt.cu)
-    bfloat16 engine  up to 4 rows: weight-streaming kernel (csrc/gemv.cu);
-                     otherwise the tensor-core kernel (csrc/gemm_tc.cu: TMA, tcgen05.mma, tensor
-                     memory); operands it refuses (rows not on 16-byte boundaries) go to the
-                     CUDA-core kernel.
+    bfloat16 engine  up to 256 rows: the weight-streaming tensor-core kernel with swapped operands
+                     (csrc/gemm_skinny.cu), cut along K so that every SM streams a share of W; a
+                     cut product comes back as `ops.Partials`, which the consuming kernel adds up;
+                     more rows: the tiled tensor-core kernel (csrc/gemm_tc.cu: TMA, tcgen05.mma,
+                     tensor memory); operands TMA refuses (rows not on 16-byte boundaries): the
+                     CUDA-core weight-streaming kernel for up to 4 rows (csrc/gemv.cu), else the
+                     CUDA-core product.
 
 The reference uses its own GEMV for M <= 2 and `cublasGemmEx` above
 (src/backend/cuda/linear/linear.cu:53-96).  Setting LLMGEN_GEMM=lib swaps the tensor-core kernel
@@ -23,7 +26,7 @@ from ..kernels import ops
 
 _FORCE = os.environ.get("LLMGEN_GEMM", "")
 
-GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc")
+GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -32,6 +35,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return out
     if x.dtype == torch.float32 or _FORCE == "simt":
         ops.gemm_simt(out, x, w)
+    elif _FORCE == "" and ops.gemm_skinny_usable(x, w):
+        ops.gemm_skinny(out, x, w)
     elif ops.gemv_usable(x, w):
         ops.gemv_bf16(out, x, w)
     elif _FORCE == "lib" and out.dtype == x.dtype:
@@ -43,8 +48,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def linear_sliced(ws, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype):
+    """x W^T into the workspace buffer `name`: the finished [M, N] array, or, when the few-rows
+    kernel cuts the product along K, an `ops.Partials` for a consumer that adds the slices."""
+    M, N = x.shape[0], w.shape[0]
+    if M > 0 and x.dtype == torch.bfloat16 and _FORCE == "" and ops.gemm_skinny_usable(x, w):
+        splits = ops.gemm_skinny_splits(M, N, x.shape[1])
+        if splits > 1:
+            part = ws.flat(name + "_slices", splits * M * N, torch.float32).view(splits, M, N)
+            ops.gemm_skinny(part, x, w, ops.SKINNY_PARTIAL)
+            return ops.Partials(part)
+    return linear(x, w, ws.buffer(name, M, N, out_dtype))
+
+
 def gated_product_usable(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """True when the tensor-core product with the gated epilogue runs for these operands (the same
-    choice `linear` makes for a plain product)."""
-    return (x.dtype == torch.bfloat16 and _FORCE == "" and not ops.gemv_usable(x, w)
-            and ops.gemm_tc_usable(x, w) and w.shape[0] % 32 == 0)
+    """True when a tensor-core product with the gated epilogue runs for these operands."""
+    return (x.dtype == torch.bfloat16 and _FORCE == "" and ops.gemm_tc_usable(x, w) and w.shape[0] % 32 == 0)

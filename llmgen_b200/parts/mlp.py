@@ -5,7 +5,7 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward
-from .linear import GEMM_MODULES, gated_product_usable, linear
+from .linear import GEMM_MODULES, gated_product_usable, linear, linear_sliced
 from .registry import register_feed_forward
 from .spec import GatedMLPSpec, WeightDecl
 
@@ -26,8 +26,9 @@ class GatedMLP(FeedForward):
     """down( silu(x Wg^T) * (x Wu^T) ).  Gate and up are packed into one [2F, H] matrix at load
     (values untouched) so that one product yields both.  In bfloat16 the rows alternate in groups
     of 16 and the tensor-core product applies the activation in its epilogue, so the [T, 2F]
-    intermediate is never written; for a handful of rows (weight-streaming product) and in float32
-    the activation is one pass over the packed result.  The reference runs gate, up, silu and mul
+    intermediate is never written; when the few-rows product is cut along K, and in float32, the
+    activation is one pass over the packed result (or its partial sums).  The down projection may
+    come back as partial sums (`ops.Partials`) that the next norm adds up.  The reference runs gate, up, silu and mul
     as four nodes, each rounded to bfloat16 (src/models/qwen3.zig:153-162); here act * up is
     rounded once."""
 
@@ -57,17 +58,20 @@ class GatedMLP(FeedForward):
         self.w_gate_up = packed.to(device=device, dtype=dtype).contiguous()
         self.w_down = weights.device_tensor(spec.down_proj, dtype, device)
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, x: torch.Tensor):
         T = x.shape[0]
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
         act = ws.buffer("ffn_act", T, F, self.dtype)
-        if self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up):
+        gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
+        if gated and T <= ops.SKINNY_MAX_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
+            ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_GATED)
+        elif gated and T > ops.SKINNY_MAX_ROWS:
             ops.gemm_tc(act, x, self.w_gate_up, gated=True)
         else:
-            gate_up = linear(x, self.w_gate_up, ws.buffer("ffn_gate_up", T, 2 * F, self.dtype))
+            gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
             ops.silu_mul(act, gate_up, group=self.group)
-        return linear(act, self.w_down, ws.buffer("ffn_out", T, H, self.dtype))
+        return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

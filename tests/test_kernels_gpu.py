@@ -256,6 +256,123 @@ def test_gemm_tc_gated(ops, M, F, K):
     assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 1024, 2048), (5, 72, 136), (16, 4096, 1024), (17, 200, 1032),
+                                   (64, 1024, 3072), (100, 384, 512), (256, 130, 2048), (8, 151936 // 8, 1024)])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemm_skinny_direct(ops, M, N, K, out_dtype):
+    """The few-rows tcgen05 product written directly: every padded row count, tails in N and K."""
+    torch.manual_seed(150 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+    ops.gemm_skinny(out, dev(a), dev(w))
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    ref = a.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err < (2e-5 if out_dtype == torch.float32 else 6e-3) * scale, (err, scale)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 1024, 2048, 16), (1, 136, 200, 2), (33, 1024, 3072, 12), (8, 4096, 1024, 4),
+                                          (200, 256, 1024, 2), (4, 64, 64, 1)])
+def test_gemm_skinny_partial_sums(ops, M, N, K, splits):
+    """Cut along K: the slices add up to the product, and the plan never leaves a slice empty."""
+    torch.manual_seed(160 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    part = torch.full((splits, M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_skinny(part, dev(a), dev(w), ops.SKINNY_PARTIAL)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(part.device)
+    ref = a.double() @ w.double().t()
+    got = ops.Partials(part).sum().double().cpu()
+    assert float((got - ref).abs().max()) < 2e-5 * float(ref.abs().max())
+    planned = ops.gemm_skinny_splits(M, N, K)
+    kb = (K + 63) // 64
+    per = (kb + planned - 1) // planned
+    assert planned >= 1 and (planned - 1) * per < kb and planned * M * N * 4 <= max(2 * N * K, M * N * 4)
+    with pytest.raises(ops.KernelError, match="empty|slices"):
+        ops.gemm_skinny(torch.empty(kb + 1, M, N, dtype=torch.float32, device="cuda"), dev(a), dev(w), ops.SKINNY_PARTIAL)
+
+
+@pytest.mark.parametrize("M,F,K", [(3, 48, 64), (8, 3072, 1024), (130, 176, 80)])
+def test_gemm_skinny_gated(ops, M, F, K):
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    torch.manual_seed(170)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    wg = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_skinny(out, dev(a), dev(interleave_gate_up(wg, wu)), ops.SKINNY_GATED)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    g = a.double() @ wg.double().t()
+    u = a.double() @ wu.double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do(ops):
+    w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="above 256"):
+        ops.gemm_skinny(torch.empty(257, 64, dtype=torch.bfloat16, device="cuda"),
+                        torch.zeros(257, 64, dtype=torch.bfloat16, device="cuda"), w)
+    big = torch.zeros(4, 80, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="usable"):
+        ops.gemm_skinny(torch.empty(4, 64, dtype=torch.bfloat16, device="cuda"), big[:, 1:65], w)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_consumers_add_up_partial_sums(ops, dtype):
+    """add_rmsnorm, silu_mul and attn_prep given float32 slices equal the same kernels given the sum."""
+    torch.manual_seed(180)
+    n, H, S = 5, 136, 3
+    slices = torch.randn(S, n, H).cuda()
+    total = slices.sum(0)
+    resid = torch.randn(n, H).cuda()
+    w = (1 + 0.1 * torch.randn(H)).cuda()
+    r1, r2 = resid.clone(), resid.clone()
+    o1 = torch.empty(n, H, dtype=dtype, device="cuda")
+    o2 = torch.empty_like(o1)
+    ops.add_rmsnorm(r1, ops.Partials(slices), w, o1, 1e-5)
+    r2 += total
+    ops.add_rmsnorm(r2, None, w, o2, 1e-5)
+    assert torch.allclose(r1, r2, atol=1e-5) and torch.allclose(o1.float(), o2.float(), atol=tol(dtype))
+    rows = torch.tensor([4, 0, 2], dtype=torch.int32, device="cuda")
+    g1 = torch.empty(3, H, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(resid.clone(), ops.Partials(slices), w, g1, 1e-5, rows=rows)
+    assert torch.allclose(g1.float(), o2[rows.long()].float(), atol=tol(dtype))
+    # gated activation, groups of 16
+    F = 48
+    gu = torch.randn(S, n, 2 * F).cuda()
+    a1 = torch.empty(n, F, dtype=dtype, device="cuda")
+    a2 = torch.empty_like(a1)
+    ops.silu_mul(a1, ops.Partials(gu), group=16)
+    ops.silu_mul(a2, gu.sum(0).to(dtype).contiguous(), group=16)
+    assert torch.allclose(a1.float(), a2.float(), atol=tol(dtype, 4))
+    # q/k norm + rotary + cache write
+    nq, nkv, hd, page = 4, 2, 32, 8
+    width = (nq + 2 * nkv) * hd
+    qkv = torch.randn(S, n, width).cuda()
+    whole = qkv.sum(0).to(dtype).contiguous()
+    pos = torch.arange(n, dtype=torch.int32, device="cuda") + 3
+    slots = torch.tensor([9, 2, -1, 17, 4], dtype=torch.int32, device="cuda")
+    cos, sin = plain.rope_tables(64, hd, 10000.0)
+    cos, sin = dev(cos.float()), dev(sin.float())
+    qg, kg = (1 + 0.1 * torch.randn(hd)).cuda(), (1 + 0.1 * torch.randn(hd)).cuda()
+    caches = [[torch.zeros(4, nkv, page, hd, dtype=dtype, device="cuda") for _ in range(2)] for _ in range(2)]
+    q1 = torch.empty(n, nq * hd, dtype=dtype, device="cuda")
+    ops.attn_prep(ops.Partials(qkv), caches[0][0], caches[0][1], pos, slots, cos, sin, qg, kg, nq, nkv, hd, hd, page, 1e-6, q_out=q1)
+    ops.attn_prep(whole, caches[1][0], caches[1][1], pos, slots, cos, sin, qg, kg, nq, nkv, hd, hd, page, 1e-6)
+    assert torch.allclose(q1.float(), whole[:, : nq * hd].float(), atol=tol(dtype, 4))
+    for a, b in zip(caches[0], caches[1]):
+        assert torch.allclose(a.float(), b.float(), atol=tol(dtype, 4))
+
+
+
 @pytest.mark.parametrize("M", [1, 2, 3, 4])
 @pytest.mark.parametrize("out_dtype", DTYPES)
 def test_gemv_bf16(ops, M, out_dtype):
@@ -404,6 +521,129 @@ def test_window_edge(ops, dtype, window, offset):
     q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 14, sharpen=WindowEdge(window, offset))
     got = run_attention(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, window=window)
     assert float((got - ref).abs().max()) < tol(dtype, 3)
+
+
+# ------------------------------------------------- tensor-core attention (prompts, bfloat16)
+def run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, max_blocks, nq, nkv, hd, page, window=0, v_lbo=0, v_sbo=0):
+    T = q.shape[0]
+    bq = ops.attention_tc_tile_queries(nq, nkv, hd, page)
+    assert bq > 0
+    seq, q0 = [], []
+    for s in range(len(ctxs)):
+        n = int(cu[s + 1] - cu[s])
+        for start in range(0, max(n, 1), bq):
+            seq.append(s)
+            q0.append(start)
+    out = torch.full((T, nq * hd), 9.0, dtype=q.dtype, device="cuda")
+    qd = dev(q.view(T, nq * hd))
+    ops.attention_tc(out, qd, nq * hd, dev(kc), dev(vc), dev(bt), max_blocks, dev(ctxs), dev(cu),
+                     dev(torch.tensor(seq, dtype=torch.int32)), dev(torch.tensor(q0, dtype=torch.int32)), len(seq), T,
+                     nq, nkv, hd, page, window, 1.0 / math.sqrt(hd), v_lbo, v_sbo)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    return out.float().cpu().view(T, nq, hd)
+
+
+TC_SHAPES = [(4, 2, 64, 16), (16, 8, 128, 16), (8, 1, 128, 32), (6, 2, 64, 16), (2, 2, 128, 64), (12, 2, 128, 128)]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page", TC_SHAPES)
+def test_attention_tc_mixed_batch(ops, nq, nkv, hd, page):
+    """Whole prompts over several key tiles, prompt tails, single tokens, a padding row, a prompt that
+    ends on a tile's edge; groups of 1, 2, 3, 6 and 8 heads."""
+    dtype = torch.bfloat16
+    seqs = [(70, 30), (41, 1), (0, 1), (256, 256), (1, 1), (150, 100), (700, 390), (129, 129)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 21)
+    got = run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
+    assert float((got - ref).abs().max()) < tol(dtype, 3)
+    assert float(got[31].abs().max()) == 0.0        # the padding row gives zeros
+
+
+@pytest.mark.parametrize("where", [lambda c: 0, lambda c: 15, lambda c: 16, lambda c: 127, lambda c: 128, lambda c: c - 1,
+                                   lambda c: 255, lambda c: 256, lambda c: c // 2])
+def test_attention_tc_far_key(ops, where):
+    nq, nkv, hd, page = 2, 1, 64, 16
+    seqs = [(700, 1), (513, 3), (640, 200)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 23, sharpen=FarKey(where))
+    got = run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
+    assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
+
+
+@pytest.mark.parametrize("window", [1, 7, 16, 40, 100, 200])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_attention_tc_window_edge(ops, window, offset):
+    nq, nkv, hd, page = 6, 2, 64, 16
+    seqs = [(130, 1), (97, 33), (40, 40), (0, 1), (400, 250)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 24, sharpen=WindowEdge(window, offset))
+    got = run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, window=window)
+    assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
+
+
+def test_attention_tc_refuses_what_it_cannot_do(ops):
+    assert ops.attention_tc_tile_queries(4, 2, 48, 16) == 0       # head_dim
+    assert ops.attention_tc_tile_queries(4, 2, 64, 8) == 0        # page size
+    assert ops.attention_tc_tile_queries(4, 3, 64, 16) == 0       # heads
+    z = torch.zeros(1, 96, dtype=torch.bfloat16, device="cuda")
+    zi = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="not taken"):
+        ops.attention_tc(z, z, 96, z.view(1, 1, 2, 48), z.view(1, 1, 2, 48), zi, 1, zi, zi, zi, zi, 1, 1, 2, 1, 48, 2, 0, 1.0)
+
+
+# ------------------------------------------------- decode attention (single tokens, bfloat16)
+def run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, max_blocks, nq, nkv, hd, page, window=0, parts=1, counters=None):
+    S = len(ctxs)
+    T = q.shape[0]
+    assert T == S
+    out = torch.full((T, nq * hd), 9.0, dtype=q.dtype, device="cuda")
+    scratch = None
+    if parts > 1:
+        scratch = torch.empty(ops.attention_decode_scratch_floats(S, nq, hd, parts), dtype=torch.float32, device="cuda")
+        if counters is None:
+            counters = torch.zeros(ops.attention_decode_counters(S, nq, nkv), dtype=torch.int32, device="cuda")
+    qd = dev(q.view(T, nq * hd))
+    ops.attention_decode(out, qd, nq * hd, dev(kc), dev(vc), dev(bt), max_blocks, dev(ctxs), dev(cu), S, nq, nkv, hd,
+                         page, window, 1.0 / math.sqrt(hd), parts, int(max(ctxs)), scratch, counters)
+    return out.float().cpu().view(T, nq, hd)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page", [(4, 2, 128, 16), (16, 8, 128, 16), (8, 1, 64, 32), (6, 2, 64, 16), (3, 3, 128, 8),
+                                            (40, 2, 64, 16), (24, 2, 128, 16)])
+@pytest.mark.parametrize("parts", [1, 4, 7, 37])
+def test_attention_decode(ops, nq, nkv, hd, page, parts):
+    """Single tokens against contexts of 1 to 700 keys and a padding row, one part and many (more
+    parts than some contexts have keys); groups of 1, 2, 3, 8, 12 and 20 heads; the counters are
+    left zero, so a second launch with the same counters gives the same result."""
+    dtype = torch.bfloat16
+    seqs = [(150, 1), (1, 1), (0, 1), (333, 1), (64, 1), (65, 1), (700, 1), (9, 1)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 31)
+    counters = torch.zeros(ops.attention_decode_counters(len(seqs), nq, nkv), dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        got = run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, parts=parts, counters=counters)
+        assert float((got - ref).abs().max()) < tol(dtype, 3)
+        assert float(got[2].abs().max()) == 0.0
+        assert int(counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("where", [lambda c: 0, lambda c: 15, lambda c: 16, lambda c: c - 1, lambda c: 255, lambda c: 256,
+                                   lambda c: c // 2])
+@pytest.mark.parametrize("parts", [1, 3, 8])
+def test_attention_decode_far_key(ops, where, parts):
+    nq, nkv, hd, page = 2, 1, 64, 16
+    seqs = [(700, 1), (513, 1)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 33, sharpen=FarKey(where))
+    got = run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, parts=parts)
+    assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
+
+
+@pytest.mark.parametrize("window", [1, 7, 16, 40, 100])
+@pytest.mark.parametrize("offset", [0, 1])
+@pytest.mark.parametrize("parts", [1, 3])
+def test_attention_decode_window_edge(ops, window, offset, parts):
+    nq, nkv, hd, page = 6, 2, 64, 16
+    seqs = [(130, 1), (97, 1), (40, 1), (0, 1)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 34, sharpen=WindowEdge(window, offset))
+    got = run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, window=window, parts=parts)
+    assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
 
 
 def test_attention_refuses_what_it_cannot_do(ops):

@@ -109,7 +109,7 @@ def manual_context(q_lens, starts, tables, page_size, dtype, mixers=(), max_step
     from llmgen_b200.engine.context import GroupView, StepContext, StepMetaBuilder, Workspace
     S, T = len(q_lens), sum(q_lens)
     max_blocks = max(len(t) for t in tables)
-    b = StepMetaBuilder(q_lens, starts, all(n == 1 for n in q_lens))
+    b = StepMetaBuilder(q_lens, starts, all(n == 1 for n in q_lens), page_size)
     pos, seq_of, slots = [], [], []
     cu = [0]
     for s, (n, st) in enumerate(zip(q_lens, starts)):
@@ -127,7 +127,7 @@ def manual_context(q_lens, starts, tables, page_size, dtype, mixers=(), max_step
     ctx = StepContext(
         n_tokens=T, n_seqs=S, dtype=dtype, device=torch.device("cuda:0"), workspace=Workspace(torch.device("cuda:0"), max_step_tokens),
         requests=list(range(S)), starts=list(starts), q_lens=list(q_lens), pure_decode=b.pure_decode,
-        max_ctx=max(s + n for s, n in zip(starts, q_lens)), max_ctx_bound=max_blocks * page_size,
+        max_ctx=max(s + n for s, n in zip(starts, q_lens)), max_ctx_bound=max_blocks * page_size, max_seqs_bound=S,
         ids=dev([0] * T), positions=dev(pos), cu_q=dev(cu), ctx_len=dev([s + n for s, n in zip(starts, q_lens)]),
         state_slots=dev(state_slots if state_slots is not None else list(range(S))), seq_of_token=dev(seq_of),
         groups=[GroupView(dev(slots), dev(bt.reshape(-1)), max_blocks)],
