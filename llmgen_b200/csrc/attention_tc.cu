@@ -4,19 +4,23 @@
 //
 // Block = one tile of 128 rows of one (sequence, kv head): 128 / gc queries x gc query heads of the
 // kv head's group (gc = the largest power of two dividing the group size, at most 16), so a K/V
-// tile is read once for gc heads.  192 threads:
+// tile is read once for gc heads.  352 threads:
 //   warp 0     TMA producer: the Q tile once (a 3-D box [queries, gc heads, 64] per half of the head),
-//              then per tile of 128 keys the K pages and the V pages of the block table into a ring
-//              of two stages.
-//   warp 1     owns tensor memory (S0 | S1 | O: 128 + 128 + head_dim columns) and issues the MMAs:
+//              then per tile of 128 keys the K pages of the block table into a ring of two stages.
+//   warp 10    TMA producer of the V pages, a ring of two stages of its own.
+//   warp 1     owns tensor memory (S0 | S1 | O0 | O1: 2 x 128 + 2 x head_dim columns) and issues the MMAs:
 //              S[j] = Q K_j^T (K-major operands), O_j = P_j V_j (V read MN-major: keys are V's rows
 //              in shared memory).  S is double-buffered so that Q K_{j+1}^T runs under the softmax of
 //              tile j.
-//   warps 2-5  softmax: one thread per row.  Pass 1 reads S from tensor memory and finds the row
-//              maximum (causal and window mask on the tiles that need it); then the previous tile's
-//              O_j is read back and added to the float32 accumulator in registers, rescaled by
-//              exp(m_old - m_new); pass 2 writes P = exp2((s - m) * scale * log2 e) as bfloat16 into
-//              shared memory in the swizzled K-major layout the second MMA reads.
+//   warps 2-9  softmax: two threads per row, each with half of the row's key columns and half of the
+//              head.  Pass 1 reads S from tensor memory and finds the row maximum (causal and window
+//              mask on the tiles that need it; the two halves exchange maxima through shared memory);
+//              pass 2 writes P = exp2((s - m) * scale *
+//              log2 e) as bfloat16 into shared memory in the swizzled K-major layout the second MMA
+//              reads; then, while the tensor core multiplies it with V, the previous tile's O_j is read
+//              back from the other O buffer and added to the float32 accumulator in registers, rescaled
+//              by exp(m_old - m_new).  Reductions run as four independent chains: with so few warps per SM the
+//              latency of a dependent chain is what costs.
 // Statistics (m, l), the accumulator and the final division are float32.
 //
 // Tiles follow the reference's prefill kernel in spirit (src/backend/cuda/attention/attention.cu:300-466:
@@ -38,7 +42,7 @@ namespace {
 
 constexpr int BM = 128;     // rows of a tile
 constexpr int BN = 128;     // keys per tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 352;    // K producer, MMA, eight softmax warps, V producer
 constexpr int MAX_PAGES_PER_TILE = 8;   // page size >= 16
 
 struct Params {
@@ -53,7 +57,20 @@ struct Params {
     int max_blocks, nq, nkv, page_size, window, gc, bq, chunks;
     float scale_log2;
     unsigned v_lbo, v_sbo;
+#ifdef LLMK_ATTN_TIMELINE
+    long long* timeline;     // profiling builds only: clock64() stamps of block 0's first softmax warp
+#endif
 };
+
+#ifdef LLMK_ATTN_TIMELINE
+#define TL_STAMP(slot)                                                                                    \
+    do {                                                                                                  \
+        if (p.timeline && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && warp == 2 && lane == 0 && j < 16) \
+            p.timeline[j * 8 + (slot)] = clock64();                                                       \
+    } while (0)
+#else
+#define TL_STAMP(slot) do {} while (0)
+#endif
 
 template <int HD>
 struct Smem {
@@ -63,16 +80,49 @@ struct Smem {
     static constexpr int Q_OFF = 0;
     static constexpr int K_OFF = Q_OFF + Q_BYTES;       // 2 stages
     static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;  // 2 stages
-    static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
-    static constexpr int BAR_OFF = P_OFF + P_BYTES;
-    static constexpr int NUM_BARS = 13;
-    static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
+    static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;  // 2 buffers
+    static constexpr int XCHG_OFF = P_OFF + 2 * P_BYTES;   // float [2][2][BM]: row maxima (and at the end sums) of the two halves
+    static constexpr int BAR_OFF = XCHG_OFF + 2 * 2 * BM * 4;
+    static constexpr int NUM_BARS = 14;
+    // No slack for aligning the base: the kernel has no static shared memory, so the dynamic part
+    // starts on a 1024-byte boundary; the kernel checks that and reports an error otherwise.
+    static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// First cache row of each page of the tile of keys starting at `k0` (pages past the sequence's last
+// one, or already given back by a window, are replaced by the last page: their keys are masked).
+__device__ __forceinline__ void page_rows(int (&rows)[MAX_PAGES_PER_TILE], const int* bt, int k0, int ctx, int ps,
+                                          int nkv, int kvh) {
+    const int pages_per_tile = BN / ps;
+    const int last_page = (ctx - 1) / ps;
+    const int page0 = k0 / ps;
+#pragma unroll
+    for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg) {
+        if (pg < pages_per_tile) {
+            int page = __ldg(bt + min(page0 + pg, last_page));
+            if (page < 0) page = __ldg(bt + last_page);
+            rows[pg] = (page * nkv + kvh) * ps;
+        }
+    }
+}
+
+// One tile of BN keys, page by page: per page and 64-wide block of the head a box [page_size, 64].
+template <int HB>
+__device__ __forceinline__ void load_pages(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                           const int (&rows)[MAX_PAGES_PER_TILE], int ps, int bytes) {
+    const int pages_per_tile = BN / ps;
+    tc::mbar_expect_tx(bar, bytes);
+#pragma unroll
+    for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg)
+        if (pg < pages_per_tile)
+#pragma unroll
+            for (int h = 0; h < HB; ++h) tc::tma_load_2d(dst + h * BN * 128 + pg * ps * 128, map, bar, h * 64, rows[pg]);
 }
 
 template <int HD>
@@ -82,9 +132,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     using L = Smem<HD>;
     constexpr int HB = HD / 64;                 // 64-wide blocks of the head
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t S_COL0 = 0, S_COL1 = BN, O_COL = 2 * BN;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr uint32_t S_COL0 = 0, S_COL1 = BN, O_COL0 = 2 * BN, O_COL1 = 2 * BN + HD;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((tc::smem_u32(smem) & 1023u) != 0) {      // uniform over the block: nothing has been set up yet
+        if (threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+        return;
+    }
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
     uint64_t* q_full = bars;            // 1
     uint64_t* k_full = bars + 1;        // 2
@@ -92,8 +145,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint64_t* k_empty = bars + 5;       // 2
     uint64_t* v_empty = bars + 7;       // 2
     uint64_t* s_full = bars + 9;        // 2
-    uint64_t* p_full = bars + 11;       // 1, 128 arrivals
-    uint64_t* o_full = bars + 12;       // 1
+    uint64_t* p_full = bars + 11;       // 1, 256 arrivals
+    uint64_t* o_full = bars + 12;       // 2
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -104,7 +157,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < L::NUM_BARS; ++i) tc::mbar_init(tc::smem_u32(&bars[i]), i == 11 ? 128 : 1);
+        for (int i = 0; i < L::NUM_BARS; ++i) tc::mbar_init(tc::smem_u32(&bars[i]), i == 11 ? 256 : 1);
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_q);
         tc::prefetch_tensormap(&map_k);
@@ -146,42 +199,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int h = 0; h < HB; ++h)
                 tc::tma_load_3d(tc::smem_u32(smem + L::Q_OFF + h * BM * 128), &map_q, qbar, h * 64, head0, q_beg + q0);
             const int* bt = p.block_tables + (size_t)s * p.max_blocks;
-            const int ps = p.page_size;
-            const int pages_per_tile = BN / ps;
-            const int last_page = (ctx - 1) / ps;
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j & 1;
                 const uint32_t round = j >> 1;
                 int rows[MAX_PAGES_PER_TILE];
-                const int page0 = (kt0 + j * BN) / ps;
-#pragma unroll
-                for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg) {
-                    if (pg < pages_per_tile) {
-                        int page = __ldg(bt + min(page0 + pg, last_page));
-                        if (page < 0) page = __ldg(bt + last_page);   // a page the window has passed: masked anyway
-                        rows[pg] = (page * p.nkv + kvh) * ps;
-                    }
-                }
+                page_rows(rows, bt, kt0 + j * BN, ctx, p.page_size, p.nkv, kvh);
                 if (!tc::mbar_wait(tc::smem_u32(&k_empty[st]), (round & 1) ^ 1, abort_flag)) break;
-                uint32_t bar = tc::smem_u32(&k_full[st]);
-                tc::mbar_expect_tx(bar, L::KV_BYTES);
-                uint32_t dst = tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
-#pragma unroll
-                for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg)
-                    if (pg < pages_per_tile)
-#pragma unroll
-                        for (int h = 0; h < HB; ++h)
-                            tc::tma_load_2d(dst + h * BN * 128 + pg * ps * 128, &map_k, bar, h * 64, rows[pg]);
+                load_pages<HB>(tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES), &map_k, tc::smem_u32(&k_full[st]), rows,
+                               p.page_size, L::KV_BYTES);
+            }
+        }
+    } else if (warp == 10) {
+        // V producer: a ring of its own, so that K of the next tiles never waits for a V slot.
+        if (lane == 0 && n_tiles > 0) {
+            const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j & 1;
+                const uint32_t round = j >> 1;
+                int rows[MAX_PAGES_PER_TILE];
+                page_rows(rows, bt, kt0 + j * BN, ctx, p.page_size, p.nkv, kvh);
                 if (!tc::mbar_wait(tc::smem_u32(&v_empty[st]), (round & 1) ^ 1, abort_flag)) break;
-                bar = tc::smem_u32(&v_full[st]);
-                tc::mbar_expect_tx(bar, L::KV_BYTES);
-                dst = tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
-#pragma unroll
-                for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg)
-                    if (pg < pages_per_tile)
-#pragma unroll
-                        for (int h = 0; h < HB; ++h)
-                            tc::tma_load_2d(dst + h * BN * 128 + pg * ps * 128, &map_v, bar, h * 64, rows[pg]);
+                load_pages<HB>(tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES), &map_v, tc::smem_u32(&v_full[st]), rows,
+                               p.page_size, L::KV_BYTES);
             }
         }
     } else if (warp == 1) {
@@ -189,7 +228,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             constexpr uint32_t idesc_s = tc::idesc_bf16_f32(BM, BN);
             constexpr uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(BM, HD);
             const uint32_t q_addr = tc::smem_u32(smem + L::Q_OFF);
-            const uint32_t p_addr = tc::smem_u32(smem + L::P_OFF);
+            const uint32_t p_base = tc::smem_u32(smem + L::P_OFF);
             auto issue_qk = [&](int j) -> bool {
                 const int st = j & 1;
                 if (!tc::mbar_wait(tc::smem_u32(&k_full[st]), (j >> 1) & 1, abort_flag)) return false;
@@ -216,20 +255,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (!ok) break;
                 tc::tc_fence_after_sync();
                 const uint32_t v_addr = tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+                const uint32_t p_addr = p_base + st * L::P_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t da = tc::smem_desc_sw128(p_addr + (kk / 4) * (BM * 128) + (kk % 4) * 32);
                     const uint64_t db = tc::smem_desc_sw128_mn(v_addr + kk * 16 * 128, p.v_lbo, p.v_sbo);
-                    tc::mma_bf16_ss(tmem_base + O_COL, da, db, idesc_o, kk != 0);
+                    tc::mma_bf16_ss(tmem_base + (st ? O_COL1 : O_COL0), da, db, idesc_o, kk != 0);
                 }
-                tc::mma_commit(tc::smem_u32(o_full));
+                tc::mma_commit(tc::smem_u32(&o_full[st]));
                 tc::mma_commit(tc::smem_u32(&v_empty[st]));
                 if (j + 2 < n_tiles) ok = issue_qk(j + 2);
             }
         }
     } else {
-        // Softmax and accumulation: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
+        // Softmax and accumulation, eight warps.  Warp w may touch tensor-memory lanes
+        // 32 * (w % 4) .. + 31, so a row of the tile belongs to two warps: `half` 0 takes key columns
+        // 0..63 of S and the first half of the head in O, `half` 1 the rest.  The two exchange their
+        // row maxima through shared memory once per tile; sums stay separate until the end.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const int qi = r / p.gc;
         const int head = head0 + r % p.gc;
@@ -238,19 +282,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int lo = p.window > 0 ? qpos - p.window : -1;   // keys at positions > lo are visible
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const float sl2 = p.scale_log2;
+        constexpr int OC = HD / 2;            // columns of O this thread accumulates
+        constexpr int SC = BN / 2;            // columns of S this thread turns into P
         float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
-        float acc[HD];
+        float acc[OC];
 #pragma unroll
-        for (int i = 0; i < HD; ++i) acc[i] = 0.f;
-        uint8_t* p_row = smem + L::P_OFF + r * 128;
+        for (int i = 0; i < OC; ++i) acc[i] = 0.f;
+        uint8_t* p_row0 = smem + L::P_OFF + half * (BM * 128) + r * 128;
+        float* xchg = reinterpret_cast<float*>(smem + L::XCHG_OFF);      // [2 tiles][2 halves][128 rows]
         bool ok = true;
 
-        auto accumulate = [&](float alpha) {
+        auto accumulate = [&](float alpha, int buf) {
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < OC / 32; ++c) {
                 uint32_t o[32];
-                tc::tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
-                tc::tmem_ld_wait();
+                tc::tmem_ld_32x32_wait(tmem_base + lane_addr + (buf ? O_COL1 : O_COL0) + half * OC + c * 32, o);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(o[i]));
             }
@@ -258,83 +304,108 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
-            const int k0 = kt0 + j * BN;
-            ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag));
-            if (!ok) break;
+            const int k0 = kt0 + j * BN + half * SC;      // first key of this thread's columns
+            TL_STAMP(0);
+            if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag));
             tc::tc_fence_after_sync();
-            const uint32_t s_addr = tmem_base + lane_addr + (st ? S_COL1 : S_COL0);
-            const bool need_mask = (k0 + BN - 1 > qpos) || (k0 <= lo);
-            // pass 1: the row maximum
-            float mx = -INFINITY;
+            TL_STAMP(1);
+            const uint32_t s_addr = tmem_base + lane_addr + (st ? S_COL1 : S_COL0) + half * SC;
+            const bool need_mask = (k0 + SC - 1 > qpos) || (k0 <= lo);
+            uint8_t* p_row = p_row0 + st * L::P_BYTES;       // P is double-buffered: P V of the tile before may still read the other
+            // pass 1: the maximum of this thread's half of the row (four independent chains)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (ok) {
+                uint32_t v[SC / 32][32];
+                static_assert(SC == 64, "two loads of 32 columns per pass");
+                tc::tmem_ld_32x32_x2_wait(s_addr, s_addr + 32, v[0], v[1]);
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tc::tmem_ld_32x32(s_addr + c * 32, v);
-                tc::tmem_ld_wait();
-                if (need_mask) {
+                for (int c = 0; c < SC / 32; ++c) {
+                    if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int kpos = k0 + c * 32 + i;
-                        if (kpos <= qpos && kpos > lo) mx = fmaxf(mx, __uint_as_float(v[i]));
+                        for (int i = 0; i < 32; ++i) {
+                            const int kpos = k0 + c * 32 + i;
+                            if (kpos <= qpos && kpos > lo) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
                 }
             }
+            const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            TL_STAMP(2);
+            xchg[(st * 2 + half) * BM + r] = mx_own;
+            asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight softmax warps
+            TL_STAMP(3);
+            const float mx = fmaxf(mx_own, xchg[(st * 2 + (half ^ 1)) * BM + r]);
             const float m_new = fmaxf(m, mx);
             const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * sl2);
-            // the previous tile's P V, now that its MMA has had pass 1 to finish
-            if (j > 0) {
-                ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(o_full), (j - 1) & 1, abort_flag));
-                if (!ok) break;
+            TL_STAMP(4);
+            // pass 2: P into shared memory, row sum
+            if (ok) {
+                const float mb = (m_new == -INFINITY) ? 0.f : m_new * sl2;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t v[SC / 32][32];
+                static_assert(SC == 64, "two loads of 32 columns per pass");
+                tc::tmem_ld_32x32_x2_wait(s_addr, s_addr + 32, v[0], v[1]);
+#pragma unroll
+                for (int c = 0; c < SC / 32; ++c) {
+                    float pv[32];
+                    if (need_mask) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int kpos = k0 + c * 32 + i;
+                            const bool vis = kpos <= qpos && kpos > lo;
+                            pv[i] = vis ? fast_exp2(fmaf(__uint_as_float(v[c][i]), sl2, -mb)) : 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(v[c][i]), sl2, -mb));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) sum4[i & 3] += pv[i];
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        Vec16<bf16> pk;
+                        pk.pack(pv + q8 * 8);
+                        const int chunk16 = c * 4 + q8;       // 16-byte chunk inside this half's 64 columns
+                        *reinterpret_cast<uint4*>(p_row + ((chunk16 ^ (r & 7)) << 4)) = pk.raw;
+                    }
+                }
+                l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                m = m_new;
+                tc::fence_proxy_async();
+                tc::tc_fence_before_sync();
+                tc::mbar_arrive(tc::smem_u32(p_full));
+                TL_STAMP(5);
+            }
+            // the previous tile's P V (in the other O buffer), while the tensor core works on this one's
+            if (ok && j > 0) {
+                ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&o_full[(j - 1) & 1]), ((j - 1) >> 1) & 1, abort_flag));
                 tc::tc_fence_after_sync();
-                accumulate(alpha_pending);
+                TL_STAMP(6);
+                if (ok) accumulate(alpha_pending, (j - 1) & 1);
             }
             alpha_pending = alpha;
-            // pass 2: P into shared memory, row sum
-            const float mb = (m_new == -INFINITY) ? 0.f : m_new * sl2;
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tc::tmem_ld_32x32(s_addr + c * 32, v);
-                tc::tmem_ld_wait();
-                float pv[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int kpos = k0 + c * 32 + i;
-                    const bool vis = !need_mask || (kpos <= qpos && kpos > lo);
-                    pv[i] = vis ? fast_exp2(fmaf(__uint_as_float(v[i]), sl2, -mb)) : 0.f;
-                    sum += pv[i];
-                }
-#pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                    Vec16<bf16> pk;
-                    pk.pack(pv + q8 * 8);
-                    const int col = c * 32 + q8 * 8;
-                    const int chunk16 = (col % 64) / 8;
-                    *reinterpret_cast<uint4*>(p_row + (col / 64) * (BM * 128) + ((chunk16 ^ (r & 7)) << 4)) = pk.raw;
-                }
-            }
-            l = l * alpha + sum;
-            m = m_new;
-            tc::fence_proxy_async();
-            tc::tc_fence_before_sync();
-            tc::mbar_arrive(tc::smem_u32(p_full));
+            TL_STAMP(7);
         }
         if (ok && n_tiles > 0) {
-            ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(o_full), (n_tiles - 1) & 1, abort_flag));
+            ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&o_full[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag));
             if (ok) {
                 tc::tc_fence_after_sync();
-                accumulate(alpha_pending);
+                accumulate(alpha_pending, (n_tiles - 1) & 1);
             }
         }
+        // the row's sum is the two halves' sums (both were kept against the same maxima)
+        asm volatile("bar.sync 1, 256;" ::: "memory");       // every read of the last tile's maxima is done
+        xchg[half * BM + r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float l_row = l + xchg[(half ^ 1) * BM + r];
         if (ok && qi < max(nq_tile, 0) && (chunk * p.gc + r % p.gc) < G) {
-            const float inv = (row_valid && l > 0.f) ? 1.0f / l : 0.f;
-            bf16* o = p.out + (size_t)(q_beg + q0 + qi) * p.o_stride + (size_t)head * HD;
+            const float inv = (row_valid && l_row > 0.f) ? 1.0f / l_row : 0.f;
+            bf16* o = p.out + (size_t)(q_beg + q0 + qi) * p.o_stride + (size_t)head * HD + half * OC;
 #pragma unroll
-            for (int i = 0; i < HD; i += 8) {
+            for (int i = 0; i < OC; i += 8) {
                 float f[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = acc[i + e] * inv;
@@ -392,7 +463,11 @@ LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, 
                                   const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,
                                   const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd,
                                   int page_size, int window, float scale, int* error_flag, unsigned v_lbo,
-                                  unsigned v_sbo, void* stream) {
+                                  unsigned v_sbo, void* stream
+#ifdef LLMK_ATTN_TIMELINE
+                                  , long long* timeline
+#endif
+) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     const int bq = llmk_attention_tc_tile_queries(nq, nkv, hd, page_size);
     if (bq == 0)
@@ -423,6 +498,9 @@ LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.v_lbo = v_lbo ? v_lbo : (unsigned)(BN * 128);
     p.v_sbo = v_sbo ? v_sbo : 1024u;
+#ifdef LLMK_ATTN_TIMELINE
+    p.timeline = timeline;
+#endif
     CUtensorMap mq, mk, mv;
     if (!tc_host::make_map_bf16_3d(&mq, q, hd, nq, n_tokens, hd, q_stride, p.gc, p.bq))
         LLMK_FAIL("attention_tc: cuTensorMapEncodeTiled failed for q");

@@ -189,6 +189,110 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
     }
 }
 
+// The same for whole prompts, with 16-byte accesses: `LPR` lanes share one (token, head) row, each
+// holding one 16-byte vector of it, so a warp works on 32 / LPR rows at a time; the rotary partner of
+// a value sits LPR / 2 lanes away.  Taken when the rotary width is the head width, the rows are not
+// partial sums, and everything is 16-byte aligned.
+template <typename T, int LPR>
+__global__ void __launch_bounds__(256)
+attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restrict__ q_out, long long q_stride,
+                     T* __restrict__ kcache, T* __restrict__ vcache, const int* __restrict__ positions,
+                     const int* __restrict__ slots, const float* __restrict__ cos_tab,
+                     const float* __restrict__ sin_tab, const float* __restrict__ q_gain,
+                     const float* __restrict__ k_gain, int n_tokens, int nq, int nk, int nkv_cache, int hd,
+                     int page_size, float eps, float q_off, float k_off) {
+    constexpr int EPL = Vec16<T>::N;            // elements per lane
+    constexpr int RPW = 32 / LPR;               // rows per warp
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int sub = lane % LPR;                 // which vector of the row
+    const int heads = nq + 2 * nk;
+    const long long n_rows = (long long)n_tokens * heads;
+    const long long warp_id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long n_warps = (long long)gridDim.x * (blockDim.x >> 5);
+    const int half_lanes = LPR / 2;
+    for (long long row0 = warp_id * RPW; row0 < n_rows; row0 += n_warps * RPW) {
+        const long long row = row0 + lane / LPR;
+        const bool live = row < n_rows;
+        const int t = live ? (int)(row / heads) : 0;
+        const int h = live ? (int)(row % heads) : 0;
+        const int slot = slots ? slots[t] : -1;
+        Vec16<T> x;
+        x.raw = *reinterpret_cast<const decltype(x.raw)*>(qkv + (size_t)t * row_stride + (size_t)h * hd + sub * EPL);
+        float f[EPL];
+        x.unpack(f);
+        const bool is_v = h >= nq + nk;
+        const bool is_q = h < nq;
+        const float* gain = is_q ? q_gain : k_gain;
+        const float goff = is_q ? q_off : k_off;
+        // every lane takes part in the shuffles, whatever kind of row it holds
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) ss += f[i] * f[i];
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (!is_v && gain) {
+            const float rinv = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) f[i] = f[i] * rinv * (gain[sub * EPL + i] + goff);
+        }
+        float partner[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, f[i], half_lanes);
+        if (!is_v && cos_tab) {
+            const int pos = positions[t];
+            const int p0 = (sub % half_lanes) * EPL;          // index of the pair inside the half
+            const float* c = cos_tab + (size_t)pos * (hd / 2) + p0;
+            const float* sn = sin_tab + (size_t)pos * (hd / 2) + p0;
+            const float sign = sub < half_lanes ? -1.f : 1.f;  // low half: x cos - y sin; high half: x cos + y sin
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) f[i] = f[i] * c[i] + sign * partner[i] * sn[i];
+        }
+        if (!live) continue;
+        T* dst = nullptr;
+        if (is_q) {
+            dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
+        } else if (slot >= 0) {
+            T* cache = is_v ? vcache : kcache;
+            const int kvh = is_v ? h - nq - nk : h - nq;
+            if (cache) dst = cache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd;
+        }
+        if (dst) {
+            Vec16<T> y;
+            y.pack(f);
+            *reinterpret_cast<decltype(y.raw)*>(dst + sub * EPL) = is_v ? x.raw : y.raw;
+        }
+    }
+}
+
+template <typename T>
+static bool launch_vec(const void* qkv, long long row_stride, void* q_out, long long q_stride, void* kcache, void* vcache,
+                       const int* positions, const int* slots, const float* cos_tab, const float* sin_tab,
+                       const float* q_gain, const float* k_gain, int n_tokens, int nq, int nk, int nkv_cache, int hd,
+                       int rot, int page_size, float eps, float q_off, float k_off, cudaStream_t s, cudaError_t* err) {
+    constexpr int EPL = Vec16<T>::N;
+    if (hd % EPL != 0 || (cos_tab && rot != hd)) return false;
+    const int lpr = hd / EPL;
+    if (lpr != 8 && lpr != 16 && lpr != 32) return false;
+    if (row_stride % EPL != 0 || q_stride % EPL != 0 || !host_aligned16(qkv) || !host_aligned16(q_out) ||
+        (kcache && !host_aligned16(kcache)) || (vcache && !host_aligned16(vcache)))
+        return false;
+    const long long rows = (long long)n_tokens * (nq + 2 * nk);
+    const int rpw = 32 / lpr;
+    long long blocks = (rows + 8 * rpw - 1) / (8 * rpw);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+#define LAUNCH_VEC(L)                                                                                                   \
+    *err = llmk_launch(attn_prep_vec_kernel<T, L>, dim3((unsigned)blocks), dim3(256), 0, s, true, (const T*)qkv, row_stride, \
+                       (T*)q_out, q_stride, (T*)kcache, (T*)vcache, positions, slots, cos_tab, sin_tab, q_gain, k_gain,  \
+                       n_tokens, nq, nk, nkv_cache, hd, page_size, eps, q_off, k_off)
+    if (lpr == 8) LAUNCH_VEC(8);
+    else if (lpr == 16) LAUNCH_VEC(16);
+    else LAUNCH_VEC(32);
+#undef LAUNCH_VEC
+    return true;
+}
+
 // nk = number of k (and v) heads present in the packed rows: num_kv_heads for a layer that
 // writes its cache, 0 for a layer that only reads another layer's cache.
 LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits, long long split_stride, void* q_out,
@@ -212,6 +316,19 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 2147483647LL) LLMK_FAIL("attn_prep: too many rows");
     cudaError_t e;
+    if (splits == 0 && n_tokens >= 32) {
+        bool taken = false;
+        if (dtype == LLMK_F32)
+            taken = launch_vec<float>(qkv, row_stride, q_out, q_stride, kcache, vcache, positions, slots, cos_tab, sin_tab,
+                                      q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off, k_off, s, &e);
+        else if (dtype == LLMK_BF16)
+            taken = launch_vec<bf16>(qkv, row_stride, q_out, q_stride, kcache, vcache, positions, slots, cos_tab, sin_tab,
+                                     q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off, k_off, s, &e);
+        if (taken) {
+            LLMK_CHECK_LAUNCH_RC("attn_prep", e);
+            return LLMK_OK;
+        }
+    }
     if (dtype == LLMK_F32)
         e = llmk_launch(attn_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
                         splits, split_stride, (float*)q_out, q_stride, (float*)kcache, (float*)vcache, positions, slots,

@@ -111,6 +111,85 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __rest
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<T>(srow[i] * rinv * (w[i] + w_offset));
 }
 
+// The same with the row kept in registers and 16-byte accesses: thread t holds the float4 vectors
+// t, t + blockDim, ... of the row (at most VPT of them).  Taken when H is a multiple of 4, at most
+// 4 * VPT * blockDim, and the arrays are 16-byte aligned.
+template <int N> struct Pack4;
+template <> struct Pack4<4> { typedef float4 type; };     // four float32
+template <> struct Pack4<2> { typedef uint2 type; };      // four bfloat16
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __restrict__ delta,
+                                       const float* __restrict__ w, T* __restrict__ out,
+                                       const int* __restrict__ rows, int H, float eps, float w_offset,
+                                       int write_resid, int splits, long long split_stride) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = rows ? rows[r] : r;
+    float* x = resid + (size_t)s * H;
+    const T* d = (delta && splits == 0) ? static_cast<const T*>(delta) + (size_t)s * H : nullptr;
+    const float* dp = (delta && splits > 0) ? static_cast<const float*>(delta) + (size_t)s * H : nullptr;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < VPT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < H) {
+            v[it] = load4(x + i);
+            if (d) {
+                const float4 a = load4(d + i);
+                v[it].x += a.x; v[it].y += a.y; v[it].z += a.z; v[it].w += a.w;
+            }
+            if (dp) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp0 = 0; sp0 < splits; sp0 += 8) {
+                    float4 t[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        t[u] = sp0 + u < splits ? __ldcg(reinterpret_cast<const float4*>(dp + (size_t)(sp0 + u) * split_stride + i))
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w;
+                    }
+                }
+                v[it].x += acc.x; v[it].y += acc.y; v[it].z += acc.z; v[it].w += acc.w;
+            }
+            ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
+            if (write_resid) store4(x + i, v[it]);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+#pragma unroll
+    for (int it = 0; it < VPT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        if (i < H) {
+            const float4 g = load4(w + i);
+            store4(o + i, make_float4(v[it].x * rinv * (g.x + w_offset), v[it].y * rinv * (g.y + w_offset),
+                                      v[it].z * rinv * (g.z + w_offset), v[it].w * rinv * (g.w + w_offset)));
+        }
+    }
+}
+
 LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, const int* rows,
                                  int n_rows, int H, float eps, float w_offset, int write_resid, int splits,
                                  long long split_stride, int dtype, void* stream) {
@@ -122,6 +201,25 @@ LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w
     if (splits < 0 || (splits > 0 && split_stride < H)) LLMK_FAIL("add_rmsnorm: bad partial sums (%d slices, stride %lld)", splits, split_stride);
     cudaStream_t s = (cudaStream_t)stream;
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const bool aligned = host_aligned16(resid) && host_aligned16(w) && host_aligned16(out) &&
+                         (!delta || host_aligned16(delta)) && (splits == 0 || split_stride % 4 == 0);
+    if (H % 4 == 0 && H <= 8192 && aligned && (dtype == LLMK_F32 || dtype == LLMK_BF16)) {
+        int vthreads = (H / 4 + 31) / 32 * 32;
+        if (vthreads > 512) vthreads = 512;
+        const int vpt = (H / 4 + vthreads - 1) / vthreads;
+        cudaError_t e;
+#define LAUNCH_VEC(T, V)                                                                                               \
+    e = llmk_launch(add_rmsnorm_vec_kernel<T, V>, dim3(n_rows), dim3(vthreads), 0, s, true, resid, delta, w, (T*)out, rows, H, \
+                    eps, w_offset, write_resid, splits, split_stride)
+        if (dtype == LLMK_F32) {
+            if (vpt == 1) LAUNCH_VEC(float, 1); else if (vpt == 2) LAUNCH_VEC(float, 2); else LAUNCH_VEC(float, 4);
+        } else {
+            if (vpt == 1) LAUNCH_VEC(bf16, 1); else if (vpt == 2) LAUNCH_VEC(bf16, 2); else LAUNCH_VEC(bf16, 4);
+        }
+#undef LAUNCH_VEC
+        LLMK_CHECK_LAUNCH_RC("add_rmsnorm", e);
+        return LLMK_OK;
+    }
 #define LAUNCH(T)                                                                                            \
     do {                                                                                                     \
         if (smem > 48 * 1024) {                                                                              \

@@ -161,8 +161,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (c0 >= M) break;   // uniform over the block
                 uint32_t r[16];
                 __syncwarp();
-                tc::tmem_ld_32x16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-                tc::tmem_ld_wait();
+                tc::tmem_ld_32x16_wait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int m = c0 + i;

@@ -148,8 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (n0 + c0 >= N) break;   // uniform over the warp
                 uint32_t r[32];
                 __syncwarp();
-                tc::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-                tc::tmem_ld_wait();
+                tc::tmem_ld_32x32_wait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
                 if (row >= M) {
                     // nothing to store for this lane; it still takes part in the loads above
                 } else if constexpr (GATED) {

@@ -46,7 +46,7 @@ def test_embed_rows(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H", [100, 1032, 5120])
+@pytest.mark.parametrize("H", [100, 1030, 1032, 5120, 8200])
 def test_add_rmsnorm(ops, dtype, H):
     torch.manual_seed(1)
     n, eps = 7, 3e-5
@@ -126,6 +126,45 @@ def test_attn_prep(ops, dtype, nq, nkv, hd, rot):
     assert torch.equal(vc.float().cpu(), vc_ref)                       # values are copied bit for bit
     # the k and v columns of the packed rows are left as they were
     assert torch.equal(x.cpu()[:, nq * hd:], qkv[:, nq * hd:])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 64), (16, 8, 128), (3, 1, 256), (5, 2, 32), (2, 2, 48)])
+@pytest.mark.parametrize("T", [32, 77, 300])
+def test_attn_prep_on_prompts(ops, dtype, nq, nkv, hd, T):
+    """Many rows: the path with 16-byte accesses (head sizes it takes) and the general one agree with
+    the plain functions; slots include -1 and a page's last place; q lands in a buffer of its own."""
+    torch.manual_seed(4)
+    page, eps = 16, 1e-6
+    pages = (T + page - 1) // page + 1
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(dtype)
+    positions = [(7 * t) % 200 for t in range(T)]
+    perm = torch.randperm(pages * page)[:T].tolist()
+    slots = [-1 if t % 11 == 5 else perm[t] for t in range(T)]
+    qg, kg = 1 + 0.3 * torch.randn(hd), 1 + 0.3 * torch.randn(hd)
+    cos, sin = plain.rope_tables(200, hd, 10000.0)
+    kc = torch.full((pages, nkv, page, hd), 7.0, dtype=dtype, device="cuda")
+    vc = torch.full((pages, nkv, page, hd), 7.0, dtype=dtype, device="cuda")
+    x = dev(qkv)
+    q_out = torch.full((T, nq * hd), 9.0, dtype=dtype, device="cuda")
+    ops.attn_prep(x, kc, vc, dev(torch.tensor(positions, dtype=torch.int32)), dev(torch.tensor(slots, dtype=torch.int32)),
+                  dev(cos.float()), dev(sin.float()), dev(qg), dev(kg), nq, nkv, hd, hd, page, eps, q_out=q_out)
+    f = qkv.float()
+    q = f[:, :nq * hd].view(T, nq, hd)
+    k = f[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
+    v = f[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    q_ref = plain.apply_rope(plain.rmsnorm(q, qg, eps), positions, cos, sin, hd)
+    k_ref = plain.apply_rope(plain.rmsnorm(k, kg, eps), positions, cos, sin, hd)
+    assert float((q_out.float().cpu().view(T, nq, hd) - q_ref).abs().max()) < tol(dtype, 6)
+    kc_ref = torch.full((pages, nkv, page, hd), 7.0)
+    vc_ref = torch.full((pages, nkv, page, hd), 7.0)
+    for t, s in enumerate(slots):
+        if s >= 0:
+            kc_ref[s // page, :, s % page] = k_ref[t]
+            vc_ref[s // page, :, s % page] = v[t]
+    assert float((kc.float().cpu() - kc_ref).abs().max()) < tol(dtype, 6)
+    assert torch.equal(vc.float().cpu(), vc_ref)
+    assert torch.equal(x.cpu(), qkv)                                   # the packed rows are left as they were
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -557,6 +596,15 @@ def test_attention_tc_mixed_batch(ops, nq, nkv, hd, page):
     got = run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
     assert float((got - ref).abs().max()) < tol(dtype, 3)
     assert float(got[31].abs().max()) == 0.0        # the padding row gives zeros
+
+
+def test_attention_tc_long_prompt(ops):
+    """One prompt of 2,048 tokens at the heads of the benchmark's shape: 16 key tiles, 32 query tiles."""
+    nq, nkv, hd, page = 16, 8, 128, 16
+    seqs = [(2048, 2048)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 22)
+    got = run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
+    assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
 
 
 @pytest.mark.parametrize("where", [lambda c: 0, lambda c: 15, lambda c: 16, lambda c: 127, lambda c: 128, lambda c: c - 1,
