@@ -205,10 +205,9 @@ def main():
         for r in reqs:
             assert ex.admit(r) and ex.reserve(r, 0, total)
         ex.step([StepEntry(r, p, 0, [PROMPT_TOKENS - 1], 0.6) for r, p in zip(reqs, prompts)], sample=True, return_logits=False)
-        bucket = ex._bucket_for(batch)
-        g = ex.graphs.get(bucket) or ex._capture(bucket)
         toks = rng.integers(0, V, batch).tolist()
         pos = PROMPT_TOKENS
+        bucket, g = ex.decode_graph(batch, total)     # one graph for the whole run: the class of the last context
 
         def one(pos):
             ex._build_meta([StepEntry(r, [t], pos, [0], 0.6) for r, t in zip(reqs, toks)], pad_to=bucket)

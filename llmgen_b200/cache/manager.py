@@ -90,10 +90,19 @@ class CacheGroup:
         self.page_size = page_size
         self.pool = PagePool(num_pages)
         self.tables: Dict[Hashable, List[int]] = {}
+        self.births: Dict[Hashable, int] = {}      # which table of the group's history a request's table is
+        self._born = 0
 
     # -- queries
     def table(self, req: Hashable) -> List[int]:
         return self.tables.get(req, [])
+
+    def table_stamp(self, req: Hashable):
+        """Changes whenever the contents of `req`'s table may have changed: a full-attention table
+        only grows, a windowed one also loses pages, so its stamp is never equal to an earlier one."""
+        if self.spec.kind == WINDOW:
+            return None
+        return (self.births.get(req, 0), len(self.tables.get(req, ())))
 
     def first_needed_position(self, start: int) -> int:
         """Oldest position that the token at `start` still attends to."""
@@ -122,7 +131,11 @@ class CacheGroup:
         give, new, skipped = self._plan(req, start, end)
         if new > self.pool.num_free + len(give):
             return False
-        table = self.tables.setdefault(req, [])
+        table = self.tables.get(req)
+        if table is None:
+            table = self.tables[req] = []
+            self._born += 1
+            self.births[req] = self._born
         self.pool.give([table[i] for i in give])
         for i in give:
             table[i] = -1
@@ -134,6 +147,7 @@ class CacheGroup:
 
     def release(self, req: Hashable) -> None:
         table = self.tables.pop(req, None)
+        self.births.pop(req, None)
         if table:
             self.pool.give([p for p in reversed(table) if p >= 0])
 

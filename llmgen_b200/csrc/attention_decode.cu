@@ -33,7 +33,7 @@ namespace {
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
 constexpr int KPW = 8;        // keys a warp takes per step
-constexpr int STAGES = 4;     // depth of each warp's cp.async ring
+constexpr int STAGES = 3;     // depth of each warp's cp.async ring
 
 struct DecodeParams {
     const bf16* q;

@@ -113,6 +113,8 @@ class Executor:
             if m is not None and hasattr(m, "prepare_step"):
                 self._unique_mixers.append(m)
 
+        # mixers whose own step arrays depend only on the batch's shape let decode steps reuse them
+        self._static_step_arrays = all(getattr(m, "step_arrays_follow_shapes", False) for m in self._unique_mixers)
         self.workspace = Workspace(self.device, limits.max_step_tokens)
         Tm, Sm, G = limits.max_step_tokens, limits.max_num_seqs, len(self.group_specs)
         words = 64 + 10 * Tm + 10 * Sm + G * (Tm + Sm * self.max_blocks + 8)
@@ -123,7 +125,10 @@ class Executor:
         self.sample_scratch = torch.empty(ops.sample_scratch_bytes(max(Sm, 64)) // 4, dtype=torch.float32,
                                           device=self.device)
         self.ids_host = torch.empty(max(Tm, Sm), dtype=torch.int32).pin_memory()
-        self.graphs: Dict[int, dict] = {}
+        self.graphs: Dict[Tuple[int, int], dict] = {}     # (batch-size bucket, context-length class) -> graph
+        # decode steps rewrite only what changed in a host buffer that the same bucket filled last
+        self._host_owner = [None, None]                   # per pinned buffer: (bucket, layout) of its last fill
+        self._host_rows = [None, None]                    # per pinned buffer: per group, per row: table stamp
 
     # ------------------------------------------------------------------ sizing
     def _pages_per_group(self) -> List[int]:
@@ -232,8 +237,11 @@ class Executor:
             if e.start < 0 or e.start + n > lim.max_model_len:
                 raise StepError(f"request {e.req!r}: positions [{e.start}, {e.start + n}) exceed max_model_len "
                                 f"{lim.max_model_len}")
-            toks = np.asarray(e.tokens)
-            if toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= V:
+            if n == 1 and type(e.tokens[0]) is int and 0 <= e.tokens[0] < V:
+                toks = None                                    # the common case of a decoded token, checked without numpy
+            else:
+                toks = np.asarray(e.tokens)
+            if toks is not None and (toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= V):
                 bad = [int(t) for t in toks.tolist() if not (isinstance(t, int) and 0 <= t < V)][:1]
                 raise StepError(f"request {e.req!r}: token id {bad[0] if bad else '?'} outside the vocabulary [0, {V})")
             for w in e.want:
@@ -272,7 +280,7 @@ class Executor:
         return passes
 
     # -- metadata
-    def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0):
+    def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0, ctx_bound: int = 0):
         """Fill and upload the step's metadata; returns (StepContext, want rows view, temps view,
         seed view, number of wanted rows)."""
         lim = self.limits
@@ -341,6 +349,8 @@ class Executor:
         if self.meta_events[turn] is not None:
             self.meta_events[turn].synchronize()
         layout, total = b.pack_into(self.meta_host[turn])
+        self._host_owner[turn] = None
+        self._last_fill = (turn, layout, total)
         self.meta_dev[:total].copy_(self.meta_host[turn][:total], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -354,7 +364,7 @@ class Executor:
         ctx = StepContext(
             n_tokens=T, n_seqs=S, dtype=self.dtype, device=self.device, workspace=self.workspace,
             requests=[e.req for e in entries], starts=starts, q_lens=q_lens, pure_decode=pure_decode,
-            max_ctx=int(ctx_len.max()) if S else 0, max_ctx_bound=lim.max_model_len,
+            max_ctx=int(ctx_len.max()) if S else 0, max_ctx_bound=ctx_bound or lim.max_model_len,
             max_seqs_bound=lim.max_num_seqs,
             ids=view("ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_len=view("ctx_len"),
             state_slots=view("state_slots"), seq_of_token=view("seq_of_token"),
@@ -408,16 +418,34 @@ class Executor:
                 return b
         raise StepError(f"{n} sequences exceed max_num_seqs {self.limits.max_num_seqs}")
 
-    def _capture(self, bucket: int) -> dict:
+    def context_class(self, max_ctx: int) -> int:
+        """Captured graphs fix their launch shapes, and how the keys of a sequence are best cut into
+        parts depends on how many there are: graphs are kept per class of context length (512,
+        1024, 2048, ... up to max_model_len) and a step replays the graph of the smallest class
+        that holds its longest sequence."""
+        bound = 512
+        while bound < max_ctx:
+            bound *= 2
+        return min(bound, self.limits.max_model_len)
+
+    def decode_graph(self, n_seqs: int, max_ctx: int) -> Tuple[int, dict]:
+        """(bucket, captured graph) for a step of `n_seqs` single tokens whose longest sequence
+        has `max_ctx` keys; captured on first use."""
+        bucket = self._bucket_for(n_seqs)
+        bound = self.context_class(max_ctx)
+        return bucket, (self.graphs.get((bucket, bound)) or self._capture(bucket, bound))
+
+    def _capture(self, bucket: int, ctx_bound: int = 0) -> dict:
         """Warm up once with an all-padding batch (loads kernels, lets the library pick its
         algorithms, creates the workspaces), then record the same launches into a graph
         (src/executor.zig:609-660)."""
+        ctx_bound = ctx_bound or self.limits.max_model_len
         V = self.model.spec.vocab_size
         logits = torch.empty((bucket, V), dtype=torch.float32, device=self.device)
         ids_dev = torch.zeros(bucket, dtype=torch.int32, device=self.device)
 
         def run():
-            ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket)
+            ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
             ctx.fixed_shapes = True
             self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
             ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
@@ -431,7 +459,7 @@ class Executor:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         # the metadata upload stays outside the graph: build it first, then capture the launches
-        ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket)
+        ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
         ctx.fixed_shapes = True
         torch.cuda.synchronize(self.device)
         self.workspace.frozen = True
@@ -443,23 +471,96 @@ class Executor:
         finally:
             self.workspace.frozen = False
         entry = {"graph": graph, "ids": ids_dev, "logits": logits, "launches": ops.launches() - launches_before}
-        self.graphs[bucket] = entry
+        self.graphs[(bucket, ctx_bound)] = entry
         return entry
 
     def capture_all(self) -> None:
+        """Capture every batch-size bucket at the largest context class."""
         for b in self.buckets():
-            if b not in self.graphs:
-                self._capture(b)
+            if (b, self.limits.max_model_len) not in self.graphs:
+                self._capture(b, self.limits.max_model_len)
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> StepOutput:
-        bucket = self._bucket_for(len(entries))
-        g = self.graphs.get(bucket) or self._capture(bucket)
-        self._build_meta(entries, pad_to=bucket)
+        n = len(entries)
+        bucket, g = self.decode_graph(n, max(e.start for e in entries) + 1)
+        self._fill_decode_meta(entries, bucket)
         g["graph"].replay()
         self.launch_count += g["launches"]
-        n = len(entries)
         host = self.ids_host[:n]
         host.copy_(g["ids"][:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.n_graph_steps += 1
         return StepOutput(None, host.tolist())
+
+    def _fill_decode_meta(self, entries: Sequence[StepEntry], bucket: int) -> None:
+        """The metadata of a step of single tokens.  The first fill of a pinned buffer for a bucket
+        goes through `_build_meta`; later ones rewrite only what a decode step changes (tokens,
+        positions, lengths, slots, the seed, and block-table rows whose table grew), with the
+        layout of that first fill."""
+        turn = self._meta_turn
+        owner = self._host_owner[turn]
+        if not self._static_step_arrays:
+            self._build_meta(entries, pad_to=bucket)
+            return
+        if owner is None or owner[0] != bucket:
+            self._build_meta(entries, pad_to=bucket)
+            t, layout, total = self._last_fill
+            self._host_owner[t] = (bucket, layout, total)
+            self._host_rows[t] = [[None] * bucket for _ in self.cache.groups]
+            for gi, g in enumerate(self.cache.groups):
+                for s_, e in enumerate(entries):
+                    self._host_rows[t][gi][s_] = (e.req, g.table_stamp(e.req))
+            return
+        _, layout, total = owner
+        self._meta_turn ^= 1
+        if self.meta_events[turn] is not None:
+            self.meta_events[turn].synchronize()
+        hv = self.meta_host[turn].numpy()
+        n, ps, S = len(entries), self.limits.page_size, bucket
+
+        def arr(name):
+            off, size, _ = layout[name]
+            return hv[off:off + size]
+
+        self.step_seed = (self.step_seed + SEED_STRIDE) & MASK64
+        arr("seed")[:] = np.array([self.step_seed], dtype=np.uint64).view(np.int32)
+        starts = [e.start for e in entries]
+        ids = arr("ids")
+        ids[:n] = [e.tokens[0] for e in entries]
+        ids[n:] = 0
+        pos = arr("positions")
+        pos[:n] = starts
+        pos[n:] = 0
+        cl = arr("ctx_len")
+        cl[:n] = starts
+        cl[:n] += 1
+        cl[n:] = 0
+        st = arr("state_slots")
+        st[:n] = [self.cache.state.slot(e.req) for e in entries]
+        st[n:] = -1
+        temps = arr("temps").view(np.float32)
+        temps[:n] = [e.temperature for e in entries]
+        temps[n:] = 0.0
+        for gi, g in enumerate(self.cache.groups):
+            slots = arr(f"slots_{gi}")
+            bt = arr(f"block_tables_{gi}").reshape(S, self.max_blocks)
+            rows = self._host_rows[turn][gi]
+            for s_, e in enumerate(entries):
+                table = g.table(e.req)
+                stamp = g.table_stamp(e.req)
+                key = (e.req, stamp)
+                if stamp is None or rows[s_] != key:
+                    bt[s_, :len(table)] = table
+                    bt[s_, len(table):] = 0
+                    rows[s_] = key
+                p = e.start
+                slots[s_] = table[p // ps] * ps + p % ps
+            for s_ in range(n, S):
+                if rows[s_] is not None:
+                    bt[s_, :] = 0
+                    rows[s_] = None
+            slots[n:] = -1
+        self.meta_dev[:total].copy_(self.meta_host[turn][:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.meta_events[turn] = ev

@@ -30,6 +30,10 @@ class GQAAttention(Mixer):
     shared by all heads), src/module/attention.zig:85-92, src/backend/cpu/attention.zig:64-118.
     A run item with `writes=False` projects q only and reads the cache another item wrote."""
 
+    # what `prepare_step` adds depends on the lengths of the step's portions only, not on their
+    # positions or requests: the engine may keep it across decode steps of one batch size
+    step_arrays_follow_shapes = True
+
     @staticmethod
     def weight_decls(spec: AttentionSpec):
         qd, kd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
@@ -165,8 +169,8 @@ class GQAAttention(Mixer):
 
 
     def _decode(self, ctx, o, q, cache, group, scale) -> None:
-        """Single decoded tokens: as many key parts as fill the SMs about twice, at least 64 keys
-        a part; under graph capture the bound on the context length decides, not the lengths."""
+        """Single decoded tokens: as many key parts as fill the SMs, at least 128 keys a part;
+        under graph capture the bound of the step's context class decides, not the lengths."""
         ws = ctx.workspace
         S = ctx.n_seqs
         G = self.nq // self.nkv
@@ -174,8 +178,8 @@ class GQAAttention(Mixer):
         bound = ctx.max_ctx_bound if ctx.fixed_shapes else max(ctx.max_ctx, 1)
         visible = min(bound, self.window) if self.window else bound
         blocks = max(1, S * self.nkv * chunks)
-        parts = max(1, min((2 * NUM_SMS + blocks - 1) // blocks, visible // 64, 64))
-        parts = max(parts, (visible + 4095) // 4096)          # shared memory holds a part's scores
+        # about 3.5 blocks per SM (4 fit), at least 128 keys a part, at most 64 parts
+        parts = max(1, min((7 * NUM_SMS // 2) // blocks, visible // 128, 64))
         scratch = counters = None
         if parts > 1:
             scratch = ws.flat("attn_decode_split", ops.attention_decode_scratch_floats(S, self.nq, self.hd, parts),

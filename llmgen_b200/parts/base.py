@@ -19,6 +19,8 @@ Mixer:
     cache_request() -> KVRequest | None       pages it needs (group kind, kv heads, head width)
     state_request() -> StateRequest | None    fixed-size per-request state (shape, dtype)
     prepare_step(builder)                     optional: add int32 arrays to the step's metadata
+    step_arrays_follow_shapes = True          optional class attribute: those arrays depend on the
+                                              portions' lengths only (lets decode steps reuse them)
     forward(ctx, x, cache) -> [T, H]          x is the normed input; `cache` is this run
                                               item's `LayerCache`; returns an array or a
                                               `Partials` (see `parts.linear.linear_sliced`)
