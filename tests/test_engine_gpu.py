@@ -71,16 +71,18 @@ def test_preemption_recomputes_and_gives_the_same_ids(tmp):
         assert llm.executor.cache.all_free()
 
 
-def test_graph_replay_equals_eager_and_duplicates_agree(tmp):
+@pytest.mark.parametrize("name,prompt_len,model_len", [("C", 21, 128), ("D", 21, 128), ("D", 505, 1024), ("E", 500, 1024)])
+def test_graph_replay_equals_eager_and_duplicates_agree(tmp, name, prompt_len, model_len):
     """The reference's `--dup` check (src/llmgen.zig:229-240): copies of one prompt in one batch
-    give identical ids; and graph replay gives what eager steps give."""
+    give identical ids; and graph replay gives what eager steps give.  D and E run the
+    flash-decoding kernel; the long prompts cross a context-length class while decoding."""
     from llmgen_b200 import LLM, SamplingParams
-    path = make_folder(tmp, "C")
-    prompt = random_ids(21, 301, 70)
+    path = make_folder(tmp, name)
+    prompt = random_ids(prompt_len, TINY[name][0]["vocab_size"], 70)
     outs = {}
     for eager in (False, True):
-        llm = LLM(path, dtype="bfloat16", max_model_len=128, max_num_seqs=8, max_batched_tokens=128, kv_blocks=64,
-                  eager=eager)
+        llm = LLM(path, dtype="bfloat16", max_model_len=model_len, max_num_seqs=8, max_batched_tokens=8 * model_len,
+                  kv_blocks=8 * model_len // TINY[name][5], block_size=TINY[name][5], eager=eager)
         res = llm.generate([prompt] * 5, SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True))
         assert all(r["token_ids"] == res[0]["token_ids"] for r in res)
         outs[eager] = res[0]["token_ids"]

@@ -2,7 +2,8 @@
 plain implementation: each request alone and whole; most of it in one step and the last 32
 tokens one by one; in portions of changing size down to two tokens; mixed, up to four live
 requests with so few pages that they are used again; long decoding; the first tokens of a
-sequence.  In float32 and in bfloat16, on three tiny configurations."""
+sequence; prompts of several hundred tokens.  In float32 and in bfloat16, on five tiny
+configurations (D and E have the head sizes the tensor-core and flash-decoding kernels take)."""
 import json
 import os
 import random
@@ -62,7 +63,7 @@ def sharpen(path, tmp, name):
     return out
 
 
-CASES = [(n, d) for n in "ABC" for d in ("float32", "bfloat16")]
+CASES = [(n, d) for n in "ABCDE" for d in ("float32", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -199,6 +200,37 @@ def test_first_tokens(tmp, name, dtype):
     got_b.append(d.step([("b", reqs[1][2:4], [0, 1])]))
     logits_close(torch.cat(got_a), ref[:3], dtype)
     logits_close(torch.cat(got_b), refs[1][:4], dtype)
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_in_portions_beside_decoding(tmp, name, dtype):
+    """517 and 330 tokens: several query and key tiles of the tensor-core kernel, portions that
+    start inside a tile, a portion beside a decoded token, then both decoding (the flash-decoding
+    kernel with several key parts), then a portion again."""
+    path = make_folder(tmp, name)
+    vocab = TINY[name][0]["vocab_size"]
+    a, b = random_ids(517, vocab, 41), random_ids(330, vocab, 42)
+    plain = PlainQwen3(path)
+    ref_a, ref_b = plain.logits(a), plain.logits(b)
+    d = Driver(path, dtype, 1024, TINY[name][5])
+    worst = 0.0
+
+    def check(got, *parts):
+        nonlocal worst
+        row = 0
+        for ref, lo, hi in parts:
+            worst = max(worst, logits_close(got[row:row + hi - lo], ref[lo:hi], dtype))
+            row += hi - lo
+
+    check(d.step([("a", a[0:260], range(260))]), (ref_a, 0, 260))
+    check(d.step([("a", a[260:500], range(240)), ("b", b[0:150], range(150))]), (ref_a, 260, 500), (ref_b, 0, 150))
+    check(d.step([("a", a[500:501], [0]), ("b", b[150:300], range(150))]), (ref_a, 500, 501), (ref_b, 150, 300))
+    for i in range(16):
+        check(d.step([("a", a[501 + i:502 + i], [0]), ("b", b[300 + i:301 + i], [0])]),
+              (ref_a, 501 + i, 502 + i), (ref_b, 300 + i, 301 + i))
+    check(d.step([("b", b[316:330], range(14))], end=["a", "b"]), (ref_b, 316, 330))
+    assert d.executor.cache.all_free()
 
 
 def test_want_order_and_empty_want(tmp):

@@ -37,9 +37,27 @@ TINY_C = {  # sizes that are no power of two, group of 3, a window on some layer
     "sliding_window": 40, "use_sliding_window": True,
     "layer_types": ["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
 }
+TINY_D = {  # head_dim 64 and a group of 3: the tensor-core and flash-decoding kernels of the bfloat16 path; a window
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "vocab_size": 333, "hidden_size": 128, "intermediate_size": 208, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
+    "rms_norm_eps": 2e-6, "rope_theta": 100000.0, "max_position_embeddings": 1024,
+    "tie_word_embeddings": True, "hidden_act": "silu",
+    "sliding_window": 150, "use_sliding_window": True,
+    "layer_types": ["full_attention", "sliding_attention", "full_attention"],
+}
+TINY_E = {  # head_dim 128, group of 2, pages of 32: the benchmark's head geometry in small
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "vocab_size": 290, "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128,
+    "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 1024,
+    "tie_word_embeddings": False, "hidden_act": "silu",
+}
 TINY = {"A": (TINY_A, 0, 0.02, 0.1, "bfloat16", 16),     # config, seed, sigma, sigma_norm, stored as, page
         "B": (TINY_B, 1, 0.03, 0.05, "float32", 32),
-        "C": (TINY_C, 5, 0.05, 0.2, "bfloat16", 16)}
+        "C": (TINY_C, 5, 0.05, 0.2, "bfloat16", 16),
+        "D": (TINY_D, 6, 0.04, 0.1, "bfloat16", 16),
+        "E": (TINY_E, 7, 0.05, 0.1, "float32", 32)}
 
 
 def make_folder(tmpdir: str, name: str) -> str:
