@@ -19,6 +19,12 @@
 //            merges.  Counters must be zero before the first launch and are left zero.
 // A sequence with ctx <= 0 (a padding row of a captured batch) gets zeros.
 //
+// Optionally the kernel starts from the packed q/k/v projection (bfloat16 rows or the float32 slices
+// of a product cut along K) and does the per-head RMSNorm, the rotary encoding and the cache write
+// itself: every block makes its q heads, and the block whose part holds the sequence's newest
+// position makes that position's k and v, stores them in the cache and then reads them back with
+// the rest of its keys.  That saves the launch of csrc/attn_prep.cu in a decode step.
+//
 // Same algorithm as the reference's `attn_decode_kernel<G>` + `attn_decode_reduce_kernel`
 // (src/backend/cuda/attention/attention.cu:51-207): one block per (kv head, sequence, part), the
 // group's heads share K/V reads, three phases, partial (m, l, o) merged afterwards; here the merge
@@ -49,7 +55,67 @@ struct DecodeParams {
     long long q_stride, o_stride;
     int max_blocks, nq, nkv, log2_page, window, chunks, page_cap;
     float scale;
+    // With `packed` set, q is not read from `q`: the block makes it (and, in the block that owns the
+    // sequence's newest key, k and v, which it also writes to the cache) from the packed projection
+    // rows [q heads | k heads | v heads]: per-head RMSNorm of q and k, then rotary encoding.
+    const void* packed;          // bfloat16 rows, or float32 partial sums (splits > 0)
+    long long packed_stride, split_stride;
+    int splits, nk, rot;         // nk: k (and v) heads present in the packed rows (0: q only)
+    const int* positions;
+    const int* slots;
+    const float* cos_tab;
+    const float* sin_tab;
+    const float* q_gain;
+    const float* k_gain;
+    float eps, q_off, k_off;
 };
+
+// One head's row of the packed projection: lane holds the values lane, lane + 32, ... of the head
+// (slices added in order), optionally normalised (RMSNorm over the head, gain + offset) and rotated
+// (half-split pairs (i, i + rot / 2), rot a multiple of 64, so that a pair sits in one lane).
+template <int HD>
+__device__ __forceinline__ void prep_head(const DecodeParams& p, int t, int head_in_row, const float* gain, float goff,
+                                          bool rotate, int lane, float (&vals)[HD / 32]) {
+    constexpr int VPL = HD / 32;
+    const size_t base = (size_t)t * p.packed_stride + (size_t)head_in_row * HD;
+    if (p.splits == 0) {
+        const bf16* x = static_cast<const bf16*>(p.packed) + base;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) vals[i] = to_float(x[lane + 32 * i]);
+    } else {
+        const float* x = static_cast<const float*>(p.packed) + base;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) vals[i] = 0.f;
+#pragma unroll 4
+        for (int sp = 0; sp < p.splits; ++sp)
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) vals[i] += __ldcg(x + (size_t)sp * p.split_stride + lane + 32 * i);
+    }
+    if (gain) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) ss += vals[i] * vals[i];
+        ss = warp_sum(ss);
+        const float rinv = 1.0f / sqrtf(ss / (float)HD + p.eps);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) vals[i] = vals[i] * rinv * (gain[lane + 32 * i] + goff);
+    }
+    if (rotate && p.cos_tab) {
+        const int half = p.rot / 2;
+        const int hv = half / 32;               // values per lane in each half of the rotated part
+        const int pos = p.positions[t];
+        const float* c = p.cos_tab + (size_t)pos * half;
+        const float* sn = p.sin_tab + (size_t)pos * half;
+#pragma unroll
+        for (int i = 0; i < VPL / 2; ++i) {
+            if (i < hv) {
+                const float x0 = vals[i], x1 = vals[i + hv], cs = c[lane + 32 * i], sv = sn[lane + 32 * i];
+                vals[i] = x0 * cs - x1 * sv;
+                vals[i + hv] = x1 * cs + x0 * sv;
+            }
+        }
+    }
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
     const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -113,9 +179,40 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
 
     // The part's page ids and q (float32, pre-multiplied by scale; zeros for heads beyond the group).
     for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = bt[page_base + i];
-    for (int i = tid; i < GC * HD; i += THREADS) {
-        const int g = i / HD;
-        q_s[i] = g < n_heads ? to_float(p.q[(size_t)t * p.q_stride + (size_t)(kvh * G + g0 + g) * HD + i % HD]) * p.scale : 0.f;
+    if (p.packed == nullptr) {
+        for (int i = tid; i < GC * HD; i += THREADS) {
+            const int g = i / HD;
+            q_s[i] = g < n_heads ? to_float(p.q[(size_t)t * p.q_stride + (size_t)(kvh * G + g0 + g) * HD + i % HD]) * p.scale : 0.f;
+        }
+    } else {
+        // A warp per row of the packed projection: the chunk's q heads, and in the block whose part
+        // holds the newest position also this kv head's k and v, which go to the cache before the
+        // block reads its keys (other blocks of the same kv head write the same values).
+        const bool newest = p.nk > 0 && k_beg <= ctx - 1 && ctx - 1 < k_end;
+        const int n_tasks = GC + (newest ? 2 : 0);
+        for (int task = warp; task < n_tasks; task += WARPS) {
+            float vals[DPL];
+            if (task < GC) {
+                if (task < n_heads) {
+                    prep_head<HD>(p, t, kvh * G + g0 + task, p.q_gain, p.q_off, true, lane, vals);
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = vals[i] * p.scale;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = 0.f;
+                }
+            } else {
+                const bool is_v = task == GC + 1;
+                prep_head<HD>(p, t, p.nq + (is_v ? p.nk : 0) + kvh, is_v ? nullptr : p.k_gain, p.k_off, !is_v, lane, vals);
+                const int slot = p.slots ? p.slots[t] : -1;
+                if (slot >= 0) {
+                    bf16* dst = const_cast<bf16*>(is_v ? p.vcache : p.kcache) +
+                                ((((size_t)(slot >> lps)) * p.nkv + kvh) * (size_t)(ps_mask + 1) + (slot & ps_mask)) * HD;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) dst[lane + 32 * i] = from_float<bf16>(vals[i]);
+                }
+            }
+        }
     }
     __syncthreads();
 
@@ -374,22 +471,42 @@ LLMK_EXPORT long long llmk_attention_decode_counters(int n_seqs, int nq, int nkv
     return (long long)n_seqs * nkv * ceil_div(G, chunk_heads(G));
 }
 
-// out[t, nq*hd] for the single token t = cu_q[s] of each of n_seqs sequences.  `max_ctx` bounds every
+// 1 if the kernel can make q, k and v from the packed projection rows itself for this rotary width.
+LLMK_EXPORT int llmk_attention_decode_fuses_prep(int hd, int rot) { return (rot % 64 == 0 && rot <= hd) ? 1 : 0; }
+
+// out[t, nq*hd] for the single token t = cu_q[s] of each of n_seqs sequences.  With `packed` the
+// kernel also does what csrc/attn_prep.cu does (see DecodeParams); `q` is then not read.  `max_ctx` bounds every
 // ctx_len[s] of this launch (it sizes the shared-memory copy of a part's page ids).
 LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void* q, long long q_stride,
                                       const void* kcache, const void* vcache, const int* block_tables,
                                       int max_blocks, const int* ctx_len, const int* cu_q, int n_seqs, int nq,
                                       int nkv, int hd, int page_size, int window, float scale, int parts,
-                                      int max_ctx, float* scratch, int* counters, void* stream) {
+                                      int max_ctx, float* scratch, int* counters, const void* packed,
+                                      long long packed_stride, int splits, long long split_stride, int nk, int rot,
+                                      const int* positions, const int* slots, const float* cos_tab,
+                                      const float* sin_tab, const float* q_gain, const float* k_gain, float eps,
+                                      float q_off, float k_off, void* stream) {
     if (n_seqs <= 0) return LLMK_OK;
     if (!llmk_attention_decode_usable(nq, nkv, hd, page_size))
         LLMK_FAIL("attention_decode: not taken (heads %d/%d, head_dim %d must be 64 or 128, page size %d must be a power of two)", nq, nkv, hd, page_size);
     if (parts < 1 || parts > 128 || (parts > 1 && (!scratch || !counters)))
         LLMK_FAIL("attention_decode: bad split (%d parts, scratch %p, counters %p)", parts, (void*)scratch, (void*)counters);
     if (n_seqs > 65535) LLMK_FAIL("attention_decode: %d sequences exceed the grid", n_seqs);
-    if (!host_aligned16(q) || !host_aligned16(kcache) || !host_aligned16(vcache) || q_stride % 8 != 0)
-        LLMK_FAIL("attention_decode: q and the cache must start on 16-byte boundaries");
+    if (!host_aligned16(kcache) || !host_aligned16(vcache))
+        LLMK_FAIL("attention_decode: the cache must start on a 16-byte boundary");
+    if (!packed && !q) LLMK_FAIL("attention_decode: neither q nor packed projection rows");
+    if (packed) {
+        if (splits < 0 || (splits > 0 && split_stride <= 0)) LLMK_FAIL("attention_decode: bad partial sums (%d slices)", splits);
+        if (nk != 0 && nk != nkv) LLMK_FAIL("attention_decode: packed rows hold %d k heads, the cache %d", nk, nkv);
+        if (!cos_tab) rot = 0;
+        if (rot % 64 != 0 || rot > hd) LLMK_FAIL("attention_decode: rotary width %d must be a multiple of 64, at most head_dim", rot);
+        if (cos_tab && (!sin_tab || !positions)) LLMK_FAIL("attention_decode: rotary tables need sin and positions");
+        if (nk > 0 && !slots) LLMK_FAIL("attention_decode: packed k and v need slots");
+    }
     DecodeParams p;
+    p.packed = packed; p.packed_stride = packed_stride; p.splits = splits; p.split_stride = split_stride;
+    p.nk = nk; p.rot = rot; p.positions = positions; p.slots = slots; p.cos_tab = cos_tab; p.sin_tab = sin_tab;
+    p.q_gain = q_gain; p.k_gain = k_gain; p.eps = eps; p.q_off = q_off; p.k_off = k_off;
     const int G = nq / nkv;
     const int gc = chunk_heads(G);
     p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;

@@ -348,25 +348,46 @@ def attention_decode_counters(n_seqs: int, nq: int, nkv: int) -> int:
     return int(lib.llmk_attention_decode_counters(c_int(n_seqs), c_int(nq), c_int(nkv)))
 
 
-def attention_decode(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+def attention_decode_fuses_prep(hd: int, rot: int) -> bool:
+    return bool(build.load("attention_decode").llmk_attention_decode_fuses_prep(c_int(hd), c_int(rot)))
+
+
+def attention_decode(out: torch.Tensor, q: Optional[torch.Tensor], q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                      block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
                      n_seqs: int, nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
-                     parts: int, max_ctx: int, scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor]) -> None:
+                     parts: int, max_ctx: int, scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor],
+                     packed=None, nk: int = 0, rot: int = 0, positions: Optional[torch.Tensor] = None,
+                     slots: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                     sin: Optional[torch.Tensor] = None, q_gain: Optional[torch.Tensor] = None,
+                     k_gain: Optional[torch.Tensor] = None, eps: float = 0.0, q_offset: float = 0.0,
+                     k_offset: float = 0.0) -> None:
     """out[t] = attention of the single token of each sequence over the paged cache, bfloat16
-    (csrc/attention_decode.cu).  `counters` (int32) must be zero before the first call."""
+    (csrc/attention_decode.cu).  `counters` (int32) must be zero before the first call.  With
+    `packed` (the q/k/v projection rows as an array or a `Partials`) the kernel also normalises and
+    rotates q and k and writes k and v to the cache, and `q` is not read."""
     lib = build.load("attention_decode")
-    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+    if kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or (q is not None and q.dtype != torch.bfloat16):
         raise KernelError("attention_decode: bfloat16 only")
     if parts > 1:
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < attention_decode_scratch_floats(n_seqs, nq, hd, parts):
             raise KernelError("attention_decode: scratch too small")
         if counters is None or counters.dtype != torch.int32 or counters.numel() < attention_decode_counters(n_seqs, nq, nkv):
             raise KernelError("attention_decode: counters too small")
+    splits, split_stride, packed_stride, src = 0, 0, 0, None
+    if isinstance(packed, Partials):
+        src, splits, split_stride, packed_stride = packed.tensor, packed.splits, packed.split_stride, packed.cols
+    elif packed is not None:
+        if packed.dtype != torch.bfloat16:
+            raise KernelError("attention_decode: packed rows must be bfloat16 or partial sums")
+        src, packed_stride = packed, _row_stride(packed)
     _check(lib, lib.llmk_attention_decode(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(q_stride),
                                           _ptr(kcache), _ptr(vcache), _ptr(block_tables), c_int(max_blocks),
                                           _ptr(ctx_len), _ptr(cu_q), c_int(n_seqs), c_int(nq), c_int(nkv), c_int(hd),
                                           c_int(page_size), c_int(window), c_float(scale), c_int(parts), c_int(max_ctx),
-                                          _ptr(scratch), _ptr(counters), _stream()))
+                                          _ptr(scratch), _ptr(counters), _ptr(src), c_longlong(packed_stride),
+                                          c_int(splits), c_longlong(split_stride), c_int(nk), c_int(rot),
+                                          _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(q_gain), _ptr(k_gain),
+                                          c_float(eps), c_float(q_offset), c_float(k_offset), _stream()))
 
 
 def attention_tc_tile_queries(nq: int, nkv: int, hd: int, page_size: int) -> int:

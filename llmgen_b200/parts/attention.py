@@ -138,14 +138,22 @@ class GQAAttention(Mixer):
                                self.w_qkv if cache.writes else self.w_q, self.dtype)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rot = self.position.rotary_dim if self.position is not None else 0
+        o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
+        scale = float(self.spec.scale)
+        decode = (self.dtype == torch.bfloat16 and ctx.pure_decode and _FORCE_ATTN != "simt"
+                  and ops.attention_decode_usable(self.nq, self.nkv, self.hd, cache.page_size))
+        if decode and ops.attention_decode_fuses_prep(self.hd, rot):
+            # single decoded tokens: the attention kernel normalises, rotates and stores q, k and v itself
+            self._decode(ctx, o, None, cache, group, scale,
+                         prep=dict(packed=packed, nk=nk, rot=rot, positions=ctx.positions, slots=group.slots, cos=cos,
+                                   sin=sin, q_gain=self.q_gain, k_gain=self.k_gain, eps=self.norm_eps,
+                                   q_offset=self.q_off, k_offset=self.k_off))
+            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         q = ws.buffer("attn_q", T, self.nq * self.hd, self.dtype) if isinstance(packed, ops.Partials) else packed
         ops.attn_prep(packed, cache.k, cache.v, ctx.positions, group.slots, cos, sin, self.q_gain, self.k_gain,
                       self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q)
         packed = q
-        o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
-        scale = float(self.spec.scale)
-        if (self.dtype == torch.bfloat16 and ctx.pure_decode and _FORCE_ATTN != "simt"
-                and ops.attention_decode_usable(self.nq, self.nkv, self.hd, cache.page_size)):
+        if decode:
             self._decode(ctx, o, packed, cache, group, scale)
             return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         tc_bq = 0 if ctx.pure_decode else self.tc_tile_queries(cache.page_size)
@@ -168,7 +176,7 @@ class GQAAttention(Mixer):
         return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
 
 
-    def _decode(self, ctx, o, q, cache, group, scale) -> None:
+    def _decode(self, ctx, o, q, cache, group, scale, prep=None) -> None:
         """Single decoded tokens: as many key parts as fill the SMs, at least 128 keys a part;
         under graph capture the bound of the step's context class decides, not the lengths."""
         ws = ctx.workspace
@@ -186,9 +194,9 @@ class GQAAttention(Mixer):
                               torch.float32)
             counters = ws.flat("attn_decode_counters", ops.attention_decode_counters(max(ctx.max_seqs_bound, S), self.nq, self.nkv),
                                torch.int32, zero=True)
-        ops.attention_decode(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len,
-                             ctx.cu_q, S, self.nq, self.nkv, self.hd, cache.page_size, self.window, scale, parts,
-                             bound, scratch, counters)
+        ops.attention_decode(o, q, q.stride(0) if q is not None else 0, cache.k, cache.v, group.block_tables,
+                             group.max_blocks, ctx.ctx_len, ctx.cu_q, S, self.nq, self.nkv, self.hd, cache.page_size,
+                             self.window, scale, parts, bound, scratch, counters, **(prep or {}))
 
 
 register_mixer("attention", GQAAttention)

@@ -672,6 +672,53 @@ def test_attention_decode(ops, nq, nkv, hd, page, parts):
         assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,rot", [(4, 2, 128, 16, 128), (16, 8, 128, 16, 128), (6, 2, 64, 16, 64), (20, 2, 64, 32, 64),
+                                                (4, 2, 128, 16, 64), (2, 1, 64, 8, 0)])
+@pytest.mark.parametrize("parts", [1, 5])
+@pytest.mark.parametrize("sliced", [False, True])
+def test_attention_decode_makes_q_k_v_itself(ops, nq, nkv, hd, page, rot, parts, sliced):
+    """Given the packed projection rows, the kernel equals attn_prep followed by itself: same outputs,
+    same cache contents (the newest key and value of every sequence land in their slots)."""
+    dtype = torch.bfloat16
+    seqs = [(150, 1), (1, 1), (0, 1), (333, 1), (64, 1), (65, 1), (17, 1)]
+    S = len(seqs)
+    _, kc, vc, bt, ctxs, cu, _, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 35)
+    g = torch.Generator().manual_seed(36)
+    width = (nq + 2 * nkv) * hd
+    slices = torch.randn(3, S, width, generator=g) * 0.6
+    whole = slices.sum(0).to(dtype)
+    positions = torch.tensor([max(c - 1, 0) for c, _ in seqs], dtype=torch.int32)
+    slots = torch.tensor([int(bt[s, (c - 1) // page]) * page + (c - 1) % page if c > 0 else -1 for s, (c, _) in enumerate(seqs)],
+                         dtype=torch.int32)
+    qg, kg = (1 + 0.2 * torch.randn(hd, generator=g)), (1 + 0.2 * torch.randn(hd, generator=g))
+    cos = sin = None
+    if rot:
+        c64, s64 = plain.rope_tables(400, rot, 10000.0)
+        cos, sin = dev(c64.float()), dev(s64.float())
+    scale = 1.0 / math.sqrt(hd)
+    args = dict(positions=dev(positions), slots=dev(slots), cos=cos, sin=sin, q_gain=dev(qg), k_gain=dev(kg), eps=1e-6)
+    # the two kernels one after the other
+    k1, v1 = dev(kc), dev(vc)
+    q1 = torch.empty(S, nq * hd, dtype=dtype, device="cuda")
+    ops.attn_prep(dev(whole), k1, v1, args["positions"], args["slots"], cos, sin, args["q_gain"], args["k_gain"],
+                  nq, nkv, hd, rot, page, 1e-6, q_out=q1)
+    out1 = torch.full((S, nq * hd), 9.0, dtype=dtype, device="cuda")
+    scratch = torch.empty(max(1, ops.attention_decode_scratch_floats(S, nq, hd, parts)), dtype=torch.float32, device="cuda")
+    counters = torch.zeros(ops.attention_decode_counters(S, nq, nkv), dtype=torch.int32, device="cuda")
+    common = (dev(bt), mb, dev(ctxs), dev(cu), S, nq, nkv, hd, page, 0, scale, parts, int(max(ctxs)), scratch, counters)
+    ops.attention_decode(out1, q1, nq * hd, k1, v1, *common)
+    # the one kernel
+    k2, v2 = dev(kc), dev(vc)
+    out2 = torch.full((S, nq * hd), 9.0, dtype=dtype, device="cuda")
+    packed = ops.Partials(dev(slices)) if sliced else dev(whole)
+    ops.attention_decode(out2, None, 0, k2, v2, *common, packed=packed, nk=nkv, rot=rot, **args)
+    torch.cuda.synchronize()
+    assert float((out1.float() - out2.float()).abs().max()) < tol(dtype, 2)
+    assert float((k1.float() - k2.float()).abs().max()) < tol(dtype, 2 if sliced else 0.5)
+    assert float((v1.float() - v2.float()).abs().max()) < tol(dtype, 2 if sliced else 0.01)
+    assert float(out2[2].abs().max()) == 0.0 and int(counters.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("where", [lambda c: 0, lambda c: 15, lambda c: 16, lambda c: c - 1, lambda c: 255, lambda c: 256,
                                    lambda c: c // 2])
 @pytest.mark.parametrize("parts", [1, 3, 8])
