@@ -3,12 +3,13 @@
 // one thread issues `tcgen05.mma` with the float32 accumulator in tensor memory, and four
 // epilogue warps read it back with `tcgen05.ld`, round once and store.
 //
-// Block = one 128 x BN output tile (BN = 64, 128 or 256), 192 threads:
+// A block computes 128 x BN output tiles (BN = 64, 128 or 256) one after the other, 192 threads:
 //   warp 0     TMA producer: for every 64-wide slice of K, one A box [128, 64] and one W box
 //              [BN, 64] into a ring of STAGES buffers; `full[s]` counts the bytes.
-//   warp 1     owns the tensor memory (allocates BN columns) and issues the MMAs: 4 instructions of
-//              K = 16 per slice; `tcgen05.commit` releases the buffer (`empty[s]`) when they have read
-//              it, and signals `acc_full` after the last slice.
+//   warp 1     owns the tensor memory (two accumulators of BN columns) and issues the MMAs: 4
+//              instructions of K = 16 per slice; `tcgen05.commit` releases the buffer (`empty[s]`) when
+//              they have read it, and signals `acc_full[i]` after a tile's last slice; the next tile
+//              goes to the other accumulator once the epilogue has released it (`acc_empty[i]`).
 //   warps 2-5  epilogue: each reads the 32 accumulator lanes its warp id allows, 32 columns at a
 //              time, and writes 64 (bfloat16) or 128 (float32) contiguous bytes per row.
 // Rows of A beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA, so any M and
@@ -36,35 +37,49 @@ constexpr int BM = 128;
 constexpr int BK = 64;           // one 128-byte swizzle row of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
+constexpr int NUM_SMS = 148;
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MB>
 struct Smem {
-    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int A_BYTES = BM * BK * 2;        // one block of 128 rows of A
     static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = MB * A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+    static constexpr int NUM_BARS = 2 * STAGES + 4;     // full, empty, acc_full[2], acc_empty[2]
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
 
-template <typename TC, int BN, int STAGES, bool GATED>
+// Persistent: block b computes tiles b, b + gridDim.x, ... (tile t = (t % m_tiles) rows, (t / m_tiles)
+// columns, so blocks that run together share W tiles).  A tile is MB blocks of 128 rows by BN
+// columns: with MB = 2 the two MMAs of a k-step share the W tile, which halves what the block pulls
+// from L2 per flop (the wide products are bound by that, not by the tensor core).  When two
+// accumulator sets fit into tensor memory (2 * MB * BN <= 512 columns) they are used in turn: while
+// the epilogue warps read tile i out of one, the MMA warp fills the other with tile i + 1; the TMA
+// ring runs on across tiles either way.
+template <typename TC, int BN, int STAGES, bool GATED, int MB>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag) {
-    using L = Smem<BN, STAGES>;
+    using L = Smem<BN, STAGES, MB>;
+    constexpr int ACC_SETS = 2 * MB * BN <= 512 ? 2 : 1;
+    constexpr uint32_t TMEM_COLS = ACC_SETS * MB * BN;             // 128, 256 or 512: a power of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
-    uint64_t* acc_full = bars + 2 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    uint64_t* acc_full = bars + 2 * STAGES;         // 2
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;    // 2, four arrivals each (one per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int num_kb = (K + BK - 1) / BK;
+    const int m_tiles = (M + MB * BM - 1) / (MB * BM);
+    const int n_tiles = (N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -72,13 +87,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc::mbar_init(tc::smem_u32(&full[s]), 1);
             tc::mbar_init(tc::smem_u32(&empty[s]), 1);
         }
-        tc::mbar_init(tc::smem_u32(acc_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(tc::smem_u32(&acc_full[i]), 1);
+            tc::mbar_init(tc::smem_u32(&acc_empty[i]), 4);
+        }
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_a);
         tc::prefetch_tensormap(&map_w);
     }
     if (warp == 1) {
-        tc::tmem_alloc(tc::smem_u32(tmem_slot), BN);
+        tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
         tc::tmem_relinquish();
     }
     tc::tc_fence_before_sync();
@@ -88,26 +106,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            pdl_wait();   // A was written by the kernel before this one
-            int issued = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                if (!tc::mbar_wait(tc::smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) break;
-                const uint32_t bar = tc::smem_u32(&full[s]);
-                tc::mbar_expect_tx(bar, L::STAGE_BYTES);
-                const uint32_t a_dst = tc::smem_u32(smem + s * L::STAGE_BYTES);
-                tc::tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
-                tc::tma_load_2d(a_dst + L::A_BYTES, &map_w, bar, kb * BK, n0);
-                issued = kb + 1;
-            }
             pdl_launch_dependents();
+            pdl_wait();   // A was written by the kernel before this one
+            uint32_t it = 0;        // k-slices loaded so far, over all tiles of this block
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * (MB * BM), n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (!tc::mbar_wait(tc::smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t bar = tc::smem_u32(&full[s]);
+                    tc::mbar_expect_tx(bar, L::STAGE_BYTES);
+                    const uint32_t a_dst = tc::smem_u32(smem + s * L::STAGE_BYTES);
+#pragma unroll
+                    for (int i = 0; i < MB; ++i) tc::tma_load_2d(a_dst + i * L::A_BYTES, &map_a, bar, kb * BK, m0 + i * BM);
+                    tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, kb * BK, n0);
+                }
+            }
             if (*abort_flag) {
                 // Let the copies that are in flight land before the block's memory is given up.
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-                    const unsigned long long t0 = tc::global_timer();
-                    while (!tc::mbar_try_wait(tc::smem_u32(&full[kb % STAGES]), (kb / STAGES) & 1) &&
-                           tc::global_timer() - t0 < tc::WAIT_LIMIT_NS) {
+                for (uint32_t k = it > (uint32_t)STAGES ? it - STAGES : 0; k < it; ++k) {
+                    const long long t0 = clock64();
+                    while (!tc::mbar_try_wait(tc::smem_u32(&full[k % STAGES]), (k / STAGES) & 1) &&
+                           clock64() - t0 < tc::WAIT_LIMIT_CYCLES) {
                     }
                 }
             }
@@ -115,40 +137,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, BN);
+            uint32_t it = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                ok = tc::mbar_wait(tc::smem_u32(&full[s]), round & 1, abort_flag);
+            int tile_iter = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+                const int buf = tile_iter % ACC_SETS;
+                // the epilogue must have read this accumulator set before it is filled again
+                ok = tc::mbar_wait(tc::smem_u32(&acc_empty[buf]), ((tile_iter / ACC_SETS) & 1) ^ 1, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after_sync();
-                const uint32_t a_addr = tc::smem_u32(smem + s * L::STAGE_BYTES);
-                const uint32_t b_addr = a_addr + L::A_BYTES;
+                const uint32_t acc = tmem_base + (uint32_t)(buf * MB * BN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    ok = tc::mbar_wait(tc::smem_u32(&full[s]), round & 1, abort_flag);
+                    if (!ok) break;
+                    tc::tc_fence_after_sync();
+                    const uint32_t a_addr = tc::smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + MB * L::A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    const uint64_t da = tc::smem_desc_sw128(a_addr + k * UMMA_K * 2);
-                    const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
-                    tc::mma_bf16_ss(tmem_base, da, db, idesc, (kb | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
+#pragma unroll
+                        for (int i = 0; i < MB; ++i)
+                            tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
+                                            db, idesc, (kb | k) != 0);
+                    }
+                    tc::mma_commit(tc::smem_u32(&empty[s]));
                 }
-                tc::mma_commit(tc::smem_u32(&empty[s]));
+                if (ok) tc::mma_commit(tc::smem_u32(&acc_full[buf]));
             }
-            if (ok) tc::mma_commit(tc::smem_u32(acc_full));
         }
     } else {
         // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(acc_full), 0, abort_flag));
-        tc::tc_fence_after_sync();
-        if (ok) {
-            const int n_out = GATED ? N / 2 : N;
-            const bool vec_ok = (ldc % (16 / (int)sizeof(TC)) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        const int n_out = GATED ? N / 2 : N;
+        const bool vec_ok = (ldc % (16 / (int)sizeof(TC)) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        bool ok = true;
+        int tile_iter = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+            const int buf = tile_iter % ACC_SETS;
+            const int m0 = (tile % m_tiles) * (MB * BM), n0 = (tile / m_tiles) * BN;
+            ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&acc_full[buf]), (tile_iter / ACC_SETS) & 1, abort_flag));
+            if (!ok) break;
+            tc::tc_fence_after_sync();
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= N) break;   // uniform over the warp
+            for (int cc = 0; cc < MB * BN; cc += 32) {
+                const int mb = cc / BN, c0 = cc % BN;          // which block of rows, which columns of it
+                const int row = m0 + mb * BM + quarter * 32 + lane;
+                const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * MB * BN + mb * BN);
+                if (n0 + c0 >= N || m0 + mb * BM >= M) continue;   // uniform over the warp
                 uint32_t r[32];
                 __syncwarp();
-                tc::tmem_ld_32x32_wait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                tc::tmem_ld_32x32_wait(acc + (uint32_t)c0, r);
                 if (row >= M) {
                     // nothing to store for this lane; it still takes part in the loads above
                 } else if constexpr (GATED) {
@@ -200,13 +241,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
+            // this warp has read its lanes of the half: let the MMA warp fill it again
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&acc_empty[buf]));
         }
     }
     tc::tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         tc::tc_fence_after_sync();
-        tc::tmem_dealloc(tmem_base, BN);
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag && error_flag) atomicExch(error_flag, 1);
 }
@@ -246,51 +291,50 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
     return true;
 }
 
-template <typename TC, int BN, int STAGES, bool GATED>
+template <typename TC, int BN, int STAGES, bool GATED, int MB>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, long long ldc,
            int* error_flag, int pdl, cudaStream_t s) {
-    using L = Smem<BN, STAGES>;
-    auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED>;
+    using L = Smem<BN, STAGES, MB>;
+    auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB>;
     static bool configured = false;   // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) LLMK_FAIL("gemm_tc: cannot raise shared memory to %d: %s", L::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(N, BN), ceil_div(M, BM));
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = L::TOTAL;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mw, (TC*)C, M, N, K, ldc, error_flag);
-    if (e != cudaSuccess) {
-        snprintf(g_llmk_error, sizeof(g_llmk_error), "gemm_tc: launch failed: %s", cudaGetErrorString(e));
-        return LLMK_CUDA_ERROR;
-    }
+    const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM);
+    LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
+                                                pdl != 0, ma, mw, (TC*)C, M, N, K, ldc, error_flag));
     return LLMK_OK;
 }
 
 template <typename TC, bool GATED>
 int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
                   long long ldc, int* error_flag, int pdl, cudaStream_t s) {
-    // Tile width: 256 fills the tensor core best, narrower tiles give more blocks when the grid
-    // would leave SMs idle.
-    const int mt = ceil_div(M, BM);
-    int bn = 256;
-    if (GATED || mt * ceil_div(N, 256) < 148) bn = 128;
-    if (!GATED && mt * ceil_div(N, 128) < 148 && N <= 64 * 148) bn = 64;
+    // Tile width: the one whose tiles take the least time in rounds over the SMs.  The relative times
+    // of a tile were measured on the products of a 2,048-token prompt.  (Tiles of two row blocks,
+    // MB = 2, were measured too: 256 x 256 is no faster than 128 x 256 with its epilogue overlapped,
+    // so they are not used.)
+    struct Shape { int bn; long long time; };
+    const Shape shapes[] = {{256, 528}, {128, 348}, {64, 264}};
+    int bn = GATED ? 128 : 64;
+    long long best = -1;
+    for (const Shape& sh : shapes) {
+        if (GATED && sh.bn == 64) continue;          // the gated epilogue is built for the wider tiles only
+        const long long tiles = (long long)ceil_div(M, BM) * ceil_div(N, sh.bn);
+        const long long cost = ((tiles + NUM_SMS - 1) / NUM_SMS) * sh.time;
+        if (best < 0 || cost < best) {
+            best = cost;
+            bn = sh.bn;
+        }
+    }
     CUtensorMap ma, mw;
     if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, N, K, ldw, bn))
         LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
     switch (bn) {
-        case 256: return launch<TC, 256, 4, GATED>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
-        case 128: return launch<TC, 128, 3, GATED>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
-        default: return launch<TC, 64, 4, false>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
+        case 256: return launch<TC, 256, 4, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
+        case 128: return launch<TC, 128, 4, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
+        default: return launch<TC, 64, 4, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
     }
 }
 

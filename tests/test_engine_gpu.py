@@ -155,3 +155,31 @@ def test_command_line_chat_and_bench(tmp):
     summary = json.load(open(out_json))
     assert summary["n_requests"] == 3 and summary["output_tokens"] == 24 and summary["throughput_out"] > 0
     assert summary["policy"] == "chunked" and summary["kv_leak"] is False
+
+
+def test_layer_sizes_of_the_larger_models(tmp):
+    """One layer with the head geometry of the larger Qwen3 models (32 query heads on 8 kv heads of
+    128, q width twice the hidden size) and a vocabulary that is no multiple of 128: bfloat16 logits
+    of a prompt and of decoded tokens against the plain implementation, and graph replay against
+    eager steps."""
+    from llmgen_b200 import LLM, SamplingParams
+    from llmgen_b200.engine.api import write_random_model
+    from tests.util import Driver, logits_close
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 1500, "hidden_size": 2048,
+           "intermediate_size": 6144, "num_hidden_layers": 1, "num_attention_heads": 32, "num_key_value_heads": 8,
+           "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 1024,
+           "tie_word_embeddings": False, "hidden_act": "silu"}
+    path = os.path.join(tmp, "wide")
+    write_random_model(path, cfg, 11, 0.02, 0.1, "bfloat16")
+    ids = random_ids(300, 1500, 5)
+    ref = PlainQwen3(path).logits(ids)
+    d = Driver(path, "bfloat16", 512, 16)
+    got = d.step([("a", ids[:280], range(280))])
+    logits_close(got, ref[:280], "bfloat16")
+    for i in range(280, 300):
+        logits_close(d.step([("a", ids[i:i + 1], [0])]), ref[i:i + 1], "bfloat16")
+    outs = {}
+    for eager in (False, True):
+        llm = LLM(path, dtype="bfloat16", max_model_len=512, max_num_seqs=4, max_batched_tokens=2048, kv_blocks=128, eager=eager)
+        outs[eager] = [r["token_ids"] for r in llm.generate([ids[:200], ids[:37]], SamplingParams(0.0, 12, True))]
+    assert outs[False] == outs[True]
