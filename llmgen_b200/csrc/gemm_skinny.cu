@@ -35,7 +35,7 @@ constexpr int BK = 64;           // one 128-byte swizzle row of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
-enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2 };
+enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2, OUT_CLUSTER = 3 };
 
 template <int MPAD, int STAGES>
 struct Smem {
@@ -166,7 +166,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int i = 0; i < 16; ++i) {
                     const int m = c0 + i;
                     const float v = __uint_as_float(r[i]);
-                    if constexpr (MODE == OUT_GATED) {
+                    if constexpr (MODE == OUT_CLUSTER) {
+                        // this block's slice of the sum, for the cluster to add up: [row of X][row of W]
+                        if (m < M) reinterpret_cast<float*>(smem)[m * BW + quarter * 32 + lane] = v;
+                    } else if constexpr (MODE == OUT_GATED) {
                         // lanes 0..15 hold 16 gate rows, lanes 16..31 the matching up rows
                         const float u = __shfl_down_sync(0xffffffffu, v, 16);
                         if (m < M && lane < 16 && n < N)
@@ -187,6 +190,25 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc::tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag && error_flag) atomicExch(error_flag, 1);
+    if constexpr (MODE == OUT_CLUSTER) {
+        // The blocks of a cluster hold the slices of K of one tile.  Each left its float32 slice in its
+        // own shared memory (over the TMA ring, which is idle by now); block r now adds up, in slice
+        // order, rows [r, r + 1) * 128 / S of W for every row of X, reading the other blocks' shared
+        // memory, and writes the finished values.  Nobody leaves before all have read.
+        cluster_sync_all();
+        const uint32_t S = gridDim.y, rank = cluster_ctarank();
+        const int rows_per = BW / (int)S;
+        const uint32_t red = tc::smem_u32(smem);
+        for (int idx = threadIdx.x; idx < rows_per * M; idx += THREADS) {
+            const int m = idx / rows_per, rr = (int)rank * rows_per + idx % rows_per;
+            const uint32_t local = red + (uint32_t)(m * BW + rr) * 4u;
+            float acc = 0.f;
+            for (uint32_t q = 0; q < S; ++q) acc += cluster_ld_f32(cluster_map_shared(local, q));
+            const int n = n0 + rr;
+            if (n < N) C[(size_t)m * ldc + n] = from_float<TC>(acc);
+        }
+        cluster_sync_all();
+    }
 }
 
 template <typename TC, int MPAD, int STAGES, int MODE>
@@ -200,8 +222,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, 
         if (e != cudaSuccess) LLMK_FAIL("gemm_skinny: cannot raise shared memory to %d: %s", L::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), L::TOTAL, s,
-                                                    true, mw, mx, (TC*)C, M, N, K, ldc, kb_per_split, error_flag));
+    if constexpr (MODE == OUT_CLUSTER) {
+        static bool wide_ok = false;
+        if (splits > 8 && !wide_ok) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) LLMK_FAIL("gemm_skinny: clusters of %d blocks are not allowed: %s", splits, cudaGetErrorString(e));
+            wide_ok = true;
+        }
+        LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch_cluster(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), L::TOTAL, s,
+                                                                true, (unsigned)splits, mw, mx, (TC*)C, M, N, K, ldc,
+                                                                kb_per_split, error_flag));
+    } else {
+        LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), L::TOTAL, s,
+                                                        true, mw, mx, (TC*)C, M, N, K, ldc, kb_per_split, error_flag));
+    }
     return LLMK_OK;
 }
 
@@ -216,8 +250,13 @@ int dispatch_rows(const CUtensorMap& mw, const void* X, void* C, int M, int N, i
         case 16: return launch<TC, 16, 6, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
         case 32: return launch<TC, 32, 5, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
         case 64: return launch<TC, 64, 4, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
-        case 128: return launch<TC, 128, 6, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
-        default: return launch<TC, 256, 4, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
+        default: break;
+    }
+    if constexpr (MODE == OUT_CLUSTER) {
+        LLMK_FAIL("gemm_skinny: the sum over a cluster takes at most 64 rows, not %d", M);
+    } else {
+        if (mpad == 128) return launch<TC, 128, 6, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
+        return launch<TC, 256, 4, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
     }
 }
 
@@ -239,8 +278,21 @@ LLMK_EXPORT int llmk_gemm_skinny_splits(int M, int N, int K) {
     return ceil_div(num_kb, per);
 }
 
+// Into how many slices of K a product whose slices are added up inside a thread-block cluster is
+// cut: a power of two up to 16 (it is the cluster's size), about 200 blocks in all, at least two
+// 64-wide slices of K per block.  1: use the plain product.
+LLMK_EXPORT int llmk_gemm_skinny_cluster_splits(int M, int N, int K) {
+    if (M <= 0 || M > 64 || N <= 0 || K <= 0) return 1;
+    const int tiles = ceil_div(N, BW);
+    const int num_kb = ceil_div(K, BK);
+    int splits = 1;
+    while (splits * 2 <= 16 && tiles * splits * 2 <= 200 && num_kb / (splits * 2) >= 2 && num_kb % (splits * 2) == 0) splits *= 2;
+    return splits;
+}
+
 // mode 0: C[M, N] (out_dtype), splits must be 1.  mode 1: C is float32 [splits, M, ldc] partial sums.
 // mode 2: gated, W interleaves gate and up rows in groups of 16, C is [M, N / 2] (out_dtype), splits 1.
+// mode 3: C[M, N] (out_dtype) from `splits` slices of K (2, 4, 8 or 16) added up inside a cluster, M <= 64.
 LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, int N, int K, long long ldx,
                                  long long ldw, long long ldc, int splits, int mode, int out_dtype, int* error_flag,
                                  void* stream) {
@@ -252,7 +304,10 @@ LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, i
     if (splits < 1 || splits > num_kb || splits > 65535) LLMK_FAIL("gemm_skinny: %d slices for K=%d", splits, K);
     const int per = ceil_div(num_kb, splits);
     if ((splits - 1) * per >= num_kb) LLMK_FAIL("gemm_skinny: %d slices of K=%d would leave one empty", splits, K);
-    if (mode != OUT_PARTIAL && splits != 1) LLMK_FAIL("gemm_skinny: a product written directly cannot be sliced (%d)", splits);
+    if (mode != OUT_PARTIAL && mode != OUT_CLUSTER && splits != 1)
+        LLMK_FAIL("gemm_skinny: a product written directly cannot be sliced (%d)", splits);
+    if (mode == OUT_CLUSTER && (splits < 2 || splits > 16 || (splits & (splits - 1)) != 0 || M > 64))
+        LLMK_FAIL("gemm_skinny: a cluster adds up 2, 4, 8 or 16 slices of at most 64 rows (%d slices, %d rows)", splits, M);
     if (mode == OUT_GATED && N % 32 != 0) LLMK_FAIL("gemm_skinny: gated epilogue needs N=%d to be a multiple of 32", N);
     if (ldc < (mode == OUT_GATED ? N / 2 : N)) LLMK_FAIL("gemm_skinny: ldc=%lld too small", ldc);
     CUtensorMap mw;
@@ -263,6 +318,11 @@ LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, i
     if (mode == OUT_GATED) {
         if (out_dtype != LLMK_BF16) LLMK_FAIL("gemm_skinny: the gated epilogue writes bfloat16");
         return dispatch_rows<bf16, OUT_GATED>(mw, X, C, M, N, K, ldx, ldc, 1, per, error_flag, s);
+    }
+    if (mode == OUT_CLUSTER) {
+        if (out_dtype == LLMK_BF16) return dispatch_rows<bf16, OUT_CLUSTER>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s);
+        if (out_dtype == LLMK_F32) return dispatch_rows<float, OUT_CLUSTER>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s);
+        LLMK_FAIL("gemm_skinny: unknown output dtype %d", out_dtype);
     }
     if (mode != OUT_DIRECT) LLMK_FAIL("gemm_skinny: unknown mode %d", mode);
     if (out_dtype == LLMK_BF16) return dispatch_rows<bf16, OUT_DIRECT>(mw, X, C, M, N, K, ldx, ldc, 1, per, error_flag, s);

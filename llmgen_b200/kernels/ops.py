@@ -261,7 +261,9 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
 
 
 SKINNY_MAX_ROWS = 256
-SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED = 0, 1, 2
+SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED, SKINNY_CLUSTER = 0, 1, 2, 3
+SKINNY_CLUSTER_MAX_ROWS = 64
+_cluster_plans = {}
 _skinny_plans = {}
 
 
@@ -275,10 +277,22 @@ def gemm_skinny_splits(M: int, N: int, K: int) -> int:
     return v
 
 
-def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int = SKINNY_DIRECT) -> None:
+def gemm_skinny_cluster_splits(M: int, N: int, K: int) -> int:
+    """Into how many slices of K the product is cut when a thread-block cluster adds them up
+    (1: it is not cut)."""
+    key = (M, N, K)
+    v = _cluster_plans.get(key)
+    if v is None:
+        v = int(build.load("gemm_skinny").llmk_gemm_skinny_cluster_splits(c_int(M), c_int(N), c_int(K)))
+        _cluster_plans[key] = v
+    return v
+
+
+def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int = SKINNY_DIRECT, splits: int = 1) -> None:
     """The weight-streaming tensor-core product for M <= 256 rows (csrc/gemm_skinny.cu).
     SKINNY_DIRECT: out[M, N]; SKINNY_GATED: out[M, N/2] = silu(gate) * up; SKINNY_PARTIAL: out is
-    float32 [splits, M, N] and receives the partial sums of `splits` slices of K."""
+    float32 [splits, M, N] and receives the partial sums of `splits` slices of K; SKINNY_CLUSTER:
+    out[M, N] from `splits` slices of K added up inside a thread-block cluster (M <= 64)."""
     lib = build.load("gemm_skinny")
     M, K = a.shape
     N = w.shape[0]
@@ -292,7 +306,7 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int =
         n_out = N // 2 if mode == SKINNY_GATED else N
         if out.shape[0] != M or out.shape[1] != n_out:
             raise KernelError(f"gemm_skinny: out{list(out.shape)} does not fit [{M}, {n_out}]")
-        splits, ldc = 1, _row_stride(out)
+        splits, ldc = (splits if mode == SKINNY_CLUSTER else 1), _row_stride(out)
     _check(lib, lib.llmk_gemm_skinny(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
                                      c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(ldc),
                                      c_int(splits), c_int(mode), c_int(dtype_code(out.dtype)),

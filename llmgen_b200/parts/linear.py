@@ -2,8 +2,9 @@
 
     float32 engine   CUDA-core kernel with a fixed summation order (csrc/gemm_simt.cu)
     bfloat16 engine  up to 256 rows: the weight-streaming tensor-core kernel with swapped operands
-                     (csrc/gemm_skinny.cu), cut along K so that every SM streams a share of W; a
-                     cut product comes back as `ops.Partials`, which the consuming kernel adds up;
+                     (csrc/gemm_skinny.cu), cut along K so that every SM streams a share of W; the
+                     float32 slices come back as an `ops.Partials`, which the consuming kernel adds
+                     up (LLMGEN_SPLITK=cluster adds them up inside a thread-block cluster instead);
                      more rows: the tiled tensor-core kernel (csrc/gemm_tc.cu: TMA, tcgen05.mma,
                      tensor memory); operands TMA refuses (rows not on 16-byte boundaries): the
                      CUDA-core weight-streaming kernel for up to 4 rows (csrc/gemv.cu), else the
@@ -25,6 +26,7 @@ import torch
 from ..kernels import ops
 
 _FORCE = os.environ.get("LLMGEN_GEMM", "")
+_SPLITK = os.environ.get("LLMGEN_SPLITK", "")      # "cluster": add the slices of K up inside a thread-block cluster
 
 GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny")
 
@@ -53,6 +55,15 @@ def linear_sliced(ws, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: to
     kernel cuts the product along K, an `ops.Partials` for a consumer that adds the slices."""
     M, N = x.shape[0], w.shape[0]
     if M > 0 and x.dtype == torch.bfloat16 and _FORCE == "" and ops.gemm_skinny_usable(x, w):
+        if M <= ops.SKINNY_CLUSTER_MAX_ROWS and _SPLITK == "cluster":
+            # the slices are added up inside a thread-block cluster: one float32 array comes back.
+            # Measured at the benchmark's sizes this costs 1-1.7 us more per product than writing the
+            # slices, and saves 1.2 us in the kernel that adds them: not the default.
+            splits = ops.gemm_skinny_cluster_splits(M, N, x.shape[1])
+            if splits > 1:
+                total = ws.flat(name + "_sum", M * N, torch.float32).view(1, M, N)
+                ops.gemm_skinny(total[0], x, w, ops.SKINNY_CLUSTER, splits=splits)
+                return ops.Partials(total)
         splits = ops.gemm_skinny_splits(M, N, x.shape[1])
         if splits > 1:
             part = ws.flat(name + "_slices", splits * M * N, torch.float32).view(splits, M, N)

@@ -337,6 +337,30 @@ def test_gemm_skinny_partial_sums(ops, M, N, K, splits):
         ops.gemm_skinny(torch.empty(kb + 1, M, N, dtype=torch.float32, device="cuda"), dev(a), dev(w), ops.SKINNY_PARTIAL)
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(8, 1024, 2048, 16), (1, 136, 256, 2), (33, 1024, 3072, 8), (8, 4096, 1024, 4),
+                                          (64, 200, 1024, 16), (5, 6144, 1024, 4)])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemm_skinny_summed_in_a_cluster(ops, M, N, K, splits, out_dtype):
+    """Cut along K with the slices added up through the distributed shared memory of a cluster."""
+    torch.manual_seed(165 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    out = torch.full((M, N), 7.0, dtype=out_dtype, device="cuda")
+    for _ in range(2):
+        ops.gemm_skinny(out, dev(a), dev(w), ops.SKINNY_CLUSTER, splits=splits)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    ref = a.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    assert float((out.double().cpu() - ref).abs().max()) < (2e-5 if out_dtype == torch.float32 else 6e-3) * scale
+    planned = ops.gemm_skinny_cluster_splits(M, N, K)
+    assert planned in (1, 2, 4, 8, 16) and ((K + 63) // 64) % planned == 0
+    with pytest.raises(ops.KernelError, match="cluster adds up|empty"):
+        ops.gemm_skinny(out, dev(a), dev(w), ops.SKINNY_CLUSTER, splits=3)
+
+
 @pytest.mark.parametrize("M,F,K", [(3, 48, 64), (8, 3072, 1024), (130, 176, 80)])
 def test_gemm_skinny_gated(ops, M, F, K):
     from llmgen_b200.parts.mlp import interleave_gate_up
