@@ -38,8 +38,6 @@ namespace {
 
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
-constexpr int KPW = 8;        // keys a warp takes per step
-constexpr int STAGES = 3;     // depth of each warp's cp.async ring
 
 struct DecodeParams {
     const bf16* q;
@@ -126,8 +124,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int HD, int GC>
+template <int HD, int GC, int KPW>
 struct DecodeSmem {
+    static constexpr int STAGES = 3;
     static constexpr int ROW = HD * 2;                        // bytes of one key's K or V row
     static constexpr int STAGE = 2 * KPW * ROW;               // one warp's stage: KPW rows of K, then of V
     static constexpr int KV_OFF = 0;                          // [WARPS][STAGES][STAGE]
@@ -137,9 +136,35 @@ struct DecodeSmem {
     static size_t bytes(int page_cap) { return (size_t)PAGES_OFF + (size_t)page_cap * 4; }
 };
 
-template <int HD, int GC>
+// Tensor-core helpers of the MMA variant (warp-level `mma.sync`, enough for a kernel bound by memory).
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr) : "memory");
+}
+// d (16 x 8, float32) += a (16 x 16, bfloat16, row-major) * b (16 x 8, bfloat16, column-major)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// MMA = false: float32 arithmetic on the CUDA cores, 8 keys a warp per step.  MMA = true: the two
+// products of a step of 16 keys run on the tensor cores (`mma.sync.m16n8k16`, the chunk's heads are
+// the rows of a 16-row tile), which cuts the instructions per key about eightfold; with many heads per
+// kv head the CUDA-core variant is bound by its arithmetic, not by memory.
+template <int HD, int GC, bool MMA>
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeParams p) {
-    using L = DecodeSmem<HD, GC>;
+    constexpr int KPW = MMA ? 16 : 8;   // keys a warp takes per step
+    constexpr int STAGES = 3;           // depth of each warp's cp.async ring
+    using L = DecodeSmem<HD, GC, KPW>;
     constexpr int DPL = HD / 32;        // output values per lane
     constexpr int CH = HD / 32;         // 16-byte chunks of a K row per lane (4 lanes per key)
     constexpr int CPR = HD / 8;         // 16-byte chunks per row
@@ -168,7 +193,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
         return;
     }
     const int lo = p.window > 0 ? max(0, ctx - p.window) : 0;
-    const int part_len = ceil_div(ceil_div(ctx - lo, parts), 8) * 8;
+    const int part_len = ceil_div(ceil_div(ctx - lo, parts), KPW) * KPW;
     const int k_beg = lo + part * part_len;
     const int k_end = min(ctx, k_beg + part_len);
     const int n_keys = max(0, k_end - k_beg);
@@ -222,19 +247,46 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     // bank groups.  Keys past the part's end are zero-filled.
     const int n_steps = ceil_div(n_keys, WARPS * KPW);
     unsigned char* ring = smem + L::KV_OFF + warp * STAGES * L::STAGE;
+    // When a step's 8 keys always lie in one page (parts start on multiples of 8 and pages hold a
+    // multiple of 8 keys) the page is looked up once per step and every copy's source is a constant
+    // offset from the page's row: a handful of instructions per copy instead of a dozen.
+    const bool one_page = ((k_beg & (KPW - 1)) == 0) && (((ps_mask + 1) & (KPW - 1)) == 0);
+    const size_t lane_off = (size_t)(lane / CPR) * HD + (size_t)(lane % CPR) * 8;     // this lane's first copy inside the 8 rows
+    // where a 16-byte chunk of a row goes: the CUDA-core variant swizzles K by the key's parity (see
+    // above) and leaves V plain; the MMA variant XORs the chunk with the key's low 3 bits in both,
+    // which is what `ldmatrix` needs to read 8 rows without bank conflicts
+    auto k_chunk = [](int key, int l) { return MMA ? (l ^ (key & 7)) : (l ^ ((key & 1) << 2)); };
+    auto v_chunk = [](int key, int l) { return MMA ? (l ^ (key & 7)) : l; };
+    constexpr int KSTEP = 32 / CPR;       // keys between two copies of one lane
     auto issue = [&](int step, int stage) {
         unsigned char* dst = ring + stage * L::STAGE;
+        const int kidx0 = step * (WARPS * KPW) + warp * KPW;
+        if (one_page) {
+            const int kpos0 = k_beg + min(kidx0, max(n_keys - 1, 0));
+            const int page = pages_s[(kpos0 >> lps) - page_base];
+            const size_t row0 = ((((size_t)page * p.nkv + kvh) << lps) + (kpos0 & ps_mask)) * HD + lane_off;
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            const int c = lane + 32 * i;
-            const int key = c / CPR, l = c % CPR;
-            const int kidx = step * (WARPS * KPW) + warp * KPW + key;
-            const bool valid = kidx < n_keys;
-            const int kpos = k_beg + (valid ? kidx : 0);
-            const int page = pages_s[(kpos >> lps) - page_base];
-            const size_t off = ((((size_t)page * p.nkv + kvh) << lps) + (kpos & ps_mask)) * HD + l * 8;
-            cp_async_16(dst + key * L::ROW + ((l ^ ((key & 1) << 2)) << 4), p.kcache + off, valid);
-            cp_async_16(dst + KPW * L::ROW + key * L::ROW + (l << 4), p.vcache + off, valid);
+            for (int i = 0; i < CPL; ++i) {
+                // copy i of this lane: key (lane / CPR) + i * KSTEP, the same 16-byte chunk of the row
+                const int key = lane / CPR + i * KSTEP, l = lane % CPR;
+                const bool valid = kidx0 + key < n_keys;
+                const size_t off = row0 + (size_t)(i * KSTEP) * HD;
+                cp_async_16(dst + key * L::ROW + (k_chunk(key, l) << 4), p.kcache + off, valid);
+                cp_async_16(dst + KPW * L::ROW + key * L::ROW + (v_chunk(key, l) << 4), p.vcache + off, valid);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+                const int c = lane + 32 * i;
+                const int key = c / CPR, l = c % CPR;
+                const int kidx = kidx0 + key;
+                const bool valid = kidx < n_keys;
+                const int kpos = k_beg + (valid ? kidx : 0);
+                const int page = pages_s[(kpos >> lps) - page_base];
+                const size_t off = ((((size_t)page * p.nkv + kvh) << lps) + (kpos & ps_mask)) * HD + l * 8;
+                cp_async_16(dst + key * L::ROW + (k_chunk(key, l) << 4), p.kcache + off, valid);
+                cp_async_16(dst + KPW * L::ROW + key * L::ROW + (v_chunk(key, l) << 4), p.vcache + off, valid);
+            }
         }
         cp_async_commit();
     };
@@ -243,102 +295,226 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
         if (st < n_steps) issue(st, st); else cp_async_commit();
     }
 
-    const int grp = lane >> 2, j = lane & 3;
-    float m[GC], l[GC], acc[GC][DPL];
+    if constexpr (MMA) {
+        // ---- tensor-core variant.  Lane (g = lane / 4, t = lane % 4) of a warp holds, of every
+        // 16 x 8 accumulator tile, row g columns 2t, 2t + 1 (and row g + 8, which no head uses: a
+        // chunk has at most 8 heads).  Q's rows are the chunk's heads.
+        const int g = lane >> 2, t4 = lane & 3;
+        uint32_t qa[HD / 16][4];
 #pragma unroll
-    for (int g = 0; g < GC; ++g) {
-        m[g] = -INFINITY;
-        l[g] = 0.f;
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const float* qrow = q_s + (g < GC ? g : 0) * HD + kk * 16 + 2 * t4;
+            qa[kk][0] = g < GC ? pack_bf16x2(qrow[0], qrow[1]) : 0u;
+            qa[kk][1] = 0u;
+            qa[kk][2] = g < GC ? pack_bf16x2(qrow[8], qrow[9]) : 0u;
+            qa[kk][3] = 0u;
+        }
+        float m_run = -INFINITY, l_run = 0.f;
+        float o[HD / 8][4];
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
-    }
-    for (int step = 0; step < n_steps; ++step) {
-        const int stage = step % STAGES;
-        // the ring slot freed by the previous step takes the load of step + STAGES - 1
-        if (step + STAGES - 1 < n_steps) issue(step + STAGES - 1, (step + STAGES - 1) % STAGES); else cp_async_commit();
-        cp_async_wait<STAGES - 1>();
-        __syncwarp();
-        const unsigned char* Ks = ring + stage * L::STAGE;
-        const unsigned char* Vs = Ks + KPW * L::ROW;
-        const int key = grp;
-        const bool valid = step * (WARPS * KPW) + warp * KPW + key < n_keys;
-        float dot[GC];
+        for (int nt = 0; nt < HD / 8; ++nt)
 #pragma unroll
-        for (int g = 0; g < GC; ++g) dot[g] = 0.f;
+            for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+        const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
+        // ldmatrix row addresses: lane i gives row i % 8 of matrix i / 8
+        const int lm_row = lane & 7, lm_mat = lane >> 3;
+        for (int step = 0; step < n_steps; ++step) {
+            const int stage = step % STAGES;
+            if (step + STAGES - 1 < n_steps) issue(step + STAGES - 1, (step + STAGES - 1) % STAGES); else cp_async_commit();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            const uint32_t Ks = ring_addr + stage * L::STAGE;
+            const uint32_t Vs = Ks + KPW * L::ROW;
+            const int kidx0 = step * (WARPS * KPW) + warp * KPW;
+            // S = Q K^T for two tiles of 8 keys
+            float sc[2][4];
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int lc = c * 4 + j;
-            Vec16<bf16> v;
-            v.raw = *reinterpret_cast<const uint4*>(Ks + key * L::ROW + ((lc ^ ((key & 1) << 2)) << 4));
-            float kf[8];
-            v.unpack(kf);
+            for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-            for (int g = 0; g < GC; ++g) {
-                const float4* qa = reinterpret_cast<const float4*>(q_s + g * HD + lc * 8);
-                const float4 a = qa[0], b = qa[1];
-                dot[g] = fmaf(a.x, kf[0], dot[g]); dot[g] = fmaf(a.y, kf[1], dot[g]);
-                dot[g] = fmaf(a.z, kf[2], dot[g]); dot[g] = fmaf(a.w, kf[3], dot[g]);
-                dot[g] = fmaf(b.x, kf[4], dot[g]); dot[g] = fmaf(b.y, kf[5], dot[g]);
-                dot[g] = fmaf(b.z, kf[6], dot[g]); dot[g] = fmaf(b.w, kf[7], dot[g]);
+                for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; kk += 2) {
+                    // four 8 x 8 matrices: keys nt*8.., head values [kk*16, +8), [kk*16+8, +8), [(kk+1)*16, +8), [(kk+1)*16+8, +8)
+                    const int key = nt * 8 + lm_row, chunk = kk * 2 + lm_mat;
+                    uint32_t b[4];
+                    ldmatrix_x4(b, Ks + key * L::ROW + ((chunk ^ (key & 7)) << 4));
+                    mma_16816(sc[nt], qa[kk], b[0], b[1]);
+                    mma_16816(sc[nt], qa[kk + 1], b[2], b[3]);
+                }
+            }
+            // online softmax of row g over the step's 16 keys: this lane has keys 2t, 2t+1, 8+2t, 8+2t+1
+            float pv[4];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = (e >> 1) * 8 + 2 * t4 + (e & 1);
+                pv[e] = kidx0 + key < n_keys ? sc[e >> 1][e & 1] : -INFINITY;
+                mx = fmaxf(mx, pv[e]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);
+            const float alpha = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+            float sum = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                pv[e] = pv[e] == -INFINITY ? 0.f : __expf(pv[e] - m_new);
+                sum += pv[e];
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; ++nt) {
+                o[nt][0] *= alpha;
+                o[nt][1] *= alpha;
+            }
+            // P (16 heads x 16 keys) as the A operand: the accumulator layout of the two key tiles is it
+            uint32_t pa[4];
+            pa[0] = pack_bf16x2(pv[0], pv[1]);
+            pa[1] = 0u;
+            pa[2] = pack_bf16x2(pv[2], pv[3]);
+            pa[3] = 0u;
+            // O += P V: V rows are keys; ldmatrix.trans hands out the column-major fragments
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; nt += 2) {
+                // matrices: (keys 0-7, values nt*8..), (keys 8-15, same), (keys 0-7, values (nt+1)*8..), (keys 8-15, same)
+                const int key = (lm_mat & 1) * 8 + lm_row, chunk = nt + (lm_mat >> 1);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, Vs + key * L::ROW + ((chunk ^ (key & 7)) << 4));
+                mma_16816(o[nt], pa, b[0], b[1]);
+                mma_16816(o[nt + 1], pa, b[2], b[3]);
+            }
+            __syncwarp();    // every lane has read the stage before it is refilled
+        }
+        cp_async_wait<0>();
+        if (g < GC) {
+            float* row = mrg + (warp * GC + g) * (HD + 2);
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; ++nt) {
+                row[nt * 8 + 2 * t4] = o[nt][0];
+                row[nt * 8 + 2 * t4 + 1] = o[nt][1];
+            }
+            if (t4 == 0) {
+                row[HD] = m_run;
+                row[HD + 1] = l_run;
             }
         }
-        float pr[GC];
-#pragma unroll
+    } else {
+        const int grp = lane >> 2, j = lane & 3;
+        // the 32 (16) values of each q head that this lane multiplies: in registers for up to 2 heads
+        constexpr bool Q_IN_REGS = GC <= 2;
+        float qr[Q_IN_REGS ? GC : 1][Q_IN_REGS ? CH * 8 : 1];
+        if constexpr (Q_IN_REGS) {
+    #pragma unroll
+            for (int g = 0; g < GC; ++g)
+    #pragma unroll
+                for (int c = 0; c < CH; ++c)
+    #pragma unroll
+                    for (int e = 0; e < 8; ++e) qr[g][c * 8 + e] = q_s[g * HD + (c * 4 + j) * 8 + e];
+        }
+        float m[GC], l[GC], acc[GC][DPL];
+    #pragma unroll
         for (int g = 0; g < GC; ++g) {
-            float d = dot[g];
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            const float sv = valid ? d : -INFINITY;
-            float mx = sv;
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-            const float m_new = fmaxf(m[g], mx);
-            const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
-            pr[g] = valid ? __expf(sv - m_new) : 0.f;
-            float sum = pr[g];
-            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-            l[g] = l[g] * alpha + sum;
-            m[g] = m_new;
-#pragma unroll
-            for (int dd = 0; dd < DPL; ++dd) acc[g][dd] *= alpha;
+            m[g] = -INFINITY;
+            l[g] = 0.f;
+    #pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
         }
-#pragma unroll
-        for (int kk = 0; kk < KPW; ++kk) {
-            const unsigned char* vr = Vs + kk * L::ROW + lane * DPL * 2;
-            float vf[DPL];
-            if constexpr (DPL == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
-            } else {
-                const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
-                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
-                vf[0] = a.x; vf[1] = a.y;
+        for (int step = 0; step < n_steps; ++step) {
+            const int stage = step % STAGES;
+            // the ring slot freed by the previous step takes the load of step + STAGES - 1
+            if (step + STAGES - 1 < n_steps) issue(step + STAGES - 1, (step + STAGES - 1) % STAGES); else cp_async_commit();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            const unsigned char* Ks = ring + stage * L::STAGE;
+            const unsigned char* Vs = Ks + KPW * L::ROW;
+            const int key = grp;
+            const bool valid = step * (WARPS * KPW) + warp * KPW + key < n_keys;
+            float dot[GC];
+    #pragma unroll
+            for (int g = 0; g < GC; ++g) dot[g] = 0.f;
+    #pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const int lc = c * 4 + j;
+                Vec16<bf16> v;
+                v.raw = *reinterpret_cast<const uint4*>(Ks + key * L::ROW + ((lc ^ ((key & 1) << 2)) << 4));
+                float kf[8];
+                v.unpack(kf);
+    #pragma unroll
+                for (int g = 0; g < GC; ++g) {
+                    if constexpr (Q_IN_REGS) {
+    #pragma unroll
+                        for (int e = 0; e < 8; ++e) dot[g] = fmaf(qr[g][c * 8 + e], kf[e], dot[g]);
+                    } else {
+                        const float4* qa = reinterpret_cast<const float4*>(q_s + g * HD + lc * 8);
+                        const float4 a = qa[0], b = qa[1];
+                        dot[g] = fmaf(a.x, kf[0], dot[g]); dot[g] = fmaf(a.y, kf[1], dot[g]);
+                        dot[g] = fmaf(a.z, kf[2], dot[g]); dot[g] = fmaf(a.w, kf[3], dot[g]);
+                        dot[g] = fmaf(b.x, kf[4], dot[g]); dot[g] = fmaf(b.y, kf[5], dot[g]);
+                        dot[g] = fmaf(b.z, kf[6], dot[g]); dot[g] = fmaf(b.w, kf[7], dot[g]);
+                    }
+                }
             }
-#pragma unroll
+            float pr[GC];
+    #pragma unroll
             for (int g = 0; g < GC; ++g) {
-                const float pk = __shfl_sync(0xffffffffu, pr[g], kk * 4);
-#pragma unroll
-                for (int dd = 0; dd < DPL; ++dd) acc[g][dd] = fmaf(pk, vf[dd], acc[g][dd]);
+                float d = dot[g];
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                const float sv = valid ? d : -INFINITY;
+                float mx = sv;
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m[g], mx);
+                const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
+                pr[g] = valid ? __expf(sv - m_new) : 0.f;
+                float sum = pr[g];
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+                l[g] = l[g] * alpha + sum;
+                m[g] = m_new;
+    #pragma unroll
+                for (int dd = 0; dd < DPL; ++dd) acc[g][dd] *= alpha;
             }
+    #pragma unroll
+            for (int kk = 0; kk < KPW; ++kk) {
+                const unsigned char* vr = Vs + kk * L::ROW + lane * DPL * 2;
+                float vf[DPL];
+                if constexpr (DPL == 4) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
+                } else {
+                    const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+                    vf[0] = a.x; vf[1] = a.y;
+                }
+    #pragma unroll
+                for (int g = 0; g < GC; ++g) {
+                    const float pk = __shfl_sync(0xffffffffu, pr[g], kk * 4);
+    #pragma unroll
+                    for (int dd = 0; dd < DPL; ++dd) acc[g][dd] = fmaf(pk, vf[dd], acc[g][dd]);
+                }
+            }
+            __syncwarp();    // every lane has read the stage before it is refilled
         }
-        __syncwarp();    // every lane has read the stage before it is refilled
-    }
-    cp_async_wait<0>();
+        cp_async_wait<0>();
 
-    // Merge the warps' states: M = max m_w, o = sum_w e^{m_w - M} acc_w, L = sum_w e^{m_w - M} l_w.
-#pragma unroll
-    for (int g = 0; g < GC; ++g) {
-        float* row = mrg + (warp * GC + g) * (HD + 2);
-#pragma unroll
-        for (int dd = 0; dd < DPL; ++dd) row[lane * DPL + dd] = acc[g][dd];
-        if (lane == 0) {
-            row[HD] = m[g];
-            row[HD + 1] = l[g];
+        // Merge the warps' states: M = max m_w, o = sum_w e^{m_w - M} acc_w, L = sum_w e^{m_w - M} l_w.
+    #pragma unroll
+        for (int g = 0; g < GC; ++g) {
+            float* row = mrg + (warp * GC + g) * (HD + 2);
+    #pragma unroll
+            for (int dd = 0; dd < DPL; ++dd) row[lane * DPL + dd] = acc[g][dd];
+            if (lane == 0) {
+                row[HD] = m[g];
+                row[HD + 1] = l[g];
+            }
         }
     }
     __syncthreads();
@@ -425,9 +601,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     }
 }
 
-template <int HD, int GC>
-int launch(const DecodeParams& p, dim3 grid, size_t smem, cudaStream_t s) {
-    auto kernel = attention_decode_kernel<HD, GC>;
+template <int HD, int GC, bool MMA>
+int launch(const DecodeParams& p, dim3 grid, cudaStream_t s) {
+    const size_t smem = DecodeSmem<HD, GC, MMA ? 16 : 8>::bytes(p.page_cap);
+    auto kernel = attention_decode_kernel<HD, GC, MMA>;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -438,14 +615,24 @@ int launch(const DecodeParams& p, dim3 grid, size_t smem, cudaStream_t s) {
     return LLMK_OK;
 }
 
-template <int HD>
+template <int HD, bool MMA>
 int dispatch_group(int gc, const DecodeParams& p, dim3 grid, cudaStream_t s) {
     switch (gc) {
-        case 1: return launch<HD, 1>(p, grid, DecodeSmem<HD, 1>::bytes(p.page_cap), s);
-        case 2: return launch<HD, 2>(p, grid, DecodeSmem<HD, 2>::bytes(p.page_cap), s);
-        case 4: return launch<HD, 4>(p, grid, DecodeSmem<HD, 4>::bytes(p.page_cap), s);
-        default: return launch<HD, 8>(p, grid, DecodeSmem<HD, 8>::bytes(p.page_cap), s);
+        case 1: return launch<HD, 1, MMA>(p, grid, s);
+        case 2: return launch<HD, 2, MMA>(p, grid, s);
+        case 4: return launch<HD, 4, MMA>(p, grid, s);
+        default: return launch<HD, 8, MMA>(p, grid, s);
     }
+}
+
+// Which variant runs: the tensor-core one unless LLMGEN_DECODE_MATH=simt asks for the other.
+bool use_mma() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("LLMGEN_DECODE_MATH");
+        v = (e && e[0] == 's') ? 0 : 1;
+    }
+    return v != 0;
 }
 
 int chunk_heads(int G) { return G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8; }
@@ -520,12 +707,13 @@ LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void*
     while ((1 << p.log2_page) < page_size) ++p.log2_page;
     p.chunks = ceil_div(G, gc);
     const int visible = window > 0 ? min(window, max_ctx) : max_ctx;
-    const int part_cap = ceil_div(ceil_div(max(visible, 1), parts), 8) * 8;
+    const int part_cap = ceil_div(ceil_div(max(visible, 1), parts), 16) * 16;
     p.page_cap = part_cap / page_size + 2;       // page ids of one part, kept in shared memory
     p.scale = scale;
     if ((size_t)p.page_cap * 4 > 64 * 1024)
         LLMK_FAIL("attention_decode: %d keys per part in pages of %d need too much shared memory; use more parts", part_cap, page_size);
     dim3 grid(parts, nkv * p.chunks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    return hd == 128 ? dispatch_group<128>(gc, p, grid, s) : dispatch_group<64>(gc, p, grid, s);
+    if (use_mma()) return hd == 128 ? dispatch_group<128, true>(gc, p, grid, s) : dispatch_group<64, true>(gc, p, grid, s);
+    return hd == 128 ? dispatch_group<128, false>(gc, p, grid, s) : dispatch_group<64, false>(gc, p, grid, s);
 }

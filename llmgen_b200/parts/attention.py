@@ -186,8 +186,8 @@ class GQAAttention(Mixer):
         bound = ctx.max_ctx_bound if ctx.fixed_shapes else max(ctx.max_ctx, 1)
         visible = min(bound, self.window) if self.window else bound
         blocks = max(1, S * self.nkv * chunks)
-        # about 3.5 blocks per SM (4 fit), at least 128 keys a part, at most 64 parts
-        parts = max(1, min((7 * NUM_SMS // 2) // blocks, visible // 128, 64))
+        # as many blocks as are resident at a time (2 per SM), at least 128 keys a part, at most 64 parts
+        parts = max(1, min((2 * NUM_SMS) // blocks, visible // 128, 64))
         scratch = counters = None
         if parts > 1:
             scratch = ws.flat("attn_decode_split", ops.attention_decode_scratch_floats(S, self.nq, self.hd, parts),

@@ -696,6 +696,17 @@ def test_attention_decode(ops, nq, nkv, hd, page, parts):
         assert int(counters.abs().sum()) == 0
 
 
+def test_attention_decode_batch_64(ops):
+    """64 sequences of 577 to 640 keys at the benchmark's head geometry (168 MB of cache would be the
+    full model's 28 layers; this is one layer, 5.9 MB per kv head pair): one part and two."""
+    nq, nkv, hd, page = 16, 8, 128, 16
+    seqs = [(640 - s, 1) for s in range(64)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 37)
+    for parts in (1, 2):
+        got = run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, parts=parts)
+        assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
+
+
 @pytest.mark.parametrize("nq,nkv,hd,page,rot", [(4, 2, 128, 16, 128), (16, 8, 128, 16, 128), (6, 2, 64, 16, 64), (20, 2, 64, 32, 64),
                                                 (4, 2, 128, 16, 64), (2, 1, 64, 8, 0)])
 @pytest.mark.parametrize("parts", [1, 5])
