@@ -193,8 +193,14 @@ class Executor:
             return StepOutput(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
                               if return_logits else None, [] if sample else None)
         pure_decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-        if pure_decode and sample and not return_logits and not self.eager:
-            return self._graph_step(entries)
+        if pure_decode and sample and not return_logits:
+            if not self.eager:
+                return self._graph_step(entries)
+            # eager generation runs exactly what the graph of this step would replay (the batch
+            # padded to its bucket), so that both give the same bits
+            out = self._eager_pass(entries, True, False, pad_to=self._bucket_for(len(entries)))
+            self.n_eager_steps += 1
+            return out
         passes = self._passes(entries)
         logits_parts, ids_parts, order = [], [], []
         for sub, keys in passes:
@@ -364,7 +370,8 @@ class Executor:
         ctx = StepContext(
             n_tokens=T, n_seqs=S, dtype=self.dtype, device=self.device, workspace=self.workspace,
             requests=[e.req for e in entries], starts=starts, q_lens=q_lens, pure_decode=pure_decode,
-            max_ctx=int(ctx_len.max()) if S else 0, max_ctx_bound=ctx_bound or lim.max_model_len,
+            max_ctx=int(ctx_len.max()) if S else 0,
+            max_ctx_bound=ctx_bound or self.context_class(int(ctx_len.max()) if S else 0),
             max_seqs_bound=lim.max_num_seqs,
             ids=view("ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_len=view("ctx_len"),
             state_slots=view("state_slots"), seq_of_token=view("seq_of_token"),
@@ -377,8 +384,10 @@ class Executor:
         if self.sync_each:
             torch.cuda.synchronize(self.device)
 
-    def _eager_pass(self, entries: Sequence[StepEntry], sample: bool, return_logits: bool) -> StepOutput:
-        ctx, want_rows, temps, seed, n_want = self._build_meta(entries)
+    def _eager_pass(self, entries: Sequence[StepEntry], sample: bool, return_logits: bool, pad_to: int = 0) -> StepOutput:
+        ctx, want_rows, temps, seed, n_want = self._build_meta(entries, pad_to=pad_to)
+        ctx.fixed_shapes = pad_to > 0      # the launch shapes a captured graph of this step would have
+        n_real = sum(len(e.want) for e in entries)
         out = StepOutput()
         if n_want == 0:
             self.model.hidden_states(ctx, self.layer_caches)
@@ -396,9 +405,9 @@ class Executor:
             host = self.ids_host[:n_want] if n_want <= self.ids_host.numel() else torch.empty(n_want, dtype=torch.int32).pin_memory()
             host.copy_(ids_dev, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-            out.token_ids = host.tolist()
+            out.token_ids = host.tolist()[:n_real]
         if return_logits:
-            out.logits = logits
+            out.logits = logits[:n_real]
         return out
 
     # ------------------------------------------------------------------ CUDA graphs

@@ -177,13 +177,15 @@ class GQAAttention(Mixer):
 
 
     def _decode(self, ctx, o, q, cache, group, scale, prep=None) -> None:
-        """Single decoded tokens: as many key parts as fill the SMs, at least 128 keys a part;
-        under graph capture the bound of the step's context class decides, not the lengths."""
+        """Single decoded tokens: as many key parts as fill the SMs, at least 128 keys a part; the
+        bound of the step's context class decides, not the lengths."""
         ws = ctx.workspace
         S = ctx.n_seqs
         G = self.nq // self.nkv
         chunks = (G + 7) // 8
-        bound = ctx.max_ctx_bound if ctx.fixed_shapes else max(ctx.max_ctx, 1)
+        # the bound of the step's context class, for eager steps too: a step then cuts its keys the
+        # same way whether it is replayed from a graph or launched directly, and gives the same bits
+        bound = max(ctx.max_ctx_bound, ctx.max_ctx, 1)
         visible = min(bound, self.window) if self.window else bound
         blocks = max(1, S * self.nkv * chunks)
         # as many blocks as are resident at a time (2 per SM), at least 128 keys a part, at most 64 parts

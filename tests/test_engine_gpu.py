@@ -157,19 +157,20 @@ def test_command_line_chat_and_bench(tmp):
     assert summary["policy"] == "chunked" and summary["kv_leak"] is False
 
 
-def test_layer_sizes_of_the_larger_models(tmp):
-    """One layer with the head geometry of the larger Qwen3 models (32 query heads on 8 kv heads of
-    128, q width twice the hidden size) and a vocabulary that is no multiple of 128: bfloat16 logits
-    of a prompt and of decoded tokens against the plain implementation, and graph replay against
-    eager steps."""
+@pytest.mark.parametrize("hidden,heads,kv_heads,inter", [(2048, 32, 8, 6144), (5120, 64, 8, 4096)])
+def test_layer_sizes_of_the_larger_models(tmp, hidden, heads, kv_heads, inter):
+    """One layer with the head geometry of the larger Qwen3 models (32 or 64 query heads on 8 kv
+    heads of 128: groups of 4 and 8, a q width that is not the hidden size) and a vocabulary that is
+    no multiple of 128: bfloat16 logits of a prompt and of decoded tokens against the plain
+    implementation, and graph replay against eager steps."""
     from llmgen_b200 import LLM, SamplingParams
     from llmgen_b200.engine.api import write_random_model
     from tests.util import Driver, logits_close
-    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 1500, "hidden_size": 2048,
-           "intermediate_size": 6144, "num_hidden_layers": 1, "num_attention_heads": 32, "num_key_value_heads": 8,
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 1500, "hidden_size": hidden,
+           "intermediate_size": inter, "num_hidden_layers": 1, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
            "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 1024,
            "tie_word_embeddings": False, "hidden_act": "silu"}
-    path = os.path.join(tmp, "wide")
+    path = os.path.join(tmp, f"wide_{hidden}")
     write_random_model(path, cfg, 11, 0.02, 0.1, "bfloat16")
     ids = random_ids(300, 1500, 5)
     ref = PlainQwen3(path).logits(ids)

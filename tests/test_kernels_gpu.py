@@ -679,7 +679,7 @@ def run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, max_blocks, nq, nkv, hd, 
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page", [(4, 2, 128, 16), (16, 8, 128, 16), (8, 1, 64, 32), (6, 2, 64, 16), (3, 3, 128, 8),
-                                            (40, 2, 64, 16), (24, 2, 128, 16)])
+                                            (40, 2, 64, 16), (24, 2, 128, 16), (64, 8, 128, 16), (8, 2, 128, 32)])
 @pytest.mark.parametrize("parts", [1, 4, 7, 37])
 def test_attention_decode(ops, nq, nkv, hd, page, parts):
     """Single tokens against contexts of 1 to 700 keys and a padding row, one part and many (more
@@ -708,7 +708,7 @@ def test_attention_decode_batch_64(ops):
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page,rot", [(4, 2, 128, 16, 128), (16, 8, 128, 16, 128), (6, 2, 64, 16, 64), (20, 2, 64, 32, 64),
-                                                (4, 2, 128, 16, 64), (2, 1, 64, 8, 0)])
+                                                (4, 2, 128, 16, 64), (2, 1, 64, 8, 0), (64, 8, 128, 16, 128), (8, 2, 128, 16, 128)])
 @pytest.mark.parametrize("parts", [1, 5])
 @pytest.mark.parametrize("sliced", [False, True])
 def test_attention_decode_makes_q_k_v_itself(ops, nq, nkv, hd, page, rot, parts, sliced):
