@@ -16,6 +16,7 @@ or the replay program does that, as the reference's scheduler calls `ensure`.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -23,6 +24,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheError, CacheManager
+from ..cache.manager import runtime as cache_runtime
 from ..cache.storage import CacheStorage, bytes_per_page, plan_groups
 from ..kernels import ops
 from .context import GroupView, StepContext, StepMetaBuilder, Workspace
@@ -128,7 +130,11 @@ class Executor:
         self.graphs: Dict[Tuple[int, int], dict] = {}     # (batch-size bucket, context-length class) -> graph
         # decode steps rewrite only what changed in a host buffer that the same bucket filled last
         self._host_owner = [None, None]                   # per pinned buffer: (bucket, layout) of its last fill
-        self._host_rows = [None, None]                    # per pinned buffer: per group, per row: table stamp
+        self._host_rows = [None, None]                    # per pinned buffer: per group and row, (request, table stamp)
+        self._runtime = cache_runtime()
+        top = self.limits.max_num_seqs
+        self._decode_args = ((ctypes.c_longlong * top)(), (ctypes.c_int * top)(), (ctypes.c_int * top)(),
+                             (ctypes.c_float * top)())      # requests, tokens, positions, temperatures of a decode step
 
     # ------------------------------------------------------------------ sizing
     def _pages_per_group(self) -> List[int]:
@@ -168,10 +174,15 @@ class Executor:
     # ------------------------------------------------------------------ cache front
     def admit(self, req: Hashable) -> bool:
         slot = self.cache.admit(req)
-        if self.cache.fresh_state:
-            self.storage.reset_state(self.cache.fresh_state)
-            self.cache.fresh_state.clear()
+        self._reset_fresh_state()
         return slot is not None
+
+    def _reset_fresh_state(self) -> None:
+        """Zero the per-request state of slots that new requests received since the last look
+        (through `admit` here or through the scheduler, which admits on the native side)."""
+        if self.cache.fresh_state:
+            self.storage.reset_state(list(self.cache.fresh_state))
+            self.cache.fresh_state.clear()
 
     def reserve(self, req: Hashable, start: int, end: int) -> bool:
         return self.cache.reserve(req, start, end)
@@ -188,6 +199,7 @@ class Executor:
         of the entries and, inside an entry, of its `want` list."""
         entries = [e for e in entries]
         self._validate(entries)
+        self._reset_fresh_state()
         n_tokens = sum(len(e.tokens) for e in entries)
         if n_tokens == 0:
             return StepOutput(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -253,14 +265,9 @@ class Executor:
             for w in e.want:
                 if not 0 <= w < n:
                     raise StepError(f"request {e.req!r}: wanted place {w} outside its {n} tokens")
-            if not self.cache.is_admitted(e.req):
-                raise StepError(f"request {e.req!r} was not admitted")
-            for g in self.cache.groups:
-                table = g.table(e.req)
-                last_page = (e.start + n - 1) // lim.page_size
-                first_live = g.first_needed_position(e.start) // lim.page_size
-                if last_page >= len(table) or any(table[i] < 0 for i in range(first_live, last_page + 1)):
-                    raise StepError(f"request {e.req!r}: no pages reserved for positions up to {e.start + n - 1}")
+            why = self.cache.check_step(e.req, e.start, n)
+            if why:
+                raise StepError(why)
 
     def _passes(self, entries: Sequence[StepEntry]):
         """Cut the entries into passes of at most `max_step_tokens` tokens.  Each pass is a list of
@@ -514,61 +521,38 @@ class Executor:
         if owner is None or owner[0] != bucket:
             self._build_meta(entries, pad_to=bucket)
             t, layout, total = self._last_fill
-            self._host_owner[t] = (bucket, layout, total)
-            self._host_rows[t] = [[None] * bucket for _ in self.cache.groups]
-            for gi, g in enumerate(self.cache.groups):
-                for s_, e in enumerate(entries):
-                    self._host_rows[t][gi][s_] = (e.req, g.table_stamp(e.req))
+            names = ["ids", "positions", "ctx_len", "state_slots", "temps"]
+            for gi in range(len(self.cache.groups)):
+                names += [f"slots_{gi}", f"block_tables_{gi}"]
+            offs = (ctypes.c_int * len(names))(*[layout[name][0] for name in names])
+            self._host_owner[t] = (bucket, layout, total, offs)
+            # (request, table stamp) per group and row; -1 = unknown, so the first native fill writes every row
+            stamps = (ctypes.c_longlong * (2 * bucket * len(self.cache.groups)))()
+            for i in range(len(stamps)):
+                stamps[i] = -1
+            self._host_rows[t] = stamps
             return
-        _, layout, total = owner
+        _, layout, total, offs = owner
         self._meta_turn ^= 1
         if self.meta_events[turn] is not None:
             self.meta_events[turn].synchronize()
-        hv = self.meta_host[turn].numpy()
-        n, ps, S = len(entries), self.limits.page_size, bucket
-
-        def arr(name):
-            off, size, _ = layout[name]
-            return hv[off:off + size]
-
+        host = self.meta_host[turn]
+        n = len(entries)
         self.step_seed = (self.step_seed + SEED_STRIDE) & MASK64
-        arr("seed")[:] = np.array([self.step_seed], dtype=np.uint64).view(np.int32)
-        starts = [e.start for e in entries]
-        ids = arr("ids")
-        ids[:n] = [e.tokens[0] for e in entries]
-        ids[n:] = 0
-        pos = arr("positions")
-        pos[:n] = starts
-        pos[n:] = 0
-        cl = arr("ctx_len")
-        cl[:n] = starts
-        cl[:n] += 1
-        cl[n:] = 0
-        st = arr("state_slots")
-        st[:n] = [self.cache.state.slot(e.req) for e in entries]
-        st[n:] = -1
-        temps = arr("temps").view(np.float32)
-        temps[:n] = [e.temperature for e in entries]
-        temps[n:] = 0.0
-        for gi, g in enumerate(self.cache.groups):
-            slots = arr(f"slots_{gi}")
-            bt = arr(f"block_tables_{gi}").reshape(S, self.max_blocks)
-            rows = self._host_rows[turn][gi]
-            for s_, e in enumerate(entries):
-                table = g.table(e.req)
-                stamp = g.table_stamp(e.req)
-                key = (e.req, stamp)
-                if stamp is None or rows[s_] != key:
-                    bt[s_, :len(table)] = table
-                    bt[s_, len(table):] = 0
-                    rows[s_] = key
-                p = e.start
-                slots[s_] = table[p // ps] * ps + p % ps
-            for s_ in range(n, S):
-                if rows[s_] is not None:
-                    bt[s_, :] = 0
-                    rows[s_] = None
-            slots[n:] = -1
+        off, size, _ = layout["seed"]
+        host.numpy()[off:off + size] = np.array([self.step_seed], dtype=np.uint64).view(np.int32)
+        a = self._decode_args
+        key = self.cache.key
+        a[0][:n] = [key(e.req) for e in entries]
+        a[1][:n] = [e.tokens[0] for e in entries]
+        a[2][:n] = [e.start for e in entries]
+        a[3][:n] = [e.temperature for e in entries]
+        rc = self._runtime.llmr_fill_decode(self.cache.native_handle, ctypes.c_void_p(host.data_ptr()), offs,
+                                            ctypes.c_int(n), ctypes.c_int(bucket), ctypes.c_int(self.max_blocks),
+                                            a[0], a[1], a[2], a[3], self._host_rows[turn])
+        if rc != 0:
+            self._host_owner[turn] = None
+            raise StepError(self._runtime.llmr_last_error().decode("utf-8", "replace"))
         self.meta_dev[:total].copy_(self.meta_host[turn][:total], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()

@@ -15,15 +15,17 @@ When pages run out for the sequence being scheduled, the LAST running sequence i
 again from position 0, generated tokens included); if the sequence is itself the last, it
 preempts itself and scheduling stops for this step.
 
-Pure host logic over the cache manager's interface (`admit`, `reserve`, `can_reserve`,
-`release`), so it is tested without a GPU.
+The decisions are taken in C++ (`csrc/runtime.cu`, next to the cache manager whose pages they
+spend); `BatchScheduler` here owns the native scheduler, hands requests to it and mirrors what it
+decided into the `Request` objects.  Pure host logic, so it is tested without a GPU.
 """
 from __future__ import annotations
 
-import time
-from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from ctypes import byref, c_int, c_longlong, c_void_p
+from dataclasses import dataclass
+from typing import Dict, List, Sequence
 
+from ..cache.manager import CacheManager, runtime
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
@@ -90,154 +92,135 @@ class SchedulerConfig:
 
 
 class BatchScheduler:
+    """The native scheduler and its Python mirror.
+
+    `cache` is the `CacheManager` whose pages are spent, or anything that holds it as `.cache`
+    (the executor).  State slots that admissions hand out are listed by the manager
+    (`fresh_state`); whoever owns per-request state clears them before the next step."""
+
+    _POLICY_CODE = {PREFILL_FIRST: 0, CHUNKED: 1}
+    _STATUS = {0: WAITING, 1: RUNNING, 2: FINISHED}
+
     def __init__(self, cache, config: SchedulerConfig):
-        self.cache = cache          # anything with admit / reserve / can_reserve / release
+        manager = cache if isinstance(cache, CacheManager) else getattr(cache, "cache", None)
+        if not isinstance(manager, CacheManager):
+            raise SchedulerError("the scheduler needs a CacheManager (or an executor that holds one as .cache)")
+        self.cache = cache
+        self.manager = manager
         self.config = config
-        self.waiting: List[Request] = []
-        self.running: List[Request] = []
-        self.num_preemptions = 0
+        self._lib = runtime()
+        eos = [int(t) for t in config.eos_token_ids]
+        self._eos_sent = tuple(eos)
+        self._h = c_void_p(self._lib.llmr_sched_new(
+            manager.native_handle, c_int(self._POLICY_CODE[config.policy]), c_int(config.max_num_seqs),
+            c_int(config.max_num_batched_tokens), c_int(config.chunk_tokens), (c_int * max(len(eos), 1))(*eos),
+            c_int(len(eos))))
+        if not self._h:
+            raise SchedulerError("the native scheduler refused its configuration")
+        self._requests: Dict[int, Request] = {}       # native key -> request, while the scheduler knows it
+        self._cap = 0
+        self._grow(max(16, min(config.max_num_seqs, 4096)))
+
+    def __del__(self):
+        if getattr(self, "_h", None) and self._lib is not None:
+            self._lib.llmr_sched_delete(self._h)
+            self._h = None
+
+    def _grow(self, cap: int) -> None:
+        self._cap = cap
+        self._keys = (c_longlong * cap)()
+        self._starts = (c_int * cap)()
+        self._lens = (c_int * cap)()
+        self._tokens = (c_int * cap)()
+        self._other = (c_longlong * cap)()
+        self._count = c_int(0)
+
+    # ---------------------------------------------------------------- queues
+    def _queue(self, which: int) -> List[Request]:
+        n = self._lib.llmr_sched_queue(self._h, c_int(which), self._other, c_int(self._cap))
+        if n > self._cap:
+            self._grow(2 * n)
+            n = self._lib.llmr_sched_queue(self._h, c_int(which), self._other, c_int(self._cap))
+        return [self._requests[self._other[i]] for i in range(n)]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._queue(1)
+
+    @property
+    def num_preemptions(self) -> int:
+        return int(self._lib.llmr_sched_num_preemptions(self._h))
 
     def is_finished(self) -> bool:
-        return not self.waiting and not self.running
+        return bool(self._lib.llmr_sched_is_finished(self._h))
 
     def add(self, request: Request) -> None:
+        if len(request) != request.num_prompt_tokens:
+            raise SchedulerError("a request is added before it has generated tokens")
+        key = self.manager.key(request.id)
+        if key in self._requests:
+            raise SchedulerError(f"request {request.id!r} is already scheduled")
         request.status = WAITING
-        self.waiting.append(request)
+        self._requests[key] = request
+        if len(self._requests) > self._cap:
+            self._grow(2 * self._cap)
+        self._lib.llmr_sched_add(self._h, c_longlong(key), c_int(len(request)), c_int(request.params.max_tokens),
+                                 c_int(1 if request.params.ignore_eos else 0))
 
     # ---------------------------------------------------------------- scheduling
     def schedule(self) -> List[Scheduled]:
-        if self.config.policy == PREFILL_FIRST:
-            return self._schedule_prefill_first()
-        return self._schedule_chunked()
-
-    def _admit(self, request: Request, upto: int) -> bool:
-        """State slot and pages for positions [0, upto) of a waiting request, or nothing."""
-        if len(self.running) >= self.config.max_num_seqs:
-            return False
-        admitted = self.cache.admit(request.id)     # a slot number (0 counts) or True; None / False: full
-        if admitted is None or admitted is False:
-            return False
-        if not self.cache.reserve(request.id, 0, upto):
-            self.cache.release(request.id)
-            return False
-        return True
-
-    def _make_room(self, index: int, start: int, upto: int) -> bool:
-        """Preempt from the tail of `running` until positions [start, upto) of running[index]
-        can be reserved.  False if the sequence had to preempt itself."""
-        request = self.running[index]
-        while not self.cache.can_reserve(request.id, start, upto):
-            if len(self.running) - 1 > index:
-                self._preempt(self.running.pop())
-            else:
-                self.running.pop(index)
-                self._preempt(request)
-                return False
-        return True
-
-    def _schedule_prefill_first(self) -> List[Scheduled]:
-        cfg = self.config
-        out: List[Scheduled] = []
-        tokens = 0
-        while self.waiting and len(out) < cfg.max_num_seqs:
-            request = self.waiting[0]
-            n = len(request)
-            if tokens + n > cfg.max_num_batched_tokens:
-                break
-            if not self._admit(request, n):
-                break
-            self.waiting.pop(0)
-            request.status = RUNNING
+        """This step's portions.  Requests that lost their place are back at the front of `waiting`
+        with nothing computed."""
+        n = self._lib.llmr_sched_schedule(self._h, self._keys, self._starts, self._lens, c_int(self._cap),
+                                          self._other, c_int(self._cap), byref(self._count))
+        assert n <= self._cap and self._count.value <= self._cap     # both are bounded by the known requests
+        for i in range(self._count.value):
+            request = self._requests[self._other[i]]
+            request.status = WAITING
             request.num_computed_tokens = 0
-            self.running.append(request)
-            out.append(Scheduled(request, 0, n))
-            tokens += n
-        if out:
-            return out
-        i = 0
-        while i < len(self.running) and len(out) < cfg.max_num_seqs:
-            request = self.running[i]
-            n = len(request)
-            if not self._make_room(i, n - 1, n):
-                break
-            ok = self.cache.reserve(request.id, n - 1, n)
-            assert ok
-            out.append(Scheduled(request, n - 1, 1))
-            i += 1
-        return out
-
-    def _schedule_chunked(self) -> List[Scheduled]:
-        cfg = self.config
-        out: List[Scheduled] = []
-        budget = cfg.max_num_batched_tokens
-        prefill_budget = cfg.chunk_tokens
-        preemptions_before = self.num_preemptions
-        i = 0
-        while i < len(self.running) and len(out) < cfg.max_num_seqs and budget > 0:
-            request = self.running[i]
-            remaining = len(request) - request.num_computed_tokens
-            in_prefill = remaining > 1
-            q_len = min(remaining, budget)
-            if in_prefill:
-                q_len = min(q_len, prefill_budget)
-            if q_len == 0:
-                i += 1
-                continue
-            start = request.num_computed_tokens
-            if not self._make_room(i, start, start + q_len):
-                break
-            ok = self.cache.reserve(request.id, start, start + q_len)
-            assert ok
-            out.append(Scheduled(request, start, q_len))
-            budget -= q_len
-            if in_prefill:
-                prefill_budget -= q_len
-            i += 1
-        if self.num_preemptions != preemptions_before:
-            return out
-        while self.waiting and len(out) < cfg.max_num_seqs and budget > 0 and prefill_budget > 0:
-            request = self.waiting[0]
-            q_len = min(len(request), budget, prefill_budget)
-            if not self._admit(request, q_len):
-                break
-            self.waiting.pop(0)
+            request.num_preemptions += 1
+        out = []
+        for i in range(n):
+            request = self._requests[self._keys[i]]
             request.status = RUNNING
-            request.num_computed_tokens = 0
-            self.running.append(request)
-            out.append(Scheduled(request, 0, q_len))
-            budget -= q_len
-            prefill_budget -= q_len
+            if self._starts[i] == 0:
+                request.num_computed_tokens = 0
+            out.append(Scheduled(request, self._starts[i], self._lens[i]))
         return out
-
-    def _preempt(self, request: Request) -> None:
-        request.status = WAITING
-        request.num_computed_tokens = 0
-        request.num_preemptions += 1
-        self.cache.release(request.id)
-        self.waiting.insert(0, request)
-        self.num_preemptions += 1
 
     # ---------------------------------------------------------------- after the step
     def postprocess(self, scheduled: Sequence[Scheduled], tokens: Sequence[int]) -> int:
         """Record what the step computed; append the new token of every emitting portion
         (`tokens`, in order); finish on EOS or max_tokens and free (src/runner/batching.zig:323-355).
         Returns the number of requests that finished."""
+        n = len(scheduled)
+        if n > self._cap:
+            self._grow(2 * n)
+        if tuple(self.config.eos_token_ids) != self._eos_sent:       # the configuration's list is the one that counts
+            self._eos_sent = tuple(int(t) for t in self.config.eos_token_ids)
+            self._lib.llmr_sched_set_eos(self._h, (c_int * max(len(self._eos_sent), 1))(*self._eos_sent),
+                                         c_int(len(self._eos_sent)))
         k = 0
-        finished = 0
-        for item in scheduled:
+        for i, item in enumerate(scheduled):
             request = item.request
+            self._keys[i] = self.manager.key(request.id)
+            self._starts[i] = item.q_start
+            self._lens[i] = item.q_len
             emits = item.emits()
             request.num_computed_tokens = item.q_start + item.q_len
-            if not emits:
-                continue
-            token = int(tokens[k])
-            k += 1
-            request.token_ids.append(token)
-            hit_eos = (not request.params.ignore_eos) and token in self.config.eos_token_ids
-            if hit_eos or request.num_completion_tokens >= request.params.max_tokens:
-                request.status = FINISHED
-                self.cache.release(request.id)
-                if request in self.running:
-                    self.running.remove(request)
-                finished += 1
-        return finished
+            if emits:
+                token = int(tokens[k])
+                self._tokens[k] = token
+                k += 1
+                request.token_ids.append(token)
+        done = self._lib.llmr_sched_postprocess(self._h, c_int(n), self._keys, self._starts, self._lens, self._tokens,
+                                                c_int(k), self._other, c_int(self._cap))
+        for i in range(done):
+            request = self._requests.pop(self._other[i])
+            request.status = FINISHED
+            self.manager.forget(request.id)
+        return done

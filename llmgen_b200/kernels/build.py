@@ -48,6 +48,7 @@ MODULES: Dict[str, List[str]] = {
     "attention_decode": [],
     "attention_tc": [],
     "sampling": [],
+    "runtime": [],      # host code only: cache manager, scheduler, step arrays
 }
 
 
