@@ -13,6 +13,16 @@
 // Consumers of partial sums are the residual add + RMSNorm, the q/k-norm + rotary + cache-write
 // kernel and the gated activation, so a split product costs no extra launch.
 //
+// Fused forms for the chain of a decoder layer at few rows (`llmk_gemm_skinny_fused`), which take
+// the norm and the activation between two products out of the launch list:
+//   X_NORM        the rows of X are built in shared memory by the block itself,
+//                 x = resid * (1 / sqrt(sum of squares / K + eps)) * (gain + offset), the sums of squares
+//                 coming in parts (one per 128 columns) from the product that wrote the residual;
+//   X_GATED       x = silu(gate) * up from the partial sums of the product before;
+//   OUT_RESIDUAL  the slices are written as in OUT_PARTIAL, and the block that finishes a tile last
+//                 (a ticket per tile) adds them in slice order to the float32 residual and leaves
+//                 the tile's share of each row's sum of squares for the norm that follows.
+//
 // Launched with programmatic dependent launch: barrier set-up, tensor-memory allocation and the
 // first TMA loads of W (which no earlier kernel writes) run before `griddepcontrol.wait`; only the
 // loads of X wait for the kernel before.
@@ -35,24 +45,87 @@ constexpr int BK = 64;           // one 128-byte swizzle row of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
-enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2, OUT_CLUSTER = 3 };
+enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2, OUT_CLUSTER = 3, OUT_RESIDUAL = 4 };
+enum { X_TMA = 0, X_NORM = 1, X_GATED = 2 };
+constexpr int BUILDERS = 128;    // the four epilogue warps build X when it does not come through TMA
+constexpr int MAX_SMEM = 227 * 1024;
 
-template <int MPAD, int STAGES>
+// With X through TMA a ring stage holds a tile of W and one of X.  When the block builds X itself
+// the ring holds W only and the block's whole slice of X, `nkb` tiles of [MPAD x 64] in the
+// 128-byte swizzle, follows the barriers (a kilobyte is kept for them).
+template <int MPAD, int STAGES, int XSRC = X_TMA>
 struct Smem {
     static constexpr int W_BYTES = BW * BK * 2;
     static constexpr int X_BYTES = MPAD * BK * 2;
-    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    static constexpr int STAGE_BYTES = W_BYTES + (XSRC == X_TMA ? X_BYTES : 0);
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+    static constexpr int XR_OFFSET = BAR_OFFSET + 1024;
+    static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 2) * 8 + 16 + 1024;  // + alignment slack
+    static constexpr int total(int nkb) { return XSRC == X_TMA ? TOTAL : XR_OFFSET + nkb * X_BYTES + 1024; }
+};
+
+// -DLLMK_SKINNY_TIMELINE: the blocks of tile 0 of a fused launch stamp the global timer at their
+// phases (a profiling build; launches take turns over 8 records of [slices][16] stamps).
+#ifdef LLMK_SKINNY_TIMELINE
+__device__ unsigned long long g_skinny_tl[8 * 32 * 16];
+#define TL_STAMP(slot)                                                                                  \
+    do {                                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y < 32)                                                         \
+            g_skinny_tl[(fa.tl_id * 32 + blockIdx.y) * 16 + (slot)] = tc::global_timer();                \
+    } while (0)
+#else
+#define TL_STAMP(slot) do {} while (0)
+#endif
+
+// What the fused forms need beyond the plain product.
+struct FusedArgs {
+    int tl_id;                   // profiling builds: which timeline record this launch writes
+    // X_NORM: x[m, k] = x_resid[m, k] * rinv[m] * (gain[k] + gain_offset), rinv from the parts of the sums of squares
+    const float* x_resid;
+    long long x_ld;
+    const float* sq_parts;       // [n_sq_parts][M]
+    int n_sq_parts;
+    const float* gain;
+    float eps, gain_offset;
+    // X_GATED: x[m, j] = silu(g) * u, g and u the sums over `gu_splits` slices of the packed gate/up product
+    const float* gu;             // [gu_splits][M][gu_ld], gate and up columns alternating in groups of `group`
+    int gu_splits;
+    long long gu_split_stride, gu_ld;
+    int group;
+    // OUT_RESIDUAL
+    float* resid;                // [M][resid_ld] float32, += the product
+    long long resid_ld;
+    float* sq_out;               // [tiles][M]: this tile's share of sum(resid[m, :]^2)
+    int* tickets;                // [tiles], zero between launches
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
 
-template <typename TC, int MPAD, int STAGES, int MODE>
+__device__ __forceinline__ void builders_sync() { asm volatile("bar.sync 1, %0;" ::"n"(BUILDERS) : "memory"); }
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Address of the 16-byte chunk `chunk` (8 bfloat16) of row `m` in tile `kb` of the block's slice of
+// X: rows of 128 bytes, the chunk index XORed with the row's index in its group of 8, which is
+// where TMA's 128-byte swizzle would have put it.
+template <int MPAD>
+__device__ __forceinline__ uint32_t x_chunk_addr(uint32_t xr, int kb, int m, int chunk) {
+    return xr + (uint32_t)kb * (MPAD * 128) + (uint32_t)m * 128 + (uint32_t)((chunk ^ (m & 7)) << 4);
+}
+
+template <typename TC, int MPAD, int STAGES, int MODE, int XSRC = X_TMA>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                   TC* __restrict__ C, int M, int N, int K, long long ldc, int kb_per_split, int* error_flag) {
-    using L = Smem<MPAD, STAGES>;
+                   TC* __restrict__ C, int M, int N, int K, long long ldc, int kb_per_split, int* error_flag,
+                   const FusedArgs fa) {
+    using L = Smem<MPAD, STAGES, XSRC>;
     constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -60,8 +133,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* acc_full = bars + 2 * STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    uint64_t* x_ready = bars + 2 * STAGES + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_slot = reinterpret_cast<int*>(tmem_slot + 2);           // is this block the last of its tile?
+    float* rinv_s = reinterpret_cast<float*>(tmem_slot + 4);          // [MPAD] for X_NORM (MPAD <= 64 there)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BW;
@@ -77,9 +153,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             tc::mbar_init(tc::smem_u32(&empty[s]), 1);
         }
         tc::mbar_init(tc::smem_u32(acc_full), 1);
+        tc::mbar_init(tc::smem_u32(x_ready), BUILDERS);
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_w);
-        tc::prefetch_tensormap(&map_x);
+        if constexpr (XSRC == X_TMA) tc::prefetch_tensormap(&map_x);
     }
     if (warp == 1) {
         tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
@@ -92,7 +169,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
     if (warp == 0) {
         if (lane == 0) {
-            pdl_launch_dependents();
+            TL_STAMP(0);
+            pdl_launch_dependents();   // at once: releasing the next kernel later (after the loads, after the products) was slower
             // W is written by no kernel of the step: its first loads go out before the wait.
             const int first = min(nkb, STAGES);
             for (int i = 0; i < first; ++i) {
@@ -100,10 +178,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 tc::mbar_expect_tx(bar, L::STAGE_BYTES);
                 tc::tma_load_2d(tc::smem_u32(smem + i * L::STAGE_BYTES), &map_w, bar, (kb0 + i) * BK, n0);
             }
-            pdl_wait();   // X was written by the kernel before this one
-            for (int i = 0; i < first; ++i)
-                tc::tma_load_2d(tc::smem_u32(smem + i * L::STAGE_BYTES + L::W_BYTES), &map_x, tc::smem_u32(&full[i]),
-                                (kb0 + i) * BK, 0);
+            if constexpr (XSRC == X_TMA) {
+                pdl_wait();   // X was written by the kernel before this one
+                for (int i = 0; i < first; ++i)
+                    tc::tma_load_2d(tc::smem_u32(smem + i * L::STAGE_BYTES + L::W_BYTES), &map_x, tc::smem_u32(&full[i]),
+                                    (kb0 + i) * BK, 0);
+            }
             int issued = first;
             for (int kb = first; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
@@ -113,7 +193,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 tc::mbar_expect_tx(bar, L::STAGE_BYTES);
                 const uint32_t dst = tc::smem_u32(smem + s * L::STAGE_BYTES);
                 tc::tma_load_2d(dst, &map_w, bar, (kb0 + kb) * BK, n0);
-                tc::tma_load_2d(dst + L::W_BYTES, &map_x, bar, (kb0 + kb) * BK, 0);
+                if constexpr (XSRC == X_TMA) tc::tma_load_2d(dst + L::W_BYTES, &map_x, bar, (kb0 + kb) * BK, 0);
                 issued = kb + 1;
             }
             if (*abort_flag) {
@@ -130,6 +210,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (lane == 0) {
             constexpr uint32_t idesc = tc::idesc_bf16_f32(BW, MPAD);
             bool ok = true;
+            if constexpr (XSRC != X_TMA) ok = tc::mbar_wait(tc::smem_u32(x_ready), 0, abort_flag);
+            TL_STAMP(4);
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t round = kb / STAGES;
@@ -137,7 +219,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (!ok) break;
                 tc::tc_fence_after_sync();
                 const uint32_t w_addr = tc::smem_u32(smem + s * L::STAGE_BYTES);
-                const uint32_t x_addr = w_addr + L::W_BYTES;
+                const uint32_t x_addr = XSRC == X_TMA ? w_addr + L::W_BYTES
+                                                      : tc::smem_u32(smem + L::XR_OFFSET) + (uint32_t)kb * L::X_BYTES;
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k) {
                     const uint64_t da = tc::smem_desc_sw128(w_addr + k * UMMA_K * 2);
@@ -147,14 +230,134 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 tc::mma_commit(tc::smem_u32(&empty[s]));
             }
             if (ok) tc::mma_commit(tc::smem_u32(acc_full));
+            TL_STAMP(5);
         }
     } else {
         // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31; a lane is a row of W
         // (an output column), a column of tensor memory is a row of X.
         const int quarter = warp & 3;
         const int n = n0 + quarter * 32 + lane;
+        const int tid = threadIdx.x - 64;        // 0 .. BUILDERS - 1
+        if constexpr (XSRC != X_TMA) {
+            // Build this block's slice of X: columns [kb0 * 64, (kb0 + nkb) * 64) of rows 0 .. MPAD - 1.
+            const uint32_t xr = tc::smem_u32(smem + L::XR_OFFSET);
+            const int chunks = nkb * (BK / 8);                      // 16-byte chunks per row
+            for (int c = tid; c < (MPAD - M) * chunks; c += BUILDERS)   // rows beyond M: zeros, before the wait
+                st_shared_v4(x_chunk_addr<MPAD>(xr, (c % chunks) / 8, M + c / chunks, (c % chunks) % 8), 0u, 0u, 0u, 0u);
+            pdl_wait();
+            if (tid == 0) TL_STAMP(1);
+            if constexpr (XSRC == X_NORM) {
+                if (tid < M) {
+                    float ss = 0.f;
+                    for (int p0 = 0; p0 < fa.n_sq_parts; p0 += 8) {
+                        float t[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) t[u] = p0 + u < fa.n_sq_parts ? __ldcg(fa.sq_parts + (size_t)(p0 + u) * M + tid) : 0.f;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) ss += t[u];
+                    }
+                    rinv_s[tid] = 1.0f / sqrtf(ss / (float)K + fa.eps);
+                }
+                // the loads of the first chunk go out before the barrier
+                float4 a[2], b[2], ga[2], gb[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int c = tid + u * BUILDERS;
+                    const int k = (kb0 * (BK / 8) + c % chunks) * 8;
+                    const bool live = c < M * chunks && k < K;
+                    const float* src = fa.x_resid + (size_t)(c / chunks) * fa.x_ld + k;
+                    a[u] = live ? __ldcg(reinterpret_cast<const float4*>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    b[u] = live ? __ldcg(reinterpret_cast<const float4*>(src + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    ga[u] = live ? *reinterpret_cast<const float4*>(fa.gain + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    gb[u] = live ? *reinterpret_cast<const float4*>(fa.gain + k + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                builders_sync();
+                for (int c0 = 0; c0 < M * chunks; c0 += 2 * BUILDERS) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int c = c0 + tid + u * BUILDERS;
+                        if (c >= M * chunks) continue;
+                        const int m = c / chunks, j = c % chunks;
+                        if (c0 > 0) {
+                            const int k = (kb0 * (BK / 8) + j) * 8;
+                            const bool live = k < K;
+                            const float* src = fa.x_resid + (size_t)m * fa.x_ld + k;
+                            a[u] = live ? __ldcg(reinterpret_cast<const float4*>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            b[u] = live ? __ldcg(reinterpret_cast<const float4*>(src + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            ga[u] = live ? *reinterpret_cast<const float4*>(fa.gain + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            gb[u] = live ? *reinterpret_cast<const float4*>(fa.gain + k + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        const float r = rinv_s[m], o = fa.gain_offset;
+                        st_shared_v4(x_chunk_addr<MPAD>(xr, j / 8, m, j % 8),
+                                     pack_bf16x2(a[u].x * r * (ga[u].x + o), a[u].y * r * (ga[u].y + o)),
+                                     pack_bf16x2(a[u].z * r * (ga[u].z + o), a[u].w * r * (ga[u].w + o)),
+                                     pack_bf16x2(b[u].x * r * (gb[u].x + o), b[u].y * r * (gb[u].y + o)),
+                                     pack_bf16x2(b[u].z * r * (gb[u].z + o), b[u].w * r * (gb[u].w + o)));
+                    }
+                }
+            } else {
+                // silu(gate) * up from the partial sums; the 8 columns of a chunk lie in one group.  Two
+                // chunks and four slices at a time keep enough loads in flight: the block waits for this.
+                for (int c0 = 0; c0 < M * chunks; c0 += 2 * BUILDERS) {
+                    float g[2][8], up[2][8];
+                    const float* base[2];
+                    bool live[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = c0 + tid + h * BUILDERS;
+                        const int col = (kb0 * (BK / 8) + c % chunks) * 8;
+                        live[h] = c < M * chunks && col < K;
+                        base[h] = fa.gu + (size_t)(live[h] ? c / chunks : 0) * fa.gu_ld +
+                                  (live[h] ? 2 * fa.group * (col / fa.group) + col % fa.group : 0);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) g[h][i] = up[h][i] = 0.f;
+                    }
+                    for (int sp0 = 0; sp0 < fa.gu_splits; sp0 += 4) {
+                        float4 t[2][4][4];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const bool on = live[h] && sp0 + u < fa.gu_splits;
+                                const float* q = base[h] + (size_t)(sp0 + u) * fa.gu_split_stride;
+                                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                                t[h][u][0] = on ? __ldcg(reinterpret_cast<const float4*>(q)) : z;
+                                t[h][u][1] = on ? __ldcg(reinterpret_cast<const float4*>(q + 4)) : z;
+                                t[h][u][2] = on ? __ldcg(reinterpret_cast<const float4*>(q + fa.group)) : z;
+                                t[h][u][3] = on ? __ldcg(reinterpret_cast<const float4*>(q + fa.group + 4)) : z;
+                            }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                g[h][0] += t[h][u][0].x; g[h][1] += t[h][u][0].y; g[h][2] += t[h][u][0].z; g[h][3] += t[h][u][0].w;
+                                g[h][4] += t[h][u][1].x; g[h][5] += t[h][u][1].y; g[h][6] += t[h][u][1].z; g[h][7] += t[h][u][1].w;
+                                up[h][0] += t[h][u][2].x; up[h][1] += t[h][u][2].y; up[h][2] += t[h][u][2].z; up[h][3] += t[h][u][2].w;
+                                up[h][4] += t[h][u][3].x; up[h][5] += t[h][u][3].y; up[h][6] += t[h][u][3].z; up[h][7] += t[h][u][3].w;
+                            }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = c0 + tid + h * BUILDERS;
+                        if (c >= M * chunks) continue;
+                        float x[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) x[i] = g[h][i] / (1.0f + expf(-g[h][i])) * up[h][i];
+                        st_shared_v4(x_chunk_addr<MPAD>(xr, (c % chunks) / 8, c / chunks, (c % chunks) % 8), pack_bf16x2(x[0], x[1]),
+                                     pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+                    }
+                }
+            }
+            if (tid == 0) TL_STAMP(2);
+            tc::fence_proxy_async();          // the tensor core reads what these threads wrote
+            tc::mbar_arrive(tc::smem_u32(x_ready));
+            if (tid == 0) TL_STAMP(3);
+        } else if constexpr (MODE == OUT_RESIDUAL) {
+            pdl_wait();                       // the residual is written by kernels before this one
+        }
         const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(acc_full), 0, abort_flag));
         tc::tc_fence_after_sync();
+        if (tid == 0) TL_STAMP(6);
         if (ok) {
 #pragma unroll 1
             for (int c0 = 0; c0 < MPAD; c0 += 16) {
@@ -174,12 +377,73 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                         const float u = __shfl_down_sync(0xffffffffu, v, 16);
                         if (m < M && lane < 16 && n < N)
                             C[(size_t)m * ldc + (n0 + quarter * 32) / 2 + lane] = from_float<TC>(silu(v) * u);
-                    } else if constexpr (MODE == OUT_PARTIAL) {
+                    } else if constexpr (MODE == OUT_PARTIAL || MODE == OUT_RESIDUAL) {
                         if (m < M && n < N) C[((size_t)split * M + m) * ldc + n] = from_float<TC>(v);
                     } else {
                         if (m < M && n < N) C[(size_t)m * ldc + n] = from_float<TC>(v);
                     }
                 }
+            }
+        }
+        if constexpr (MODE == OUT_RESIDUAL) {
+            // The block that finishes its tile last adds the slices, in slice order, to the residual.
+            if (tid == 0) TL_STAMP(7);
+            __threadfence();
+            builders_sync();
+            if (tid == 0) TL_STAMP(8);
+            if (tid == 0) *last_slot = ok && atomicAdd(fa.tickets + blockIdx.x, 1) == (int)gridDim.y - 1;
+            builders_sync();
+            if (tid == 0) TL_STAMP(9);
+            if (*last_slot) {
+                __threadfence();
+                const int S = (int)gridDim.y;
+                const float* P = reinterpret_cast<const float*>(C);
+                // a warp takes a row: 32 lanes x 4 columns are the tile's 128 columns.  Two rows and
+                // sixteen slices at a time: this block works alone now, so its loads must overlap.
+                const int nn = n0 + lane * 4;
+                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int m0 = tid >> 5; m0 < M; m0 += 2 * (BUILDERS / 32)) {
+                    float4 acc[2] = {z, z}, r[2];
+                    bool live[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int m = m0 + h * (BUILDERS / 32);
+                        live[h] = m < M && nn < N;
+                        r[h] = live[h] ? __ldcg(reinterpret_cast<const float4*>(fa.resid + (size_t)m * fa.resid_ld + nn)) : z;
+                    }
+                    for (int s0 = 0; s0 < S; s0 += 16) {
+                        float4 t[2][16];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int u = 0; u < 16; ++u)
+                                t[h][u] = live[h] && s0 + u < S
+                                              ? __ldcg(reinterpret_cast<const float4*>(
+                                                    P + ((size_t)(s0 + u) * M + m0 + h * (BUILDERS / 32)) * ldc + nn))
+                                              : z;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int u = 0; u < 16; ++u) {
+                                acc[h].x += t[h][u].x; acc[h].y += t[h][u].y; acc[h].z += t[h][u].z; acc[h].w += t[h][u].w;
+                            }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int m = m0 + h * (BUILDERS / 32);
+                        if (m >= M) continue;                       // uniform over the warp
+                        float sq = 0.f;
+                        if (live[h]) {
+                            const float4 v = make_float4(acc[h].x + r[h].x, acc[h].y + r[h].y, acc[h].z + r[h].z, acc[h].w + r[h].w);
+                            *reinterpret_cast<float4*>(fa.resid + (size_t)m * fa.resid_ld + nn) = v;
+                            sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                        }
+                        sq = warp_sum(sq);
+                        if (lane == 0) fa.sq_out[(size_t)blockIdx.x * M + m] = sq;
+                    }
+                }
+                if (tid == 0) TL_STAMP(10);
+                if (tid == 0) fa.tickets[blockIdx.x] = 0;      // ready for the next launch
             }
         }
     }
@@ -231,12 +495,40 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, 
         }
         LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch_cluster(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), L::TOTAL, s,
                                                                 true, (unsigned)splits, mw, mx, (TC*)C, M, N, K, ldc,
-                                                                kb_per_split, error_flag));
+                                                                kb_per_split, error_flag, FusedArgs{}));
     } else {
         LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), L::TOTAL, s,
-                                                        true, mw, mx, (TC*)C, M, N, K, ldc, kb_per_split, error_flag));
+                                                        true, mw, mx, (TC*)C, M, N, K, ldc, kb_per_split, error_flag, FusedArgs{}));
     }
     return LLMK_OK;
+}
+
+template <int MPAD, int STAGES, int MODE, int XSRC>
+int launch_fused(const CUtensorMap& mw, const CUtensorMap& mx, float* C, int M, int N, int K, long long ldc, int splits,
+                 int kb_per_split, int* error_flag, const FusedArgs& fa, cudaStream_t s) {
+    using L = Smem<MPAD, STAGES, XSRC>;
+    auto kernel = gemm_skinny_kernel<float, MPAD, STAGES, MODE, XSRC>;
+    const int bytes = L::total(kb_per_split);
+    if (bytes > MAX_SMEM)
+        LLMK_FAIL("gemm_skinny_fused: %d rows x %d columns of X need %d bytes of shared memory (limit %d)", MPAD,
+                  kb_per_split * BK, bytes, MAX_SMEM);
+    static int configured = 0;   // per instantiation: the largest size asked for so far
+    if (bytes > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) LLMK_FAIL("gemm_skinny_fused: cannot raise shared memory to %d: %s", bytes, cudaGetErrorString(e));
+        configured = bytes;
+    }
+    LLMK_CHECK_LAUNCH_RC("gemm_skinny_fused", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), (size_t)bytes, s,
+                                                          true, mw, mx, C, M, N, K, ldc, kb_per_split, error_flag, fa));
+    return LLMK_OK;
+}
+
+template <int MODE, int XSRC>
+int dispatch_fused(const CUtensorMap& mw, const CUtensorMap& mx, float* C, int M, int N, int K, long long ldc, int splits,
+                   int kb_per_split, int* error_flag, const FusedArgs& fa, cudaStream_t s) {
+    if (M <= 16) return launch_fused<16, 6, MODE, XSRC>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, fa, s);
+    if (M <= 32) return launch_fused<32, 5, MODE, XSRC>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, fa, s);
+    return launch_fused<64, 4, MODE, XSRC>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, fa, s);
 }
 
 template <typename TC, int MODE>
@@ -329,3 +621,86 @@ LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, i
     if (out_dtype == LLMK_F32) return dispatch_rows<float, OUT_DIRECT>(mw, X, C, M, N, K, ldx, ldc, 1, per, error_flag, s);
     LLMK_FAIL("gemm_skinny: unknown output dtype %d", out_dtype);
 }
+
+LLMK_EXPORT int llmk_gemm_skinny_fused_max_rows() { return 64; }
+
+// Can the block-built X of the fused forms be held in shared memory?  `splits` slices of K for M rows.
+LLMK_EXPORT int llmk_gemm_skinny_fused_fits(int M, int K, int splits) {
+    if (M <= 0 || M > 64 || K <= 0 || splits < 1) return 0;
+    const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+    const int stages = mpad == 16 ? 6 : mpad == 32 ? 5 : 4;
+    const int per = ceil_div(ceil_div(K, BK), splits);
+    return stages * BW * BK * 2 + 1024 + per * mpad * BK * 2 + 1024 <= MAX_SMEM ? 1 : 0;
+}
+
+// The fused forms of the few-rows product (M <= 64, bfloat16 weights, float32 slices in C):
+//   x_source 0   X is a bfloat16 array [M, K] (ldx), loaded by TMA
+//            1   X is built from the float32 rows `x_resid` (x_ld): RMS-normalised with the row sums of
+//                squares given in `n_sq_parts` parts `sq_parts[p * M + m]`, times (gain + gain_offset)
+//            2   X is silu(gate) * up from `gu_splits` float32 slices `gu` of a packed gate/up product
+//                ([M, gu_ld] each, `gu_split_stride` floats apart, columns alternating in groups of `group`)
+//   resid != null: after the slices are written, the last block of each 128-column tile adds them to
+//                resid[M, resid_ld] and writes the tile's share of every row's sum of squares to
+//                sq_out[tile * M + m]; `tickets` holds one zeroed int per tile and is left zeroed.
+//                Otherwise the slices in C are the result (as mode 1 of llmk_gemm_skinny).
+LLMK_EXPORT int llmk_gemm_skinny_fused(float* C, const void* W, int M, int N, int K, long long ldw, long long ldc,
+                                       int splits, int x_source, const void* X, long long ldx, const float* x_resid,
+                                       long long x_ld, const float* sq_parts, int n_sq_parts, const float* gain,
+                                       float eps, float gain_offset, const float* gu, int gu_splits,
+                                       long long gu_split_stride, long long gu_ld, int group, float* resid,
+                                       long long resid_ld, float* sq_out, int* tickets, int* error_flag, void* stream) {
+    if (M <= 0 || N <= 0) return LLMK_OK;
+    if (M > 64) LLMK_FAIL("gemm_skinny_fused: M=%d above 64", M);
+    if (K <= 0 || K % 8 != 0 || ldw % 8 != 0 || !host_aligned16(W))
+        LLMK_FAIL("gemm_skinny_fused: W not usable (K=%d ldw=%lld must be multiples of 8, base 16-byte aligned)", K, ldw);
+    const int num_kb = ceil_div(K, BK);
+    if (splits < 1 || splits > num_kb || splits > 65535) LLMK_FAIL("gemm_skinny_fused: %d slices for K=%d", splits, K);
+    const int per = ceil_div(num_kb, splits);
+    if ((splits - 1) * per >= num_kb) LLMK_FAIL("gemm_skinny_fused: %d slices of K=%d would leave one empty", splits, K);
+    if (ldc < N || ldc % 4 != 0 || !host_aligned16(C)) LLMK_FAIL("gemm_skinny_fused: ldc=%lld not usable for N=%d", ldc, N);
+    FusedArgs fa{};
+#ifdef LLMK_SKINNY_TIMELINE
+    static int tl_next = 0;
+    fa.tl_id = tl_next++ % 8;
+#endif
+    CUtensorMap mw, mx{};
+    if (!tc_host::cached_map_bf16_2d(&mw, W, N, K, ldw, BW))
+        LLMK_FAIL("gemm_skinny_fused: cuTensorMapEncodeTiled failed for W (N=%d K=%d ldw=%lld)", N, K, ldw);
+    if (x_source == X_TMA) {
+        if (!X || ldx % 8 != 0 || !host_aligned16(X)) LLMK_FAIL("gemm_skinny_fused: X not usable (ldx=%lld)", ldx);
+        const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        if (!tc_host::cached_map_bf16_2d(&mx, X, M, K, ldx, mpad))
+            LLMK_FAIL("gemm_skinny_fused: cuTensorMapEncodeTiled failed for X (M=%d K=%d ldx=%lld)", M, K, ldx);
+    } else if (x_source == X_NORM) {
+        if (!x_resid || !sq_parts || !gain || n_sq_parts < 1 || x_ld < K || x_ld % 4 != 0 || !host_aligned16(x_resid) ||
+            !host_aligned16(gain))
+            LLMK_FAIL("gemm_skinny_fused: the rows to normalise are not usable (x_ld=%lld, %d parts)", x_ld, n_sq_parts);
+        fa.x_resid = x_resid; fa.x_ld = x_ld; fa.sq_parts = sq_parts; fa.n_sq_parts = n_sq_parts;
+        fa.gain = gain; fa.eps = eps; fa.gain_offset = gain_offset;
+    } else if (x_source == X_GATED) {
+        if (!gu || gu_splits < 1 || group < 8 || group % 8 != 0 || K % group != 0 || gu_ld < 2 * (long long)K || gu_ld % 4 != 0 ||
+            gu_split_stride % 4 != 0 || !host_aligned16(gu))
+            LLMK_FAIL("gemm_skinny_fused: the gate/up slices are not usable (group=%d gu_ld=%lld K=%d)", group, gu_ld, K);
+        fa.gu = gu; fa.gu_splits = gu_splits; fa.gu_split_stride = gu_split_stride; fa.gu_ld = gu_ld; fa.group = group;
+    } else {
+        LLMK_FAIL("gemm_skinny_fused: unknown source of X %d", x_source);
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (resid) {
+        if (!sq_out || !tickets || N % 4 != 0 || resid_ld < N || resid_ld % 4 != 0 || !host_aligned16(resid))
+            LLMK_FAIL("gemm_skinny_fused: the residual is not usable (N=%d resid_ld=%lld)", N, resid_ld);
+        fa.resid = resid; fa.resid_ld = resid_ld; fa.sq_out = sq_out; fa.tickets = tickets;
+        if (x_source == X_TMA) return dispatch_fused<OUT_RESIDUAL, X_TMA>(mw, mx, C, M, N, K, ldc, splits, per, error_flag, fa, s);
+        if (x_source == X_NORM) return dispatch_fused<OUT_RESIDUAL, X_NORM>(mw, mx, C, M, N, K, ldc, splits, per, error_flag, fa, s);
+        return dispatch_fused<OUT_RESIDUAL, X_GATED>(mw, mx, C, M, N, K, ldc, splits, per, error_flag, fa, s);
+    }
+    if (x_source == X_TMA) return dispatch_fused<OUT_PARTIAL, X_TMA>(mw, mx, C, M, N, K, ldc, splits, per, error_flag, fa, s);
+    if (x_source == X_NORM) return dispatch_fused<OUT_PARTIAL, X_NORM>(mw, mx, C, M, N, K, ldc, splits, per, error_flag, fa, s);
+    return dispatch_fused<OUT_PARTIAL, X_GATED>(mw, mx, C, M, N, K, ldc, splits, per, error_flag, fa, s);
+}
+
+#ifdef LLMK_SKINNY_TIMELINE
+LLMK_EXPORT int llmk_gemm_skinny_timeline(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_skinny_tl, sizeof(g_skinny_tl)) == cudaSuccess ? LLMK_OK : 1;
+}
+#endif

@@ -92,6 +92,8 @@ class DecoderModel:
         H, V = self.spec.hidden_size, self.spec.vocab_size
         ws = ctx.workspace
         normed = ws.buffer("final_normed", n_rows, H, self.dtype, capacity_rows=max(n_rows, 64))
+        if isinstance(delta, ops.RowSquares):
+            delta = None                # the last block added its output to the residual itself
         self.final_norm.add_norm(resid, delta, normed, rows=rows)
         if out is None:
             out = torch.empty((n_rows, V), dtype=torch.float32, device=self.device)

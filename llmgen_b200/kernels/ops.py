@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -83,6 +83,48 @@ class Partials:
     def sum(self) -> torch.Tensor:
         """The finished product (float32), for callers that have no kernel taking slices."""
         return self.tensor.sum(dim=0)
+
+
+class RowSquares:
+    """What a product leaves when it added its result to the float32 residual itself: for every row
+    the sum of squares of the updated residual, in `parts` parts ([parts, rows] float32, one per
+    128 columns), for the RMSNorm that follows."""
+
+    def __init__(self, tensor: torch.Tensor):
+        if tensor.dim() != 2 or tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError("row sums of squares are a contiguous float32 [parts, rows] array")
+        self.tensor = tensor
+        self.parts, self.rows = tensor.shape
+
+
+class NormedRows:
+    """Rows of the float32 array `resid`, RMS-normalised, not yet computed: a product that can build
+    its operand itself takes this in place of the array (`gemm_skinny_fused`); `materialize` is the
+    same through the norm kernel.  y = resid / sqrt(sum of squares / width + eps) * (gain + offset)."""
+
+    def __init__(self, resid: torch.Tensor, squares: RowSquares, gain: torch.Tensor, eps: float, offset: float = 0.0):
+        if resid.dtype != torch.float32 or resid.dim() != 2 or squares.rows != resid.shape[0]:
+            raise KernelError("rows to normalise: a float32 [rows, width] array and one sum of squares per row")
+        self.resid, self.squares, self.gain, self.eps, self.offset = resid, squares, gain, float(eps), float(offset)
+        self.shape = resid.shape
+
+    def materialize(self, out: torch.Tensor) -> torch.Tensor:
+        add_rmsnorm(self.resid, None, self.gain, out, self.eps, self.offset)
+        return out
+
+
+class GatedRows:
+    """silu(gate) * up of a packed gate/up product that came back as slices, not yet computed."""
+
+    def __init__(self, gate_up: Partials, group: int):
+        if gate_up.cols % 2 != 0:
+            raise KernelError("a packed gate/up product has an even number of columns")
+        self.gate_up, self.group = gate_up, int(group)
+        self.shape = (gate_up.rows, gate_up.cols // 2)
+
+    def materialize(self, out: torch.Tensor) -> torch.Tensor:
+        silu_mul(out, self.gate_up, group=self.group)
+        return out
 
 
 # ---------------------------------------------------------------------------- elementwise
@@ -311,6 +353,81 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int =
                                      c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(ldc),
                                      c_int(splits), c_int(mode), c_int(dtype_code(out.dtype)),
                                      _ptr(tc_error_flag(a.device)), _stream()))
+
+
+SKINNY_FUSED_MAX_ROWS = 64
+_fused_fits: Dict[Tuple[int, int, int], bool] = {}
+
+
+def gemm_skinny_fused_usable(x, w: torch.Tensor, splits: int, add_to: Optional[torch.Tensor] = None) -> bool:
+    """Can `gemm_skinny_fused` take this operand (an array, `NormedRows` or `GatedRows`) and, with
+    `add_to`, add the product to that float32 array?"""
+    M, K = x.shape
+    N = w.shape[0]
+    if not (0 < M <= SKINNY_FUSED_MAX_ROWS) or w.dtype != torch.bfloat16 or w.shape[1] != K or K % 8 != 0:
+        return False
+    if _row_stride(w) % 8 != 0 or w.data_ptr() % 16 != 0 or N % 4 != 0:
+        return False
+    if isinstance(x, NormedRows):
+        if x.resid.stride(1) != 1 or x.resid.stride(0) % 4 != 0 or x.resid.data_ptr() % 16 != 0 or x.gain.dtype != torch.float32:
+            return False
+    elif isinstance(x, GatedRows):
+        if x.group % 8 != 0 or K % x.group != 0:
+            return False
+    elif not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+        return False
+    if not isinstance(x, torch.Tensor):
+        key = (M, K, splits)
+        fits = _fused_fits.get(key)
+        if fits is None:
+            fits = bool(build.load("gemm_skinny").llmk_gemm_skinny_fused_fits(c_int(M), c_int(K), c_int(splits)))
+            _fused_fits[key] = fits
+        if not fits:
+            return False
+    if add_to is not None:
+        if (add_to.dtype != torch.float32 or add_to.shape != (M, N) or add_to.stride(1) != 1 or add_to.stride(0) % 4 != 0
+                or add_to.data_ptr() % 16 != 0):
+            return False
+    return True
+
+
+def gemm_skinny_fused(slices: torch.Tensor, x, w: torch.Tensor, add_to: Optional[torch.Tensor] = None,
+                      squares_out: Optional[torch.Tensor] = None, tickets: Optional[torch.Tensor] = None) -> None:
+    """The few-rows product with its neighbours folded in (csrc/gemm_skinny.cu).  `slices` is float32
+    [splits, M, N]; `x` is a bfloat16 array [M, K], a `NormedRows` or a `GatedRows`, which the blocks
+    then compute themselves.  With `add_to` (float32 [M, N]) the sum of the slices is added to it by
+    the last block of each 128-column tile, and `squares_out` [ceil(N / 128), M] receives the parts of
+    each row's sum of squares; `tickets` is a zeroed int32 array with one entry per tile (left zeroed)."""
+    lib = build.load("gemm_skinny")
+    M, K = x.shape
+    N = w.shape[0]
+    if slices.dim() != 3 or slices.shape[1] != M or slices.shape[2] != N or slices.dtype != torch.float32 or not slices.is_contiguous():
+        raise KernelError("gemm_skinny_fused: the slices go to a contiguous float32 [splits, M, N] array")
+    tiles = (N + 127) // 128
+    null = c_void_p(None)
+    xs, xp, ldx = 0, null, 0
+    resid_p, x_ld, sq_p, n_sq, gain_p, eps, off = null, 0, null, 0, null, 0.0, 0.0
+    gu_p, gu_splits, gu_stride, gu_ld, group = null, 0, 0, 0, 0
+    if isinstance(x, NormedRows):
+        xs, resid_p, x_ld, sq_p, n_sq = 1, _ptr(x.resid), x.resid.stride(0), _ptr(x.squares.tensor), x.squares.parts
+        gain_p, eps, off = _ptr(x.gain), x.eps, x.offset
+    elif isinstance(x, GatedRows):
+        g = x.gate_up
+        xs, gu_p, gu_splits, gu_stride, gu_ld, group = 2, _ptr(g.tensor), g.splits, g.split_stride, g.cols, x.group
+    else:
+        xp, ldx = _ptr(x), _row_stride(x)
+    add_p, add_ld, sqo_p, tick_p = null, 0, null, null
+    if add_to is not None:
+        if squares_out is None or tickets is None or squares_out.numel() < tiles * M or tickets.numel() < tiles \
+                or squares_out.dtype != torch.float32 or tickets.dtype != torch.int32:
+            raise KernelError(f"gemm_skinny_fused: adding to the residual needs {tiles * M} float32 for the sums of "
+                              f"squares and {tiles} zeroed int32 tickets")
+        add_p, add_ld, sqo_p, tick_p = _ptr(add_to), add_to.stride(0), _ptr(squares_out), _ptr(tickets)
+    _check(lib, lib.llmk_gemm_skinny_fused(
+        _ptr(slices), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(w)), c_longlong(N),
+        c_int(slices.shape[0]), c_int(xs), xp, c_longlong(ldx), resid_p, c_longlong(x_ld), sq_p, c_int(n_sq), gain_p,
+        c_float(eps), c_float(off), gu_p, c_int(gu_splits), c_longlong(gu_stride), c_longlong(gu_ld), c_int(group),
+        add_p, c_longlong(add_ld), sqo_p, tick_p, _ptr(tc_error_flag(w.device)), _stream()))
 
 
 def gemm_skinny_usable(a: torch.Tensor, w: torch.Tensor) -> bool:

@@ -129,7 +129,9 @@ class GQAAttention(Mixer):
             return 1, 0
         return parts, 0
 
-    def forward(self, ctx, x: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+    fuses_neighbours = True      # takes an operand that is not computed yet, adds to the residual when offered it
+
+    def forward(self, ctx, x, cache: LayerCache, add_to: torch.Tensor = None):
         T = ctx.n_tokens
         ws = ctx.workspace
         group = ctx.groups[cache.group]
@@ -148,7 +150,7 @@ class GQAAttention(Mixer):
                          prep=dict(packed=packed, nk=nk, rot=rot, positions=ctx.positions, slots=group.slots, cos=cos,
                                    sin=sin, q_gain=self.q_gain, k_gain=self.k_gain, eps=self.norm_eps,
                                    q_offset=self.q_off, k_offset=self.k_off))
-            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype, add_to=add_to)
         q = ws.buffer("attn_q", T, self.nq * self.hd, self.dtype) if isinstance(packed, ops.Partials) else packed
         ops.attn_prep(packed, cache.k, cache.v, ctx.positions, group.slots, cos, sin, self.q_gain, self.k_gain,
                       self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q)

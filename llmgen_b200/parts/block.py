@@ -5,6 +5,7 @@ from typing import Optional
 
 import torch
 
+from ..kernels import ops
 from .base import LayerCache, Part
 from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward_class, mixer_class, norm_class,
                        register_block)
@@ -17,7 +18,9 @@ class PreNormBlock(Part):
     The residual stream is float32 and lives in one buffer.  Each sum is folded into the norm
     that follows it: the block receives the previous block's output as `delta`, adds it in its
     first norm, adds the mixer's output in its second norm and returns the feed-forward's
-    output as the next `delta`."""
+    output as the next `delta`.  Parts that declare `fuses_neighbours` are offered the residual
+    (`add_to`) and may add their output themselves; they then return `ops.RowSquares`, which says so
+    and carries what the next norm needs, and that norm is handed to its consumer uncomputed."""
 
     @staticmethod
     def weight_decls(spec: PreNormBlockSpec):
@@ -40,13 +43,27 @@ class PreNormBlock(Part):
         self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device)
         self.ffn = build_feed_forward(spec.ffn, weights, dtype, device)
 
-    def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], cache: LayerCache) -> torch.Tensor:
+    def _normed(self, ctx, norm, consumer, resid, delta):
+        """The consumer's input: norm(resid + delta).  When `delta` is an `ops.RowSquares` the sum is
+        already in `resid`; a norm that can defer itself and a consumer that takes deferred operands
+        then get an `ops.NormedRows` and no kernel runs here."""
+        if isinstance(delta, ops.RowSquares):
+            if hasattr(norm, "deferred") and getattr(consumer, "fuses_neighbours", False):
+                return norm.deferred(resid, delta)
+            delta = None
         T, H = resid.shape
-        normed = ctx.workspace.buffer("block_normed", T, H, self.dtype)
-        self.mixer_norm.add_norm(resid, delta, normed)
-        mixed = self.mixer.forward(ctx, normed, cache)
-        self.ffn_norm.add_norm(resid, mixed, normed)
-        return self.ffn.forward(ctx, normed)
+        return norm.add_norm(resid, delta, ctx.workspace.buffer("block_normed", T, H, self.dtype))
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
+        x = self._normed(ctx, self.mixer_norm, self.mixer, resid, delta)
+        if getattr(self.mixer, "fuses_neighbours", False):
+            mixed = self.mixer.forward(ctx, x, cache, add_to=resid)
+        else:
+            mixed = self.mixer.forward(ctx, x, cache)
+        x = self._normed(ctx, self.ffn_norm, self.ffn, resid, mixed)
+        if getattr(self.ffn, "fuses_neighbours", False):
+            return self.ffn.forward(ctx, x, add_to=resid)
+        return self.ffn.forward(ctx, x)
 
 
 register_block("prenorm", PreNormBlock)

@@ -27,6 +27,11 @@ from ..kernels import ops
 
 _FORCE = os.environ.get("LLMGEN_GEMM", "")
 _SPLITK = os.environ.get("LLMGEN_SPLITK", "")      # "cluster": add the slices of K up inside a thread-block cluster
+# "chain": at up to 16 rows the few-rows products of a layer build their operands themselves (norm,
+# gated activation) and add their results to the residual.  Measured slower than the separate
+# kernels (the same dependent memory round trips, now inside the products): not the default.
+FUSE_CHAIN = os.environ.get("LLMGEN_FUSE", "") == "chain"
+FUSE_CHAIN_MAX_ROWS = 16
 
 GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny")
 
@@ -50,9 +55,47 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def linear_sliced(ws, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype):
+def _fused(ws, name: str, x, w: torch.Tensor, add_to):
+    """The few-rows product with its neighbours folded in, when it can take these operands: the
+    slices as `ops.Partials`, or, with `add_to`, `ops.RowSquares` after the sum went into `add_to`.
+    None: it cannot."""
+    if _FORCE != "" or _SPLITK != "" or w.dtype != torch.bfloat16:
+        return None
+    M, K = x.shape
+    N = w.shape[0]
+    if not (0 < M <= min(FUSE_CHAIN_MAX_ROWS, ops.SKINNY_FUSED_MAX_ROWS)):
+        return None
+    splits = ops.gemm_skinny_splits(M, N, K)
+    if not ops.gemm_skinny_fused_usable(x, w, splits, add_to=add_to):
+        return None
+    part = ws.flat(name + "_slices", splits * M * N, torch.float32).view(splits, M, N)
+    if add_to is None:
+        ops.gemm_skinny_fused(part, x, w)
+        return ops.Partials(part)
+    tiles = (N + 127) // 128
+    squares = ws.flat(name + "_squares", tiles * M, torch.float32).view(tiles, M)
+    tickets = ws.flat(name + "_tickets", tiles, torch.int32, zero=True)
+    ops.gemm_skinny_fused(part, x, w, add_to=add_to, squares_out=squares, tickets=tickets)
+    return ops.RowSquares(squares)
+
+
+def linear_sliced(ws, name: str, x, w: torch.Tensor, out_dtype: torch.dtype, add_to: torch.Tensor = None):
     """x W^T into the workspace buffer `name`: the finished [M, N] array, or, when the few-rows
-    kernel cuts the product along K, an `ops.Partials` for a consumer that adds the slices."""
+    kernel cuts the product along K, an `ops.Partials` for a consumer that adds the slices.
+
+    `x` may be an operand that is not computed yet (`ops.NormedRows`, `ops.GatedRows`): the few-rows
+    kernel builds it block by block, otherwise it is computed here first.  With `add_to` (the
+    float32 residual) the kernel may add the product to it and return `ops.RowSquares`; whatever
+    else comes back has not been added."""
+    lazy = not isinstance(x, torch.Tensor)
+    if lazy or (add_to is not None and FUSE_CHAIN):
+        done = _fused(ws, name, x, w, add_to)
+        if done is None and add_to is not None and lazy:
+            done = _fused(ws, name, x, w, None)          # the operand at least
+        if done is not None:
+            return done
+        if lazy:
+            x = x.materialize(ws.buffer(name + "_x", x.shape[0], x.shape[1], out_dtype))
     M, N = x.shape[0], w.shape[0]
     if M > 0 and x.dtype == torch.bfloat16 and _FORCE == "" and ops.gemm_skinny_usable(x, w):
         if M <= ops.SKINNY_CLUSTER_MAX_ROWS and _SPLITK == "cluster":

@@ -5,6 +5,7 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward
+from . import linear as linear_module
 from .linear import GEMM_MODULES, gated_product_usable, linear, linear_sliced
 from .registry import register_feed_forward
 from .spec import GatedMLPSpec, WeightDecl
@@ -58,10 +59,27 @@ class GatedMLP(FeedForward):
         self.w_gate_up = packed.to(device=device, dtype=dtype).contiguous()
         self.w_down = weights.device_tensor(spec.down_proj, dtype, device)
 
-    def forward(self, ctx, x: torch.Tensor):
+    fuses_neighbours = True      # takes operands that are not computed yet, adds to the residual when offered it
+
+    def forward(self, ctx, x, add_to: torch.Tensor = None):
         T = x.shape[0]
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
+        few = self.dtype == torch.bfloat16 and T <= linear_module.FUSE_CHAIN_MAX_ROWS and linear_module.FUSE_CHAIN
+        if not isinstance(x, torch.Tensor) and not few:
+            x = x.materialize(ws.buffer("ffn_x", T, H, self.dtype))
+        lazy = not isinstance(x, torch.Tensor)
+        whole = (not lazy and self.group == GATE_UP_GROUP and gated_product_usable(x, self.w_gate_up)
+                 and ops.gemm_skinny_splits(T, 2 * F, H) == 1)          # one block column streams all of K: gated epilogue
+        if few and (lazy or add_to is not None) and not whole:
+            # few rows: the norm before, the activation between and the residual sum after are
+            # folded into the two products where the few-rows kernel can take them
+            gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
+            if isinstance(gate_up, ops.Partials) and self.group % 8 == 0:
+                return linear_sliced(ws, "ffn_out", ops.GatedRows(gate_up, self.group), self.w_down, self.dtype, add_to=add_to)
+            act = ws.buffer("ffn_act", T, F, self.dtype)
+            ops.silu_mul(act, gate_up, group=self.group)
+            return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
         act = ws.buffer("ffn_act", T, F, self.dtype)
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
         if gated and T <= ops.SKINNY_MAX_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
@@ -71,7 +89,7 @@ class GatedMLP(FeedForward):
         else:
             gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
             ops.silu_mul(act, gate_up, group=self.group)
-        return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
+        return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

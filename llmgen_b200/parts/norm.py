@@ -36,5 +36,10 @@ class RMSNorm(Part):
         ops.add_rmsnorm(resid, delta, self.weight, out, self.eps, self.offset, rows=rows)
         return out
 
+    def deferred(self, resid: torch.Tensor, squares: "ops.RowSquares") -> "ops.NormedRows":
+        """The norm of `resid` as an operand that the consuming product computes itself, given the
+        rows' sums of squares that the product before it left."""
+        return ops.NormedRows(resid, squares, self.weight, self.eps, self.offset)
+
 
 register_norm("rmsnorm", RMSNorm)

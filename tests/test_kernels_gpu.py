@@ -388,6 +388,146 @@ def test_gemm_skinny_refuses_what_it_cannot_do(ops):
         ops.gemm_skinny(torch.empty(4, 64, dtype=torch.bfloat16, device="cuda"), big[:, 1:65], w)
 
 
+def _squares(resid, parts):
+    """Row sums of squares of `resid` cut into `parts` unequal parts [parts, rows] (their sum is what counts)."""
+    n, H = resid.shape
+    sq = (resid.double() ** 2).sum(1)
+    w = torch.linspace(1, 2, parts, dtype=torch.float64)
+    return ((w / w.sum())[:, None] * sq[None, :].cpu()).float().cuda().contiguous()
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 4096, 1024, 4), (1, 136, 200, 2), (33, 1024, 3072, 12), (16, 6144, 1024, 3),
+                                          (64, 256, 1024, 2), (5, 64, 64, 1), (17, 128, 2048, 1)])
+def test_gemm_skinny_fused_normalises_its_rows_itself(ops, M, N, K, splits):
+    """X built by the blocks from float32 rows, their sums of squares (in parts) and the gain equals the
+    norm kernel followed by the plain product; one row is scaled so that a wrong row's factor shows."""
+    torch.manual_seed(190 + M)
+    resid = torch.randn(M, K).cuda()
+    resid[M - 1] *= 30.0
+    gain = (1 + 0.2 * torch.randn(K)).cuda()
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16).cuda()
+    x = ops.NormedRows(resid, ops.RowSquares(_squares(resid, 3)), gain, 1e-5, 0.25)
+    assert ops.gemm_skinny_fused_usable(x, w, splits)
+    part = torch.full((splits, M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_skinny_fused(part, x, w)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(part.device)
+    normed = x.materialize(torch.empty(M, K, dtype=torch.bfloat16, device="cuda"))
+    ref = normed.double().cpu() @ w.double().cpu().t()
+    got = part.sum(0).double().cpu()
+    # the factor 1 / sqrt(mean + eps) comes from sums in another order: the rounding of x to bfloat16 may differ in places
+    assert float((got - ref).abs().max()) < 2e-3 * float(ref.abs().max())
+    exact = (resid.double() / torch.sqrt((resid.double() ** 2).mean(1, keepdim=True) + 1e-5) * (gain.double() + 0.25)).cpu() \
+        @ w.double().cpu().t()
+    assert float((got - exact).abs().max()) < 6e-3 * float(exact.abs().max())
+
+
+@pytest.mark.parametrize("M,F,N,S", [(8, 3072, 1024, 3), (1, 48, 136, 2), (33, 176, 64, 1), (64, 1024, 256, 4)])
+def test_gemm_skinny_fused_applies_the_gated_activation_itself(ops, M, F, N, S):
+    torch.manual_seed(200 + M)
+    group = 16
+    slices = (torch.randn(S, M, 2 * F) * 0.7).cuda()
+    w = (torch.randn(N, F) * 0.5).to(torch.bfloat16).cuda()
+    x = ops.GatedRows(ops.Partials(slices), group)
+    splits = ops.gemm_skinny_splits(M, N, F)
+    assert ops.gemm_skinny_fused_usable(x, w, splits)
+    part = torch.full((splits, M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_skinny_fused(part, x, w)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(part.device)
+    act = x.materialize(torch.empty(M, F, dtype=torch.bfloat16, device="cuda"))
+    ref = act.double().cpu() @ w.double().cpu().t()
+    assert float((part.sum(0).double().cpu() - ref).abs().max()) < 2e-5 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 1024, 2048), (1, 136, 256), (33, 1024, 3072), (64, 200, 1024), (5, 64, 64)])
+@pytest.mark.parametrize("source", ["array", "gated"])
+def test_gemm_skinny_fused_adds_to_the_residual_and_leaves_the_sums_of_squares(ops, M, N, K, source):
+    """The last block of each tile adds the slices to the float32 residual; called twice to show that the
+    tickets come back to zero; the parts of the sums of squares add up to those of the new residual."""
+    torch.manual_seed(210 + M)
+    w = (torch.randn(N, K) * 0.2).to(torch.bfloat16).cuda()
+    if source == "array":
+        a = torch.randn(M, K).to(torch.bfloat16).cuda()
+        x, xd = a, a.double().cpu()
+    else:
+        x = ops.GatedRows(ops.Partials((torch.randn(2, M, 2 * K) * 0.7).cuda()), 16)
+        xd = x.materialize(torch.empty(M, K, dtype=torch.bfloat16, device="cuda")).double().cpu()
+    splits = ops.gemm_skinny_splits(M, N, K)
+    assert ops.gemm_skinny_fused_usable(x, w, splits, add_to=torch.empty(M, N, device="cuda"))
+    tiles = (N + 127) // 128
+    resid = torch.randn(M, N).cuda()
+    ref = resid.double().cpu()
+    part = torch.empty(splits, M, N, dtype=torch.float32, device="cuda")
+    squares = torch.full((tiles, M), -1.0, device="cuda")
+    tickets = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        ops.gemm_skinny_fused(part, x, w, add_to=resid, squares_out=squares, tickets=tickets)
+        ref = ref + xd @ w.double().cpu().t()
+    torch.cuda.synchronize()
+    ops.check_tc_errors(part.device)
+    assert int(tickets.abs().sum()) == 0
+    assert float((resid.double().cpu() - ref).abs().max()) < 3e-5 * max(1.0, float(ref.abs().max()))
+    sq = squares.double().sum(0).cpu()
+    want = (resid.double().cpu() ** 2).sum(1)
+    assert float(((sq - want).abs() / want).max()) < 1e-5
+
+
+def test_gemm_skinny_fused_chain_of_a_layer(ops):
+    """norm -> product -> (activation) -> product added to the residual -> norm -> product, all through the
+    fused forms, against the separate kernels."""
+    torch.manual_seed(220)
+    M, H, F = 8, 1024, 3072
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    resid = torch.randn(M, H).cuda()
+    gain = (1 + 0.1 * torch.randn(H)).cuda()
+    w_gu = interleave_gate_up((torch.randn(F, H) * 0.05).to(torch.bfloat16), (torch.randn(F, H) * 0.05).to(torch.bfloat16)).cuda()
+    w_d = (torch.randn(H, F) * 0.05).to(torch.bfloat16).cuda()
+    w_next = (torch.randn(256, H) * 0.05).to(torch.bfloat16).cuda()
+    # separate kernels
+    r0 = resid.clone()
+    normed = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    ops.add_rmsnorm(r0, None, gain, normed, 1e-6)
+    s_gu = ops.gemm_skinny_splits(M, 2 * F, H)
+    gu = torch.empty(s_gu, M, 2 * F, device="cuda")
+    ops.gemm_skinny(gu, normed, w_gu, ops.SKINNY_PARTIAL)
+    act = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.silu_mul(act, ops.Partials(gu), group=16)
+    s_d = ops.gemm_skinny_splits(M, H, F)
+    d = torch.empty(s_d, M, H, device="cuda")
+    ops.gemm_skinny(d, act, w_d, ops.SKINNY_PARTIAL)
+    ops.add_rmsnorm(r0, ops.Partials(d), gain, normed, 1e-6)
+    want = torch.empty(M, 256, dtype=torch.float32, device="cuda")
+    ops.gemm_skinny(want, normed, w_next)
+    # fused
+    r1 = resid.clone()
+    x = ops.NormedRows(r1, ops.RowSquares((r1 ** 2).sum(1)[None, :].contiguous()), gain, 1e-6)
+    gu1 = torch.empty(s_gu, M, 2 * F, device="cuda")
+    ops.gemm_skinny_fused(gu1, x, w_gu)
+    d1 = torch.empty(s_d, M, H, device="cuda")
+    squares = torch.empty(H // 128, M, device="cuda")
+    tickets = torch.zeros(H // 128, dtype=torch.int32, device="cuda")
+    ops.gemm_skinny_fused(d1, ops.GatedRows(ops.Partials(gu1), 16), w_d, add_to=r1, squares_out=squares, tickets=tickets)
+    s_n = ops.gemm_skinny_splits(M, 256, H)
+    out = torch.empty(s_n, M, 256, device="cuda")
+    ops.gemm_skinny_fused(out, ops.NormedRows(r1, ops.RowSquares(squares), gain, 1e-6), w_next)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    assert float((r1 - r0).abs().max()) < 2e-3 * float(r0.abs().max())
+    assert float((out.sum(0) - want).abs().max()) < 1e-2 * float(want.abs().max())
+
+
+def test_gemm_skinny_fused_refuses_what_it_cannot_hold(ops):
+    w = torch.zeros(128, 16384, dtype=torch.bfloat16, device="cuda")
+    resid = torch.zeros(64, 16384, device="cuda")
+    x = ops.NormedRows(resid, ops.RowSquares(torch.ones(1, 64, device="cuda")), torch.ones(16384, device="cuda"), 1e-6)
+    assert not ops.gemm_skinny_fused_usable(x, w, 1)          # 64 rows x 16384 columns of X do not fit in shared memory
+    with pytest.raises(ops.KernelError, match="shared memory"):
+        ops.gemm_skinny_fused(torch.empty(1, 64, 128, device="cuda"), x, w)
+    assert not ops.gemm_skinny_fused_usable(torch.zeros(65, 64, dtype=torch.bfloat16, device="cuda"),
+                                            torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda"), 1)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_consumers_add_up_partial_sums(ops, dtype):
     """add_rmsnorm, silu_mul and attn_prep given float32 slices equal the same kernels given the sum."""
