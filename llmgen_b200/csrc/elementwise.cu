@@ -14,14 +14,18 @@ LLMK_DEFINE_LAST_ERROR()
 // ---------------------------------------------------------------- embedding gather
 // out[t, :] = table[ids[t], :] widened to float32.  An id outside [0, V) gives a zero row and
 // raises *bad (the host checks ids before the step, this is the device-side guard the
-// reference's kernel lacks).
+// reference's kernel lacks).  With `ids_from`, row t whose ids_from[t] >= 0 takes its id from
+// sampled[ids_from[t]] instead: the token that the step before sampled for that row and that
+// the host has not read yet.
 template <typename T>
 __global__ void embed_rows_kernel(float* __restrict__ out, const T* __restrict__ table,
-                                  const int* __restrict__ ids, int H, int V, int* bad) {
+                                  const int* __restrict__ ids, const int* __restrict__ ids_from,
+                                  const int* __restrict__ sampled, int H, int V, int* bad) {
     const int t = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    const int id = ids[t];
+    const int from = ids_from ? ids_from[t] : -1;
+    const int id = from >= 0 ? sampled[from] : ids[t];
     const bool ok = id >= 0 && id < V;
     if (!ok && threadIdx.x == 0 && bad) atomicAdd(bad, 1);
     const T* row = table + (size_t)(ok ? id : 0) * H;
@@ -29,17 +33,18 @@ __global__ void embed_rows_kernel(float* __restrict__ out, const T* __restrict__
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_float(row[i]) : 0.f;
 }
 
-LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, int n_tokens, int H, int V,
-                                int* bad_flag, int dtype, void* stream) {
+LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, const int* ids_from, const int* sampled,
+                                int n_tokens, int H, int V, int* bad_flag, int dtype, void* stream) {
     if (n_tokens <= 0) return LLMK_OK;
     if (H <= 0 || V <= 0) LLMK_FAIL("embed_rows: bad sizes H=%d V=%d", H, V);
+    if ((ids_from != nullptr) != (sampled != nullptr)) LLMK_FAIL("embed_rows: ids_from and sampled come together");
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     cudaError_t e;
     if (dtype == LLMK_F32)
-        e = llmk_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const float*)table, ids, H, V, bad_flag);
+        e = llmk_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const float*)table, ids, ids_from, sampled, H, V, bad_flag);
     else if (dtype == LLMK_BF16)
-        e = llmk_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const bf16*)table, ids, H, V, bad_flag);
+        e = llmk_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const bf16*)table, ids, ids_from, sampled, H, V, bad_flag);
     else
         LLMK_FAIL("embed_rows: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("embed_rows", e);

@@ -222,6 +222,8 @@ struct Req {
     bool ignore_eos;
     int status;
     int preemptions;
+    int pending = 0;         // tokens of launched steps that the host has not read yet
+    bool reported = false;   // its last token has been named
 };
 
 struct Item {
@@ -273,6 +275,16 @@ struct Sched {
             }
         }
         return true;
+    }
+    // The request leaves the queues and gives back what it holds; its record stays until the tokens
+    // it still expects have been read.
+    void finish(Req& r) {
+        r.status = ST_FINISHED;
+        cache->release(r.id);
+        auto pos = std::find(running.begin(), running.end(), r.id);
+        if (pos != running.end()) running.erase(pos);
+        auto wpos = std::find(waiting.begin(), waiting.end(), r.id);
+        if (wpos != waiting.end()) waiting.erase(wpos);
     }
     void start_running(Req& r) {
         waiting.pop_front();
@@ -488,7 +500,7 @@ LLMR_EXPORT void llmr_sched_delete(void* s) { delete static_cast<Sched*>(s); }
 LLMR_EXPORT void llmr_sched_set_eos(void* s, const int* eos, int n_eos) { static_cast<Sched*>(s)->eos.assign(eos, eos + n_eos); }
 LLMR_EXPORT void llmr_sched_add(void* sp, long long req, int prompt_len, int max_tokens, int ignore_eos) {
     Sched* s = static_cast<Sched*>(sp);
-    s->reqs[req] = Req{req, prompt_len, prompt_len, 0, max_tokens, ignore_eos != 0, ST_WAITING, 0};
+    s->reqs[req] = Req{req, prompt_len, prompt_len, 0, max_tokens, ignore_eos != 0, ST_WAITING, 0, 0, false};
     s->waiting.push_back(req);
 }
 LLMR_EXPORT int llmr_sched_is_finished(void* sp) {
@@ -497,8 +509,10 @@ LLMR_EXPORT int llmr_sched_is_finished(void* sp) {
 }
 // One step's portions: (request, first position, length) triples; returns how many (at most `cap`
 // are written).  `preempted` receives the requests that lost their place in this call.
-LLMR_EXPORT int llmr_sched_schedule(void* sp, long long* reqs, int* q_start, int* q_len, int cap, long long* preempted,
-                                    int preempted_cap, int* n_preempted) {
+// `emits[i]` is 1 when portion i reaches the last known token of its sequence, so that the step
+// yields a new token for it.
+LLMR_EXPORT int llmr_sched_schedule(void* sp, long long* reqs, int* q_start, int* q_len, int* emits, int cap,
+                                    long long* preempted, int preempted_cap, int* n_preempted) {
     Sched* s = static_cast<Sched*>(sp);
     s->preempted_now.clear();
     std::vector<Item> out;
@@ -509,39 +523,64 @@ LLMR_EXPORT int llmr_sched_schedule(void* sp, long long* reqs, int* q_start, int
         reqs[i] = out[i].req;
         q_start[i] = out[i].q_start;
         q_len[i] = out[i].q_len;
+        emits[i] = out[i].q_start + out[i].q_len == s->reqs[out[i].req].length ? 1 : 0;
     }
     const int np = std::min((int)s->preempted_now.size(), preempted_cap);
     for (int i = 0; i < np; ++i) preempted[i] = s->preempted_now[i];
     *n_preempted = (int)s->preempted_now.size();
     return (int)out.size();
 }
-// Record what the step computed; `tokens` holds the new token of every portion that reached the end
-// of its sequence, in order.  Finished requests (end-of-sequence token or max_tokens) are released
-// and listed in `finished`; returns their number.
-LLMR_EXPORT int llmr_sched_postprocess(void* sp, int n, const long long* reqs, const int* q_start, const int* q_len,
-                                       const int* tokens, int n_tokens, long long* finished, int cap) {
+// After a step has been launched, what does not depend on the tokens it will sample: the portions
+// count as computed, a sequence whose portion reached its end grows by one token (one more token
+// of it is now pending), and a request that has its max_tokens with it leaves the queues and gives
+// back what it holds.  The step may still be running: pages given back here are written again only
+// by steps launched later on the same stream.  Returns how many requests left the queues.
+LLMR_EXPORT int llmr_sched_advance(void* sp, int n, const long long* reqs, const int* q_start, const int* q_len) {
     Sched* s = static_cast<Sched*>(sp);
-    int k = 0, done = 0;
+    int done = 0;
     for (int i = 0; i < n; ++i) {
         auto it = s->reqs.find(reqs[i]);
         if (it == s->reqs.end()) continue;
         Req& r = it->second;
+        if (r.status == ST_FINISHED) continue;
         const bool emits = q_start[i] + q_len[i] == r.length;
         r.computed = q_start[i] + q_len[i];
         if (!emits) continue;
-        if (k >= n_tokens) break;
-        const int token = tokens[k++];
         r.length += 1;
-        const bool hit_eos = !r.ignore_eos && std::find(s->eos.begin(), s->eos.end(), token) != s->eos.end();
-        if (hit_eos || r.length - r.num_prompt >= r.max_tokens) {
-            r.status = ST_FINISHED;
-            s->cache->release(r.id);
-            auto pos = std::find(s->running.begin(), s->running.end(), r.id);
-            if (pos != s->running.end()) s->running.erase(pos);
-            if (done < cap) finished[done] = r.id;
+        r.pending += 1;
+        if (r.length - r.num_prompt >= r.max_tokens) {
+            s->finish(r);
             ++done;
-            s->reqs.erase(it);
         }
+    }
+    return done;
+}
+// When the tokens of a step are known: `reqs[i]`, `tokens[i]` for every portion that yielded one, in
+// the order of the step.  `last[i]` becomes 1 when that token is the request's last one: it ends the
+// sequence (and the request does not ignore that), or it is the token that filled max_tokens.  A
+// request that ended is released wherever it is (running, or waiting after a preemption); tokens
+// that a later step, launched before this one was read, sampled for it are to be dropped
+// (`last[i]` = -1 for those).  Returns how many requests ended here.
+LLMR_EXPORT int llmr_sched_resolve(void* sp, int n, const long long* reqs, const int* tokens, int* last) {
+    Sched* s = static_cast<Sched*>(sp);
+    int done = 0;
+    for (int i = 0; i < n; ++i) {
+        last[i] = -1;
+        auto it = s->reqs.find(reqs[i]);
+        if (it == s->reqs.end()) continue;
+        Req& r = it->second;
+        r.pending -= 1;
+        if (!r.reported) {
+            last[i] = 0;
+            const bool hit_eos = !r.ignore_eos && std::find(s->eos.begin(), s->eos.end(), tokens[i]) != s->eos.end();
+            if (hit_eos || (r.status == ST_FINISHED && r.pending == 0)) {
+                if (r.status != ST_FINISHED) s->finish(r);
+                r.reported = true;
+                last[i] = 1;
+                ++done;
+            }
+        }
+        if (r.reported && r.pending <= 0) s->reqs.erase(it);
     }
     return done;
 }
@@ -579,11 +618,13 @@ LLMR_EXPORT int llmr_sched_request(void* sp, long long req, int* out4) {
 // single tokens changes: ids, positions, lengths, state slots, temperatures, and per group the slots
 // and the block-table rows whose table changed (`row_stamps[g * bucket + s]` remembers request and
 // stamp of what row s of group g holds; 0 = padding).  Offsets are in 4-byte words:
-// offs = [ids, positions, ctx_len, state_slots, temps, then (slots_g, block_tables_g) per group].
+// offs = [ids, positions, ctx_len, state_slots, temps, ids_from, then (slots_g, block_tables_g) per group].
+// `from[s]` >= 0 names the row of the step before whose sampled token is row s's id (the host has
+// not read it yet; tokens[s] is then ignored), -1 takes tokens[s].
 // Returns 0, or 1 when a position has no page.
 LLMR_EXPORT int llmr_fill_decode(void* c, int* host, const int* offs, int n, int bucket, int max_blocks,
-                                 const long long* reqs, const int* tokens, const int* starts, const float* temps,
-                                 long long* row_stamps) {
+                                 const long long* reqs, const int* tokens, const int* from, const int* starts,
+                                 const float* temps, long long* row_stamps) {
     Cache* cache = static_cast<Cache*>(c);
     const int ps = cache->page_size;
     int* ids = host + offs[0];
@@ -591,9 +632,11 @@ LLMR_EXPORT int llmr_fill_decode(void* c, int* host, const int* offs, int n, int
     int* ctx = host + offs[2];
     int* st = host + offs[3];
     float* tp = reinterpret_cast<float*>(host + offs[4]);
+    int* fr = host + offs[5];
     for (int s = 0; s < bucket; ++s) {
         const bool live = s < n;
-        ids[s] = live ? tokens[s] : 0;
+        ids[s] = live && from[s] < 0 ? tokens[s] : 0;
+        fr[s] = live ? from[s] : -1;
         pos[s] = live ? starts[s] : 0;
         ctx[s] = live ? starts[s] + 1 : 0;
         st[s] = live ? cache->slots.slot(reqs[s]) : -1;
@@ -602,8 +645,8 @@ LLMR_EXPORT int llmr_fill_decode(void* c, int* host, const int* offs, int n, int
     const int n_groups = (int)cache->groups.size();
     for (int g = 0; g < n_groups; ++g) {
         Group* grp = cache->groups[g];
-        int* slots = host + offs[5 + 2 * g];
-        int* bt = host + offs[6 + 2 * g];
+        int* slots = host + offs[6 + 2 * g];
+        int* bt = host + offs[7 + 2 * g];
         long long* stamps = row_stamps + (size_t)g * bucket * 2;
         for (int s = 0; s < bucket; ++s) {
             int* row = bt + (size_t)s * max_blocks;

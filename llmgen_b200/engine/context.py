@@ -141,6 +141,8 @@ class StepContext:
     max_ctx_bound: int           # bound to use when launch shapes must not depend on the data
     # device views (int32 unless said otherwise)
     ids: torch.Tensor = None
+    ids_from: torch.Tensor = None        # per token: row of `prev_sampled` that holds its id, or -1 (use `ids`); may be None
+    prev_sampled: torch.Tensor = None    # the ids that the step before sampled, still on the device
     positions: torch.Tensor = None
     cu_q: torch.Tensor = None
     ctx_len: torch.Tensor = None

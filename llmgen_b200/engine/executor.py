@@ -40,6 +40,13 @@ class StepError(ValueError):
 
 
 @dataclass
+class PendingIds:
+    """The sampled ids of a launched decode step: a pinned host buffer that is valid once `event` has passed."""
+    host: torch.Tensor
+    event: object
+
+
+@dataclass
 class EngineLimits:
     """Engine-side limits (command-line options in the reference, src/cli.zig:33-62)."""
     max_num_seqs: int = 256          # sequences per step
@@ -127,6 +134,12 @@ class Executor:
         self.sample_scratch = torch.empty(ops.sample_scratch_bytes(max(Sm, 64)) // 4, dtype=torch.float32,
                                           device=self.device)
         self.ids_host = torch.empty(max(Tm, Sm), dtype=torch.int32).pin_memory()
+        # decode steps replayed from a graph leave their sampled ids here; the next step may take its
+        # input ids from it on the device (`decode_launch`), before the host has read them
+        self.sampled_dev = torch.zeros(Sm, dtype=torch.int32, device=self.device)
+        self._ids_hosts = [torch.empty(Sm, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._ids_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._ids_turn = 0
         self.graphs: Dict[Tuple[int, int], dict] = {}     # (batch-size bucket, context-length class) -> graph
         # decode steps rewrite only what changed in a host buffer that the same bucket filled last
         self._host_owner = [None, None]                   # per pinned buffer: (bucket, layout) of its last fill
@@ -134,7 +147,8 @@ class Executor:
         self._runtime = cache_runtime()
         top = self.limits.max_num_seqs
         self._decode_args = ((ctypes.c_longlong * top)(), (ctypes.c_int * top)(), (ctypes.c_int * top)(),
-                             (ctypes.c_float * top)())      # requests, tokens, positions, temperatures of a decode step
+                             (ctypes.c_float * top)(), (ctypes.c_int * top)())
+        # ... requests, tokens, positions, temperatures of a decode step, and the rows of the step before its ids come from
 
     # ------------------------------------------------------------------ sizing
     def _pages_per_group(self) -> List[int]:
@@ -239,13 +253,13 @@ class Executor:
             result.token_ids = [ids_parts[r] for r in perm] if perm is not None else ids_parts
         return result
 
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry], prev_rows: Optional[Sequence[int]] = None) -> None:
         lim = self.limits
         V = self.model.spec.vocab_size
         if len(entries) > lim.max_num_seqs:
             raise StepError(f"{len(entries)} sequences in one step, the limit is {lim.max_num_seqs}")
         seen = set()
-        for e in entries:
+        for i, e in enumerate(entries):
             if e.req in seen:
                 raise StepError(f"request {e.req!r} appears twice in one step")
             seen.add(e.req)
@@ -255,7 +269,9 @@ class Executor:
             if e.start < 0 or e.start + n > lim.max_model_len:
                 raise StepError(f"request {e.req!r}: positions [{e.start}, {e.start + n}) exceed max_model_len "
                                 f"{lim.max_model_len}")
-            if n == 1 and type(e.tokens[0]) is int and 0 <= e.tokens[0] < V:
+            if n == 1 and prev_rows is not None and prev_rows[i] >= 0:
+                toks = None                                    # its token is still on the device
+            elif n == 1 and type(e.tokens[0]) is int and 0 <= e.tokens[0] < V:
                 toks = None                                    # the common case of a decoded token, checked without numpy
             else:
                 toks = np.asarray(e.tokens)
@@ -293,9 +309,11 @@ class Executor:
         return passes
 
     # -- metadata
-    def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0, ctx_bound: int = 0):
+    def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0, ctx_bound: int = 0,
+                    ids_from: Optional[Sequence[int]] = None):
         """Fill and upload the step's metadata; returns (StepContext, want rows view, temps view,
-        seed view, number of wanted rows)."""
+        seed view, number of wanted rows).  A batch padded to a graph's shape (`pad_to`) also gets
+        `ids_from`: for each row the row of the step before whose sampled id is its token, or -1."""
         lim = self.limits
         ps = lim.page_size
         S_real = len(entries)
@@ -317,7 +335,7 @@ class Executor:
         t = 0
         for s, e in enumerate(entries):
             n = q_lens[s]
-            ids[t:t + n] = np.asarray(e.tokens, dtype=np.int32)
+            ids[t:t + n] = np.asarray([0 if tok is None else tok for tok in e.tokens] if n == 1 else e.tokens, dtype=np.int32)
             pos[t:t + n] = np.arange(e.start, e.start + n, dtype=np.int32)
             seq_of[t:t + n] = s
             ctx_len[s] = e.start + n
@@ -333,6 +351,11 @@ class Executor:
             want_rows.append(t - 1)
             temps.append(0.0)
         b.add("ids", ids)
+        if pad_to > 0:
+            src = np.full(T, -1, dtype=np.int32)
+            if ids_from is not None:
+                src[:S_real] = np.asarray(ids_from, dtype=np.int32)
+            b.add("ids_from", src)
         b.add("positions", pos)
         b.add("seq_of_token", seq_of)
         b.add("cu_q", cu_q)
@@ -380,7 +403,9 @@ class Executor:
             max_ctx=int(ctx_len.max()) if S else 0,
             max_ctx_bound=ctx_bound or self.context_class(int(ctx_len.max()) if S else 0),
             max_seqs_bound=lim.max_num_seqs,
-            ids=view("ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_len=view("ctx_len"),
+            ids=view("ids"), ids_from=view("ids_from") if "ids_from" in layout else None,
+            prev_sampled=self.sampled_dev if "ids_from" in layout else None,
+            positions=view("positions"), cu_q=view("cu_q"), ctx_len=view("ctx_len"),
             state_slots=view("state_slots"), seq_of_token=view("seq_of_token"),
             groups=[GroupView(view(f"slots_{gi}"), view(f"block_tables_{gi}"), self.max_blocks)
                     for gi in range(len(self.cache.groups))],
@@ -458,13 +483,16 @@ class Executor:
         ctx_bound = ctx_bound or self.limits.max_model_len
         V = self.model.spec.vocab_size
         logits = torch.empty((bucket, V), dtype=torch.float32, device=self.device)
-        ids_dev = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+        ids_dev = self.sampled_dev[:bucket]
+        # the warm-up runs sample elsewhere: a step in flight may have left ids in `sampled_dev` that the
+        # step this graph is captured for takes its tokens from
+        ids_warm = torch.zeros(bucket, dtype=torch.int32, device=self.device)
 
         def run():
             ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
             ctx.fixed_shapes = True
             self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
-            ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
+            ops.sample(ids_warm, logits, temps, seed, self.sample_scratch)
 
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -497,18 +525,47 @@ class Executor:
                 self._capture(b, self.limits.max_model_len)
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> StepOutput:
+        return StepOutput(None, self.decode_collect(self._decode_launch(entries, None)))
+
+    def decode_launch(self, entries: Sequence[StepEntry], prev_rows: Optional[Sequence[int]] = None) -> "PendingIds":
+        """Launch a step of single tokens with sampling and return at once; `decode_collect` waits for
+        its ids.  `prev_rows[i] >= 0` says that entry i's token is the id that the step launched just
+        before this one sampled in that row (its `tokens` may then be `[None]`): the GPU takes it
+        from there, so the host need not have read it.  Only with captured graphs (not `eager`)."""
+        entries = [e for e in entries]
+        if self.eager:
+            raise StepError("decode_launch needs captured graphs (the engine was built with eager=True)")
+        if prev_rows is not None and len(prev_rows) != len(entries):
+            raise StepError("one previous row (or -1) per entry is required")
+        for i, e in enumerate(entries):
+            if len(e.tokens) != 1 or list(e.want) != [0]:
+                raise StepError("decode_launch takes single tokens whose logits are sampled")
+            if e.tokens[0] is None and (prev_rows is None or not 0 <= prev_rows[i] < self.limits.max_num_seqs):
+                raise StepError(f"request {e.req!r}: no token and no row of the step before to take it from")
+        self._validate(entries, prev_rows)
+        self._reset_fresh_state()
+        return self._decode_launch(entries, prev_rows)
+
+    def _decode_launch(self, entries, prev_rows) -> "PendingIds":
         n = len(entries)
         bucket, g = self.decode_graph(n, max(e.start for e in entries) + 1)
-        self._fill_decode_meta(entries, bucket)
+        self._fill_decode_meta(entries, bucket, prev_rows)
         g["graph"].replay()
         self.launch_count += g["launches"]
-        host = self.ids_host[:n]
-        host.copy_(g["ids"][:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        turn = self._ids_turn
+        self._ids_turn ^= 1
+        host = self._ids_hosts[turn][:n]
+        host.copy_(self.sampled_dev[:n], non_blocking=True)
+        self._ids_events[turn].record()
         self.n_graph_steps += 1
-        return StepOutput(None, host.tolist())
+        return PendingIds(host, self._ids_events[turn])
 
-    def _fill_decode_meta(self, entries: Sequence[StepEntry], bucket: int) -> None:
+    def decode_collect(self, pending: "PendingIds") -> List[int]:
+        """The sampled ids of a launched step, in the order of its entries."""
+        pending.event.synchronize()
+        return pending.host.tolist()
+
+    def _fill_decode_meta(self, entries: Sequence[StepEntry], bucket: int, prev_rows: Optional[Sequence[int]] = None) -> None:
         """The metadata of a step of single tokens.  The first fill of a pinned buffer for a bucket
         goes through `_build_meta`; later ones rewrite only what a decode step changes (tokens,
         positions, lengths, slots, the seed, and block-table rows whose table grew), with the
@@ -516,12 +573,12 @@ class Executor:
         turn = self._meta_turn
         owner = self._host_owner[turn]
         if not self._static_step_arrays:
-            self._build_meta(entries, pad_to=bucket)
+            self._build_meta(entries, pad_to=bucket, ids_from=prev_rows)
             return
         if owner is None or owner[0] != bucket:
-            self._build_meta(entries, pad_to=bucket)
+            self._build_meta(entries, pad_to=bucket, ids_from=prev_rows)
             t, layout, total = self._last_fill
-            names = ["ids", "positions", "ctx_len", "state_slots", "temps"]
+            names = ["ids", "positions", "ctx_len", "state_slots", "temps", "ids_from"]
             for gi in range(len(self.cache.groups)):
                 names += [f"slots_{gi}", f"block_tables_{gi}"]
             offs = (ctypes.c_int * len(names))(*[layout[name][0] for name in names])
@@ -544,12 +601,17 @@ class Executor:
         a = self._decode_args
         key = self.cache.key
         a[0][:n] = [key(e.req) for e in entries]
-        a[1][:n] = [e.tokens[0] for e in entries]
+        if prev_rows is None:
+            a[1][:n] = [e.tokens[0] for e in entries]
+            a[4][:n] = [-1] * n
+        else:
+            a[1][:n] = [e.tokens[0] if r < 0 else 0 for e, r in zip(entries, prev_rows)]
+            a[4][:n] = list(prev_rows)
         a[2][:n] = [e.start for e in entries]
         a[3][:n] = [e.temperature for e in entries]
         rc = self._runtime.llmr_fill_decode(self.cache.native_handle, ctypes.c_void_p(host.data_ptr()), offs,
                                             ctypes.c_int(n), ctypes.c_int(bucket), ctypes.c_int(self.max_blocks),
-                                            a[0], a[1], a[2], a[3], self._host_rows[turn])
+                                            a[0], a[1], a[4], a[2], a[3], self._host_rows[turn])
         if rc != 0:
             self._host_owner[turn] = None
             raise StepError(self._runtime.llmr_last_error().decode("utf-8", "replace"))

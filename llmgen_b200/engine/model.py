@@ -80,7 +80,7 @@ class DecoderModel:
         """Run embedding and all run items; returns (residual float32 [T, H], pending delta)."""
         T, H = ctx.n_tokens, self.spec.hidden_size
         resid = ctx.workspace.buffer("residual", T, H, torch.float32)
-        ops.embed_rows(resid, self.embedding, ctx.ids, self.bad_token_flag)
+        ops.embed_rows(resid, self.embedding, ctx.ids, self.bad_token_flag, ids_from=ctx.ids_from, sampled=ctx.prev_sampled)
         delta = None
         for item, cache in zip(self.spec.run_order, caches):
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)

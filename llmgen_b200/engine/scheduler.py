@@ -23,7 +23,7 @@ from __future__ import annotations
 
 from ctypes import byref, c_int, c_longlong, c_void_p
 from dataclasses import dataclass
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 from ..cache.manager import CacheManager, runtime
 from ..sampling.params import SamplingParams
@@ -72,9 +72,14 @@ class Scheduled:
     request: Request
     q_start: int
     q_len: int
+    emit: Optional[bool] = None      # set by the scheduler; None: decided from the request's length
 
     def emits(self) -> bool:
-        """True when the portion reaches the last known token, so the step yields a new one."""
+        """True when the portion reaches the last token of the sequence, so the step yields a new one.
+        The scheduler says so itself: a token of the step before may not have been read yet, and the
+        request's list is then one short."""
+        if self.emit is not None:
+            return self.emit
         return self.q_start + self.q_len == len(self.request)
 
 
@@ -132,6 +137,7 @@ class BatchScheduler:
         self._starts = (c_int * cap)()
         self._lens = (c_int * cap)()
         self._tokens = (c_int * cap)()
+        self._flags = (c_int * cap)()
         self._other = (c_longlong * cap)()
         self._count = c_int(0)
 
@@ -175,7 +181,7 @@ class BatchScheduler:
     def schedule(self) -> List[Scheduled]:
         """This step's portions.  Requests that lost their place are back at the front of `waiting`
         with nothing computed."""
-        n = self._lib.llmr_sched_schedule(self._h, self._keys, self._starts, self._lens, c_int(self._cap),
+        n = self._lib.llmr_sched_schedule(self._h, self._keys, self._starts, self._lens, self._flags, c_int(self._cap),
                                           self._other, c_int(self._cap), byref(self._count))
         assert n <= self._cap and self._count.value <= self._cap     # both are bounded by the known requests
         for i in range(self._count.value):
@@ -189,38 +195,62 @@ class BatchScheduler:
             request.status = RUNNING
             if self._starts[i] == 0:
                 request.num_computed_tokens = 0
-            out.append(Scheduled(request, self._starts[i], self._lens[i]))
+            out.append(Scheduled(request, self._starts[i], self._lens[i], bool(self._flags[i])))
         return out
 
     # ---------------------------------------------------------------- after the step
-    def postprocess(self, scheduled: Sequence[Scheduled], tokens: Sequence[int]) -> int:
-        """Record what the step computed; append the new token of every emitting portion
-        (`tokens`, in order); finish on EOS or max_tokens and free (src/runner/batching.zig:323-355).
-        Returns the number of requests that finished."""
-        n = len(scheduled)
-        if n > self._cap:
-            self._grow(2 * n)
+    def _sync_eos(self) -> None:
         if tuple(self.config.eos_token_ids) != self._eos_sent:       # the configuration's list is the one that counts
             self._eos_sent = tuple(int(t) for t in self.config.eos_token_ids)
             self._lib.llmr_sched_set_eos(self._h, (c_int * max(len(self._eos_sent), 1))(*self._eos_sent),
                                          c_int(len(self._eos_sent)))
-        k = 0
+
+    def advance(self, scheduled: Sequence[Scheduled]) -> None:
+        """Once a step has been launched: record what it computes and let every sequence whose portion
+        reached its end grow by the token to come; a request that has its max_tokens with that token
+        leaves the queues now and frees what it holds (the step may still be running: what it frees
+        is written again only by later steps, which the GPU runs after this one).  The tokens
+        themselves come with `resolve`."""
+        n = len(scheduled)
+        if n > self._cap:
+            self._grow(2 * n)
         for i, item in enumerate(scheduled):
-            request = item.request
-            self._keys[i] = self.manager.key(request.id)
+            self._keys[i] = self.manager.key(item.request.id)
             self._starts[i] = item.q_start
             self._lens[i] = item.q_len
-            emits = item.emits()
-            request.num_computed_tokens = item.q_start + item.q_len
-            if emits:
-                token = int(tokens[k])
-                self._tokens[k] = token
-                k += 1
-                request.token_ids.append(token)
-        done = self._lib.llmr_sched_postprocess(self._h, c_int(n), self._keys, self._starts, self._lens, self._tokens,
-                                                c_int(k), self._other, c_int(self._cap))
-        for i in range(done):
-            request = self._requests.pop(self._other[i])
-            request.status = FINISHED
-            self.manager.forget(request.id)
+            if item.request.status != FINISHED:
+                item.request.num_computed_tokens = item.q_start + item.q_len
+        self._lib.llmr_sched_advance(self._h, c_int(n), self._keys, self._starts, self._lens)
+
+    def resolve(self, scheduled: Sequence[Scheduled], tokens: Sequence[int]) -> int:
+        """The tokens of a step that `advance` has recorded, in the order of its emitting portions:
+        appended to their requests; a request whose sequence the token ends (EOS, unless ignored) or
+        whose max_tokens it fills is finished and freed (src/runner/batching.zig:323-355).  A token
+        sampled for a request that had already ended (the step was launched before that was known)
+        is dropped.  Returns the number of requests that finished."""
+        self._sync_eos()
+        emitting = [item for item in scheduled if item.emits()]
+        n = len(emitting)
+        if n > self._cap:
+            self._grow(2 * n)
+        for i, item in enumerate(emitting):
+            self._keys[i] = self.manager.key(item.request.id)
+            self._tokens[i] = int(tokens[i])
+        done = self._lib.llmr_sched_resolve(self._h, c_int(n), self._keys, self._tokens, self._flags)
+        for i, item in enumerate(emitting):
+            last = self._flags[i]
+            if last < 0:
+                continue
+            request = item.request
+            request.token_ids.append(int(tokens[i]))
+            if last == 1:
+                request.status = FINISHED
+                self._requests.pop(self._keys[i], None)
+                self.manager.forget(request.id)
         return done
+
+    def postprocess(self, scheduled: Sequence[Scheduled], tokens: Sequence[int]) -> int:
+        """`advance` and `resolve` in one: for steps whose tokens are read before the next one is
+        scheduled."""
+        self.advance(scheduled)
+        return self.resolve(scheduled, tokens)

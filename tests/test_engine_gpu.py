@@ -223,3 +223,76 @@ def test_chain_of_fused_products_when_switched_on(tmp, monkeypatch):
         llm = LLM(path, dtype="bfloat16", max_model_len=256, max_num_seqs=4, max_batched_tokens=1024, kv_blocks=64, eager=eager)
         outs[eager] = [r["token_ids"] for r in llm.generate([ids[:50], ids[:7], ids[:33]], SamplingParams(0.0, 12, True))]
     assert outs[False] == outs[True]
+
+
+def test_decode_steps_launched_one_ahead_give_what_steps_read_at_once_give(tmp):
+    """The engine launches a decode step before it has read the ids of the step before (the GPU takes
+    them from where that step left them).  Same ids as with `run_ahead` off: with requests that end at
+    different times (so rows move between steps and batch sizes change), with an end-of-sequence token
+    that is only seen after one more step was launched, and with so few pages that requests are preempted."""
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "A")
+    prompts = [random_ids(n, 256, 120 + i) for i, n in enumerate((3, 11, 30, 7, 19))]
+    params = [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=True) for m in (5, 23, 9, 30, 16)]
+    ref = greedy_reference(path, prompts, 30)
+    outs = {}
+    for ahead in (True, False):
+        llm = LLM(path, dtype="float32", max_model_len=96, max_num_seqs=4, max_batched_tokens=96, kv_blocks=7)
+        llm.engine.run_ahead = ahead
+        outs[ahead] = [o["token_ids"] for o in llm.generate(prompts, params)]
+        assert llm.executor.cache.all_free() and llm.executor.n_graph_steps > 0
+        if ahead:
+            assert llm.engine.scheduler.num_preemptions > 0
+    assert outs[True] == outs[False] == [r[:p.max_tokens] for r, p in zip(ref, params)]
+    # an end-of-sequence token: the request's list stops there although the next step had been launched
+    stop = ref[1][6]
+    first = ref[1].index(stop)
+    llm = LLM(path, dtype="float32", max_model_len=128, max_num_seqs=4, max_batched_tokens=128, kv_blocks=32)
+    llm.engine.scheduler.config.eos_token_ids = (stop,)
+    got = llm.generate(prompts[:3], [SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=(i != 1)) for i in range(3)])
+    assert got[1]["token_ids"] == ref[1][:first + 1]
+    assert got[0]["token_ids"] == ref[0][:20] and got[2]["token_ids"] == ref[2][:20]
+    assert llm.executor.cache.all_free()
+
+
+def test_decode_launch_takes_ids_from_the_rows_of_the_step_before(tmp):
+    """`Executor.decode_launch` with `prev_rows`: the rows change places between steps and one row gets
+    its id from the host; compared with steps that are given every id."""
+    from llmgen_b200.engine.executor import StepEntry
+    from tests.util import Driver
+    path = make_folder(tmp, "E")
+    prompts = {r: random_ids(n, 290, 130 + i) for i, (r, n) in enumerate((("a", 9), ("b", 21), ("c", 5)))}
+    runs = {}
+    for fed in (False, True):
+        d = Driver(path, "bfloat16", 512, 32)
+        d.executor.eager = False
+        pos, last = {}, {}
+        for r, ids in prompts.items():
+            d.step([(r, ids, [])])
+            pos[r], last[r] = len(ids), ids[-1] % 7 + 1
+        orders = [["a", "b", "c"], ["c", "a", "b"], ["b", "c"], ["c", "b", "a"], ["a", "b", "c"]]
+        got, rows_before, pending = [], {}, None
+        for order in orders:
+            entries, prev = [], []
+            for r in order:
+                assert d.executor.reserve(r, pos[r], pos[r] + 1)
+                row = rows_before.get(r, -1) if fed else -1
+                entries.append(StepEntry(r, [None] if row >= 0 else [last[r]], pos[r], [0], 0.0))
+                prev.append(row)
+                pos[r] += 1
+            launched = d.executor.decode_launch(entries, prev if fed else None)
+            if pending is not None and fed:
+                ids = d.executor.decode_collect(pending[0])           # read only after the next launch
+                got.append(dict(zip(pending[1], ids)))
+                last.update(got[-1])
+            if fed:
+                pending, rows_before = (launched, order), {r: i for i, r in enumerate(order)}
+            else:
+                ids = d.executor.decode_collect(launched)
+                got.append(dict(zip(order, ids)))
+                last.update(got[-1])
+        if fed:
+            got.append(dict(zip(pending[1], d.executor.decode_collect(pending[0]))))
+        runs[fed] = got
+    # "a" sits out the third step: in the fed run its id for the fourth comes from the host (known by then)
+    assert runs[True] == runs[False]

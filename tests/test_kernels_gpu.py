@@ -43,6 +43,12 @@ def test_embed_rows(ops, dtype):
     ops.embed_rows(out, dev(table), dev(torch.tensor([1, 100, -1, 2, 5], dtype=torch.int32)), bad)
     assert int(bad.item()) == 2 and float(out[1].abs().sum()) == 0.0 and float(out[2].abs().sum()) == 0.0
     assert torch.equal(out[3].cpu(), table[2].float())
+    # rows whose id is the one the step before sampled (still on the device), beside rows the host names
+    sampled = dev(torch.tensor([7, 8, 9], dtype=torch.int32))
+    ids_from = dev(torch.tensor([-1, 2, 0, -1, 1], dtype=torch.int32))
+    bad.zero_()
+    ops.embed_rows(out, dev(table), dev(ids), bad, ids_from=ids_from, sampled=sampled)
+    assert torch.equal(out.cpu(), plain.embedding([3, 9, 7, 57, 8], table.float())) and int(bad.item()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

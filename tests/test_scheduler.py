@@ -168,3 +168,50 @@ def test_random_workloads_finish_and_free_everything(policy, seed):
         cache.check_consistency()
     assert all(r.status == FINISHED and len(r.completion) == r.params.max_tokens for r in reqs)
     assert cache.all_free()
+
+
+def test_steps_launched_before_the_tokens_of_the_step_before_are_known():
+    """`advance` right after a launch, `resolve` when the tokens arrive, one step later: lengths grow at
+    once, max_tokens ends a request at `advance`, an end-of-sequence token ends it at `resolve`, and the
+    token that a step already launched sampled for it is dropped."""
+    cache, s = make(64, eos_token_ids=(9,))
+    a, b, c = req(0, 5, max_tokens=3), req(1, 6, max_tokens=8), req(2, 4, max_tokens=8, ignore_eos=True)
+    for r in (a, b, c):
+        s.add(r)
+    first = s.schedule()                                   # the prompts: read at once
+    assert all(x.emits() for x in first) and s.postprocess(first, [1, 1, 1]) == 0
+    k1 = s.schedule()
+    assert [(x.request.id, x.q_start, x.emits()) for x in k1] == [(0, 5, True), (1, 6, True), (2, 4, True)]
+    s.advance(k1)
+    k2 = s.schedule()                                      # scheduled while k1's tokens are unknown
+    assert [(x.request.id, x.q_start, x.emits()) for x in k2] == [(0, 6, True), (1, 7, True), (2, 5, True)]
+    assert len(a) == 6                                     # the request's own list is one short
+    s.advance(k2)                                          # a has its 3 tokens with this one: it leaves the queues
+    assert [r.id for r in s.running] == [1, 2] and a.status != FINISHED
+    assert s.resolve(k1, [2, 9, 9]) == 1                   # b's token ends its sequence; c ignores that
+    assert b.status == FINISHED and b.completion == [1, 9] and c.completion == [1, 9]
+    k3 = s.schedule()
+    assert [(x.request.id, x.q_start) for x in k3] == [(2, 6)]
+    s.advance(k3)
+    assert s.resolve(k2, [3, 4, 5]) == 1                   # a's last token; b's is dropped
+    assert a.status == FINISHED and a.completion == [1, 2, 3] and b.completion == [1, 9] and c.completion == [1, 9, 5]
+    assert s.resolve(k3, [6]) == 0 and c.completion == [1, 9, 5, 6]
+    run(s)
+    assert c.status == FINISHED and len(c.completion) == 8 and cache.all_free()
+
+
+def test_a_request_preempted_while_its_token_is_unknown_keeps_that_token():
+    cache, s = make(6, max_num_seqs=4)
+    a, b = req(0, 40, max_tokens=30), req(1, 40, max_tokens=30)
+    s.add(a)
+    s.add(b)
+    run(s, steps=8)                                        # prompts, then 7 decoded tokens: lengths 48, three full pages
+    k = s.schedule()
+    s.advance(k)                                           # lengths 49 now, the tokens not yet known
+    nxt = s.schedule()                                     # position 48 needs a 4th page for each: b is preempted
+    assert [(x.request.id, x.q_start) for x in nxt] == [(0, 48)] and b.status == WAITING and s.waiting[0] is b
+    assert s.resolve(k, [7, 7]) == 0 and len(b) == 49 and len(a) == 49
+    s.advance(nxt)
+    s.resolve(nxt, [7])
+    run(s)
+    assert len(a.completion) == 30 and len(b.completion) == 30 and cache.all_free()
