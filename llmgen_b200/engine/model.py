@@ -28,7 +28,8 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, weights, dtype: torch.dtype, device):
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"the engine computes in float32 or bfloat16, not {dtype}")
-        kernel_build.ensure_built(model_kernel_modules(spec))
+        # the kernels this model's parts need, and the host runtime (cache manager, scheduler) beside them
+        kernel_build.ensure_built(list(model_kernel_modules(spec)) + ["runtime"])
         self.spec = spec
         self.dtype = dtype
         self.device = device
