@@ -218,6 +218,7 @@ attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restr
         const int t = live ? (int)(row / heads) : 0;
         const int h = live ? (int)(row % heads) : 0;
         const int slot = slots ? slots[t] : -1;
+        const int pos = cos_tab ? positions[t] : 0;        // asked for here, with the row: its cos and sin follow it
         Vec16<T> x;
         x.raw = *reinterpret_cast<const decltype(x.raw)*>(qkv + (size_t)t * row_stride + (size_t)h * hd + sub * EPL);
         float f[EPL];
@@ -241,7 +242,6 @@ attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restr
 #pragma unroll
         for (int i = 0; i < EPL; ++i) partner[i] = __shfl_xor_sync(0xffffffffu, f[i], half_lanes);
         if (!is_v && cos_tab) {
-            const int pos = positions[t];
             const int p0 = (sub % half_lanes) * EPL;          // index of the pair inside the half
             const float* c = cos_tab + (size_t)pos * (hd / 2) + p0;
             const float* sn = sin_tab + (size_t)pos * (hd / 2) + p0;

@@ -145,10 +145,10 @@ inline cudaError_t llmk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// The same for a grid of thread-block clusters of (1, cluster_y, 1) blocks.
+// The same for a grid of thread-block clusters of `cluster` blocks.
 template <typename... KArgs, typename... Args>
-inline cudaError_t llmk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                       bool pdl, unsigned cluster_y, Args&&... args) {
+inline cudaError_t llmk_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        bool pdl, dim3 cluster, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -156,14 +156,20 @@ inline cudaError_t llmk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = cluster_y;
-    attr[0].val.clusterDim.z = 1;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (pdl && llmk_pdl_enabled()) ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+// ... of (1, cluster_y, 1) blocks
+template <typename... KArgs, typename... Args>
+inline cudaError_t llmk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       bool pdl, unsigned cluster_y, Args&&... args) {
+    return llmk_launch_clusters(kernel, grid, block, smem, stream, pdl, dim3(1, cluster_y, 1), std::forward<Args>(args)...);
 }
 
 // Thread-block clusters: rank of this block, another block's view of a shared-memory address, a load

@@ -99,7 +99,9 @@ struct FusedArgs {
     int* tickets;                // [tiles], zero between launches
 };
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+// the division as a reciprocal and a product: the exact one is a call with a slow path, which keeps the
+// compiler from overlapping the elements of a row (measured: 9 us against 2 us for the epilogue of a tile)
+__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
 __device__ __forceinline__ void builders_sync() { asm volatile("bar.sync 1, %0;" ::"n"(BUILDERS) : "memory"); }
 

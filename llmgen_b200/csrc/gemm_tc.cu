@@ -39,17 +39,34 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
 
-template <int BN, int STAGES, int MB>
+template <int BN, int STAGES, int MB, bool PAIR = false>
 struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;        // one block of 128 rows of A
-    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;   // a pair's blocks hold half of the W rows each
     static constexpr int STAGE_BYTES = MB * A_BYTES + B_BYTES;
-    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    // the epilogue's staging: per epilogue warp two slabs of 32 rows x 64 bfloat16 columns (128-byte swizzle)
+    static constexpr int SLAB_BYTES = 32 * 128;
+    static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int STAGING_BYTES = 4 * 2 * SLAB_BYTES;
+    static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
     static constexpr int NUM_BARS = 2 * STAGES + 4;     // full, empty, acc_full[2], acc_empty[2]
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
 };
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+// the division as a reciprocal and a product: the exact one is a call with a slow path, which keeps the
+// compiler from overlapping the elements of a row (measured: 9 us against 2 us for the epilogue of a tile)
+__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+// -DLLMK_GEMM_TIMELINE: blocks 0..7 stamp the global timer at their phases (a profiling build).
+#ifdef LLMK_GEMM_TIMELINE
+__device__ unsigned long long g_gemm_tl[8 * 64];
+#define TL_STAMP(slot)                                                                             \
+    do {                                                                                           \
+        if (blockIdx.x < 8 && (slot) < 64) g_gemm_tl[blockIdx.x * 64 + (slot)] = tc::global_timer(); \
+    } while (0)
+#else
+#define TL_STAMP(slot) do {} while (0)
+#endif
 
 // Persistent: block b computes tiles b, b + gridDim.x, ... (tile t = (t % m_tiles) rows, (t / m_tiles)
 // columns, so blocks that run together share W tiles).  A tile is MB blocks of 128 rows by BN
@@ -58,11 +75,23 @@ __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g));
 // accumulator sets fit into tensor memory (2 * MB * BN <= 512 columns) they are used in turn: while
 // the epilogue warps read tile i out of one, the MMA warp fills the other with tile i + 1; the TMA
 // ring runs on across tiles either way.
-template <typename TC, int BN, int STAGES, bool GATED, int MB>
+//
+// PAIR: the kernel runs as clusters of two blocks (an SM pair) and a tile is 256 rows by BN columns,
+// computed by `tcgen05.mma.cta_group::2`.  Each block loads its 128 rows of A and its half of the W
+// rows (no multicast: every block loads what it holds), so a block pulls A + W/2 per k-step where a
+// lone block pulls A + W: the wide products are bound by what the SMs pull from L2.  The bytes of
+// both blocks are counted on the `full` barriers of the block of rank 0, which issues the MMAs; its
+// commits arrive on the `empty` and `acc_full` barriers of both blocks; the epilogue warps of both
+// release an accumulator set on rank 0's `acc_empty`.  Each block reads its own 128 rows of the
+// accumulator out of its own tensor memory.
+template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_c, int store_by_tma,
                TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag) {
-    using L = Smem<BN, STAGES, MB>;
+    static_assert(!PAIR || MB == 1, "a pair of blocks takes one block of rows each");
+    using L = Smem<BN, STAGES, MB, PAIR>;
+    constexpr int ROWS = (PAIR ? 2 : MB) * BM;                     // rows of a tile
     constexpr int ACC_SETS = 2 * MB * BN <= 512 ? 2 : 1;
     constexpr uint32_t TMEM_COLS = ACC_SETS * MB * BN;             // 128, 256 or 512: a power of two
     extern __shared__ uint8_t smem_raw[];
@@ -77,11 +106,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
-    const int m_tiles = (M + MB * BM - 1) / (MB * BM);
+    const int m_tiles = (M + ROWS - 1) / ROWS;
     const int n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // which block of the pair
+    const int unit = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x; // this block's (or pair's) place in the grid
+    const int units = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
+        TL_STAMP(0);
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(tc::smem_u32(&full[s]), 1);
@@ -89,43 +122,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int i = 0; i < 2; ++i) {
             tc::mbar_init(tc::smem_u32(&acc_full[i]), 1);
-            tc::mbar_init(tc::smem_u32(&acc_empty[i]), 4);
+            tc::mbar_init(tc::smem_u32(&acc_empty[i]), PAIR ? 8 : 4);
         }
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_a);
         tc::prefetch_tensormap(&map_w);
     }
     if (warp == 1) {
-        tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
-        tc::tmem_relinquish();
+        if constexpr (PAIR) {
+            tc::tmem_alloc_pair(tc::smem_u32(tmem_slot), TMEM_COLS);
+            tc::tmem_relinquish_pair();
+        } else {
+            tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
+            tc::tmem_relinquish();
+        }
     }
     tc::tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (PAIR) {
+        __syncwarp();
+        cluster_sync_all();     // both blocks' barriers and tensor memory are ready before either uses the other's
+    } else {
+        __syncthreads();
+    }
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
         if (lane == 0) {
             pdl_launch_dependents();
+            TL_STAMP(1);
             pdl_wait();   // A was written by the kernel before this one
+            TL_STAMP(2);
             uint32_t it = 0;        // k-slices loaded so far, over all tiles of this block
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * (MB * BM), n0 = (tile / m_tiles) * BN;
+            for (int tile = unit; tile < total_tiles && ok; tile += units) {
+                const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM;
+                const int n0 = (tile / m_tiles) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (!tc::mbar_wait(tc::smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t bar = tc::smem_u32(&full[s]);
-                    tc::mbar_expect_tx(bar, L::STAGE_BYTES);
                     const uint32_t a_dst = tc::smem_u32(smem + s * L::STAGE_BYTES);
+                    if constexpr (PAIR) {
+                        // both blocks' bytes are counted on rank 0's barrier
+                        if (rank == 0) tc::mbar_expect_tx(bar, 2 * L::STAGE_BYTES);
+                        const uint32_t bar0 = cluster_map_shared(bar, 0);
+                        tc::tma_load_2d_pair(a_dst, &map_a, bar0, kb * BK, m0);
+                        tc::tma_load_2d_pair(a_dst + L::A_BYTES, &map_w, bar0, kb * BK, n0);
+                    } else {
+                        tc::mbar_expect_tx(bar, L::STAGE_BYTES);
 #pragma unroll
-                    for (int i = 0; i < MB; ++i) tc::tma_load_2d(a_dst + i * L::A_BYTES, &map_a, bar, kb * BK, m0 + i * BM);
-                    tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, kb * BK, n0);
+                        for (int i = 0; i < MB; ++i) tc::tma_load_2d(a_dst + i * L::A_BYTES, &map_a, bar, kb * BK, m0 + i * BM);
+                        tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, kb * BK, n0);
+                    }
                 }
             }
-            if (*abort_flag) {
-                // Let the copies that are in flight land before the block's memory is given up.
+            if (*abort_flag && rank == 0) {
+                // Let the copies that are in flight land before the block's memory is given up (rank 0's
+                // barriers count the other block's copies too, and that block leaves only after rank 0).
                 for (uint32_t k = it > (uint32_t)STAGES ? it - STAGES : 0; k < it; ++k) {
                     const long long t0 = clock64();
                     while (!tc::mbar_try_wait(tc::smem_u32(&full[k % STAGES]), (k / STAGES) & 1) &&
@@ -135,12 +190,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(PAIR ? 2 * BM : BM, BN);
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+            for (int tile = unit; tile < total_tiles && ok; tile += units, ++tile_iter) {
                 const int buf = tile_iter % ACC_SETS;
                 // the epilogue must have read this accumulator set before it is filled again
                 ok = tc::mbar_wait(tc::smem_u32(&acc_empty[buf]), ((tile_iter / ACC_SETS) & 1) ^ 1, abort_flag);
@@ -152,20 +207,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t round = it / STAGES;
                     ok = tc::mbar_wait(tc::smem_u32(&full[s]), round & 1, abort_flag);
                     if (!ok) break;
+                    if (it < 40) TL_STAMP(8 + it);       // when the k-th slice was there
                     tc::tc_fence_after_sync();
                     const uint32_t a_addr = tc::smem_u32(smem + s * L::STAGE_BYTES);
                     const uint32_t b_addr = a_addr + MB * L::A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
+                        if constexpr (PAIR) {
+                            tc::mma_bf16_ss_pair(acc, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, (kb | k) != 0);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < MB; ++i)
-                            tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
-                                            db, idesc, (kb | k) != 0);
+                            for (int i = 0; i < MB; ++i)
+                                tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
+                                                db, idesc, (kb | k) != 0);
+                        }
                     }
-                    tc::mma_commit(tc::smem_u32(&empty[s]));
+                    if constexpr (PAIR) tc::mma_commit_pair(tc::smem_u32(&empty[s]), (uint16_t)3);
+                    else tc::mma_commit(tc::smem_u32(&empty[s]));
                 }
-                if (ok) tc::mma_commit(tc::smem_u32(&acc_full[buf]));
+                if (ok) {
+                    if constexpr (PAIR) tc::mma_commit_pair(tc::smem_u32(&acc_full[buf]), (uint16_t)3);
+                    else tc::mma_commit(tc::smem_u32(&acc_full[buf]));
+                }
             }
         }
     } else {
@@ -175,12 +239,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool vec_ok = (ldc % (16 / (int)sizeof(TC)) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         bool ok = true;
         int tile_iter = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        uint32_t box_iter = 0;          // boxes this warp has handed to TMA
+        for (int tile = unit; tile < total_tiles && ok; tile += units, ++tile_iter) {
             const int buf = tile_iter % ACC_SETS;
-            const int m0 = (tile % m_tiles) * (MB * BM), n0 = (tile / m_tiles) * BN;
+            const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM, n0 = (tile / m_tiles) * BN;
             ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&acc_full[buf]), (tile_iter / ACC_SETS) & 1, abort_flag));
             if (!ok) break;
+            if (warp == 2 && lane == 0 && tile_iter < 4) TL_STAMP(48 + 2 * tile_iter);      // accumulator complete
             tc::tc_fence_after_sync();
+            if constexpr (sizeof(TC) == 2 && MB == 1) {
+                if (store_by_tma) {
+                    // Row-per-thread stores to global memory are slow and hold up the TMA loads of the next
+                    // tile (measured: 4.3 us a tile against 1 us without them).  Each warp rounds its 32
+                    // rows into a slab of shared memory, 64 output columns at a time, in the layout of a
+                    // 128-byte-swizzled box (a lane's 16-byte pieces then fall into different banks), and
+                    // one lane hands the slab to TMA, which writes whole rows and clips at M and N.
+                    constexpr int ACC_COLS = GATED ? 128 : 64;          // accumulator columns per 64 output columns
+                    const uint32_t slabs = tc::smem_u32(smem + L::STAGING_OFFSET) + (uint32_t)quarter * 2 * L::SLAB_BYTES;
+                    const uint32_t acc0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+                    const bool rows_live = m0 + quarter * 32 < M;      // uniform over the warp
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += ACC_COLS) {
+                        if (n0 + c0 >= N || !rows_live) break;
+                        const uint32_t slab = slabs + (uint32_t)(box_iter & 1) * L::SLAB_BYTES;
+                        if (lane == 0) tc::bulk_wait_read<1>();         // the store that read this slab two boxes ago
+                        __syncwarp();
+#pragma unroll
+                        for (int h = 0; h < ACC_COLS / 32; ++h) {
+                            uint32_t r[32];
+                            tc::tmem_ld_32x32_wait(acc0 + (uint32_t)(c0 + 32 * h), r);
+                            if constexpr (GATED) {
+                                float o[16];
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) o[i] = silu(__uint_as_float(r[i])) * __uint_as_float(r[16 + i]);
+#pragma unroll
+                                for (int q = 0; q < 2; ++q) {
+                                    Vec16<bf16> v;
+                                    v.pack(o + 8 * q);
+                                    const int chunk = 2 * h + q;
+                                    tc::st_shared_v4(slab + (uint32_t)lane * 128 + (uint32_t)((chunk ^ (lane & 7)) << 4), v.raw);
+                                }
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    float f[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * q + j]);
+                                    Vec16<bf16> v;
+                                    v.pack(f);
+                                    const int chunk = 4 * h + q;
+                                    tc::st_shared_v4(slab + (uint32_t)lane * 128 + (uint32_t)((chunk ^ (lane & 7)) << 4), v.raw);
+                                }
+                            }
+                        }
+                        tc::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tc::tma_store_2d(&map_c, slab, GATED ? (n0 + c0) / 2 : n0 + c0, m0 + quarter * 32);
+                            tc::bulk_commit();
+                        }
+                        ++box_iter;
+                    }
+                    tc::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (PAIR) tc::mbar_arrive_cluster(cluster_map_shared(tc::smem_u32(&acc_empty[buf]), 0));
+                        else tc::mbar_arrive(tc::smem_u32(&acc_empty[buf]));
+                    }
+                    if (warp == 2 && lane == 0 && tile_iter < 4) TL_STAMP(49 + 2 * tile_iter);
+                    continue;
+                }
+            }
 #pragma unroll 1
             for (int cc = 0; cc < MB * BN; cc += 32) {
                 const int mb = cc / BN, c0 = cc % BN;          // which block of rows, which columns of it
@@ -244,16 +373,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // this warp has read its lanes of the half: let the MMA warp fill it again
             tc::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&acc_empty[buf]));
+            if (warp == 2 && lane == 0 && tile_iter < 4) TL_STAMP(49 + 2 * tile_iter);      // tile stored
+            if (lane == 0) {
+                if constexpr (PAIR) tc::mbar_arrive_cluster(cluster_map_shared(tc::smem_u32(&acc_empty[buf]), 0));
+                else tc::mbar_arrive(tc::smem_u32(&acc_empty[buf]));
+            }
         }
+        if (lane == 0) tc::bulk_wait_read<0>();     // the slabs are read before the block's memory is given up
     }
     tc::tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (PAIR) {
+        __syncwarp();
+        cluster_sync_all();     // neither block leaves, or frees tensor memory, while the other may still use it
+    } else {
+        __syncthreads();
+    }
     if (warp == 1) {
         tc::tc_fence_after_sync();
-        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+        if constexpr (PAIR) tc::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tc::tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag && error_flag) atomicExch(error_flag, 1);
+    if (threadIdx.x == 0) TL_STAMP(3);
 }
 
 // ------------------------------------------------------------------------ tensor-map cache
@@ -291,22 +432,51 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
     return true;
 }
 
-template <typename TC, int BN, int STAGES, bool GATED, int MB>
+int g_store_by_tma = 1;      // 0: the threads store their rows themselves (for measurements)
+
+template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, long long ldc,
            int* error_flag, int pdl, cudaStream_t s) {
-    using L = Smem<BN, STAGES, MB>;
-    auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB>;
+    using L = Smem<BN, STAGES, MB, PAIR>;
+    auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB, PAIR>;
     static bool configured = false;   // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) LLMK_FAIL("gemm_tc: cannot raise shared memory to %d: %s", L::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM);
-    LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
-                                                pdl != 0, ma, mw, (TC*)C, M, N, K, ldc, error_flag));
+    // bfloat16 results leave through shared memory and TMA stores of [32 rows x 64 columns] boxes
+    // where TMA can address C (16-byte aligned base and rows); otherwise the threads store their rows
+    CUtensorMap mc{};
+    int store_by_tma = 0;
+    if (sizeof(TC) == 2 && MB == 1 && g_store_by_tma && host_aligned16(C) && ldc % 8 == 0)
+        store_by_tma = get_map(&mc, C, M, GATED ? N / 2 : N, ldc, 32) ? 1 : 0;
+    if constexpr (PAIR) {
+        // clusters of two blocks, one pair of SMs each
+        const int tiles = ceil_div(N, BN) * ceil_div(M, 2 * BM);
+        const int pairs = tiles < NUM_SMS / 2 ? tiles : NUM_SMS / 2;
+        LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch_clusters(kernel, dim3(2 * pairs), dim3(THREADS), L::TOTAL, s, pdl != 0,
+                                                             dim3(2, 1, 1), ma, mw, mc, store_by_tma, (TC*)C, M, N, K, ldc,
+                                                             error_flag));
+    } else {
+        const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM);
+        LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
+                                                    pdl != 0, ma, mw, mc, store_by_tma, (TC*)C, M, N, K, ldc, error_flag));
+    }
     return LLMK_OK;
 }
+
+// 0: lone blocks only.  1: pairs of blocks (`cta_group::2`) where the product has rows for them.
+// 2, 3: pairs always, with tiles 256 or 128 columns wide (for measurements).
+int g_pair_mode = 1;
+
+#ifndef LLMK_GEMM_STAGES_128
+#define LLMK_GEMM_STAGES_128 4
+#endif
+#ifndef LLMK_GEMM_STAGES_64
+#define LLMK_GEMM_STAGES_64 4
+#endif
+constexpr int STAGES_128 = LLMK_GEMM_STAGES_128, STAGES_64 = LLMK_GEMM_STAGES_64;
 
 template <typename TC, bool GATED>
 int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
@@ -328,13 +498,24 @@ int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, lo
             bn = sh.bn;
         }
     }
+    int pair_bn = 0;
+    if (g_pair_mode >= 2) pair_bn = g_pair_mode == 2 ? 256 : 128;
+    else if (g_pair_mode == 1 && M >= 4096 && (long long)ceil_div(M, 2 * BM) * ceil_div(N, 256) >= 2 * (NUM_SMS / 2))
+        pair_bn = 256;      // measured: pairs win from about 4,096 rows, with two rounds of 256 x 256 tiles for the 74 SM pairs
+    if (pair_bn) {
+        CUtensorMap pa, pw;
+        if (!get_map(&pa, A, M, K, lda, BM) || !get_map(&pw, W, N, K, ldw, pair_bn / 2))
+            LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
+        if (pair_bn == 256) return launch<TC, 256, 6, GATED, 1, true>(pa, pw, C, M, N, K, ldc, error_flag, pdl, s);
+        return launch<TC, 128, 6, GATED, 1, true>(pa, pw, C, M, N, K, ldc, error_flag, pdl, s);
+    }
     CUtensorMap ma, mw;
     if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, N, K, ldw, bn))
         LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
     switch (bn) {
         case 256: return launch<TC, 256, 4, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
-        case 128: return launch<TC, 128, 4, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
-        default: return launch<TC, 64, 4, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
+        case 128: return launch<TC, 128, STAGES_128, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
+        default: return launch<TC, 64, STAGES_64, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
     }
 }
 
@@ -347,6 +528,9 @@ LLMK_EXPORT int llmk_gemm_tc_usable(const void* A, const void* W, int M, int N, 
     if (!host_aligned16(A) || !host_aligned16(W)) return 0;
     return 1;
 }
+
+LLMK_EXPORT void llmk_gemm_tc_set_pair_mode(int mode) { g_pair_mode = mode; }
+LLMK_EXPORT void llmk_gemm_tc_set_store_by_tma(int on) { g_store_by_tma = on; }
 
 // out_dtype: storage of C (bfloat16, or float32 for logits).  gated != 0: W interleaves gate and up
 // rows in groups of 16 and C is [M, N / 2].  error_flag (device int, may be null) is raised if a
@@ -369,3 +553,9 @@ LLMK_EXPORT int llmk_gemm_tc(void* C, const void* A, const void* W, int M, int N
                      : dispatch_tile<float, false>(A, W, C, M, N, K, lda, ldw, ldc, error_flag, pdl, s);
     LLMK_FAIL("gemm_tc: unknown output dtype %d", out_dtype);
 }
+
+#ifdef LLMK_GEMM_TIMELINE
+LLMK_EXPORT int llmk_gemm_tc_timeline(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_gemm_tl, sizeof(g_gemm_tl)) == cudaSuccess ? LLMK_OK : 1;
+}
+#endif

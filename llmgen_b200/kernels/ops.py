@@ -257,6 +257,13 @@ def gemv_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def gemm_tc_set_pair_mode(mode: int) -> None:
+    """How `gemm_tc` uses pairs of blocks on 256-row tiles (`tcgen05.mma.cta_group::2`): 0 never,
+    1 where the product has the rows for it (the default), 2 / 3 always, with tiles 256 / 128 columns
+    wide (for measurements and tests)."""
+    build.load("gemm_tc").llmk_gemm_tc_set_pair_mode(c_int(mode))
+
+
 def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
     """True when the tensor-core product takes these operands: bfloat16, rows starting on 16-byte
     boundaries (what its TMA loads need)."""

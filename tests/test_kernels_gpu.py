@@ -264,6 +264,50 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
     assert err < (2e-5 if out_dtype == torch.float32 else 6e-3) * scale, (err, scale)
 
 
+@pytest.mark.parametrize("mode", [3, 2])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 200, 136), (2048, 1024, 3072), (100, 4096, 1024), (1000, 520, 2048)])
+def test_gemm_tc_pairs_of_blocks(ops, M, N, K, mode):
+    """Tiles of 256 rows computed by two blocks (`cta_group::2`), forced for every shape: rows that
+    leave the second block idle, tails in N that cut its half of W, several tiles per pair."""
+    torch.manual_seed(140 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_tc_set_pair_mode(mode)
+    try:
+        ops.gemm_tc(out, dev(a), dev(w))
+        torch.cuda.synchronize()
+    finally:
+        ops.gemm_tc_set_pair_mode(1)
+    ops.check_tc_errors(out.device)
+    ref = a.double() @ w.double().t()
+    assert float((out.double().cpu() - ref).abs().max()) < 2e-5 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("mode", [3, 2])
+def test_gemm_tc_pairs_of_blocks_gated(ops, mode):
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    torch.manual_seed(141)
+    M, F, K = 600, 1040, 1024
+    a = torch.randn(M, K).to(torch.bfloat16)
+    wg = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    out = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tc_set_pair_mode(mode)
+    try:
+        ops.gemm_tc(out, dev(a), dev(interleave_gate_up(wg, wu)), gated=True)
+        torch.cuda.synchronize()
+    finally:
+        ops.gemm_tc_set_pair_mode(1)
+    ops.check_tc_errors(out.device)
+    g = a.double() @ wg.double().t()
+    u = a.double() @ wu.double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
+
+
 def test_gemm_tc_strided_operands_and_untouched_neighbours(ops):
     torch.manual_seed(60)
     M, N, K = 70, 96, 200
