@@ -207,16 +207,19 @@ attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restr
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int sub = lane % LPR;                 // which vector of the row
-    const int heads = nq + 2 * nk;
-    const long long n_rows = (long long)n_tokens * heads;
-    const long long warp_id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long long n_warps = (long long)gridDim.x * (blockDim.x >> 5);
+    // 32-bit row numbers (the launcher refuses more rows): divisions of 64-bit numbers by `heads` were
+    // a quarter of the kernel's instructions
+    const unsigned heads = (unsigned)(nq + 2 * nk);
+    const unsigned n_rows = (unsigned)n_tokens * heads;
+    const unsigned warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const unsigned n_warps = gridDim.x * (blockDim.x >> 5);
     const int half_lanes = LPR / 2;
-    for (long long row0 = warp_id * RPW; row0 < n_rows; row0 += n_warps * RPW) {
-        const long long row = row0 + lane / LPR;
+    const float inv_hd = 1.0f / (float)hd;
+    for (unsigned row0 = warp_id * RPW; row0 < n_rows; row0 += n_warps * RPW) {
+        const unsigned row = row0 + lane / LPR;
         const bool live = row < n_rows;
         const int t = live ? (int)(row / heads) : 0;
-        const int h = live ? (int)(row % heads) : 0;
+        const int h = live ? (int)(row - (unsigned)t * heads) : 0;
         const int slot = slots ? slots[t] : -1;
         const int pos = cos_tab ? positions[t] : 0;        // asked for here, with the row: its cos and sin follow it
         Vec16<T> x;
@@ -234,9 +237,19 @@ attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restr
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (!is_v && gain) {
-            const float rinv = 1.0f / sqrtf(ss / (float)hd + eps);
+            // bfloat16 rows: the reciprocal root of the special-function unit (2 ulp, far below the rounding
+            // of the result); the exact root and division are calls with slow paths that a row would wait for
+            float rinv;
+            if constexpr (sizeof(T) == 2) rinv = rsqrtf(fmaf(ss, inv_hd, eps));
+            else rinv = 1.0f / sqrtf(ss / (float)hd + eps);
+            float g[EPL];
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) f[i] = f[i] * rinv * (gain[sub * EPL + i] + goff);
+            for (int i = 0; i < EPL; i += 4) {
+                const float4 gv = *reinterpret_cast<const float4*>(gain + sub * EPL + i);
+                g[i] = gv.x; g[i + 1] = gv.y; g[i + 2] = gv.z; g[i + 3] = gv.w;
+            }
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) f[i] = f[i] * rinv * (g[i] + goff);
         }
         float partner[EPL];
 #pragma unroll
@@ -247,7 +260,14 @@ attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restr
             const float* sn = sin_tab + (size_t)pos * (hd / 2) + p0;
             const float sign = sub < half_lanes ? -1.f : 1.f;  // low half: x cos - y sin; high half: x cos + y sin
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) f[i] = f[i] * c[i] + sign * partner[i] * sn[i];
+            for (int i = 0; i < EPL; i += 4) {
+                const float4 cv = *reinterpret_cast<const float4*>(c + i);
+                const float4 sv = *reinterpret_cast<const float4*>(sn + i);
+                f[i] = f[i] * cv.x + sign * partner[i] * sv.x;
+                f[i + 1] = f[i + 1] * cv.y + sign * partner[i + 1] * sv.y;
+                f[i + 2] = f[i + 2] * cv.z + sign * partner[i + 2] * sv.z;
+                f[i + 3] = f[i + 3] * cv.w + sign * partner[i + 3] * sv.w;
+            }
         }
         if (!live) continue;
         T* dst = nullptr;
@@ -256,7 +276,8 @@ attn_prep_vec_kernel(const T* __restrict__ qkv, long long row_stride, T* __restr
         } else if (slot >= 0) {
             T* cache = is_v ? vcache : kcache;
             const int kvh = is_v ? h - nq - nk : h - nq;
-            if (cache) dst = cache + (((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd;
+            const int page = slot / page_size;
+            if (cache) dst = cache + (((size_t)page * nkv_cache + kvh) * page_size + (slot - page * page_size)) * hd;
         }
         if (dst) {
             Vec16<T> y;
@@ -278,7 +299,12 @@ static bool launch_vec(const void* qkv, long long row_stride, void* q_out, long 
     if (row_stride % EPL != 0 || q_stride % EPL != 0 || !host_aligned16(qkv) || !host_aligned16(q_out) ||
         (kcache && !host_aligned16(kcache)) || (vcache && !host_aligned16(vcache)))
         return false;
+    // gains and rotary tables are read four floats at a time
+    if ((q_gain && !host_aligned16(q_gain)) || (k_gain && !host_aligned16(k_gain)) || (cos_tab && !host_aligned16(cos_tab)) ||
+        (sin_tab && !host_aligned16(sin_tab)) || (hd / 2) % 4 != 0)
+        return false;
     const long long rows = (long long)n_tokens * (nq + 2 * nk);
+    if (rows >= (1LL << 31) - (1LL << 20)) return false;       // the kernel counts rows in 32 bits
     const int rpw = 32 / lpr;
     long long blocks = (rows + 8 * rpw - 1) / (8 * rpw);
     if (blocks > 148 * 8) blocks = 148 * 8;
