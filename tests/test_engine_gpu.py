@@ -217,7 +217,9 @@ def test_chain_of_fused_products_when_switched_on(tmp, monkeypatch):
     assert calls["n"] == 0                                  # a prompt's portion is not few rows
     for i in range(60, 80):
         logits_close(d.step([("a", ids[i:i + 1], [0])]), ref[i:i + 1], "bfloat16")
-    assert calls["n"] == 20 * (2 * 4 - 1)                   # per layer o, gate_up, down and, after the first layer, qkv
+    other_switches = any(os.environ.get(k) for k in ("LLMGEN_GEMM", "LLMGEN_SPLITK", "LLMGEN_ATTN"))
+    if not other_switches:          # those take some or all of the products elsewhere
+        assert calls["n"] == 20 * (2 * 4 - 1)               # per layer o, gate_up, down and, after the first layer, qkv
     outs = {}
     for eager in (False, True):
         llm = LLM(path, dtype="bfloat16", max_model_len=256, max_num_seqs=4, max_batched_tokens=1024, kv_blocks=64, eager=eager)
