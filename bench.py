@@ -47,7 +47,7 @@ CONTEXT = 4096
 PROMPT_TOKENS = 512
 PREFILL_TOKENS = 2048
 SEED = 2
-PUBLISHED_B8 = 1666.0      # s4, 8 requests, RTX 3090 (the nearest published figure)
+PUBLISHED_B8 = 1666.0      # the reference's published decode rate nearest to this run: 8 requests, RTX 3090 (tokens/s)
 
 
 def check_against_baseline_json():

@@ -14,7 +14,10 @@ import sys
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        print(__doc__)
+        return 2
+    ref = sys.argv[1]
     out = {}
     for name in ("linear_case", "norm_case"):
         with open(os.path.join(ref, "testdata", name + ".json"), "r", encoding="utf-8") as f:
@@ -23,7 +26,8 @@ def main():
     with open(dst, "w", encoding="utf-8") as f:
         json.dump(out, f)
     print("wrote", dst)
+    return 0
 
 
 if __name__ == "__main__":
-    main()
+    sys.exit(main())
