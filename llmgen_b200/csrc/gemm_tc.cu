@@ -3,7 +3,8 @@
 // one thread issues `tcgen05.mma` with the float32 accumulator in tensor memory, and four
 // epilogue warps read it back with `tcgen05.ld`, round once and store.
 //
-// A block computes 128 x BN output tiles (BN = 64, 128 or 256) one after the other, 192 threads:
+// A block computes 128 x BN output tiles (BN = 64, 128 or 256) one after the other, 192 threads
+// (from 4,096 rows on, two blocks of a cluster compute 256 x 256 tiles together, see PAIR below):
 //   warp 0     TMA producer: for every 64-wide slice of K, one A box [128, 64] and one W box
 //              [BN, 64] into a ring of STAGES buffers; `full[s]` counts the bytes.
 //   warp 1     owns the tensor memory (two accumulators of BN columns) and issues the MMAs: 4
@@ -11,7 +12,10 @@
 //              they have read it, and signals `acc_full[i]` after a tile's last slice; the next tile
 //              goes to the other accumulator once the epilogue has released it (`acc_empty[i]`).
 //   warps 2-5  epilogue: each reads the 32 accumulator lanes its warp id allows, 32 columns at a
-//              time, and writes 64 (bfloat16) or 128 (float32) contiguous bytes per row.
+//              time.  bfloat16 results are rounded into a slab of shared memory (32 rows x 64
+//              columns, 128-byte swizzle) that one lane hands to a TMA store, two slabs per warp in
+//              turn; float32 results, and results TMA cannot address, are stored by the threads,
+//              64 or 128 contiguous bytes per row.
 // Rows of A beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA, so any M and
 // N are taken; K must be a multiple of 8 and the bases 16-byte aligned (TMA's rules), otherwise
 // the launcher refuses and the caller uses the CUDA-core product.
