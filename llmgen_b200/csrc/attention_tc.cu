@@ -65,7 +65,7 @@ struct Params {
 #ifdef LLMK_ATTN_TIMELINE
 #define TL_STAMP(slot)                                                                                    \
     do {                                                                                                  \
-        if (p.timeline && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && warp == 2 && lane == 0 && j < 16) \
+        if (p.timeline && blockIdx.y == 0 && blockIdx.x == 0 && warp == 2 && lane == 0 && j < 16) \
             p.timeline[j * 8 + (slot)] = clock64();                                                       \
     } while (0)
 #else
@@ -152,8 +152,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.nq / p.nkv;
-    const int kvh = blockIdx.y / p.chunks;
-    const int chunk = blockIdx.y % p.chunks;
+    // heads vary fastest over the grid: the caller lists the tiles heaviest first, and the blocks of a
+    // grid start in the order of their linear index, so the long tiles of every head start first
+    const int kvh = blockIdx.x / p.chunks;
+    const int chunk = blockIdx.x % p.chunks;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -174,8 +176,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();   // q, the cache and the step's arrays come from earlier work of the stream
 
-    const int s = p.tile_seq[blockIdx.x];
-    const int q0 = p.tile_q0[blockIdx.x];
+    const int s = p.tile_seq[blockIdx.y];
+    const int q0 = p.tile_q0[blockIdx.y];
     const int q_beg = p.cu_q[s];
     const int q_len = p.cu_q[s + 1] - q_beg;
     const int ctx = p.ctx_len[s];
@@ -508,7 +510,8 @@ LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, 
     if (!tc_host::cached_map_bf16_2d(&mk, kcache, rows, hd, hd, page_size) ||
         !tc_host::cached_map_bf16_2d(&mv, vcache, rows, hd, hd, page_size))
         LLMK_FAIL("attention_tc: cuTensorMapEncodeTiled failed for the cache");
-    dim3 grid(n_tiles, nkv * p.chunks);
+    if (n_tiles > 65535) LLMK_FAIL("attention_tc: %d tiles of queries in one launch (limit 65535)", n_tiles);
+    dim3 grid(nkv * p.chunks, n_tiles);
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 128) return launch<128>(mq, mk, mv, p, grid, s);
     return launch<64>(mq, mk, mv, p, grid, s);

@@ -83,17 +83,22 @@ class GQAAttention(Mixer):
     def max_positions(self):
         return self.position.max_positions if self.position is not None else None
 
-    def _tiles(self, builder, bq: int) -> None:
+    def _tiles(self, builder, bq: int, heaviest_first: bool = False) -> None:
+        """(sequence, first query) of every tile of `bq` queries.  `heaviest_first`: in the order of
+        the keys a tile has to read, most first; the blocks of a launch start in the order of the
+        list, and a prompt's last tiles read the whole prompt while its first read one tile of keys."""
         name = f"attention_tiles_bq{bq}"
         if builder.has(name + "_seq"):
             return
-        seq, q0 = [], []
+        tiles = []
         for s, n in enumerate(builder.q_lens):
             for start in range(0, max(n, 1), bq):
-                seq.append(s)
-                q0.append(start)
-        builder.add(name + "_seq", seq)
-        builder.add(name + "_q0", q0)
+                keys = builder.starts[s] + min(start + bq, max(n, 1))
+                tiles.append((min(keys, self.window + bq) if self.window else keys, s, start))
+        if heaviest_first:
+            tiles.sort(key=lambda t: -t[0])
+        builder.add(name + "_seq", [t[1] for t in tiles])
+        builder.add(name + "_q0", [t[2] for t in tiles])
 
     def tc_tile_queries(self, page_size: int) -> int:
         if self.dtype != torch.bfloat16 or _FORCE_ATTN == "simt":
@@ -108,7 +113,7 @@ class GQAAttention(Mixer):
         self._tiles(builder, self.bq)
         page_size = getattr(builder, "page_size", 0)
         if not builder.pure_decode and page_size and self.tc_tile_queries(page_size):
-            self._tiles(builder, self.tc_tile_queries(page_size))
+            self._tiles(builder, self.tc_tile_queries(page_size), heaviest_first=True)
 
     def _split(self, ctx):
         """(num_parts, part_size) for flash-decoding; only pure-decode steps are split."""
