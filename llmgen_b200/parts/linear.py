@@ -31,6 +31,10 @@ _SPLITK = os.environ.get("LLMGEN_SPLITK", "")      # "cluster": add the slices o
 # gated activation) and add their results to the residual.  Measured slower than the separate
 # kernels (the same dependent memory round trips, now inside the products): not the default.
 FUSE_CHAIN = os.environ.get("LLMGEN_FUSE", "") == "chain"
+# "1": the tiled product of many rows and few columns is cut along K too (float32 slices for the norm to
+# add).  Measured on a 2,048-token prompt: the products win what the norms lose (5.02 against 5.04 ms
+# a step), so it is not the default.
+_TC_SPLITK = os.environ.get("LLMGEN_TC_SPLITK", "0") == "1"
 FUSE_CHAIN_MAX_ROWS = 16
 
 GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny")
@@ -111,6 +115,13 @@ def linear_sliced(ws, name: str, x, w: torch.Tensor, out_dtype: torch.dtype, add
         if splits > 1:
             part = ws.flat(name + "_slices", splits * M * N, torch.float32).view(splits, M, N)
             ops.gemm_skinny(part, x, w, ops.SKINNY_PARTIAL)
+            return ops.Partials(part)
+    if (M > ops.SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and _FORCE == "" and _TC_SPLITK and ops.gemm_tc_usable(x, w)):
+        # many rows but few columns: too few 128 x 256 tiles for the SMs, so K is cut here too
+        splits = ops.gemm_tc_splits(M, N, x.shape[1])
+        if splits > 1:
+            part = ws.flat(name + "_slices", splits * M * N, torch.float32).view(splits, M, N)
+            ops.gemm_tc_sliced(part, x, w)
             return ops.Partials(part)
     return linear(x, w, ws.buffer(name, M, N, out_dtype))
 

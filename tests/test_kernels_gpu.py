@@ -308,6 +308,28 @@ def test_gemm_tc_pairs_of_blocks_gated(ops, mode):
     assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(2048, 1024, 2048, 2), (300, 200, 1032, 3), (513, 1000, 3072, 4), (257, 64, 640, 1)])
+def test_gemm_tc_cut_along_k(ops, M, N, K, splits):
+    """Float32 slices of the tiled product, stored by TMA: they add up to the product; tails in M, N and K."""
+    torch.manual_seed(145 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    part = torch.full((splits, M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_tc_sliced(part, dev(a), dev(w))
+    torch.cuda.synchronize()
+    ops.check_tc_errors(part.device)
+    ref = a.double() @ w.double().t()
+    assert float((part.double().sum(0).cpu() - ref).abs().max()) < 2e-5 * float(ref.abs().max())
+    planned = ops.gemm_tc_splits(M, N, K)
+    kb = (K + 63) // 64
+    assert 1 <= planned <= 4 and (planned - 1) * ((kb + planned - 1) // planned) < kb
+    assert ops.gemm_tc_splits(2048, 1024, 2048) == 2 and ops.gemm_tc_splits(2048, 4096, 1024) == 1
+    with pytest.raises(ops.KernelError, match="empty|slices"):
+        ops.gemm_tc_sliced(torch.empty(kb + 1, M, N, dtype=torch.float32, device="cuda"), dev(a), dev(w))
+
+
 def test_gemm_tc_strided_operands_and_untouched_neighbours(ops):
     torch.manual_seed(60)
     M, N, K = 70, 96, 200
