@@ -156,6 +156,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS,
+                    help="for other context lengths than the default run's: the prompts' length (prompts of a batch are "
+                         "then computed one by one)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="the engine's longest sequence")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
@@ -189,7 +193,7 @@ def main():
     nums = model_numbers(cfg, n_layers)
     rng = np.random.default_rng(SEED)
     model = random_model(cfg, SEED, "bfloat16")
-    llm = LLM(model, max_num_seqs=64, max_model_len=CONTEXT, max_batched_tokens=16384, pass_tokens=8192,
+    llm = LLM(model, max_num_seqs=64, max_model_len=args.context, max_batched_tokens=16384, pass_tokens=8192,
               block_size=args.block_size, gpu_util=0.5, seed=SEED)
     ex = llm.executor
     V = cfg["vocab_size"]
@@ -200,13 +204,18 @@ def main():
     def device_decode(batch, warm, steps):
         """K graph-replayed decode steps timed with CUDA events; returns (ms per step, mean context)."""
         reqs = [f"dev{batch}_{i}" for i in range(batch)]
-        total = PROMPT_TOKENS + warm + steps + 1
-        prompts = [rng.integers(0, V, PROMPT_TOKENS).tolist() for _ in range(batch)]
+        P = args.prompt_tokens
+        total = P + warm + steps + 1
+        prompts = [rng.integers(0, V, P).tolist() for _ in range(batch)]
         for r in reqs:
             assert ex.admit(r) and ex.reserve(r, 0, total)
-        ex.step([StepEntry(r, p, 0, [PROMPT_TOKENS - 1], 0.6) for r, p in zip(reqs, prompts)], sample=True, return_logits=False)
+        if P * batch <= 65536:
+            ex.step([StepEntry(r, p, 0, [P - 1], 0.6) for r, p in zip(reqs, prompts)], sample=True, return_logits=False)
+        else:
+            for r, p in zip(reqs, prompts):
+                ex.step([StepEntry(r, p, 0, [P - 1], 0.6)], sample=True, return_logits=False)
         toks = rng.integers(0, V, batch).tolist()
-        pos = PROMPT_TOKENS
+        pos = P
         bucket, g = ex.decode_graph(batch, total)     # one graph for the whole run: the class of the last context
 
         def one(pos):
@@ -265,7 +274,7 @@ def main():
     # ---- end to end through the entry point: host token ids in, host token ids out, every step
     e2e = None
     if not args.skip_e2e:
-        prompts = [rng.integers(0, V, PROMPT_TOKENS).tolist() for _ in range(args.batch)]
+        prompts = [rng.integers(0, V, args.prompt_tokens).tolist() for _ in range(args.batch)]
         params = SamplingParams(temperature=0.6, max_tokens=warmup + K + 2, ignore_eos=True)
         for p in prompts:
             llm.engine.add_request(p, params)
@@ -304,11 +313,11 @@ def main():
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8, "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random-init weights (seed 2)",
-        "config": {"model": "Qwen3-0.6B shape", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+        "config": {"model": "Qwen3-0.6B shape", "global_batch": args.batch, "seq_len": args.context, "parallelism": "single GPU",
                    "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
                    "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "tied_embeddings": True,
-                   "prompt_tokens": PROMPT_TOKENS, "mean_context": mean_ctx, "page_size": args.block_size,
+                   "prompt_tokens": args.prompt_tokens, "mean_context": mean_ctx, "page_size": args.block_size,
                    "l2": "inputs larger than L2 (1.19 GB of weights per step), no flush", "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": launches_per_step * K, "prefill": prefill, "roofline": roofline, "points": points,
         "clocks": clocks, "impl": "ours",
