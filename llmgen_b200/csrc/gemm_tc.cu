@@ -537,13 +537,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
 // 2, 3: pairs always, with tiles 256 or 128 columns wide (for measurements).
 int g_pair_mode = 1;
 
-#ifndef LLMK_GEMM_STAGES_128
-#define LLMK_GEMM_STAGES_128 4
-#endif
-#ifndef LLMK_GEMM_STAGES_64
-#define LLMK_GEMM_STAGES_64 4
-#endif
-constexpr int STAGES_128 = LLMK_GEMM_STAGES_128, STAGES_64 = LLMK_GEMM_STAGES_64;
+// ring depth of the narrower tiles (3, 4 and 6 were measured on a prompt's products: no difference
+// beyond 4, the MMA instructions set the pace)
+constexpr int STAGES_128 = 4, STAGES_64 = 4;
 
 template <typename TC, bool GATED>
 int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
