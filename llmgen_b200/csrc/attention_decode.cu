@@ -183,10 +183,15 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     const int g0 = chunk * GC;                      // first head of the chunk inside the group
     const int n_heads = min(GC, G - g0);
     pdl_launch_dependents();
-    pdl_wait();
+    // What the step's arrays say (lengths, block tables) was uploaded before the step, and the cache holds
+    // earlier steps' keys: with the fused preparation only the packed projection comes from the kernel
+    // before this one, so the wait for it stands after the first copies of keys have been issued.
+    const bool fused = p.packed != nullptr;
+    if (!fused) pdl_wait();
     const int ctx = p.ctx_len[s];
     const int t = p.cu_q[s];
     if (ctx <= 0) {
+        if (fused) pdl_wait();          // the output rows may still be read by a kernel before the one before
         if (part == 0)
             for (int i = tid; i < n_heads * HD; i += THREADS)
                 p.out[(size_t)t * p.o_stride + (size_t)(kvh * G + g0) * HD + i] = from_float<bf16>(0.f);
@@ -202,43 +207,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     const int n_pages = n_keys > 0 ? ((k_end - 1) >> lps) - page_base + 1 : 0;
     const int* bt = p.block_tables + (size_t)s * p.max_blocks;
 
-    // The part's page ids and q (float32, pre-multiplied by scale; zeros for heads beyond the group).
+    // The part's page ids first: the copies of keys need them.
     for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = bt[page_base + i];
-    if (p.packed == nullptr) {
-        for (int i = tid; i < GC * HD; i += THREADS) {
-            const int g = i / HD;
-            q_s[i] = g < n_heads ? to_float(p.q[(size_t)t * p.q_stride + (size_t)(kvh * G + g0 + g) * HD + i % HD]) * p.scale : 0.f;
-        }
-    } else {
-        // A warp per row of the packed projection: the chunk's q heads, and in the block whose part
-        // holds the newest position also this kv head's k and v, which go to the cache before the
-        // block reads its keys (other blocks of the same kv head write the same values).
-        const bool newest = p.nk > 0 && k_beg <= ctx - 1 && ctx - 1 < k_end;
-        const int n_tasks = GC + (newest ? 2 : 0);
-        for (int task = warp; task < n_tasks; task += WARPS) {
-            float vals[DPL];
-            if (task < GC) {
-                if (task < n_heads) {
-                    prep_head<HD>(p, t, kvh * G + g0 + task, p.q_gain, p.q_off, true, lane, vals);
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = vals[i] * p.scale;
-                } else {
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = 0.f;
-                }
-            } else {
-                const bool is_v = task == GC + 1;
-                prep_head<HD>(p, t, p.nq + (is_v ? p.nk : 0) + kvh, is_v ? nullptr : p.k_gain, p.k_off, !is_v, lane, vals);
-                const int slot = p.slots ? p.slots[t] : -1;
-                if (slot >= 0) {
-                    bf16* dst = const_cast<bf16*>(is_v ? p.vcache : p.kcache) +
-                                ((((size_t)(slot >> lps)) * p.nkv + kvh) * (size_t)(ps_mask + 1) + (slot & ps_mask)) * HD;
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) dst[lane + 32 * i] = from_float<bf16>(vals[i]);
-                }
-            }
-        }
-    }
     __syncthreads();
 
     // Each warp streams the keys it is given (KPW of every WARPS * KPW) through a cp.async ring of
@@ -290,10 +260,59 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
         }
         cp_async_commit();
     };
+    // In the block that will write the newest key to the cache, copies that would read that key must wait
+    // for the write; they are among the first STAGES - 1 steps only when the part is that short.
+    const bool newest_here = fused && p.nk > 0 && k_beg <= ctx - 1 && ctx - 1 < k_end;
+    const bool early = fused && !(newest_here && n_steps <= STAGES - 1);
+    auto first_copies = [&]() {
 #pragma unroll
-    for (int st = 0; st < STAGES - 1; ++st) {
-        if (st < n_steps) issue(st, st); else cp_async_commit();
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < n_steps) issue(st, st); else cp_async_commit();
+        }
+    };
+    if (early) first_copies();
+    if (fused) pdl_wait();
+
+    // The part's page ids and q (float32, pre-multiplied by scale; zeros for heads beyond the group).
+    if (p.packed == nullptr) {
+        for (int i = tid; i < GC * HD; i += THREADS) {
+            const int g = i / HD;
+            q_s[i] = g < n_heads ? to_float(p.q[(size_t)t * p.q_stride + (size_t)(kvh * G + g0 + g) * HD + i % HD]) * p.scale : 0.f;
+        }
+    } else {
+        // A warp per row of the packed projection: the chunk's q heads, and in the block whose part
+        // holds the newest position also this kv head's k and v, which go to the cache before the
+        // block reads its keys (other blocks of the same kv head write the same values).
+        const bool newest = p.nk > 0 && k_beg <= ctx - 1 && ctx - 1 < k_end;
+        const int n_tasks = GC + (newest ? 2 : 0);
+        for (int task = warp; task < n_tasks; task += WARPS) {
+            float vals[DPL];
+            if (task < GC) {
+                if (task < n_heads) {
+                    prep_head<HD>(p, t, kvh * G + g0 + task, p.q_gain, p.q_off, true, lane, vals);
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = vals[i] * p.scale;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = 0.f;
+                }
+            } else {
+                const bool is_v = task == GC + 1;
+                prep_head<HD>(p, t, p.nq + (is_v ? p.nk : 0) + kvh, is_v ? nullptr : p.k_gain, p.k_off, !is_v, lane, vals);
+                const int slot = p.slots ? p.slots[t] : -1;
+                if (slot >= 0) {
+                    bf16* dst = const_cast<bf16*>(is_v ? p.vcache : p.kcache) +
+                                ((((size_t)(slot >> lps)) * p.nkv + kvh) * (size_t)(ps_mask + 1) + (slot & ps_mask)) * HD;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) dst[lane + 32 * i] = from_float<bf16>(vals[i]);
+                }
+            }
+        }
     }
+    __syncthreads();
+
+
+    if (!early) first_copies();
 
     if constexpr (MMA) {
         // ---- tensor-core variant.  Lane (g = lane / 4, t = lane % 4) of a warp holds, of every
