@@ -12,7 +12,10 @@
 //            lanes per key (float32 dot products against q, which sits in shared memory pre-multiplied
 //            by scale), maximum and sum over the 8 keys by shuffles, then P V with every lane owning
 //            head_dim / 32 output values for all GC heads.  The four warps' states are merged at the end.
-//   merge    with parts > 1 the block writes its un-normalised sums and (m, l) to scratch and takes
+//   merge    with 2 to 8 parts the launch makes the parts of a (sequence, kv head) one thread-block
+//            cluster: the blocks leave their sums in shared memory and, after the cluster's barrier,
+//            each merges a share of the outputs reading the others' shared memory.  With more parts
+//            (long contexts) the block writes its un-normalised sums and (m, l) to scratch and takes
 //            a ticket from a per-(sequence, head chunk) counter; the block that draws the last ticket
 //            merges all parts in part order, sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p, writes
 //            the output row and resets the counter.  The result does not depend on which block
@@ -52,6 +55,7 @@ struct DecodeParams {
     int* counters;       // [sequences][gridDim.y]
     long long q_stride, o_stride;
     int max_blocks, nq, nkv, log2_page, window, chunks, page_cap;
+    int cluster_merge;   // the blocks of a sequence's parts are a thread-block cluster and merge through shared memory
     float scale;
     // With `packed` set, q is not read from `q`: the block makes it (and, in the block that owns the
     // sequence's newest key, k and v, which it also writes to the cache) from the packed projection
@@ -562,6 +566,51 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
         }
         return;
     }
+    if (p.cluster_merge) {
+        // The parts of this (sequence, kv head) are the blocks of one cluster: each leaves its sums in its
+        // own shared memory (over q, which is no longer read), and after the cluster's barrier block r
+        // merges outputs r * THREADS + tid, ... reading the others' shared memory: no trip through global
+        // memory, no ticket.  Nobody leaves before all have read.
+        __shared__ float res_ml[2 * GC];
+        __syncthreads();                 // every warp is done with q_s
+        for (int i = tid; i < n_heads * HD; i += THREADS) {
+            float M, Ls;
+            q_s[i] = merged(i / HD, i % HD, M, Ls);
+            if (i % HD == 0) {
+                res_ml[2 * (i / HD)] = M;
+                res_ml[2 * (i / HD) + 1] = Ls;
+            }
+        }
+        cluster_sync_all();
+        const uint32_t o_base = (uint32_t)__cvta_generic_to_shared(q_s), ml_base = (uint32_t)__cvta_generic_to_shared(res_ml);
+        for (int i = part * THREADS + tid; i < n_heads * HD; i += parts * THREADS) {
+            const int g = i / HD;
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int pt = 0; pt < 8; ++pt) {
+                const bool on = pt < parts;
+                ms[pt] = on ? cluster_ld_f32(cluster_map_shared(ml_base + (uint32_t)(2 * g) * 4u, pt)) : -INFINITY;
+                ls[pt] = on ? cluster_ld_f32(cluster_map_shared(ml_base + (uint32_t)(2 * g + 1) * 4u, pt)) : 0.f;
+                os[pt] = on ? cluster_ld_f32(cluster_map_shared(o_base + (uint32_t)i * 4u, pt)) : 0.f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int pt = 0; pt < 8; ++pt)
+                if (ls[pt] > 0.f) M = fmaxf(M, ms[pt]);
+            float denom = 0.f, v = 0.f;
+#pragma unroll
+            for (int pt = 0; pt < 8; ++pt) {
+                if (ls[pt] > 0.f) {
+                    const float e = __expf(ms[pt] - M);
+                    denom += e * ls[pt];
+                    v += e * os[pt];
+                }
+            }
+            p.out[(size_t)t * p.o_stride + (size_t)(kvh * G + g0) * HD + i] = from_float<bf16>(denom > 0.f ? v / denom : 0.f);
+        }
+        cluster_sync_all();
+        return;
+    }
     for (int i = tid; i < n_heads * HD; i += THREADS) {
         const int g = i / HD, d = i % HD;
         float M, Ls;
@@ -620,6 +669,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     }
 }
 
+int g_cluster_merge = 1;      // 0: always merge through global memory and a ticket (for measurements)
+
 template <int HD, int GC, bool MMA>
 int launch(const DecodeParams& p, dim3 grid, cudaStream_t s) {
     const size_t smem = DecodeSmem<HD, GC, MMA ? 16 : 8>::bytes(p.page_cap);
@@ -630,7 +681,10 @@ int launch(const DecodeParams& p, dim3 grid, cudaStream_t s) {
         if (e != cudaSuccess) LLMK_FAIL("attention_decode: cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         configured = smem;
     }
-    LLMK_CHECK_LAUNCH_RC("attention_decode", llmk_launch(kernel, grid, dim3(THREADS), smem, s, true, p));
+    if (p.cluster_merge)
+        LLMK_CHECK_LAUNCH_RC("attention_decode", llmk_launch_clusters(kernel, grid, dim3(THREADS), smem, s, true, dim3(grid.x, 1, 1), p));
+    else
+        LLMK_CHECK_LAUNCH_RC("attention_decode", llmk_launch(kernel, grid, dim3(THREADS), smem, s, true, p));
     return LLMK_OK;
 }
 
@@ -720,6 +774,8 @@ LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void*
     p.part_o = scratch;
     p.part_ml = parts > 1 ? scratch + (size_t)n_seqs * nq * parts * hd : nullptr;
     p.counters = counters;
+    // up to 8 parts (a portable cluster) merge through the cluster's shared memory
+    p.cluster_merge = (g_cluster_merge && parts >= 2 && parts <= 8) ? 1 : 0;
     p.q_stride = q_stride; p.o_stride = o_stride; p.max_blocks = max_blocks;
     p.nq = nq; p.nkv = nkv; p.window = window;
     p.log2_page = 0;
@@ -736,3 +792,5 @@ LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void*
     if (use_mma()) return hd == 128 ? dispatch_group<128, true>(gc, p, grid, s) : dispatch_group<64, true>(gc, p, grid, s);
     return hd == 128 ? dispatch_group<128, false>(gc, p, grid, s) : dispatch_group<64, false>(gc, p, grid, s);
 }
+
+LLMK_EXPORT void llmk_attention_decode_set_cluster_merge(int on) { g_cluster_merge = on; }

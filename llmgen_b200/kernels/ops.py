@@ -502,6 +502,12 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
            2 if num_parts > 1 else 1)
 
 
+def attention_decode_set_cluster_merge(on: bool) -> None:
+    """Whether `attention_decode` merges up to 8 key parts through the shared memory of a thread-block
+    cluster (the default) or through global memory and a ticket (for measurements and tests)."""
+    build.load("attention_decode").llmk_attention_decode_set_cluster_merge(c_int(1 if on else 0))
+
+
 def attention_decode_usable(nq: int, nkv: int, hd: int, page_size: int) -> bool:
     return bool(build.load("attention_decode").llmk_attention_decode_usable(c_int(nq), c_int(nkv), c_int(hd), c_int(page_size)))
 

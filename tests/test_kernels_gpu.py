@@ -901,8 +901,14 @@ def test_attention_decode(ops, nq, nkv, hd, page, parts):
     seqs = [(150, 1), (1, 1), (0, 1), (333, 1), (64, 1), (65, 1), (700, 1), (9, 1)]
     q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, dtype, 31)
     counters = torch.zeros(ops.attention_decode_counters(len(seqs), nq, nkv), dtype=torch.int32, device="cuda")
-    for _ in range(2):
-        got = run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, parts=parts, counters=counters)
+    # up to 8 parts merge through the shared memory of a cluster, more through global memory and a ticket;
+    # the second round forces the ticket for every number of parts
+    for through_cluster in (True, False):
+        ops.attention_decode_set_cluster_merge(through_cluster)
+        try:
+            got = run_attention_decode(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page, parts=parts, counters=counters)
+        finally:
+            ops.attention_decode_set_cluster_merge(True)
         assert float((got - ref).abs().max()) < tol(dtype, 3)
         assert float(got[2].abs().max()) == 0.0
         assert int(counters.abs().sum()) == 0
