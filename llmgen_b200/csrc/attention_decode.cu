@@ -75,8 +75,34 @@ struct DecodeParams {
 // One head's row of the packed projection: lane holds the values lane, lane + 32, ... of the head
 // (slices added in order), optionally normalised (RMSNorm over the head, gain + offset) and rotated
 // (half-split pairs (i, i + rot / 2), rot a multiple of 64, so that a pair sits in one lane).
+// What a head's preparation needs besides the row itself and what no kernel of the step writes: this
+// lane's gains (offset added) for q and k rows and its cos / sin values at the token's position.  Loaded
+// before the wait for the kernel that makes the row.
 template <int HD>
-__device__ __forceinline__ void prep_head(const DecodeParams& p, int t, int head_in_row, const float* gain, float goff,
+struct HeadConsts {
+    float gq[HD / 32], gk[HD / 32], cs[HD / 64], sn[HD / 64];
+};
+template <int HD>
+__device__ __forceinline__ void load_head_consts(const DecodeParams& p, int t, int lane, HeadConsts<HD>& hc) {
+    constexpr int VPL = HD / 32;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        hc.gq[i] = p.q_gain ? p.q_gain[lane + 32 * i] + p.q_off : 1.f;
+        hc.gk[i] = p.k_gain ? p.k_gain[lane + 32 * i] + p.k_off : 1.f;
+    }
+    const int half = p.rot / 2, hv = half / 32;
+    const int pos = p.cos_tab ? p.positions[t] : 0;
+#pragma unroll
+    for (int i = 0; i < VPL / 2; ++i) {
+        const bool on = p.cos_tab && i < hv;
+        hc.cs[i] = on ? p.cos_tab[(size_t)pos * half + lane + 32 * i] : 1.f;
+        hc.sn[i] = on ? p.sin_tab[(size_t)pos * half + lane + 32 * i] : 0.f;
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void prep_head(const DecodeParams& p, int t, int head_in_row, const float* gain,
+                                          const float (&gvals)[HD / 32], const HeadConsts<HD>& hc,
                                           bool rotate, int lane, float (&vals)[HD / 32]) {
     constexpr int VPL = HD / 32;
     const size_t base = (size_t)t * p.packed_stride + (size_t)head_in_row * HD;
@@ -100,18 +126,14 @@ __device__ __forceinline__ void prep_head(const DecodeParams& p, int t, int head
         ss = warp_sum(ss);
         const float rinv = 1.0f / sqrtf(ss / (float)HD + p.eps);
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) vals[i] = vals[i] * rinv * (gain[lane + 32 * i] + goff);
+        for (int i = 0; i < VPL; ++i) vals[i] = vals[i] * rinv * gvals[i];
     }
     if (rotate && p.cos_tab) {
-        const int half = p.rot / 2;
-        const int hv = half / 32;               // values per lane in each half of the rotated part
-        const int pos = p.positions[t];
-        const float* c = p.cos_tab + (size_t)pos * half;
-        const float* sn = p.sin_tab + (size_t)pos * half;
+        const int hv = p.rot / 64;              // values per lane in each half of the rotated part
 #pragma unroll
         for (int i = 0; i < VPL / 2; ++i) {
             if (i < hv) {
-                const float x0 = vals[i], x1 = vals[i + hv], cs = c[lane + 32 * i], sv = sn[lane + 32 * i];
+                const float x0 = vals[i], x1 = vals[i + hv], cs = hc.cs[i], sv = hc.sn[i];
                 vals[i] = x0 * cs - x1 * sv;
                 vals[i + hv] = x1 * cs + x0 * sv;
             }
@@ -275,7 +297,11 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
         }
     };
     if (early) first_copies();
-    if (fused) pdl_wait();
+    HeadConsts<HD> hc;
+    if (fused) {
+        load_head_consts<HD>(p, t, lane, hc);
+        pdl_wait();
+    }
 
     // The part's page ids and q (float32, pre-multiplied by scale; zeros for heads beyond the group).
     if (p.packed == nullptr) {
@@ -293,7 +319,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
             float vals[DPL];
             if (task < GC) {
                 if (task < n_heads) {
-                    prep_head<HD>(p, t, kvh * G + g0 + task, p.q_gain, p.q_off, true, lane, vals);
+                    prep_head<HD>(p, t, kvh * G + g0 + task, p.q_gain, hc.gq, hc, true, lane, vals);
 #pragma unroll
                     for (int i = 0; i < DPL; ++i) q_s[task * HD + lane + 32 * i] = vals[i] * p.scale;
                 } else {
@@ -302,7 +328,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
                 }
             } else {
                 const bool is_v = task == GC + 1;
-                prep_head<HD>(p, t, p.nq + (is_v ? p.nk : 0) + kvh, is_v ? nullptr : p.k_gain, p.k_off, !is_v, lane, vals);
+                prep_head<HD>(p, t, p.nq + (is_v ? p.nk : 0) + kvh, is_v ? nullptr : p.k_gain, hc.gk, hc, !is_v, lane, vals);
                 const int slot = p.slots ? p.slots[t] : -1;
                 if (slot >= 0) {
                     bf16* dst = const_cast<bf16*>(is_v ? p.vcache : p.kcache) +
