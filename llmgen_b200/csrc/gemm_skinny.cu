@@ -45,7 +45,8 @@ constexpr int BK = 64;           // one 128-byte swizzle row of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
-enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2, OUT_CLUSTER = 3, OUT_RESIDUAL = 4 };
+enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2, OUT_CLUSTER = 3, OUT_RESIDUAL = 4, OUT_CLUSTER_GATED = 5 };
+constexpr bool is_cluster_mode(int mode) { return mode == OUT_CLUSTER || mode == OUT_CLUSTER_GATED; }
 enum { X_TMA = 0, X_NORM = 1, X_GATED = 2 };
 constexpr int BUILDERS = 128;    // the four epilogue warps build X when it does not come through TMA
 constexpr int MAX_SMEM = 227 * 1024;
@@ -371,7 +372,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int i = 0; i < 16; ++i) {
                     const int m = c0 + i;
                     const float v = __uint_as_float(r[i]);
-                    if constexpr (MODE == OUT_CLUSTER) {
+                    if constexpr (is_cluster_mode(MODE)) {
                         // this block's slice of the sum, for the cluster to add up: [row of X][row of W]
                         if (m < M) reinterpret_cast<float*>(smem)[m * BW + quarter * 32 + lane] = v;
                     } else if constexpr (MODE == OUT_GATED) {
@@ -456,6 +457,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc::tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag && error_flag) atomicExch(error_flag, 1);
+    if constexpr (MODE == OUT_CLUSTER_GATED) {
+        // As below, and W interleaves gate and up rows in groups of 16: block r owns whole groups of 32
+        // rows (S <= 4), adds up gate row j and up row j of each and writes silu(gate) * up, so the packed
+        // product never reaches memory and no activation kernel follows.
+        cluster_sync_all();
+        const uint32_t S = gridDim.y, rank = cluster_ctarank();
+        const int pairs_per = BW / (int)S / 2;
+        const uint32_t red = tc::smem_u32(smem);
+        for (int idx = threadIdx.x; idx < pairs_per * M; idx += THREADS) {
+            const int m = idx / pairs_per, jj = idx % pairs_per;
+            const int gate_row = (int)rank * 2 * pairs_per + (jj / 16) * 32 + jj % 16;
+            const uint32_t local = red + (uint32_t)(m * BW + gate_row) * 4u;
+            float g = 0.f, u = 0.f;
+            for (uint32_t q = 0; q < S; ++q) {
+                const uint32_t remote = cluster_map_shared(local, q);
+                g += cluster_ld_f32(remote);
+                u += cluster_ld_f32(remote + 16u * 4u);
+            }
+            const int col = (n0 + gate_row) / 32 * 16 + jj % 16;
+            if (n0 + gate_row + 16 < N) C[(size_t)m * ldc + col] = from_float<TC>(g / (1.0f + expf(-g)) * u);
+        }
+        cluster_sync_all();
+    }
     if constexpr (MODE == OUT_CLUSTER) {
         // The blocks of a cluster hold the slices of K of one tile.  Each left its float32 slice in its
         // own shared memory (over the TMA ring, which is idle by now); block r now adds up, in slice
@@ -488,7 +512,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, 
         if (e != cudaSuccess) LLMK_FAIL("gemm_skinny: cannot raise shared memory to %d: %s", L::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    if constexpr (MODE == OUT_CLUSTER) {
+    if constexpr (is_cluster_mode(MODE)) {
         static bool wide_ok = false;
         if (splits > 8 && !wide_ok) {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -546,7 +570,7 @@ int dispatch_rows(const CUtensorMap& mw, const void* X, void* C, int M, int N, i
         case 64: return launch<TC, 64, 4, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
         default: break;
     }
-    if constexpr (MODE == OUT_CLUSTER) {
+    if constexpr (is_cluster_mode(MODE)) {
         LLMK_FAIL("gemm_skinny: the sum over a cluster takes at most 64 rows, not %d", M);
     } else {
         if (mpad == 128) return launch<TC, 128, 6, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
@@ -598,12 +622,16 @@ LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, i
     if (splits < 1 || splits > num_kb || splits > 65535) LLMK_FAIL("gemm_skinny: %d slices for K=%d", splits, K);
     const int per = ceil_div(num_kb, splits);
     if ((splits - 1) * per >= num_kb) LLMK_FAIL("gemm_skinny: %d slices of K=%d would leave one empty", splits, K);
-    if (mode != OUT_PARTIAL && mode != OUT_CLUSTER && splits != 1)
+    if (mode != OUT_PARTIAL && !is_cluster_mode(mode) && splits != 1)
         LLMK_FAIL("gemm_skinny: a product written directly cannot be sliced (%d)", splits);
+    if (mode == OUT_CLUSTER_GATED && (splits != 2 && splits != 4))
+        LLMK_FAIL("gemm_skinny: the gated sum over a cluster takes 2 or 4 slices, not %d", splits);
+    if (mode == OUT_CLUSTER_GATED && (N % 32 != 0 || out_dtype != LLMK_BF16 || M > 64))
+        LLMK_FAIL("gemm_skinny: the gated sum over a cluster writes bfloat16, N=%d a multiple of 32, at most 64 rows", N);
     if (mode == OUT_CLUSTER && (splits < 2 || splits > 16 || (splits & (splits - 1)) != 0 || M > 64))
         LLMK_FAIL("gemm_skinny: a cluster adds up 2, 4, 8 or 16 slices of at most 64 rows (%d slices, %d rows)", splits, M);
     if (mode == OUT_GATED && N % 32 != 0) LLMK_FAIL("gemm_skinny: gated epilogue needs N=%d to be a multiple of 32", N);
-    if (ldc < (mode == OUT_GATED ? N / 2 : N)) LLMK_FAIL("gemm_skinny: ldc=%lld too small", ldc);
+    if (ldc < (mode == OUT_GATED || mode == OUT_CLUSTER_GATED ? N / 2 : N)) LLMK_FAIL("gemm_skinny: ldc=%lld too small", ldc);
     CUtensorMap mw;
     if (!tc_host::cached_map_bf16_2d(&mw, W, N, K, ldw, BW))
         LLMK_FAIL("gemm_skinny: cuTensorMapEncodeTiled failed for W (N=%d K=%d ldw=%lld)", N, K, ldw);
@@ -613,6 +641,7 @@ LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, i
         if (out_dtype != LLMK_BF16) LLMK_FAIL("gemm_skinny: the gated epilogue writes bfloat16");
         return dispatch_rows<bf16, OUT_GATED>(mw, X, C, M, N, K, ldx, ldc, 1, per, error_flag, s);
     }
+    if (mode == OUT_CLUSTER_GATED) return dispatch_rows<bf16, OUT_CLUSTER_GATED>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s);
     if (mode == OUT_CLUSTER) {
         if (out_dtype == LLMK_BF16) return dispatch_rows<bf16, OUT_CLUSTER>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s);
         if (out_dtype == LLMK_F32) return dispatch_rows<float, OUT_CLUSTER>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s);

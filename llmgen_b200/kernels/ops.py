@@ -341,6 +341,7 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
 
 SKINNY_MAX_ROWS = 256
 SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED, SKINNY_CLUSTER = 0, 1, 2, 3
+SKINNY_CLUSTER_GATED = 5     # slices of K added up inside a cluster (2 or 4), then silu(gate) * up: out[M, N/2]
 SKINNY_CLUSTER_MAX_ROWS = 64
 _cluster_plans = {}
 _skinny_plans = {}
@@ -382,10 +383,10 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int =
             raise KernelError("gemm_skinny: partial sums go to a contiguous float32 [splits, M, N] array")
         splits, ldc = out.shape[0], N
     else:
-        n_out = N // 2 if mode == SKINNY_GATED else N
+        n_out = N // 2 if mode in (SKINNY_GATED, SKINNY_CLUSTER_GATED) else N
         if out.shape[0] != M or out.shape[1] != n_out:
             raise KernelError(f"gemm_skinny: out{list(out.shape)} does not fit [{M}, {n_out}]")
-        splits, ldc = (splits if mode == SKINNY_CLUSTER else 1), _row_stride(out)
+        splits, ldc = (splits if mode in (SKINNY_CLUSTER, SKINNY_CLUSTER_GATED) else 1), _row_stride(out)
     _check(lib, lib.llmk_gemm_skinny(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
                                      c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(ldc),
                                      c_int(splits), c_int(mode), c_int(dtype_code(out.dtype)),

@@ -1,6 +1,8 @@
 """Dense gated feed-forward (SwiGLU for Qwen3)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
@@ -11,6 +13,7 @@ from .registry import register_feed_forward
 from .spec import GatedMLPSpec, WeightDecl
 
 
+CLUSTER_GATED = os.environ.get("LLMGEN_GATED", "") != "separate"    # "separate": slices, then a kernel for the activation
 GATE_UP_GROUP = 16   # rows of gate, then rows of up, alternating: what the gated epilogue expects
 
 
@@ -82,7 +85,13 @@ class GatedMLP(FeedForward):
             return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
         act = ws.buffer("ffn_act", T, F, self.dtype)
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
-        if gated and T <= ops.SKINNY_MAX_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
+        if gated and CLUSTER_GATED and T <= ops.SKINNY_CLUSTER_MAX_ROWS and linear_module._SPLITK == "" \
+                and min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) >= 2:
+            # few rows: K is cut, the slices are added up inside a thread-block cluster and the activation
+            # follows there, so neither the packed product nor a kernel for the activation is needed
+            ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_CLUSTER_GATED,
+                            splits=min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4))
+        elif gated and T <= ops.SKINNY_MAX_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
             ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_GATED)
         elif gated and T > ops.SKINNY_MAX_ROWS:
             ops.gemm_tc(act, x, self.w_gate_up, gated=True)

@@ -450,6 +450,26 @@ def test_gemm_skinny_gated(ops, M, F, K):
     assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("M,F,K,splits", [(8, 3072, 1024, 4), (1, 48, 128, 2), (33, 176, 256, 4), (64, 1024, 512, 2)])
+def test_gemm_skinny_gated_after_the_sum_in_a_cluster(ops, M, F, K, splits):
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    torch.manual_seed(171 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    wg = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    out = torch.full((M, F), 7.0, dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):
+        ops.gemm_skinny(out, dev(a), dev(interleave_gate_up(wg, wu)), ops.SKINNY_CLUSTER_GATED, splits=splits)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    g = a.double() @ wg.double().t()
+    u = a.double() @ wu.double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
+    with pytest.raises(ops.KernelError, match="2 or 4|slices"):
+        ops.gemm_skinny(out, dev(a), dev(interleave_gate_up(wg, wu)), ops.SKINNY_CLUSTER_GATED, splits=8)
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do(ops):
     w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="above 256"):
