@@ -582,8 +582,8 @@ int dispatch_rows(const CUtensorMap& mw, const void* X, void* C, int M, int N, i
 
 LLMK_EXPORT int llmk_gemm_skinny_max_rows() { return 256; }
 
-// How many slices of K suit this product: about one block per SM, at least two 64-wide slices of
-// K per block, and partial sums (splits * M * N floats) no larger than W itself.
+// How many slices of K suit this product: about one block per SM but at most 8 slices, at least two
+// 64-wide slices of K per block, and partial sums (splits * M * N floats) no larger than W itself.
 LLMK_EXPORT int llmk_gemm_skinny_splits(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 1;
     const int tiles = ceil_div(N, BW);
@@ -591,6 +591,10 @@ LLMK_EXPORT int llmk_gemm_skinny_splits(int M, int N, int K) {
     int splits = (NUM_SMS + tiles / 2) / tiles;
     splits = min(splits, num_kb / 2);
     splits = min(splits, K / (2 * M));
+    // at most 8: the kernel that adds the slices up pays for every one of them, and a decode step was
+    // fastest with 8 (1.171 / 0.987 / 0.939 / 0.917 / 0.921 / 0.930 / 0.966 ms at batch 8 with at most
+    // 2 / 4 / 6 / 8 / 10 / 12 / 16 slices), although the product alone likes 16
+    splits = min(splits, 8);
     splits = max(splits, 1);
     const int per = ceil_div(num_kb, splits);
     return ceil_div(num_kb, per);
