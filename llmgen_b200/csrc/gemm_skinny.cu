@@ -19,6 +19,12 @@
 //                 x = resid * (1 / sqrt(sum of squares / K + eps)) * (gain + offset), the sums of squares
 //                 coming in parts (one per 128 columns) from the product that wrote the residual;
 //   X_GATED       x = silu(gate) * up from the partial sums of the product before;
+//   X_ADDNORM     the residual add and the norm before the product, in the product: the slices of K
+//                 of a tile are a thread-block cluster; each block adds the slices of the product
+//                 before to the residual for its columns, the blocks exchange their shares of the
+//                 rows' sums of squares through each other's shared memory, and each builds its
+//                 slice of the normalised rows; the tile-0 cluster also writes the new residual (to
+//                 another array than the one all read);
 //   OUT_RESIDUAL  the slices are written as in OUT_PARTIAL, and the block that finishes a tile last
 //                 (a ticket per tile) adds them in slice order to the float32 residual and leaves
 //                 the tile's share of each row's sum of squares for the norm that follows.
@@ -47,20 +53,20 @@ constexpr int THREADS = 192;
 constexpr int NUM_SMS = 148;
 enum { OUT_DIRECT = 0, OUT_PARTIAL = 1, OUT_GATED = 2, OUT_CLUSTER = 3, OUT_RESIDUAL = 4, OUT_CLUSTER_GATED = 5 };
 constexpr bool is_cluster_mode(int mode) { return mode == OUT_CLUSTER || mode == OUT_CLUSTER_GATED; }
-enum { X_TMA = 0, X_NORM = 1, X_GATED = 2 };
+enum { X_TMA = 0, X_NORM = 1, X_GATED = 2, X_ADDNORM = 3 };
 constexpr int BUILDERS = 128;    // the four epilogue warps build X when it does not come through TMA
 constexpr int MAX_SMEM = 227 * 1024;
 
 // With X through TMA a ring stage holds a tile of W and one of X.  When the block builds X itself
 // the ring holds W only and the block's whole slice of X, `nkb` tiles of [MPAD x 64] in the
-// 128-byte swizzle, follows the barriers (a kilobyte is kept for them).
+// 128-byte swizzle, follows the barriers (two kilobytes are kept for them and the small arrays).
 template <int MPAD, int STAGES, int XSRC = X_TMA>
 struct Smem {
     static constexpr int W_BYTES = BW * BK * 2;
     static constexpr int X_BYTES = MPAD * BK * 2;
     static constexpr int STAGE_BYTES = W_BYTES + (XSRC == X_TMA ? X_BYTES : 0);
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int XR_OFFSET = BAR_OFFSET + 1024;
+    static constexpr int XR_OFFSET = BAR_OFFSET + 2048;
     static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 2) * 8 + 16 + 1024;  // + alignment slack
     static constexpr int total(int nkb) { return XSRC == X_TMA ? TOTAL : XR_OFFSET + nkb * X_BYTES + 1024; }
 };
@@ -93,6 +99,13 @@ struct FusedArgs {
     int gu_splits;
     long long gu_split_stride, gu_ld;
     int group;
+    // X_ADDNORM: v = an_resid_in + the sum of `an_splits` slices of an_delta; x = v * rinv * (gain + gain_offset);
+    // blocks with blockIdx.x == 0 write v to an_resid_out (not the array that is read)
+    const float* an_resid_in;
+    const float* an_delta;       // [an_splits][M][an_ld]
+    float* an_resid_out;
+    long long an_ld, an_split_stride;
+    int an_splits;
     // OUT_RESIDUAL
     float* resid;                // [M][resid_ld] float32, += the product
     long long resid_ld;
@@ -141,6 +154,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_slot = reinterpret_cast<int*>(tmem_slot + 2);           // is this block the last of its tile?
     float* rinv_s = reinterpret_cast<float*>(tmem_slot + 4);          // [MPAD] for X_NORM (MPAD <= 64 there)
+    // X_ADDNORM (MPAD = 16): this block's shares of the sums of squares per warp-wide segment, and the
+    // shares of every block of the cluster, pushed there by their owners
+    uint64_t* sq_ready = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET + 384);
+    float* sq_seg = reinterpret_cast<float*>(smem + L::BAR_OFFSET + 400);          // [4 segments][16 rows] ... 256 bytes
+    float* sq_all = reinterpret_cast<float*>(smem + L::BAR_OFFSET + 400 + 256);    // [8 blocks][16 rows] ... 512 bytes
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BW;
@@ -157,6 +175,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         tc::mbar_init(tc::smem_u32(acc_full), 1);
         tc::mbar_init(tc::smem_u32(x_ready), BUILDERS);
+        if constexpr (XSRC == X_ADDNORM) tc::mbar_init(tc::smem_u32(sq_ready), gridDim.y);   // one arrival per block of the cluster
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_w);
         if constexpr (XSRC == X_TMA) tc::prefetch_tensormap(&map_x);
@@ -166,7 +185,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc::tmem_relinquish();
     }
     tc::tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (XSRC == X_ADDNORM) {
+        __syncwarp();
+        cluster_sync_all();      // every block's barriers exist before another block arrives on them
+    } else {
+        __syncthreads();
+    }
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -249,7 +273,113 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 st_shared_v4(x_chunk_addr<MPAD>(xr, (c % chunks) / 8, M + c / chunks, (c % chunks) % 8), 0u, 0u, 0u, 0u);
             pdl_wait();
             if (tid == 0) TL_STAMP(1);
-            if constexpr (XSRC == X_NORM) {
+            if constexpr (XSRC == X_ADDNORM) {
+                // v = residual + slices for this block's columns (two 16-byte chunks of a row per thread and
+                // round, so that a warp's 32 chunks lie in one row: `chunks` is a multiple of 32)
+                constexpr int MAXR = 4;                              // rounds: M * chunks <= 4 * 2 * BUILDERS
+                float v[MAXR][2][8];
+                const int total = M * chunks;
+                const uint32_t S = gridDim.y, rank = cluster_ctarank();
+#pragma unroll
+                for (int rd = 0; rd < MAXR; ++rd) {
+                    if (rd * 2 * BUILDERS >= total) break;
+                    float4 t[2][2];
+                    const float* src[2];
+                    bool live[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = rd * 2 * BUILDERS + h * BUILDERS + tid;
+                        live[h] = c < total;
+                        const int m = live[h] ? c / chunks : 0, k = (kb0 * (BK / 8) + (live[h] ? c % chunks : 0)) * 8;
+                        src[h] = fa.an_delta + (size_t)m * fa.an_ld + k;
+                        const float* rp = fa.an_resid_in + (size_t)m * fa.an_ld + k;
+                        t[h][0] = live[h] ? __ldcg(reinterpret_cast<const float4*>(rp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        t[h][1] = live[h] ? __ldcg(reinterpret_cast<const float4*>(rp + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    float acc[2][8];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[h][i] = 0.f;
+                    for (int s0 = 0; s0 < fa.an_splits; s0 += 4) {
+                        float4 d[2][4][2];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const bool on = live[h] && s0 + u < fa.an_splits;
+                                const float* q = src[h] + (size_t)(s0 + u) * fa.an_split_stride;
+                                d[h][u][0] = on ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                d[h][u][1] = on ? __ldcg(reinterpret_cast<const float4*>(q + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                acc[h][0] += d[h][u][0].x; acc[h][1] += d[h][u][0].y; acc[h][2] += d[h][u][0].z; acc[h][3] += d[h][u][0].w;
+                                acc[h][4] += d[h][u][1].x; acc[h][5] += d[h][u][1].y; acc[h][6] += d[h][u][1].z; acc[h][7] += d[h][u][1].w;
+                            }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        v[rd][h][0] = t[h][0].x + acc[h][0]; v[rd][h][1] = t[h][0].y + acc[h][1];
+                        v[rd][h][2] = t[h][0].z + acc[h][2]; v[rd][h][3] = t[h][0].w + acc[h][3];
+                        v[rd][h][4] = t[h][1].x + acc[h][4]; v[rd][h][5] = t[h][1].y + acc[h][5];
+                        v[rd][h][6] = t[h][1].z + acc[h][6]; v[rd][h][7] = t[h][1].w + acc[h][7];
+                        float sq = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) sq += v[rd][h][i] * v[rd][h][i];
+                        sq = warp_sum(sq);                           // a warp's 32 chunks: one segment of one row
+                        const int c0 = rd * 2 * BUILDERS + h * BUILDERS + (tid & ~31);
+                        if (lane == 0 && c0 < total) sq_seg[((c0 % chunks) / 32) * 16 + c0 / chunks] = sq;
+                    }
+                }
+                builders_sync();
+                // one thread per row: the row's share of this block, pushed into every block of the cluster
+                if (tid < M) {
+                    float sq = 0.f;
+                    for (int sg = 0; sg < chunks / 32; ++sg) sq += sq_seg[sg * 16 + tid];
+                    const uint32_t mine = tc::smem_u32(sq_all + rank * 16 + tid);
+                    for (uint32_t q = 0; q < S; ++q)
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_map_shared(mine, q)), "f"(sq) : "memory");
+                    asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                }
+                __syncwarp();
+                if (tid == 0)
+                    for (uint32_t q = 0; q < S; ++q) tc::mbar_arrive_cluster(cluster_map_shared(tc::smem_u32(sq_ready), q));
+                const bool got = tc::mbar_wait(tc::smem_u32(sq_ready), 0, abort_flag);
+                asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                if (tid < M) {
+                    float ss = 0.f;
+                    for (uint32_t q = 0; q < S; ++q) ss += sq_all[q * 16 + tid];
+                    rinv_s[tid] = got ? 1.0f / sqrtf(ss / (float)K + fa.eps) : 0.f;
+                }
+                builders_sync();
+#pragma unroll
+                for (int rd = 0; rd < MAXR; ++rd) {
+                    if (rd * 2 * BUILDERS >= total) break;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = rd * 2 * BUILDERS + h * BUILDERS + tid;
+                        if (c >= total) continue;
+                        const int m = c / chunks, j = c % chunks, k = (kb0 * (BK / 8) + j) * 8;
+                        const float4 ga = *reinterpret_cast<const float4*>(fa.gain + k);
+                        const float4 gb = *reinterpret_cast<const float4*>(fa.gain + k + 4);
+                        const float r = rinv_s[m], o = fa.gain_offset;
+                        const float* x = v[rd][h];
+                        st_shared_v4(x_chunk_addr<MPAD>(xr, j / 8, m, j % 8),
+                                     pack_bf16x2(x[0] * r * (ga.x + o), x[1] * r * (ga.y + o)),
+                                     pack_bf16x2(x[2] * r * (ga.z + o), x[3] * r * (ga.w + o)),
+                                     pack_bf16x2(x[4] * r * (gb.x + o), x[5] * r * (gb.y + o)),
+                                     pack_bf16x2(x[6] * r * (gb.z + o), x[7] * r * (gb.w + o)));
+                        if (blockIdx.x == 0) {
+                            float* wp = fa.an_resid_out + (size_t)m * fa.an_ld + k;
+                            *reinterpret_cast<float4*>(wp) = make_float4(x[0], x[1], x[2], x[3]);
+                            *reinterpret_cast<float4*>(wp + 4) = make_float4(x[4], x[5], x[6], x[7]);
+                        }
+                    }
+                }
+            } else if constexpr (XSRC == X_NORM) {
                 if (tid < M) {
                     float ss = 0.f;
                     for (int p0 = 0; p0 < fa.n_sq_parts; p0 += 8) {
@@ -529,11 +659,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, 
     return LLMK_OK;
 }
 
-template <int MPAD, int STAGES, int MODE, int XSRC>
-int launch_fused(const CUtensorMap& mw, const CUtensorMap& mx, float* C, int M, int N, int K, long long ldc, int splits,
+template <int MPAD, int STAGES, int MODE, int XSRC, typename TC = float>
+int launch_fused(const CUtensorMap& mw, const CUtensorMap& mx, TC* C, int M, int N, int K, long long ldc, int splits,
                  int kb_per_split, int* error_flag, const FusedArgs& fa, cudaStream_t s) {
     using L = Smem<MPAD, STAGES, XSRC>;
-    auto kernel = gemm_skinny_kernel<float, MPAD, STAGES, MODE, XSRC>;
+    auto kernel = gemm_skinny_kernel<TC, MPAD, STAGES, MODE, XSRC>;
     const int bytes = L::total(kb_per_split);
     if (bytes > MAX_SMEM)
         LLMK_FAIL("gemm_skinny_fused: %d rows x %d columns of X need %d bytes of shared memory (limit %d)", MPAD,
@@ -544,8 +674,15 @@ int launch_fused(const CUtensorMap& mw, const CUtensorMap& mx, float* C, int M, 
         if (e != cudaSuccess) LLMK_FAIL("gemm_skinny_fused: cannot raise shared memory to %d: %s", bytes, cudaGetErrorString(e));
         configured = bytes;
     }
-    LLMK_CHECK_LAUNCH_RC("gemm_skinny_fused", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), (size_t)bytes, s,
-                                                          true, mw, mx, C, M, N, K, ldc, kb_per_split, error_flag, fa));
+    if constexpr (XSRC == X_ADDNORM || is_cluster_mode(MODE)) {
+        // the slices of K of a tile are one thread-block cluster
+        LLMK_CHECK_LAUNCH_RC("gemm_skinny_fused", llmk_launch_cluster(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS),
+                                                                      (size_t)bytes, s, true, (unsigned)splits, mw, mx, C, M, N, K,
+                                                                      ldc, kb_per_split, error_flag, fa));
+    } else {
+        LLMK_CHECK_LAUNCH_RC("gemm_skinny_fused", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), (size_t)bytes, s,
+                                                              true, mw, mx, C, M, N, K, ldc, kb_per_split, error_flag, fa));
+    }
     return LLMK_OK;
 }
 
@@ -665,7 +802,7 @@ LLMK_EXPORT int llmk_gemm_skinny_fused_fits(int M, int K, int splits) {
     const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : 64;
     const int stages = mpad == 16 ? 6 : mpad == 32 ? 5 : 4;
     const int per = ceil_div(ceil_div(K, BK), splits);
-    return stages * BW * BK * 2 + 1024 + per * mpad * BK * 2 + 1024 <= MAX_SMEM ? 1 : 0;
+    return stages * BW * BK * 2 + 2048 + per * mpad * BK * 2 + 1024 <= MAX_SMEM ? 1 : 0;
 }
 
 // The fused forms of the few-rows product (M <= 64, bfloat16 weights, float32 slices in C):
@@ -739,3 +876,44 @@ LLMK_EXPORT int llmk_gemm_skinny_timeline(unsigned long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, g_skinny_tl, sizeof(g_skinny_tl)) == cudaSuccess ? LLMK_OK : 1;
 }
 #endif
+
+// The residual add and the RMSNorm before a few-rows product, done by the product itself (M <= 16):
+//   v = resid_in + the sum of `delta_splits` float32 slices of delta ([delta_splits][M][ld], `delta_split_stride`
+//   floats apart); x = v / sqrt(mean(v^2) + eps) * (gain + gain_offset); C = x W^T; resid_out = v
+// K (the width of the residual) is cut into `splits` slices (2, 4 or 8, each a multiple of 256 columns),
+// the blocks of a tile's slices are a cluster and exchange their shares of the rows' sums of squares.
+// gated == 0: C is float32 [splits][M][ldc], the slices of the product.  gated != 0: W interleaves gate
+// and up rows in groups of 16, the slices are added up inside the cluster (splits 2 or 4) and C is
+// bfloat16 [M][ldc] = silu(gate) * up.  resid_out must not be resid_in: other blocks still read it.
+LLMK_EXPORT int llmk_gemm_skinny_addnorm(void* C, const void* W, int M, int N, int K, long long ldw, long long ldc,
+                                         int splits, int gated, const float* resid_in, const float* delta,
+                                         int delta_splits, long long delta_split_stride, long long ld,
+                                         float* resid_out, const float* gain, float eps, float gain_offset,
+                                         int* error_flag, void* stream) {
+    if (M <= 0 || N <= 0) return LLMK_OK;
+    if (M > 16) LLMK_FAIL("gemm_skinny_addnorm: M=%d above 16", M);
+    if (K <= 0 || K % BK != 0 || ldw % 8 != 0 || !host_aligned16(W))
+        LLMK_FAIL("gemm_skinny_addnorm: W not usable (K=%d a multiple of 64, ldw=%lld of 8, base 16-byte aligned)", K, ldw);
+    const int num_kb = K / BK;
+    if ((splits != 2 && splits != 4 && splits != 8) || num_kb % splits != 0 || (num_kb / splits) % 4 != 0 || num_kb / splits > 16)
+        LLMK_FAIL("gemm_skinny_addnorm: %d slices of K=%d (2, 4 or 8 slices of 256, 512, 768 or 1024 columns each)", splits, K);
+    if (M * (num_kb / splits) * 8 > 4 * 2 * BUILDERS) LLMK_FAIL("gemm_skinny_addnorm: %d rows of %d columns per block are too many", M, K / splits);
+    if (gated && (splits > 4 || N % 32 != 0)) LLMK_FAIL("gemm_skinny_addnorm: the gated form takes 2 or 4 slices and N=%d a multiple of 32", N);
+    if (!resid_in || !delta || !resid_out || !gain || resid_out == resid_in || delta_splits < 1 || ld < K || ld % 4 != 0 ||
+        delta_split_stride % 4 != 0 || !host_aligned16(resid_in) || !host_aligned16(delta) || !host_aligned16(resid_out) ||
+        !host_aligned16(gain))
+        LLMK_FAIL("gemm_skinny_addnorm: the residual, the slices or the gain are not usable (ld=%lld)", ld);
+    if (ldc < (gated ? N / 2 : N) || !host_aligned16(C)) LLMK_FAIL("gemm_skinny_addnorm: ldc=%lld not usable for N=%d", ldc, N);
+    FusedArgs fa{};
+    fa.an_resid_in = resid_in; fa.an_delta = delta; fa.an_resid_out = resid_out; fa.an_ld = ld;
+    fa.an_split_stride = delta_split_stride; fa.an_splits = delta_splits;
+    fa.gain = gain; fa.eps = eps; fa.gain_offset = gain_offset;
+    CUtensorMap mw, mx{};
+    if (!tc_host::cached_map_bf16_2d(&mw, W, N, K, ldw, BW))
+        LLMK_FAIL("gemm_skinny_addnorm: cuTensorMapEncodeTiled failed for W (N=%d K=%d ldw=%lld)", N, K, ldw);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int per = num_kb / splits;
+    if (gated)
+        return launch_fused<16, 6, OUT_CLUSTER_GATED, X_ADDNORM, bf16>(mw, mx, (bf16*)C, M, N, K, ldc, splits, per, error_flag, fa, s);
+    return launch_fused<16, 6, OUT_PARTIAL, X_ADDNORM, float>(mw, mx, (float*)C, M, N, K, ldc, splits, per, error_flag, fa, s);
+}

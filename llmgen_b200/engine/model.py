@@ -85,6 +85,8 @@ class DecoderModel:
         delta = None
         for item, cache in zip(self.spec.run_order, caches):
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)
+            if isinstance(delta, ops.Moved):        # the block left the residual stream in another array
+                resid, delta = delta.resid, delta.delta
         return resid, delta
 
     def logits(self, ctx: StepContext, resid: torch.Tensor, delta: Optional[torch.Tensor],

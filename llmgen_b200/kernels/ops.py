@@ -468,6 +468,82 @@ def gemm_skinny_fused(slices: torch.Tensor, x, w: torch.Tensor, add_to: Optional
         add_p, c_longlong(add_ld), sqo_p, tick_p, _ptr(tc_error_flag(w.device)), _stream()))
 
 
+class AddNormRows:
+    """norm(resid_in + delta) as an operand that a few-rows product computes itself, delta being the
+    slices of the product before; the product also writes the sum to `resid_out`, another array than
+    the one it reads (the blocks of other tiles still read that one).  `materialize` is the same through
+    the norm kernel."""
+
+    def __init__(self, resid_in: torch.Tensor, delta: Partials, resid_out: torch.Tensor, gain: torch.Tensor, eps: float,
+                 offset: float = 0.0):
+        if resid_in.dtype != torch.float32 or resid_in.shape != resid_out.shape or resid_in.data_ptr() == resid_out.data_ptr():
+            raise KernelError("the residual is read from one float32 array and written to another of the same shape")
+        if delta.rows != resid_in.shape[0] or delta.cols != resid_in.shape[1]:
+            raise KernelError("the slices to add do not have the residual's shape")
+        self.resid_in, self.delta, self.resid_out, self.gain = resid_in, delta, resid_out, gain
+        self.eps, self.offset = float(eps), float(offset)
+        self.shape = resid_in.shape
+
+    def materialize(self, out: torch.Tensor) -> torch.Tensor:
+        self.resid_out.copy_(self.resid_in)
+        add_rmsnorm(self.resid_out, self.delta, self.gain, out, self.eps, self.offset)
+        return out
+
+
+class Moved:
+    """What a block returns in place of its pending output when the residual stream now lives in another
+    array than the one it was given: (`resid`, `delta`)."""
+
+    def __init__(self, resid: torch.Tensor, delta):
+        self.resid, self.delta = resid, delta
+
+
+ADDNORM_MAX_ROWS = 16
+
+
+def gemm_skinny_addnorm_splits(x: AddNormRows, w: torch.Tensor, gated: bool) -> int:
+    """Into how many slices of K `gemm_skinny_addnorm` would cut this product, 0 if it cannot take it."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not (0 < M <= ADDNORM_MAX_ROWS) or w.dtype != torch.bfloat16 or w.shape[1] != K or K % 64 != 0:
+        return 0
+    if _row_stride(w) % 8 != 0 or w.data_ptr() % 16 != 0 or x.gain.dtype != torch.float32 or (gated and N % 32 != 0):
+        return 0
+    for t in (x.resid_in, x.resid_out):
+        if t.stride(1) != 1 or t.stride(0) != K or t.data_ptr() % 16 != 0:
+            return 0
+    num_kb = K // 64
+    splits = min(gemm_skinny_cluster_splits(M, N, K), 4 if gated else 8)
+    while splits >= 2:
+        per = num_kb // splits
+        if num_kb % splits == 0 and per % 4 == 0 and per <= 16 and M * per * 8 <= 1024:
+            return splits
+        splits //= 2
+    return 0
+
+
+def gemm_skinny_addnorm(out: torch.Tensor, x: AddNormRows, w: torch.Tensor, splits: int, gated: bool = False) -> None:
+    """The few-rows product that adds the slices before it to the residual and normalises its rows itself
+    (csrc/gemm_skinny.cu, X_ADDNORM).  gated: out is bfloat16 [M, N/2] = silu(gate) * up; else out is
+    float32 [splits, M, N], the slices of the product."""
+    lib = build.load("gemm_skinny")
+    M, K = x.shape
+    N = w.shape[0]
+    if gated:
+        if out.shape != (M, N // 2) or out.dtype != torch.bfloat16:
+            raise KernelError(f"gemm_skinny_addnorm: out{list(out.shape)} {out.dtype} does not fit bfloat16 [{M}, {N // 2}]")
+        ldc = _row_stride(out)
+    else:
+        if out.dim() != 3 or out.shape != (splits, M, N) or out.dtype != torch.float32 or not out.is_contiguous():
+            raise KernelError("gemm_skinny_addnorm: the slices go to a contiguous float32 [splits, M, N] array")
+        ldc = N
+    d = x.delta
+    _check(lib, lib.llmk_gemm_skinny_addnorm(
+        _ptr(out), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(w)), c_longlong(ldc), c_int(splits),
+        c_int(1 if gated else 0), _ptr(x.resid_in), _ptr(d.tensor), c_int(d.splits), c_longlong(d.split_stride), c_longlong(K),
+        _ptr(x.resid_out), _ptr(x.gain), c_float(x.eps), c_float(x.offset), _ptr(tc_error_flag(w.device)), _stream()))
+
+
 def gemm_skinny_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
     return a.shape[0] <= SKINNY_MAX_ROWS and gemm_tc_usable(a, w)
 

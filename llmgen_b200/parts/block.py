@@ -6,6 +6,7 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from . import linear as linear_module
 from .base import LayerCache, Part
 from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward_class, mixer_class, norm_class,
                        register_block)
@@ -44,26 +45,39 @@ class PreNormBlock(Part):
         self.ffn = build_feed_forward(spec.ffn, weights, dtype, device)
 
     def _normed(self, ctx, norm, consumer, resid, delta):
-        """The consumer's input: norm(resid + delta).  When `delta` is an `ops.RowSquares` the sum is
-        already in `resid`; a norm that can defer itself and a consumer that takes deferred operands
-        then get an `ops.NormedRows` and no kernel runs here."""
+        """(the consumer's input norm(resid + delta), the array that holds the residual afterwards).
+
+        When `delta` is an `ops.RowSquares` the sum is already in `resid`; a norm that can defer itself
+        and a consumer that takes deferred operands then get an `ops.NormedRows` and no kernel runs here.
+        When `delta` is the slices of a product (`ops.Partials`) and there are few rows, such a consumer
+        gets an `ops.AddNormRows`: its product adds the slices, normalises and leaves the new residual in
+        the other of the residual's two arrays."""
+        fuses = getattr(consumer, "fuses_neighbours", False)
         if isinstance(delta, ops.RowSquares):
-            if hasattr(norm, "deferred") and getattr(consumer, "fuses_neighbours", False):
-                return norm.deferred(resid, delta)
+            if hasattr(norm, "deferred") and fuses:
+                return norm.deferred(resid, delta), resid
             delta = None
         T, H = resid.shape
-        return norm.add_norm(resid, delta, ctx.workspace.buffer("block_normed", T, H, self.dtype))
+        if (isinstance(delta, ops.Partials) and fuses and hasattr(norm, "deferred_add") and linear_module.ADDNORM
+                and self.dtype == torch.bfloat16 and T <= ops.ADDNORM_MAX_ROWS and resid.is_contiguous()):
+            first = ctx.workspace.buffer("residual", T, H, torch.float32)
+            other = ctx.workspace.buffer("residual_other", T, H, torch.float32) if resid.data_ptr() == first.data_ptr() else first
+            return norm.deferred_add(resid, delta, other), other
+        return norm.add_norm(resid, delta, ctx.workspace.buffer("block_normed", T, H, self.dtype)), resid
 
     def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
-        x = self._normed(ctx, self.mixer_norm, self.mixer, resid, delta)
+        given = resid
+        x, resid = self._normed(ctx, self.mixer_norm, self.mixer, resid, delta)
         if getattr(self.mixer, "fuses_neighbours", False):
             mixed = self.mixer.forward(ctx, x, cache, add_to=resid)
         else:
             mixed = self.mixer.forward(ctx, x, cache)
-        x = self._normed(ctx, self.ffn_norm, self.ffn, resid, mixed)
+        x, resid = self._normed(ctx, self.ffn_norm, self.ffn, resid, mixed)
         if getattr(self.ffn, "fuses_neighbours", False):
-            return self.ffn.forward(ctx, x, add_to=resid)
-        return self.ffn.forward(ctx, x)
+            out = self.ffn.forward(ctx, x, add_to=resid)
+        else:
+            out = self.ffn.forward(ctx, x)
+        return out if resid is given else ops.Moved(resid, out)
 
 
 register_block("prenorm", PreNormBlock)

@@ -36,6 +36,11 @@ FUSE_CHAIN = os.environ.get("LLMGEN_FUSE", "") == "chain"
 # a step), so it is not the default.
 _TC_SPLITK = os.environ.get("LLMGEN_TC_SPLITK", "0") == "1"
 FUSE_CHAIN_MAX_ROWS = 16
+# "fused": at up to 16 rows the residual add and the norm before a few-rows product are done by the product
+# itself (the slices of K of a tile, a cluster, exchange their shares of the sums of squares).  Every tile's
+# cluster then reads the slices and the residual again, 32 to 48 times the same lines at once: measured
+# 1.150 ms a decode step against 0.916 ms with the norm as a kernel of its own.  Not the default.
+ADDNORM = os.environ.get("LLMGEN_ADDNORM", "") == "fused"
 
 GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny")
 
@@ -91,6 +96,14 @@ def linear_sliced(ws, name: str, x, w: torch.Tensor, out_dtype: torch.dtype, add
     kernel builds it block by block, otherwise it is computed here first.  With `add_to` (the
     float32 residual) the kernel may add the product to it and return `ops.RowSquares`; whatever
     else comes back has not been added."""
+    if isinstance(x, ops.AddNormRows):
+        M, N = x.shape[0], w.shape[0]
+        splits = ops.gemm_skinny_addnorm_splits(x, w, False) if (_FORCE == "" and _SPLITK == "") else 0
+        if splits >= 2:
+            part = ws.flat(name + "_slices", splits * M * N, torch.float32).view(splits, M, N)
+            ops.gemm_skinny_addnorm(part, x, w, splits)
+            return ops.Partials(part)
+        x = x.materialize(ws.buffer(name + "_x", M, x.shape[1], out_dtype))
     lazy = not isinstance(x, torch.Tensor)
     if lazy or (add_to is not None and FUSE_CHAIN):
         done = _fused(ws, name, x, w, add_to)

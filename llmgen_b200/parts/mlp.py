@@ -68,6 +68,16 @@ class GatedMLP(FeedForward):
         T = x.shape[0]
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
+        if isinstance(x, ops.AddNormRows):
+            # the residual add and the norm before, the sum of the slices and the activation after: one product
+            splits = 0
+            if self.group == GATE_UP_GROUP and CLUSTER_GATED and linear_module._FORCE == "" and linear_module._SPLITK == "":
+                splits = ops.gemm_skinny_addnorm_splits(x, self.w_gate_up, True)
+            if splits >= 2:
+                act = ws.buffer("ffn_act", T, F, self.dtype)
+                ops.gemm_skinny_addnorm(act, x, self.w_gate_up, splits, gated=True)
+                return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
+            x = x.materialize(ws.buffer("ffn_x", T, H, self.dtype))
         few = self.dtype == torch.bfloat16 and T <= linear_module.FUSE_CHAIN_MAX_ROWS and linear_module.FUSE_CHAIN
         if not isinstance(x, torch.Tensor) and not few:
             x = x.materialize(ws.buffer("ffn_x", T, H, self.dtype))

@@ -470,6 +470,63 @@ def test_gemm_skinny_gated_after_the_sum_in_a_cluster(ops, M, F, K, splits):
         ops.gemm_skinny(out, dev(a), dev(interleave_gate_up(wg, wu)), ops.SKINNY_CLUSTER_GATED, splits=8)
 
 
+@pytest.mark.parametrize("M,N,K,S_delta,gated", [(8, 4096, 1024, 8, False), (8, 6144, 1024, 8, True), (1, 256, 512, 3, False),
+                                                  (16, 1024, 2048, 8, False), (5, 192, 1024, 1, True), (5, 4096, 4096, 2, False)])
+def test_gemm_skinny_adds_to_the_residual_and_normalises_itself(ops, M, N, K, S_delta, gated):
+    """X_ADDNORM: the slices before are added to the residual, the rows normalised and multiplied by W inside one
+    product (the slices of K of a tile exchange their sums of squares through a cluster); against the norm
+    kernel and the plain product.  One row is scaled so that a wrong row's factor shows; launched twice."""
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    torch.manual_seed(230 + M)
+    resid_in = torch.randn(M, K).cuda()
+    resid_in[M - 1] *= 25.0
+    delta = ops.Partials((torch.randn(S_delta, M, K) * 0.3).cuda())
+    gain = (1 + 0.2 * torch.randn(K)).cuda()
+    if gated:
+        wg, wu = (torch.randn(N // 2, K) * 0.05).to(torch.bfloat16), (torch.randn(N // 2, K) * 0.05).to(torch.bfloat16)
+        w = interleave_gate_up(wg, wu).cuda()
+    else:
+        w = (torch.randn(N, K) * 0.5).to(torch.bfloat16).cuda()
+    resid_out = torch.full((M, K), 7.0, device="cuda")
+    x = ops.AddNormRows(resid_in, delta, resid_out, gain, 1e-5, 0.25)
+    splits = ops.gemm_skinny_addnorm_splits(x, w, gated)
+    assert splits >= 2
+    out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device="cuda") if gated else \
+        torch.full((splits, M, N), 7.0, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        ops.gemm_skinny_addnorm(out, x, w, splits, gated)
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    # the separate kernels
+    want_resid = resid_in.clone()
+    normed = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    ops.add_rmsnorm(want_resid, delta, gain, normed, 1e-5, 0.25)
+    assert float((resid_out - want_resid).abs().max()) < 1e-5 * float(want_resid.abs().max())
+    ref = normed.double().cpu() @ w.double().cpu().t()
+    if gated:
+        g, u = ref.view(M, -1, 2, 16)[:, :, 0].reshape(M, -1), ref.view(M, -1, 2, 16)[:, :, 1].reshape(M, -1)
+        ref = g / (1 + torch.exp(-g)) * u
+        assert float((out.double().cpu() - ref).abs().max()) < 1e-2 * max(1.0, float(ref.abs().max()))
+    else:
+        assert float((out.sum(0).double().cpu() - ref).abs().max()) < 2e-3 * float(ref.abs().max())
+
+
+def test_gemm_skinny_addnorm_refuses_what_it_cannot_do(ops):
+    resid = torch.zeros(17, 1024, device="cuda")
+    other = torch.zeros(17, 1024, device="cuda")
+    delta = ops.Partials(torch.zeros(2, 17, 1024, device="cuda"))
+    w = torch.zeros(256, 1024, dtype=torch.bfloat16, device="cuda")
+    x = ops.AddNormRows(resid, delta, other, torch.ones(1024, device="cuda"), 1e-6)
+    assert ops.gemm_skinny_addnorm_splits(x, w, False) == 0                      # 17 rows
+    with pytest.raises(ops.KernelError, match="above 16"):
+        ops.gemm_skinny_addnorm(torch.empty(4, 17, 256, device="cuda"), x, w, 4)
+    with pytest.raises(ops.KernelError, match="another"):
+        ops.AddNormRows(resid, delta, resid, torch.ones(1024, device="cuda"), 1e-6)
+    small = ops.AddNormRows(resid[:4, :192].contiguous(), ops.Partials(torch.zeros(1, 4, 192, device="cuda")),
+                            other[:4, :192].contiguous(), torch.ones(192, device="cuda"), 1e-6)
+    assert ops.gemm_skinny_addnorm_splits(small, torch.zeros(64, 192, dtype=torch.bfloat16, device="cuda"), False) == 0
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do(ops):
     w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="above 256"):
