@@ -145,6 +145,13 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     pdl_launch_dependents();
+    // the gains are weights: a prefetch before the wait (loading them into registers here, or with the row
+    // after the wait, made a decode step 15 % slower)
+#pragma unroll
+    for (int it = 0; it < VPT; ++it) {
+        const int i = (it * blockDim.x + threadIdx.x) * 4;
+        if (i < H) asm volatile("prefetch.global.L1 [%0];" ::"l"(w + i));
+    }
     pdl_wait();
     const int s = rows ? rows[r] : r;
     float* x = resid + (size_t)s * H;
