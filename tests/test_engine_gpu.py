@@ -338,3 +338,38 @@ def test_products_that_add_and_normalise_themselves_when_switched_on(tmp, monkey
         llm = LLM(path, dtype="bfloat16", max_model_len=256, max_num_seqs=4, max_batched_tokens=1024, kv_blocks=64, eager=eager)
         outs[eager] = [r["token_ids"] for r in llm.generate([ids[:50], ids[:7], ids[:33]], SamplingParams(0.0, 12, True))]
     assert outs[False] == outs[True]
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+@pytest.mark.parametrize("policy", ["prefill_first", "chunked"])
+def test_random_requests_give_the_same_ids_one_step_ahead_and_not(tmp, seed, policy):
+    """Random prompts and lengths, an end-of-sequence token that is hit often, so few pages that requests are
+    preempted: greedy ids with decode steps launched one ahead equal those with every step read at once, and
+    every completion stops at its first end-of-sequence token or at max_tokens."""
+    import random
+    from llmgen_b200 import LLM, SamplingParams
+    path = make_folder(tmp, "A")
+    rng = random.Random(seed)
+    prompts = [random_ids(rng.randint(1, 40), 256, 200 + 10 * seed + i) for i in range(9)]
+    params = [SamplingParams(temperature=0.0, max_tokens=rng.randint(1, 30), ignore_eos=rng.random() < 0.3) for _ in prompts]
+    ref = greedy_reference(path, prompts, 30)
+    # an end-of-sequence id that several completions contain
+    counts = {}
+    for r in ref:
+        for t in set(r):
+            counts[t] = counts.get(t, 0) + 1
+    eos = max(counts, key=lambda t: (counts[t], -t))
+    want = []
+    for r, p in zip(ref, params):
+        out = r[:p.max_tokens]
+        if not p.ignore_eos and eos in out:
+            out = out[:out.index(eos) + 1]
+        want.append(out)
+    outs = {}
+    for ahead in (True, False):
+        llm = LLM(path, dtype="float32", max_model_len=96, max_num_seqs=4, max_batched_tokens=96, kv_blocks=8, policy=policy, chunk=16)
+        llm.engine.run_ahead = ahead
+        llm.engine.scheduler.config.eos_token_ids = (eos,)
+        outs[ahead] = [o["token_ids"] for o in llm.generate(prompts, params)]
+        assert llm.executor.cache.all_free()
+    assert outs[True] == outs[False] == want
