@@ -39,6 +39,7 @@
 //
 // The reference uses a one-warp-per-output-row GEMV for M <= 2 and cuBLAS above
 // (src/backend/cuda/linear/linear.cu:22-96); this kernel covers both ranges up to 256 rows.
+#include <string.h>
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -60,9 +61,9 @@ constexpr int MAX_SMEM = 227 * 1024;
 // With X through TMA a ring stage holds a tile of W and one of X.  When the block builds X itself
 // the ring holds W only and the block's whole slice of X, `nkb` tiles of [MPAD x 64] in the
 // 128-byte swizzle, follows the barriers (two kilobytes are kept for them and the small arrays).
-template <int MPAD, int STAGES, int XSRC = X_TMA>
+template <int MPAD, int STAGES, int XSRC = X_TMA, int TW = BW>
 struct Smem {
-    static constexpr int W_BYTES = BW * BK * 2;
+    static constexpr int W_BYTES = TW * BK * 2;
     static constexpr int X_BYTES = MPAD * BK * 2;
     static constexpr int STAGE_BYTES = W_BYTES + (XSRC == X_TMA ? X_BYTES : 0);
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
@@ -136,12 +137,17 @@ __device__ __forceinline__ uint32_t x_chunk_addr(uint32_t xr, int kb, int m, int
     return xr + (uint32_t)kb * (MPAD * 128) + (uint32_t)m * 128 + (uint32_t)((chunk ^ (m & 7)) << 4);
 }
 
-template <typename TC, int MPAD, int STAGES, int MODE, int XSRC = X_TMA>
+// TW: rows of W per block, 128 or 64.  With 64 the accumulator lies in lanes 0..15 of each warp's 32
+// lanes of tensor memory (row m of the tile in lane 32 * (m / 16) + m % 16), and a product of few
+// tiles fills twice as many SMs; only the forms that store their accumulator directly take it.
+template <typename TC, int MPAD, int STAGES, int MODE, int XSRC = X_TMA, int TW = BW>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    TC* __restrict__ C, int M, int N, int K, long long ldc, int kb_per_split, int* error_flag,
                    const FusedArgs fa) {
-    using L = Smem<MPAD, STAGES, XSRC>;
+    using L = Smem<MPAD, STAGES, XSRC, TW>;
+    static_assert(TW == BW || (TW == 64 && XSRC == X_TMA && (MODE == OUT_PARTIAL || MODE == OUT_DIRECT)),
+                  "64-row tiles: plain operands, accumulator stored directly");
     constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -161,7 +167,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     float* sq_all = reinterpret_cast<float*>(smem + L::BAR_OFFSET + 400 + 256);    // [8 blocks][16 rows] ... 512 bytes
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BW;
+    const int n0 = blockIdx.x * TW;
     const int split = blockIdx.y;
     const int num_kb = (K + BK - 1) / BK;
     const int kb0 = split * kb_per_split;
@@ -235,7 +241,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = tc::idesc_bf16_f32(BW, MPAD);
+            constexpr uint32_t idesc = tc::idesc_bf16_f32(TW, MPAD);
             bool ok = true;
             if constexpr (XSRC != X_TMA) ok = tc::mbar_wait(tc::smem_u32(x_ready), 0, abort_flag);
             TL_STAMP(4);
@@ -263,7 +269,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31; a lane is a row of W
         // (an output column), a column of tensor memory is a row of X.
         const int quarter = warp & 3;
-        const int n = n0 + quarter * 32 + lane;
+        const int n = TW == BW || lane < TW / 4 ? n0 + quarter * (TW / 4) + lane : N;   // N: a lane without a row
         const int tid = threadIdx.x - 64;        // 0 .. BUILDERS - 1
         if constexpr (XSRC != X_TMA) {
             // Build this block's slice of X: columns [kb0 * 64, (kb0 + nkb) * 64) of rows 0 .. MPAD - 1.
@@ -631,11 +637,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
 }
 
-template <typename TC, int MPAD, int STAGES, int MODE>
+template <typename TC, int MPAD, int STAGES, int MODE, int TW = BW>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, int K, long long ldc, int splits,
            int kb_per_split, int* error_flag, cudaStream_t s) {
-    using L = Smem<MPAD, STAGES>;
-    auto kernel = gemm_skinny_kernel<TC, MPAD, STAGES, MODE>;
+    using L = Smem<MPAD, STAGES, X_TMA, TW>;
+    auto kernel = gemm_skinny_kernel<TC, MPAD, STAGES, MODE, X_TMA, TW>;
     static bool configured = false;   // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -653,7 +659,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int M, int N, 
                                                                 true, (unsigned)splits, mw, mx, (TC*)C, M, N, K, ldc,
                                                                 kb_per_split, error_flag, FusedArgs{}));
     } else {
-        LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch(kernel, dim3(ceil_div(N, BW), splits), dim3(THREADS), L::TOTAL, s,
+        LLMK_CHECK_LAUNCH_RC("gemm_skinny", llmk_launch(kernel, dim3(ceil_div(N, TW), splits), dim3(THREADS), L::TOTAL, s,
                                                         true, mw, mx, (TC*)C, M, N, K, ldc, kb_per_split, error_flag, FusedArgs{}));
     }
     return LLMK_OK;
@@ -696,11 +702,21 @@ int dispatch_fused(const CUtensorMap& mw, const CUtensorMap& mx, float* C, int M
 
 template <typename TC, int MODE>
 int dispatch_rows(const CUtensorMap& mw, const void* X, void* C, int M, int N, int K, long long ldx, long long ldc,
-                  int splits, int kb_per_split, int* error_flag, cudaStream_t s) {
+                  int splits, int kb_per_split, int* error_flag, cudaStream_t s, bool half_tiles = false) {
     const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     CUtensorMap mx;
     if (!tc_host::cached_map_bf16_2d(&mx, X, M, K, ldx, mpad))
         LLMK_FAIL("gemm_skinny: cuTensorMapEncodeTiled failed for X (M=%d K=%d ldx=%lld)", M, K, ldx);
+    if constexpr (MODE == OUT_PARTIAL) {
+        if (half_tiles) {            // `mw` then has boxes of 64 rows
+            switch (mpad) {
+                case 16: return launch<TC, 16, 6, MODE, 64>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
+                case 32: return launch<TC, 32, 5, MODE, 64>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
+                case 64: return launch<TC, 64, 4, MODE, 64>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
+                default: LLMK_FAIL("gemm_skinny: 64-row tiles take at most 64 rows of X, not %d", M);
+            }
+        }
+    }
     switch (mpad) {
         case 16: return launch<TC, 16, 6, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
         case 32: return launch<TC, 32, 5, MODE>(mw, mx, C, M, N, K, ldc, splits, kb_per_split, error_flag, s);
@@ -718,6 +734,14 @@ int dispatch_rows(const CUtensorMap& mw, const void* X, void* C, int M, int N, i
 }  // namespace
 
 LLMK_EXPORT int llmk_gemm_skinny_max_rows() { return 256; }
+
+// Tiles of 64 rows of W for partial sums of products with few tiles: off unless LLMGEN_SKINNY_TILES=64
+// is in the environment.  Twice the blocks (128 instead of 64 for a [1024, K] matrix in 8 slices), yet a
+// decode step at batch 8 took 0.925 ms with them and 0.910 ms without: the blocks' fixed cost counts
+// for more than the SMs left idle.
+static bool g_half_tiles = [] { const char* v = getenv("LLMGEN_SKINNY_TILES"); return v && strcmp(v, "64") == 0; }();
+// 0: tiles of 128 rows everywhere; 1: 64-row tiles where 128-row tiles leave half the SMs without a block.
+LLMK_EXPORT void llmk_gemm_skinny_set_half_tiles(int on) { g_half_tiles = on != 0; }
 
 // How many slices of K suit this product: about one block per SM but at most 8 slices, at least two
 // 64-wide slices of K per block, and partial sums (splits * M * N floats) no larger than W itself.
@@ -773,11 +797,14 @@ LLMK_EXPORT int llmk_gemm_skinny(void* C, const void* X, const void* W, int M, i
         LLMK_FAIL("gemm_skinny: a cluster adds up 2, 4, 8 or 16 slices of at most 64 rows (%d slices, %d rows)", splits, M);
     if (mode == OUT_GATED && N % 32 != 0) LLMK_FAIL("gemm_skinny: gated epilogue needs N=%d to be a multiple of 32", N);
     if (ldc < (mode == OUT_GATED || mode == OUT_CLUSTER_GATED ? N / 2 : N)) LLMK_FAIL("gemm_skinny: ldc=%lld too small", ldc);
+    // Partial sums of a product with so few tiles that half the SMs would idle: tiles of 64 rows of W.
+    const bool half_tiles = mode == OUT_PARTIAL && g_half_tiles && M <= 64 && ceil_div(N, BW) * splits * 2 <= NUM_SMS;
     CUtensorMap mw;
-    if (!tc_host::cached_map_bf16_2d(&mw, W, N, K, ldw, BW))
+    if (!tc_host::cached_map_bf16_2d(&mw, W, N, K, ldw, half_tiles ? 64 : BW))
         LLMK_FAIL("gemm_skinny: cuTensorMapEncodeTiled failed for W (N=%d K=%d ldw=%lld)", N, K, ldw);
     cudaStream_t s = (cudaStream_t)stream;
-    if (mode == OUT_PARTIAL) return dispatch_rows<float, OUT_PARTIAL>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s);
+    if (mode == OUT_PARTIAL)
+        return dispatch_rows<float, OUT_PARTIAL>(mw, X, C, M, N, K, ldx, ldc, splits, per, error_flag, s, half_tiles);
     if (mode == OUT_GATED) {
         if (out_dtype != LLMK_BF16) LLMK_FAIL("gemm_skinny: the gated epilogue writes bfloat16");
         return dispatch_rows<bf16, OUT_GATED>(mw, X, C, M, N, K, ldx, ldc, 1, per, error_flag, s);

@@ -347,6 +347,13 @@ _cluster_plans = {}
 _skinny_plans = {}
 
 
+def gemm_skinny_set_half_tiles(on: bool) -> None:
+    """Whether the few-rows product cut along K takes tiles of 64 rows of W (`tcgen05.mma` with M = 64)
+    where tiles of 128 would leave half the SMs without a block.  Off by default (it was slower in a
+    decode step); LLMGEN_SKINNY_TILES=64 in the environment turns it on at load."""
+    build.load("gemm_skinny").llmk_gemm_skinny_set_half_tiles(c_int(1 if on else 0))
+
+
 def gemm_skinny_splits(M: int, N: int, K: int) -> int:
     """Into how many slices of K the few-rows product cuts [M, K] x [N, K]^T (1: no cut)."""
     key = (M, N, K)

@@ -2,6 +2,7 @@
 test models use (odd widths, head sizes in steps of 16, groups of 1 to 8, vocabularies that
 are no power of two)."""
 import math
+import os
 import random
 
 import pytest
@@ -407,6 +408,31 @@ def test_gemm_skinny_partial_sums(ops, M, N, K, splits):
     assert planned >= 1 and (planned - 1) * per < kb and planned * M * N * 4 <= max(2 * N * K, M * N * 4)
     with pytest.raises(ops.KernelError, match="empty|slices"):
         ops.gemm_skinny(torch.empty(kb + 1, M, N, dtype=torch.float32, device="cuda"), dev(a), dev(w), ops.SKINNY_PARTIAL)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 1024, 2048, 8), (8, 1024, 3072, 8), (40, 200, 512, 3), (64, 1024, 2048, 8),
+                                          (17, 1096, 1024, 4), (3, 24, 128, 2)])
+def test_gemm_skinny_partial_sums_on_64_row_tiles(ops, M, N, K, splits):
+    """Few tiles: blocks take 64 rows of W each (twice the blocks).  Same slices as with 128-row tiles,
+    bit for bit (each value is one accumulator over the same K steps), and the same product."""
+    torch.manual_seed(170 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    assert (N + 127) // 128 * splits * 2 <= 148       # the sizes at which the launcher takes them
+    parts = []
+    try:
+        for half in (True, False):
+            ops.gemm_skinny_set_half_tiles(half)
+            part = torch.full((splits, M, N), 7.0, dtype=torch.float32, device="cuda")
+            ops.gemm_skinny(part, dev(a), dev(w), ops.SKINNY_PARTIAL)
+            torch.cuda.synchronize()
+            ops.check_tc_errors(part.device)
+            parts.append(part.cpu())
+    finally:
+        ops.gemm_skinny_set_half_tiles(os.environ.get("LLMGEN_SKINNY_TILES", "") == "64")
+    ref = a.double() @ w.double().t()
+    assert float((parts[0].double().sum(0) - ref).abs().max()) < 2e-5 * float(ref.abs().max())
+    assert torch.equal(parts[0], parts[1])
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(8, 1024, 2048, 16), (1, 136, 256, 2), (33, 1024, 3072, 8), (8, 4096, 1024, 4),
