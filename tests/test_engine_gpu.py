@@ -157,12 +157,13 @@ def test_command_line_chat_and_bench(tmp):
     assert summary["policy"] == "chunked" and summary["kv_leak"] is False
 
 
-@pytest.mark.parametrize("hidden,heads,kv_heads,inter", [(2048, 32, 8, 6144), (5120, 64, 8, 4096)])
+@pytest.mark.parametrize("hidden,heads,kv_heads,inter", [(4096, 32, 8, 12288), (5120, 64, 8, 25600)])
 def test_layer_sizes_of_the_larger_models(tmp, hidden, heads, kv_heads, inter):
-    """One layer with the head geometry of the larger Qwen3 models (32 or 64 query heads on 8 kv
-    heads of 128: groups of 4 and 8, a q width that is not the hidden size) and a vocabulary that is
-    no multiple of 128: bfloat16 logits of a prompt and of decoded tokens against the plain
-    implementation, and graph replay against eager steps."""
+    """One layer with the sizes of the 8B and 32B Qwen3 models (32 or 64 query heads on 8 kv heads of
+    128: groups of 4 and 8, a q width that is not the hidden size, intermediate sizes of 12,288 and
+    25,600) and a vocabulary that is no multiple of 128: bfloat16 logits of a prompt, of a portion
+    beside a decoded token and of decoded tokens against the plain implementation, and graph replay
+    against eager steps."""
     from llmgen_b200 import LLM, SamplingParams
     from llmgen_b200.engine.api import write_random_model
     from tests.util import Driver, logits_close
@@ -173,12 +174,21 @@ def test_layer_sizes_of_the_larger_models(tmp, hidden, heads, kv_heads, inter):
     path = os.path.join(tmp, f"wide_{hidden}")
     write_random_model(path, cfg, 11, 0.02, 0.1, "bfloat16")
     ids = random_ids(300, 1500, 5)
-    ref = PlainQwen3(path).logits(ids)
+    ids_b = random_ids(60, 1500, 6)
+    plain_model = PlainQwen3(path)
+    ref, ref_b = plain_model.logits(ids), plain_model.logits(ids_b)
+    del plain_model
     d = Driver(path, "bfloat16", 512, 16)
     got = d.step([("a", ids[:280], range(280))])
     logits_close(got, ref[:280], "bfloat16")
-    for i in range(280, 300):
-        logits_close(d.step([("a", ids[i:i + 1], [0])]), ref[i:i + 1], "bfloat16")
+    got = d.step([("b", ids_b[:40], range(40)), ("a", ids[280:281], [0])])       # 41 rows: a portion beside a decoded token
+    logits_close(got[:40], ref_b[:40], "bfloat16")
+    logits_close(got[40:], ref[280:281], "bfloat16")
+    for i in range(19):                                                          # then both decode
+        got = d.step([("a", ids[281 + i:282 + i], [0])] + ([("b", ids_b[40 + i:41 + i], [0])] if 40 + i < 60 else []))
+        logits_close(got[:1], ref[281 + i:282 + i], "bfloat16")
+        if got.shape[0] > 1:
+            logits_close(got[1:], ref_b[40 + i:41 + i], "bfloat16")
     outs = {}
     for eager in (False, True):
         llm = LLM(path, dtype="bfloat16", max_model_len=512, max_num_seqs=4, max_batched_tokens=2048, kv_blocks=128, eager=eager)
