@@ -2,6 +2,7 @@
 """Benchmark of the engine's decode step and prefill on one B200, at the Qwen3-0.6B shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+                    [--shape 0.6b|8b|32b --layers L]      (other layer sizes, beside the default run)
 
 Prints ONE JSON line.  A "step" is one decode step of `--batch` sequences (default 8) whose
 prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
@@ -43,6 +44,13 @@ QWEN3_0_6B = {
     "head_dim": 128, "intermediate_size": 3072, "vocab_size": 151936, "rope_theta": 1000000.0,
     "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 40960, "hidden_act": "silu",
 }
+# BASELINE.json configs[3] and configs[4]: the layer sizes of Qwen3-8B and Qwen3-32B, for runs beside the
+# default one (`--shape 8b --layers 8`): the same kernels at wider layers.
+QWEN3_8B = dict(QWEN3_0_6B, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, intermediate_size=12288,
+                tie_word_embeddings=False)
+QWEN3_32B = dict(QWEN3_0_6B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600,
+                 tie_word_embeddings=False)
+SHAPES = {"0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "8b": ("Qwen3-8B shape", QWEN3_8B), "32b": ("Qwen3-32B shape", QWEN3_32B)}
 CONTEXT = 4096
 PROMPT_TOKENS = 512
 PREFILL_TOKENS = 2048
@@ -155,6 +163,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="0.6b",
+                    help="layer sizes of another model than the default run's (use with --layers where time needs it)")
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS,
                     help="for other context lengths than the default run's: the prompts' length (prompts of a batch are "
@@ -173,7 +183,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    check_against_baseline_json()
+    if args.shape == "0.6b":
+        check_against_baseline_json()
     warmup = max(3, args.warmup)
     K = max(1, args.steps)
 
@@ -184,7 +195,8 @@ def main():
     from llmgen_b200.kernels import ops
     from llmgen_b200.sampling import SamplingParams
 
-    cfg = dict(QWEN3_0_6B)
+    shape_name, shape_cfg = SHAPES[args.shape]
+    cfg = dict(shape_cfg)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -309,16 +321,16 @@ def main():
     clocks = sampler.stop(windows)
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-0.6B shape, bf16, random weights, 512-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} ({shape_name}, bf16, random weights, {args.prompt_tokens}-token prompts)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8 if args.shape == "0.6b" else None, "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random-init weights (seed 2)",
-        "config": {"model": "Qwen3-0.6B shape", "global_batch": args.batch, "seq_len": args.context, "parallelism": "single GPU",
+        "config": {"model": shape_name, "global_batch": args.batch, "seq_len": args.context, "parallelism": "single GPU",
                    "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
                    "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": V, "tied_embeddings": True,
+                   "intermediate": cfg["intermediate_size"], "vocab": V, "tied_embeddings": bool(cfg["tie_word_embeddings"]),
                    "prompt_tokens": args.prompt_tokens, "mean_context": mean_ctx, "page_size": args.block_size,
-                   "l2": "inputs larger than L2 (1.19 GB of weights per step), no flush", "peaks": pk["source"]},
+                   "l2": f"inputs larger than L2 ({nums['weight_bytes'] / 1e9:.2f} GB of weights per step), no flush", "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": launches_per_step * K, "prefill": prefill, "roofline": roofline, "points": points,
         "clocks": clocks, "impl": "ours",
     }
