@@ -202,6 +202,59 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __
     }
 }
 
+// Many rows (a prompt): a warp per row, the row in registers as LPT float4 per lane, all loads of a
+// row in flight at once and nothing but warp shuffles between the two passes.  Rows in order, delta
+// in T or absent.  (A block per row with one float4 per thread ran at 2.5 TB/s on 2,048 rows of 1,024.)
+template <typename T, int LPT>
+__global__ void __launch_bounds__(128)
+add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w,
+                        T* __restrict__ out, int n_rows, int H, float eps, float w_offset, int write_resid) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const int lane = threadIdx.x & 31;
+    float* x = resid + (size_t)r * H;
+    float4 v[LPT];
+#pragma unroll
+    for (int it = 0; it < LPT; ++it) {
+        const int i = (it * 32 + lane) * 4;
+        v[it] = i < H ? load4(x + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (delta) {
+        const T* d = delta + (size_t)r * H;
+        float4 a[LPT];
+#pragma unroll
+        for (int it = 0; it < LPT; ++it) {
+            const int i = (it * 32 + lane) * 4;
+            a[it] = i < H ? load4(d + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int it = 0; it < LPT; ++it) {
+            v[it].x += a[it].x; v[it].y += a[it].y; v[it].z += a[it].z; v[it].w += a[it].w;
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < LPT; ++it) {
+        const int i = (it * 32 + lane) * 4;
+        ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
+        if (write_resid && i < H) store4(x + i, v[it]);
+    }
+    ss = warp_sum(ss);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+#pragma unroll
+    for (int it = 0; it < LPT; ++it) {
+        const int i = (it * 32 + lane) * 4;
+        if (i < H) {
+            const float4 g = load4(w + i);
+            store4(o + i, make_float4(v[it].x * rinv * (g.x + w_offset), v[it].y * rinv * (g.y + w_offset),
+                                      v[it].z * rinv * (g.z + w_offset), v[it].w * rinv * (g.w + w_offset)));
+        }
+    }
+}
+
 LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w, void* out, const int* rows,
                                  int n_rows, int H, float eps, float w_offset, int write_resid, int splits,
                                  long long split_stride, int dtype, void* stream) {
@@ -215,6 +268,22 @@ LLMK_EXPORT int llmk_add_rmsnorm(float* resid, const void* delta, const float* w
     int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const bool aligned = host_aligned16(resid) && host_aligned16(w) && host_aligned16(out) &&
                          (!delta || host_aligned16(delta)) && (splits == 0 || split_stride % 4 == 0);
+    if (H % 4 == 0 && H <= 2048 && n_rows >= 512 && !rows && splits == 0 && aligned && (dtype == LLMK_F32 || dtype == LLMK_BF16)) {
+        const int lpt = (H / 4 + 31) / 32;
+        const dim3 grid((n_rows + 3) / 4), block(128);
+        cudaError_t e;
+#define LAUNCH_WARP(T, L)                                                                                          \
+    e = llmk_launch(add_rmsnorm_warp_kernel<T, L>, grid, block, 0, s, true, resid, (const T*)delta, w, (T*)out, n_rows, H, \
+                    eps, w_offset, write_resid)
+        if (dtype == LLMK_F32) {
+            if (lpt <= 4) LAUNCH_WARP(float, 4); else if (lpt <= 8) LAUNCH_WARP(float, 8); else LAUNCH_WARP(float, 16);
+        } else {
+            if (lpt <= 4) LAUNCH_WARP(bf16, 4); else if (lpt <= 8) LAUNCH_WARP(bf16, 8); else LAUNCH_WARP(bf16, 16);
+        }
+#undef LAUNCH_WARP
+        LLMK_CHECK_LAUNCH_RC("add_rmsnorm", e);
+        return LLMK_OK;
+    }
     if (H % 4 == 0 && H <= 8192 && aligned && (dtype == LLMK_F32 || dtype == LLMK_BF16)) {
         int vthreads = (H / 4 + 31) / 32 * 32;
         if (vthreads > 512) vthreads = 512;

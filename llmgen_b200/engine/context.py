@@ -33,10 +33,24 @@ class Workspace:
         self.device = device
         self.default_rows = default_rows
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[Tuple, torch.Tensor] = {}   # (name, rows, cols, dtype) -> the view handed out last time
         self._retired: List[torch.Tensor] = []   # replaced buffers stay alive: captured graphs still use them
         self.frozen = False   # set while a graph is being captured: no new allocations
 
     def buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, capacity_rows: Optional[int] = None) -> torch.Tensor:
+        # the same view object for the same request: a step asks for a few hundred, and making a
+        # view costs more than finding one
+        vkey = (name, rows, cols, dtype)
+        view = self._views.get(vkey)
+        if view is not None:
+            return view
+        view = self._buffer(name, rows, cols, dtype, capacity_rows)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[vkey] = view
+        return view
+
+    def _buffer(self, name: str, rows: int, cols: int, dtype: torch.dtype, capacity_rows: Optional[int]) -> torch.Tensor:
         cap = max(capacity_rows or self.default_rows, 1)
         key = f"{name}:{cols}:{dtype}"
         buf = self._buffers.get(key)
@@ -46,6 +60,7 @@ class Workspace:
             cap = max(cap, rows)
             if buf is not None:
                 self._retired.append(buf)
+                self._views.clear()              # views of the replaced buffer must not be handed out again
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:rows]

@@ -212,7 +212,9 @@ class Executor:
         """Run the entries' tokens as one batch.  Logits rows (and sampled ids) come in the order
         of the entries and, inside an entry, of its `want` list."""
         entries = [e for e in entries]
-        self._validate(entries)
+        arrays = self._validate(entries)
+        # a portion's ids were turned into an array for the check: the step's arrays are filled from it
+        entries = [e if a is None else StepEntry(e.req, a, e.start, e.want, e.temperature) for e, a in zip(entries, arrays)]
         self._reset_fresh_state()
         n_tokens = sum(len(e.tokens) for e in entries)
         if n_tokens == 0:
@@ -253,8 +255,11 @@ class Executor:
             result.token_ids = [ids_parts[r] for r in perm] if perm is not None else ids_parts
         return result
 
-    def _validate(self, entries: Sequence[StepEntry], prev_rows: Optional[Sequence[int]] = None) -> None:
+    def _validate(self, entries: Sequence[StepEntry], prev_rows: Optional[Sequence[int]] = None) -> List[Optional[np.ndarray]]:
+        """Raise `StepError` for a step that cannot run.  Returns, per entry, its token ids as an integer
+        array where the check made one (None for a single token)."""
         lim = self.limits
+        arrays: List[Optional[np.ndarray]] = []
         V = self.model.spec.vocab_size
         if len(entries) > lim.max_num_seqs:
             raise StepError(f"{len(entries)} sequences in one step, the limit is {lim.max_num_seqs}")
@@ -278,12 +283,14 @@ class Executor:
             if toks is not None and (toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= V):
                 bad = [int(t) for t in toks.tolist() if not (isinstance(t, int) and 0 <= t < V)][:1]
                 raise StepError(f"request {e.req!r}: token id {bad[0] if bad else '?'} outside the vocabulary [0, {V})")
+            arrays.append(toks if n > 1 else None)
             for w in e.want:
                 if not 0 <= w < n:
                     raise StepError(f"request {e.req!r}: wanted place {w} outside its {n} tokens")
             why = self.cache.check_step(e.req, e.start, n)
             if why:
                 raise StepError(why)
+        return arrays
 
     def _passes(self, entries: Sequence[StepEntry]):
         """Cut the entries into passes of at most `max_step_tokens` tokens.  Each pass is a list of

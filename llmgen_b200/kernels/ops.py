@@ -38,7 +38,15 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream's handle.  Asked of torch's C layer directly where it offers that: the
+    `torch.cuda.current_stream()` object costs several microseconds, more than a launch."""
+    if _raw_stream is not None and _raw_device is not None:
+        return c_void_p(_raw_stream(_raw_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -188,6 +196,12 @@ def widen(out: torch.Tensor, src: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------ attn_prep
+def attn_prep_set_by_token(on: bool) -> None:
+    """Which 16-byte variant `attn_prep` runs on prompts: a warp on several heads of one token at a
+    time (the default) or a row at a time (for comparisons and tests)."""
+    build.load("attn_prep").llmk_attn_prep_set_by_token(c_int(1 if on else 0))
+
+
 def attn_prep(qkv, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
               positions: Optional[torch.Tensor], slots: Optional[torch.Tensor], cos: Optional[torch.Tensor],
               sin: Optional[torch.Tensor], q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
@@ -305,11 +319,13 @@ _tc_error_flags = {}
 
 def tc_error_flag(device) -> torch.Tensor:
     """Device int that a tensor-core kernel raises when one of its bounded waits gave up."""
-    key = str(device)
-    flag = _tc_error_flags.get(key)
+    flag = _tc_error_flags.get(device)
     if flag is None:
-        flag = torch.zeros(1, dtype=torch.int32, device=device)
-        _tc_error_flags[key] = flag
+        flag = _tc_error_flags.get(str(device))
+        if flag is None:
+            flag = torch.zeros(1, dtype=torch.int32, device=device)
+            _tc_error_flags[str(device)] = flag
+        _tc_error_flags[device] = flag          # the device object itself as a second key: no string per launch
     return flag
 
 

@@ -108,12 +108,14 @@ class GQAAttention(Mixer):
         return self._tc_bq[page_size]
 
     def prepare_step(self, builder) -> None:
-        """Tiles of queries, (sequence, first query of the tile) pairs, for the kernel this step
-        will run: none for a step of single decoded tokens in bfloat16."""
-        self._tiles(builder, self.bq)
+        """Tiles of queries, (sequence, first query of the tile) pairs, for the kernel this step will
+        run: the tensor-core kernel's where it takes the step, else the CUDA-core kernel's."""
         page_size = getattr(builder, "page_size", 0)
-        if not builder.pure_decode and page_size and self.tc_tile_queries(page_size):
-            self._tiles(builder, self.tc_tile_queries(page_size), heaviest_first=True)
+        tc_bq = self.tc_tile_queries(page_size) if page_size and not builder.pure_decode else 0
+        if tc_bq:
+            self._tiles(builder, tc_bq, heaviest_first=True)
+        else:
+            self._tiles(builder, self.bq)
 
     def _split(self, ctx):
         """(num_parts, part_size) for flash-decoding; only pure-decode steps are split."""

@@ -83,6 +83,32 @@ def test_add_rmsnorm(ops, dtype, H):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,H", [(603, 1024), (512, 80), (700, 1536), (515, 2048), (513, 132)])
+def test_add_rmsnorm_of_many_rows(ops, dtype, n, H):
+    """A prompt's rows: the variant with a warp per row (512 rows and more, widths up to 2,048), with
+    a delta, without one, and with the residual left as it was."""
+    torch.manual_seed(3)
+    eps = 2e-6
+    resid = torch.randn(n, H) * 2
+    resid[n - 1] *= 40.0                                        # a last row that stands out: no row is skipped or swapped
+    delta = torch.randn(n, H).to(dtype)
+    w = 1 + 0.2 * torch.randn(H)
+    r = dev(resid)
+    out = torch.empty(n, H, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r, dev(delta), dev(w), out, eps, 0.0)
+    summed = resid + delta.float()
+    assert torch.allclose(r.cpu(), summed, atol=1e-5)
+    assert float((out.float().cpu() - plain.rmsnorm(summed, w, eps)).abs().max()) < tol(dtype, 6)
+    before = r.clone()
+    ops.add_rmsnorm(r, None, dev(w), out, eps, 1.0)
+    assert torch.equal(r, before)
+    assert float((out.float().cpu() - plain.rmsnorm(summed, w, eps, weight_offset=1.0)).abs().max()) < tol(dtype, 10)
+    ops.add_rmsnorm(r, dev(delta), dev(w), out, eps, 0.0, write_resid=False)
+    assert torch.equal(r, before)
+    assert float((out.float().cpu() - plain.rmsnorm(summed + delta.float(), w, eps)).abs().max()) < tol(dtype, 6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("F", [50, 64, 176])
 def test_silu_mul(ops, dtype, F):
     torch.manual_seed(2)
@@ -138,9 +164,19 @@ def test_attn_prep(ops, dtype, nq, nkv, hd, rot):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 64), (16, 8, 128), (3, 1, 256), (5, 2, 32), (2, 2, 48)])
 @pytest.mark.parametrize("T", [32, 77, 300])
-def test_attn_prep_on_prompts(ops, dtype, nq, nkv, hd, T):
-    """Many rows: the path with 16-byte accesses (head sizes it takes) and the general one agree with
-    the plain functions; slots include -1 and a page's last place; q lands in a buffer of its own."""
+@pytest.mark.parametrize("by_token", [True, False])
+def test_attn_prep_on_prompts(ops, dtype, nq, nkv, hd, T, by_token):
+    """Many rows: the paths with 16-byte accesses (head sizes they take; a warp on several heads of a
+    token, or a row at a time) and the general one agree with the plain functions; slots include -1
+    and a page's last place; q lands in a buffer of its own."""
+    ops.attn_prep_set_by_token(by_token)
+    try:
+        _attn_prep_on_prompts(ops, dtype, nq, nkv, hd, T)
+    finally:
+        ops.attn_prep_set_by_token(True)
+
+
+def _attn_prep_on_prompts(ops, dtype, nq, nkv, hd, T):
     torch.manual_seed(4)
     page, eps = 16, 1e-6
     pages = (T + page - 1) // page + 1
