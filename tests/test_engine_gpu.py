@@ -131,6 +131,25 @@ def test_requests_that_cannot_be_served_are_refused(tmp):
         LLM(path, dtype="float32", max_model_len=4096)            # beyond the model's positions
 
 
+def test_steps_with_ids_outside_the_vocabulary_are_refused(tmp):
+    """The step function checks every id before a kernel reads the table with it: lists, arrays, ids too
+    large for 32 bits, negative ones and ones that are no integers; a good step still runs afterwards."""
+    import numpy as np
+    from llmgen_b200.engine.executor import StepEntry, StepError
+    from tests.util import Driver
+    d = Driver(make_folder(tmp, "A"), "float32", 128, 16)
+    assert d.executor.admit("x") and d.executor.reserve("x", 0, 3)
+    for bad in ([1, 2, 256], [1, -1, 3], [1, 2 ** 40, 3], [1, 2.5, 3], np.array([3, 4, 999]), [300]):
+        with pytest.raises(StepError, match="vocabulary"):
+            d.executor.step([StepEntry("x", bad, 0, [0])])
+    d.executor.release("x")
+    ids = random_ids(9, 256, 3)
+    got = d.step([("y", ids, range(9))])
+    assert float((got - PlainQwen3(make_folder(tmp, "A")).logits(ids)).abs().max()) < 1e-4
+    got2 = d.step([("z", np.asarray(ids, dtype=np.int64), range(9))])          # ids as an array
+    assert torch.equal(got, got2)
+
+
 def test_command_line_chat_and_bench(tmp):
     path = make_folder(tmp, "A")
     prompt = random_ids(11, 256, 95)
