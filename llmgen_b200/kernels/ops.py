@@ -337,10 +337,12 @@ def check_tc_errors(device) -> None:
         raise KernelError("a tensor-core kernel gave up waiting on a barrier (results of that step are invalid)")
 
 
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pdl: bool = False) -> None:
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pdl: bool = True) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T on the tensor cores (tcgen05), bfloat16 operands, float32
     accumulation; `out` is bfloat16 or float32.  With `gated`, w interleaves gate and up rows in
-    groups of 16 and out[M, N/2] = silu(gate) * up."""
+    groups of 16 and out[M, N/2] = silu(gate) * up.  `pdl`: launched as a programmatic dependent of the
+    kernel before it, like every other kernel here (its set-up then runs under that kernel's tail; a
+    2,048-token prompt took 4.85 ms without and 4.45 ms with it)."""
     lib = build.load("gemm_tc")
     M, K = a.shape
     N = w.shape[0]
