@@ -8,19 +8,21 @@
 //   warp 0     TMA producer: the Q tile once (a 3-D box [queries, gc heads, 64] per half of the head),
 //              then per tile of 128 keys the K pages of the block table into a ring of two stages.
 //   warp 10    TMA producer of the V pages, a ring of two stages of its own.
-//   warp 1     owns tensor memory (S0 | S1 | O0 | O1: 2 x 128 + 2 x head_dim columns) and issues the MMAs:
-//              S[j] = Q K_j^T (K-major operands), O_j = P_j V_j (V read MN-major: keys are V's rows
-//              in shared memory).  S is double-buffered so that Q K_{j+1}^T runs under the softmax of
-//              tile j.
+//   warp 1     owns tensor memory (S0 | S1 | O: 2 x 128 + head_dim columns) and issues the MMAs:
+//              S[j] = Q K_j^T (K-major operands), O += P_j V_j (V read MN-major: keys are V's rows
+//              in shared memory; O adds up in tensor memory over all tiles).  S is double-buffered so
+//              that Q K_{j+1}^T runs under the softmax of tile j.
 //   warps 2-9  softmax: two threads per row, each with half of the row's key columns and half of the
 //              head.  Pass 1 reads S from tensor memory and finds the row maximum (causal and window
 //              mask on the tiles that need it; the two halves exchange maxima through shared memory);
 //              pass 2 writes P = exp2((s - m) * scale *
 //              log2 e) as bfloat16 into shared memory in the swizzled K-major layout the second MMA
-//              reads; then, while the tensor core multiplies it with V, the previous tile's O_j is read
-//              back from the other O buffer and added to the float32 accumulator in registers, rescaled
-//              by exp(m_old - m_new).  Reductions run as four independent chains: with so few warps per SM the
-//              latency of a dependent chain is what costs.
+//              reads.  m is the row's reference maximum: it follows the true maximum only when that grew
+//              by more than 8 in the exponent's scale, and only then is O rescaled (read from tensor
+//              memory, multiplied by exp(m_old - m_new), written back) before the tile's P V is issued;
+//              l and O are kept against the same reference, so the quotient is the softmax whatever the
+//              reference.  O is read once, after the last tile.  Reductions run as four independent
+//              chains: with so few warps per SM the latency of a dependent chain is what costs.
 // Statistics (m, l), the accumulator and the final division are float32.
 //
 // Tiles follow the reference's prefill kernel in spirit (src/backend/cuda/attention/attention.cu:300-466:
@@ -132,7 +134,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     using L = Smem<HD>;
     constexpr int HB = HD / 64;                 // 64-wide blocks of the head
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t S_COL0 = 0, S_COL1 = BN, O_COL0 = 2 * BN, O_COL1 = 2 * BN + HD;
+    constexpr uint32_t S_COL0 = 0, S_COL1 = BN, O_COL0 = 2 * BN;
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((tc::smem_u32(smem) & 1023u) != 0) {      // uniform over the block: nothing has been set up yet
         if (threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 2);
@@ -262,7 +264,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t da = tc::smem_desc_sw128(p_addr + (kk / 4) * (BM * 128) + (kk % 4) * 32);
                     const uint64_t db = tc::smem_desc_sw128_mn(v_addr + kk * 16 * 128, p.v_lbo, p.v_sbo);
-                    tc::mma_bf16_ss(tmem_base + (st ? O_COL1 : O_COL0), da, db, idesc_o, kk != 0);
+                    tc::mma_bf16_ss(tmem_base + O_COL0, da, db, idesc_o, (j | kk) != 0);   // O adds up in tensor memory over the tiles
                 }
                 tc::mma_commit(tc::smem_u32(&o_full[st]));
                 tc::mma_commit(tc::smem_u32(&v_empty[st]));
@@ -286,23 +288,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const float sl2 = p.scale_log2;
         constexpr int OC = HD / 2;            // columns of O this thread accumulates
         constexpr int SC = BN / 2;            // columns of S this thread turns into P
-        float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
-        float acc[OC];
-#pragma unroll
-        for (int i = 0; i < OC; ++i) acc[i] = 0.f;
+        float m = -INFINITY, l = 0.f;
         uint8_t* p_row0 = smem + L::P_OFF + half * (BM * 128) + r * 128;
         float* xchg = reinterpret_cast<float*>(smem + L::XCHG_OFF);      // [2 tiles][2 halves][128 rows]
         bool ok = true;
 
-        auto accumulate = [&](float alpha, int buf) {
-#pragma unroll
-            for (int c = 0; c < OC / 32; ++c) {
-                uint32_t o[32];
-                tc::tmem_ld_32x32_wait(tmem_base + lane_addr + (buf ? O_COL1 : O_COL0) + half * OC + c * 32, o);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(o[i]));
-            }
-        };
+        const uint32_t o_addr = tmem_base + lane_addr + O_COL0 + half * OC;     // this thread's columns of O
 
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
@@ -316,9 +307,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             uint8_t* p_row = p_row0 + st * L::P_BYTES;       // P is double-buffered: P V of the tile before may still read the other
             // pass 1: the maximum of this thread's half of the row (four independent chains)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            uint32_t v[SC / 32][32];      // this thread's scores of the tile: read once, kept for both passes
+            static_assert(SC == 64, "two loads of 32 columns");
             if (ok) {
-                uint32_t v[SC / 32][32];
-                static_assert(SC == 64, "two loads of 32 columns per pass");
                 tc::tmem_ld_32x32_x2_wait(s_addr, s_addr + 32, v[0], v[1]);
 #pragma unroll
                 for (int c = 0; c < SC / 32; ++c) {
@@ -340,16 +331,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight softmax warps
             TL_STAMP(3);
             const float mx = fmaxf(mx_own, xchg[(st * 2 + (half ^ 1)) * BM + r]);
+            // The row's reference maximum follows the true one lazily: only when that grew by more than 8 in
+            // the exponent's scale (P then stays below 2^8, and the result is the same up to rounding, as
+            // l and O are kept against the same reference).  O lives in tensor memory and is rescaled there
+            // on the few tiles where a row of the warp moves its reference.
             const float m_new = fmaxf(m, mx);
-            const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_new) * sl2);
+            const bool move = m_new > m && (m == -INFINITY || (m_new - m) * sl2 > 8.f);
+            const bool fix = move && m != -INFINITY && j > 0;      // O and l hold something to rescale
+            const float alpha = fix ? fast_exp2((m - m_new) * sl2) : 1.f;
+            if (move) m = m_new;
+            if (ok && __any_sync(0xffffffffu, fix)) {
+                ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&o_full[(j - 1) & 1]), ((j - 1) >> 1) & 1, abort_flag));
+                tc::tc_fence_after_sync();
+                if (ok) {
+#pragma unroll
+                    for (int c = 0; c < OC / 32; ++c) {
+                        uint32_t o[32];
+                        tc::tmem_ld_32x32_wait(o_addr + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tc::tmem_st_32x32(o_addr + c * 32, o);
+                    }
+                    tc::tmem_st_wait();
+                }
+            }
             TL_STAMP(4);
             // pass 2: P into shared memory, row sum
             if (ok) {
-                const float mb = (m_new == -INFINITY) ? 0.f : m_new * sl2;
+                const float mb = (m == -INFINITY) ? 0.f : m * sl2;
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t v[SC / 32][32];
-                static_assert(SC == 64, "two loads of 32 columns per pass");
-                tc::tmem_ld_32x32_x2_wait(s_addr, s_addr + 32, v[0], v[1]);
 #pragma unroll
                 for (int c = 0; c < SC / 32; ++c) {
                     float pv[32];
@@ -375,45 +385,44 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     }
                 }
                 l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-                m = m_new;
                 tc::fence_proxy_async();
                 tc::tc_fence_before_sync();
                 tc::mbar_arrive(tc::smem_u32(p_full));
                 TL_STAMP(5);
             }
-            // the previous tile's P V (in the other O buffer), while the tensor core works on this one's
-            if (ok && j > 0) {
-                ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&o_full[(j - 1) & 1]), ((j - 1) >> 1) & 1, abort_flag));
-                tc::tc_fence_after_sync();
-                TL_STAMP(6);
-                if (ok) accumulate(alpha_pending, (j - 1) & 1);
-            }
-            alpha_pending = alpha;
             TL_STAMP(7);
         }
         if (ok && n_tiles > 0) {
             ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&o_full[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag));
-            if (ok) {
-                tc::tc_fence_after_sync();
-                accumulate(alpha_pending, (n_tiles - 1) & 1);
-            }
+            tc::tc_fence_after_sync();
         }
         // the row's sum is the two halves' sums (both were kept against the same maxima)
         asm volatile("bar.sync 1, 256;" ::: "memory");       // every read of the last tile's maxima is done
         xchg[half * BM + r] = l;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const float l_row = l + xchg[(half ^ 1) * BM + r];
-        if (ok && qi < max(nq_tile, 0) && (chunk * p.gc + r % p.gc) < G) {
-            const float inv = (row_valid && l_row > 0.f) ? 1.0f / l_row : 0.f;
-            bf16* o = p.out + (size_t)(q_beg + q0 + qi) * p.o_stride + (size_t)head * HD + half * OC;
+        const bool writes = ok && qi < max(nq_tile, 0) && (chunk * p.gc + r % p.gc) < G;
+        const float inv = (row_valid && l_row > 0.f) ? 1.0f / l_row : 0.f;
+        bf16* o = p.out + (size_t)(q_beg + q0 + qi) * p.o_stride + (size_t)head * HD + half * OC;
 #pragma unroll
-            for (int i = 0; i < OC; i += 8) {
-                float f[8];
+        for (int c = 0; c < OC / 32; ++c) {
+            uint32_t acc[32];
+            if (ok && n_tiles > 0) {                     // uniform over the warp: the load is a warp's instruction
+                tc::tmem_ld_32x32_wait(o_addr + c * 32, acc);
+            } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = acc[i + e] * inv;
-                Vec16<bf16> pk;
-                pk.pack(f);
-                *reinterpret_cast<uint4*>(o + i) = pk.raw;
+                for (int i = 0; i < 32; ++i) acc[i] = 0u;
+            }
+            if (writes) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    float f[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f[e] = inv > 0.f ? __uint_as_float(acc[i + e]) * inv : 0.f;
+                    Vec16<bf16> pk;
+                    pk.pack(f);
+                    *reinterpret_cast<uint4*>(o + c * 32 + i) = pk.raw;
+                }
             }
         }
     }

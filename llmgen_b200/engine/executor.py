@@ -117,11 +117,17 @@ class Executor:
         self.storage = CacheStorage(kv_requests, state_requests, self.group_index, pages, limits.page_size,
                                     limits.max_num_seqs, self.dtype, self.device)
         self.layer_caches = [self.storage.layer_cache(item.cache, item.writes_cache) for item in model.spec.run_order]
+        # one mixer for every set of step arrays: mixers that say, by `step_arrays_key()`, that they add the
+        # same arrays are asked once
         self._unique_mixers = []
+        keys = set()
         for layer in model.layers:
             m = getattr(layer, "mixer", None)
             if m is not None and hasattr(m, "prepare_step"):
-                self._unique_mixers.append(m)
+                key = m.step_arrays_key() if hasattr(m, "step_arrays_key") else id(m)
+                if key not in keys:
+                    keys.add(key)
+                    self._unique_mixers.append(m)
 
         # mixers whose own step arrays depend only on the batch's shape let decode steps reuse them
         self._static_step_arrays = all(getattr(m, "step_arrays_follow_shapes", False) for m in self._unique_mixers)

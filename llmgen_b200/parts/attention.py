@@ -107,6 +107,10 @@ class GQAAttention(Mixer):
             self._tc_bq[page_size] = ops.attention_tc_tile_queries(self.nq, self.nkv, self.hd, page_size)
         return self._tc_bq[page_size]
 
+    def step_arrays_key(self):
+        """Mixers with equal keys add the same arrays in `prepare_step`: the engine asks one of them."""
+        return ("attention_tiles", self.bq, self.nq, self.nkv, self.hd, self.window, str(self.dtype))
+
     def prepare_step(self, builder) -> None:
         """Tiles of queries, (sequence, first query of the tile) pairs, for the kernel this step will
         run: the tensor-core kernel's where it takes the step, else the CUDA-core kernel's."""

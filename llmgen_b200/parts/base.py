@@ -24,6 +24,8 @@ Mixer:
     prepare_step(builder)                     optional: add int32 arrays to the step's metadata
     step_arrays_follow_shapes = True          optional class attribute: those arrays depend on the
                                               portions' lengths only (lets decode steps reuse them)
+    step_arrays_key()                         optional: mixers with equal keys add the same arrays,
+                                              and only one of them is asked each step
     forward(ctx, x, cache) -> [T, H]          x is the normed input; `cache` is this run
                                               item's `LayerCache`; returns an array or a
                                               `Partials` (see `parts.linear.linear_sliced`)
