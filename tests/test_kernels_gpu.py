@@ -992,6 +992,31 @@ def test_attention_tc_far_key(ops, where):
     assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
 
 
+class RisingKeys:
+    """Keys along the last query's direction with a length that grows with the position: the row maximum
+    rises from tile to tile, slowly (the reference maximum of the tensor-core kernel lags behind it) or
+    fast (it moves on every tile), and the last keys carry nearly all the weight."""
+    def __init__(self, top):
+        self.top = top
+
+    def __call__(self, s, ctx, q_len, q, t, k_seq, kc, pages, page):
+        direction = q[t + q_len - 1, 0].float()
+        unit = direction / direction.norm()
+        for j in range(ctx):
+            key = (unit * (self.top * (j + 1) / ctx)).to(kc.dtype)
+            kc[pages[j // page], :, j % page] = key
+            k_seq[j] = key.float()
+
+
+@pytest.mark.parametrize("top", [6.0, 14.0, 30.0, 70.0])
+def test_attention_tc_rising_scores(ops, top):
+    nq, nkv, hd, page = 4, 2, 64, 16
+    seqs = [(700, 1), (1030, 300), (640, 640)]
+    q, kc, vc, bt, ctxs, cu, ref, mb = paged_case(seqs, nq, nkv, hd, page, torch.bfloat16, 25, sharpen=RisingKeys(top))
+    got = run_attention_tc(ops, q, kc, vc, bt, ctxs, cu, mb, nq, nkv, hd, page)
+    assert float((got - ref).abs().max()) < tol(torch.bfloat16, 3)
+
+
 @pytest.mark.parametrize("window", [1, 7, 16, 40, 100, 200])
 @pytest.mark.parametrize("offset", [0, 1])
 def test_attention_tc_window_edge(ops, window, offset):
