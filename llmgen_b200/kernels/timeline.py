@@ -3,6 +3,7 @@
     python -m llmgen_b200.kernels.timeline gemm_tc M N K [gated] [pairs]
     python -m llmgen_b200.kernels.timeline skinny_chain ROWS
     python -m llmgen_b200.kernels.timeline products
+    python -m llmgen_b200.kernels.timeline attention_tc [TOKENS]
 
 `gemm_tc`, `gemm_skinny` and `attention_tc` can be compiled with `-DLLMK_GEMM_TIMELINE`,
 `-DLLMK_SKINNY_TIMELINE`, `-DLLMK_ATTN_TIMELINE`: a few blocks then stamp the global timer at their
@@ -178,7 +179,52 @@ def products() -> None:
     ops.check_tc_errors(torch.device("cuda"))
 
 
+def attention_tc(tokens: int = 2048) -> None:
+    """Stamps (SM clock cycles) of the first softmax warp of the heaviest block of `attention_tc` on one
+    prompt of `tokens` tokens (16 query heads on 8 kv heads of 128, pages of 16), tile by tile: when the
+    loop came round, when S was there, after the row maximum, after the exchange of maxima, after the
+    decision on the reference maximum, after P was handed over, at the tile's end."""
+    import ctypes as C
+    import math
+    lib = _timeline_library("attention_tc", "LLMK_ATTN_TIMELINE")
+    nq, nkv, hd, page, T = 16, 8, 128, 16, tokens
+    n_pages = (T + page - 1) // page
+    kc = torch.randn(n_pages, nkv, page, hd, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(n_pages, nkv, page, hd, device="cuda").to(torch.bfloat16)
+    q = torch.randn(T, nq * hd, device="cuda").to(torch.bfloat16)
+    out = torch.empty(T, nq * hd, device="cuda", dtype=torch.bfloat16)
+    bt = torch.arange(n_pages, dtype=torch.int32, device="cuda")
+    ctx = torch.tensor([T], dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    bq = ops.attention_tc_tile_queries(nq, nkv, hd, page)
+    q0 = torch.arange(0, T, bq, dtype=torch.int32, device="cuda").flip(0).contiguous()      # heaviest tile first: block 0
+    seq = torch.zeros_like(q0)
+    stamps = torch.zeros(16 * 8, dtype=torch.int64, device="cuda")
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    for _ in range(3):
+        rc = lib.llmk_attention_tc(ptr(out), C.c_longlong(nq * hd), ptr(q), C.c_longlong(nq * hd), C.c_int(T), ptr(kc), ptr(vc),
+                                   C.c_longlong(n_pages), ptr(bt), C.c_int(n_pages), ptr(ctx), ptr(cu), ptr(seq), ptr(q0),
+                                   C.c_int(q0.numel()), C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page), C.c_int(0),
+                                   C.c_float(1 / math.sqrt(hd)), ptr(ops.tc_error_flag(q.device)), C.c_uint(0), C.c_uint(0),
+                                   ops._stream(), ptr(stamps))
+        if rc != 0:
+            raise ops.KernelError(lib.llmk_last_error().decode())
+        torch.cuda.synchronize()
+    ops.check_tc_errors(q.device)
+    t = stamps.cpu().view(16, 8)
+    tiles = min(16, (T + 127) // 128)
+    print(f"attention_tc, {T} tokens: cycles per key tile of the heaviest block's first softmax warp")
+    print("tile   wait for S   pass 1   exchange   reference   pass 2   rest   whole tile")
+    for j in range(tiles - 1):
+        d = [int(t[j, 1] - t[j, 0]), int(t[j, 2] - t[j, 1]), int(t[j, 3] - t[j, 2]), int(t[j, 4] - t[j, 3]),
+             int(t[j, 5] - t[j, 4]), int(t[j, 7] - t[j, 5]), int(t[j + 1, 0] - t[j, 0])]
+        print(f"{j:4d} " + " ".join(f"{v:10d}" for v in d))
+
+
 def main(argv) -> int:
+    if argv[:1] == ["attention_tc"] and len(argv) <= 2:
+        attention_tc(int(argv[1]) if len(argv) == 2 else 2048)
+        return 0
     if argv == ["products"]:
         products()
         return 0
