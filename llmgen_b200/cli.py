@@ -2,6 +2,7 @@
 
     python -m llmgen_b200 chat  [prompt] [max_new] [options]   generate and print `token ids: ...`
     python -m llmgen_b200 bench <workload.json>    [options]   run a workload, print a JSON summary
+    python -m llmgen_b200 workload <out.json>      [options]   write a seeded random workload for `bench`
 
 Options keep the reference's names and meanings:
     --model <dir>  --temp <f>  --max-model-len <n>  --max-num-seqs <n>  --max-batched-tokens <n>
@@ -10,6 +11,10 @@ Options keep the reference's names and meanings:
 Added: --dtype bfloat16|float32, --seed <n>, --random <config.json> (random weights drawn from
 --seed instead of a model folder).  The model is a folder with config.json and model.safetensors
 (default: environment variable LLMGEN_MODEL).
+`workload` takes --scenario single|concurrent8|concurrent32|bench256|longctx (the reference's
+bench/gen_workload.py scenarios) and / or --requests <n> --rounds <n> --input <n|lo:hi>
+--output <n|lo:hi>, with --vocab <n>, --request-temp <f> and --seed; with --max-model-len given it
+shortens outputs that would not fit.  It needs no GPU.
 
 There is no tokenizer here (the engine's contract is token ids in, token ids out): the chat
 prompt is a list of token ids, "12,7,99" or "12 7 99", or @file with a JSON list.  The
@@ -36,15 +41,15 @@ from .engine.scheduler import CHUNKED, PREFILL_FIRST
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="llmgen_b200", description="Single-GPU inference engine for sm_100a")
-    ap.add_argument("cmd", choices=["chat", "bench"])
-    ap.add_argument("arg0", nargs="?", help="chat: prompt token ids; bench: workload.json")
+    ap.add_argument("cmd", choices=["chat", "bench", "workload"])
+    ap.add_argument("arg0", nargs="?", help="chat: prompt token ids; bench: workload.json; workload: the file to write")
     ap.add_argument("max_new", nargs="?", type=int, default=2000, help="chat: most tokens to generate")
     ap.add_argument("--model", default=os.environ.get("LLMGEN_MODEL"))
     ap.add_argument("--random", metavar="CONFIG_JSON", help="draw random weights for this config.json instead of --model")
     ap.add_argument("--seed", type=int, default=0x5EED)
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--temp", type=float, default=0.0)
-    ap.add_argument("--max-model-len", type=int, default=4096)
+    ap.add_argument("--max-model-len", type=int, default=None, help="default 4096")
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--max-batched-tokens", type=int, default=16384)
     ap.add_argument("--pass-tokens", type=int, default=8192)
@@ -57,6 +62,14 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dup", type=int, default=1)
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--sync-each", action="store_true")
+    wl = ap.add_argument_group("workload")
+    wl.add_argument("--scenario", help="single, concurrent8, concurrent32, bench256 or longctx")
+    wl.add_argument("--requests", type=int, help="requests per round")
+    wl.add_argument("--rounds", type=int)
+    wl.add_argument("--input", help="prompt length: N or LOW:HIGH")
+    wl.add_argument("--output", help="tokens to generate: N or LOW:HIGH")
+    wl.add_argument("--vocab", type=int, default=10001, help="token ids are drawn from [0, vocab)")
+    wl.add_argument("--request-temp", type=float, default=0.6, help="temperature written into every request")
     return ap
 
 
@@ -204,8 +217,29 @@ def bench(args) -> int:
     return 0
 
 
+def workload(args) -> int:
+    from . import workload as wl
+    if not args.arg0:
+        raise SystemExit("workload needs the name of the file to write")
+    try:
+        name, shape = wl.resolve_shape(args.scenario, args.requests, args.rounds,
+                                       wl.parse_range(args.input, "--input") if args.input else None,
+                                       wl.parse_range(args.output, "--output") if args.output else None)
+        made = wl.make_workload(name, shape, vocab=args.vocab, seed=args.seed, temperature=args.request_temp,
+                                max_model_len=args.max_model_len)
+    except wl.WorkloadError as e:
+        raise SystemExit(f"workload: {e}")
+    wl.write_workload(args.arg0, made)
+    print(wl.summary(made), file=sys.stderr)
+    return 0
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    if args.cmd == "workload":
+        return workload(args)
+    if args.max_model_len is None:
+        args.max_model_len = 4096
     if args.sync_each:
         args.eager = True
     return chat(args) if args.cmd == "chat" else bench(args)
