@@ -11,6 +11,10 @@ Options keep the reference's names and meanings:
 Added: --dtype bfloat16|float32, --seed <n>, --random <config.json> (random weights drawn from
 --seed instead of a model folder).  The model is a folder with config.json and model.safetensors
 (default: environment variable LLMGEN_MODEL).
+Environment, for `chat` (the reference's names): LLMGEN_PROFILE prints the time, FLOP/s and bytes/s
+of every kernel by phase (eager steps); LLMGEN_METRICS prints TTFT, inter-token latencies and
+throughputs with the model's FLOP and byte rates (shares of LLMGEN_PEAK_TFLOPS / LLMGEN_PEAK_GBPS
+when given) and writes them as JSON to the path in LLMGEN_METRICS_JSON.
 `workload` takes --scenario single|concurrent8|concurrent32|bench256|longctx (the reference's
 bench/gen_workload.py scenarios) and / or --requests <n> --rounds <n> --input <n|lo:hi>
 --output <n|lo:hi>, with --vocab <n>, --request-temp <f> and --seed; with --max-model-len given it
@@ -101,22 +105,50 @@ def chat(args) -> int:
     if not args.arg0:
         raise SystemExit("chat needs a prompt: token ids such as \"12,7,99\" or @ids.json")
     prompt = parse_prompt(args.arg0)
+    # the reference's switches (src/profiler/profiler.zig:95-101, src/profiler/metrics.zig:47-51): a table of
+    # kernel times, which needs eager steps, and the latencies of the request with the model's efficiency
+    profile = os.environ.get("LLMGEN_PROFILE") is not None
+    metrics = None
+    if profile:
+        args.eager = True
     llm = make_llm(args)
     print(f"[load] {llm.load_seconds:.2f} s", file=sys.stderr)
+    if profile:
+        from .engine.profiler import OpProfiler
+        llm.executor.profiler = OpProfiler().enable()
+    if os.environ.get("LLMGEN_METRICS") is not None:
+        from .engine.profiler import GenMetrics
+        metrics = GenMetrics()
     room = args.max_model_len - len(prompt)
     params = SamplingParams(temperature=args.temp, max_tokens=max(1, min(args.max_new, room)), ignore_eos=False)
     t0 = time.perf_counter()
+    if metrics is not None:
+        metrics.start(len(prompt), t0)
     requests = [llm.engine.add_request(prompt, params) for _ in range(max(1, args.dup))]
     first = None
     while not llm.engine.is_finished():
         llm.engine.step()
         for r, tok in llm.engine.last_emitted:
             if r is requests[0]:
+                now = time.perf_counter()
                 if first is None:
-                    first = time.perf_counter()
+                    first = now
+                if metrics is not None:
+                    metrics.on_token(now)
                 print(tok, end=" ", flush=True)
     t1 = time.perf_counter()
     print()
+    if metrics is not None:
+        from .engine.profiler import ModelCost, efficiency_text
+        metrics.finish(t1)
+        elem = 2 if args.dtype == "bfloat16" else 4
+        print(metrics.text(), file=sys.stderr)
+        print(efficiency_text(metrics, ModelCost.from_spec(llm.model.spec, elem, elem)), file=sys.stderr)
+        metrics.write_json()
+    if profile:
+        print(llm.executor.profiler.text(), file=sys.stderr)
+        llm.executor.profiler.disable()
+        llm.executor.profiler = None
     ids = requests[0].completion
     n = len(ids)
     if first is not None:

@@ -91,6 +91,7 @@ class Executor:
         self.n_graph_steps = 0
         self.n_eager_steps = 0
         self.launch_count = 0
+        self.profiler = None             # an `engine.profiler.OpProfiler`: told of every eager pass
         if limits.max_model_len > model.max_positions():
             raise StepError(f"max_model_len {limits.max_model_len} exceeds the model's "
                             f"{model.max_positions()} positions")
@@ -439,6 +440,8 @@ class Executor:
             torch.cuda.synchronize(self.device)
 
     def _eager_pass(self, entries: Sequence[StepEntry], sample: bool, return_logits: bool, pad_to: int = 0) -> StepOutput:
+        if self.profiler is not None:
+            self.profiler.begin_pass([e.start for e in entries], [len(e.tokens) for e in entries])
         ctx, want_rows, temps, seed, n_want = self._build_meta(entries, pad_to=pad_to)
         ctx.fixed_shapes = pad_to > 0      # the launch shapes a captured graph of this step would have
         n_real = sum(len(e.want) for e in entries)
