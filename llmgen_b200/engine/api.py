@@ -10,6 +10,7 @@ block_size, gpu_util, kv_blocks, policy, chunk, eager, sync_each.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import tempfile
 import time
@@ -101,6 +102,22 @@ class LLM:
             max_num_seqs=max_num_seqs, max_num_batched_tokens=max_batched_tokens, policy=policy,
             chunk_tokens=chunk, eos_token_ids=tuple(self.model.spec.eos_token_ids)))
         self.load_seconds = time.perf_counter() - t0
+
+    @contextlib.contextmanager
+    def profile(self):
+        """`with llm.profile() as prof: llm.generate(...)`, then `prof.text()` or `prof.rows(phase)`: device time,
+        FLOPs and bytes of every kernel by phase (`engine.profiler.OpProfiler`).  Only launches made directly
+        are seen, so the engine must have been built with `eager=True`."""
+        from .profiler import OpProfiler
+        if not self.executor.eager:
+            raise ValueError("profiling needs eager steps: build the LLM with eager=True")
+        prof = OpProfiler().enable()
+        self.executor.profiler = prof
+        try:
+            yield prof
+        finally:
+            prof.disable()
+            self.executor.profiler = None
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None
                  ) -> List[Dict]:

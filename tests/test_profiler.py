@@ -283,3 +283,19 @@ def test_every_listed_binding_exists_with_the_operands_its_cost_reads():
         params = inspect.signature(getattr(ops, name)).parameters
         for alternatives in needs[cost]:
             assert any(p in params for p in alternatives), f"{name} has none of {alternatives}"
+
+
+def test_llm_profile_needs_eager_steps_and_cleans_up(monkeypatch):
+    from llmgen_b200.engine.api import LLM
+    monkeypatch.setattr(pf, "CudaEventClock", CountingClock)
+    llm = LLM.__new__(LLM)                                   # no GPU here: only what profile() touches
+    llm.executor = types.SimpleNamespace(eager=False, profiler=None)
+    with pytest.raises(ValueError, match="eager=True"):
+        with llm.profile():
+            pass
+    llm.executor.eager = True
+    with pytest.raises(KeyError):
+        with llm.profile() as prof:
+            assert llm.executor.profiler is prof and pf.OpProfiler._active is prof
+            raise KeyError("inside")
+    assert llm.executor.profiler is None and pf.OpProfiler._active is None
