@@ -8,7 +8,6 @@ import sys
 import tempfile
 
 import pytest
-import torch
 
 from tests.plain.qwen3_plain import PlainQwen3
 from tests.util import ROOT, TINY, Driver, logits_close, make_folder, random_ids
