@@ -3,6 +3,7 @@
     python -m llmgen_b200 chat  [prompt] [max_new] [options]   generate and print `token ids: ...`
     python -m llmgen_b200 bench <workload.json>    [options]   run a workload, print a JSON summary
     python -m llmgen_b200 workload <out.json>      [options]   write a seeded random workload for `bench`
+    python -m llmgen_b200 info --model <dir> | --random <config.json>   sizes, tensors checked, costs; no GPU needed
 
 Options keep the reference's names and meanings:
     --model <dir>  --temp <f>  --max-model-len <n>  --max-num-seqs <n>  --max-batched-tokens <n>
@@ -45,7 +46,7 @@ from .engine.scheduler import CHUNKED, PREFILL_FIRST
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="llmgen_b200", description="Single-GPU inference engine for sm_100a")
-    ap.add_argument("cmd", choices=["chat", "bench", "workload"])
+    ap.add_argument("cmd", choices=["chat", "bench", "workload", "info"])
     ap.add_argument("arg0", nargs="?", help="chat: prompt token ids; bench: workload.json; workload: the file to write")
     ap.add_argument("max_new", nargs="?", type=int, default=2000, help="chat: most tokens to generate")
     ap.add_argument("--model", default=os.environ.get("LLMGEN_MODEL"))
@@ -266,10 +267,33 @@ def workload(args) -> int:
     return 0
 
 
+def info(args) -> int:
+    """The model's sizes and costs, and its tensors checked against what the model declares
+    (the reference prints its sizes at start-up, src/models/qwen3.zig:406-419)."""
+    from .config.base import ConfigError
+    from .info import describe
+    from .weights.loader import WeightError
+    try:
+        if args.random:
+            with open(args.random, "r", encoding="utf-8") as f:
+                text = describe(config=json.load(f), context=args.max_model_len or 4096)
+        elif args.model:
+            text = describe(model_dir=args.model, context=args.max_model_len or 4096)
+        else:
+            raise SystemExit("info needs --model <dir> (or LLMGEN_MODEL) or --random <config.json>")
+    except (ConfigError, WeightError, OSError, ValueError) as e:
+        print(f"info: {e}", file=sys.stderr)
+        return 1
+    print(text)
+    return 0
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     if args.cmd == "workload":
         return workload(args)
+    if args.cmd == "info":
+        return info(args)
     if args.max_model_len is None:
         args.max_model_len = 4096
     if args.sync_each:
