@@ -4,6 +4,7 @@
     python -m llmgen_b200 bench <workload.json>    [options]   run a workload, print a JSON summary
     python -m llmgen_b200 workload <out.json>      [options]   write a seeded random workload for `bench`
     python -m llmgen_b200 info --model <dir> | --random <config.json>   sizes, tensors checked, costs; no GPU needed
+    python -m llmgen_b200 convert <model.gguf> <out_dir>       the reference's model file as a model folder; no GPU needed
 
 Options keep the reference's names and meanings:
     --model <dir>  --temp <f>  --max-model-len <n>  --max-num-seqs <n>  --max-batched-tokens <n>
@@ -46,9 +47,9 @@ from .engine.scheduler import CHUNKED, PREFILL_FIRST
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="llmgen_b200", description="Single-GPU inference engine for sm_100a")
-    ap.add_argument("cmd", choices=["chat", "bench", "workload", "info"])
+    ap.add_argument("cmd", choices=["chat", "bench", "workload", "info", "convert"])
     ap.add_argument("arg0", nargs="?", help="chat: prompt token ids; bench: workload.json; workload: the file to write")
-    ap.add_argument("max_new", nargs="?", type=int, default=2000, help="chat: most tokens to generate")
+    ap.add_argument("max_new", nargs="?", default=None, help="chat: most tokens to generate (default 2000); convert: the folder to write")
     ap.add_argument("--model", default=os.environ.get("LLMGEN_MODEL"))
     ap.add_argument("--random", metavar="CONFIG_JSON", help="draw random weights for this config.json instead of --model")
     ap.add_argument("--seed", type=int, default=0x5EED)
@@ -288,8 +289,31 @@ def info(args) -> int:
     return 0
 
 
+def convert(args) -> int:
+    """A GGUF file of the reference (F32, F16 or BF16 tensors) as config.json + model.safetensors."""
+    from .config.base import ConfigError
+    from .info import describe
+    from .weights.gguf import GGUFError, convert_gguf
+    from .weights.loader import WeightError
+    if not args.arg0 or not args.max_new:
+        raise SystemExit("convert needs the GGUF file and the folder to write")
+    try:
+        out = convert_gguf(args.arg0, args.max_new)
+        print(describe(model_dir=out, context=args.max_model_len or 4096))
+    except (GGUFError, ConfigError, WeightError, OSError) as e:
+        print(f"convert: {e}", file=sys.stderr)
+        return 1
+    return 0
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    if args.cmd == "convert":
+        return convert(args)
+    try:
+        args.max_new = 2000 if args.max_new is None else int(args.max_new)
+    except ValueError:
+        raise SystemExit(f"the number of tokens to generate must be an integer, not {args.max_new!r}")
     if args.cmd == "workload":
         return workload(args)
     if args.cmd == "info":
