@@ -21,11 +21,13 @@ whole head, SiLU gate, pre-norm residual layout.
 from __future__ import annotations
 
 import math
+from typing import Dict, List
 
 from ..config.qwen3 import SLIDING_ATTENTION, Qwen3Config
 from ..parts.spec import (AttentionSpec, GatedMLPSpec, ModelSpec, PreNormBlockSpec, RMSNormSpec,
                           RopeSpec, default_run_order)
 from ..registry import register_architecture
+from ..weights.gguf import GGUFError, register_gguf_source
 
 
 def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
@@ -62,3 +64,85 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
 
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config, build_qwen3_spec, aliases=("qwen3",))
+
+
+# ------------------------------------------------------------------ the reference's model files
+# the reference's names (left, `.weight` appended) and this engine's (right)
+_GLOBAL_NAMES = {"token_embd": "model.embed_tokens", "output_norm": "model.norm"}
+_LAYER_NAMES = {
+    "attn_norm": "input_layernorm", "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
+    "attn_output": "self_attn.o_proj", "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",
+    "ffn_norm": "post_attention_layernorm", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj",
+}
+GGUF_ARCHITECTURE = "qwen3"      # `general.architecture` of the reference's files
+
+
+def gguf_config(g) -> dict:
+    """config.json of the Qwen3 model a GGUF file describes, from the metadata keys the reference reads
+    (src/models/qwen3.zig:100-140); one error lists every key that is missing."""
+    arch = GGUF_ARCHITECTURE
+    meta, missing = g.metadata, []
+
+    def need(*names):
+        for name in names:
+            if f"{arch}.{name}" in meta:
+                return meta[f"{arch}.{name}"]
+        missing.append(" or ".join(f"{arch}.{n}" for n in names))
+        return 0
+
+    vocab = meta.get(f"{arch}.vocab_size") or len(meta.get("tokenizer.ggml.tokens") or ())
+    if not vocab and "token_embd.weight" in g.tensors:
+        vocab = g.tensors["token_embd.weight"].shape[0]
+    if not vocab:
+        missing.append(f"{arch}.vocab_size (or tokenizer.ggml.tokens)")
+    heads = need("attention.head_count")
+    hidden = need("embedding_length")
+    cfg = {
+        "architectures": [Qwen3Config.architecture], "model_type": arch,
+        "vocab_size": int(vocab), "hidden_size": int(hidden), "intermediate_size": int(need("feed_forward_length")),
+        "num_hidden_layers": int(need("block_count")), "num_attention_heads": int(heads),
+        "num_key_value_heads": int(meta.get(f"{arch}.attention.head_count_kv", heads)),
+        "rms_norm_eps": float(meta.get(f"{arch}.attention.layer_norm_rms_epsilon", 1e-6)),
+        "rope_theta": float(need("rope.freq_base", "rope.rope_freq_base")),
+        "max_position_embeddings": int(need("context_length")),
+        "tie_word_embeddings": "output.weight" not in g.tensors, "hidden_act": "silu",
+    }
+    if f"{arch}.attention.key_length" in meta:
+        cfg["head_dim"] = int(meta[f"{arch}.attention.key_length"])
+        value_length = meta.get(f"{arch}.attention.value_length", cfg["head_dim"])
+        if int(value_length) != cfg["head_dim"]:
+            raise GGUFError(f"{g.path}: key_length {cfg['head_dim']} and value_length {value_length} differ")
+    eos = meta.get("tokenizer.ggml.eos_token_id")
+    if isinstance(eos, int) and eos >= 0:
+        cfg["eos_token_id"] = eos
+    if missing:
+        raise GGUFError(f"{g.path}: metadata keys are missing: " + "; ".join(missing))
+    return cfg
+
+
+def gguf_tensor_names(g, cfg: dict) -> Dict[str, str]:
+    """This engine's tensor name for every tensor of the file (the reference's table, src/models/qwen3.zig:34-55);
+    unknown names are an error."""
+    num_layers = cfg["num_hidden_layers"]
+    out: Dict[str, str] = {}
+    unknown: List[str] = []
+    for name in g.tensors:
+        stem, dot, last = name.rpartition(".")
+        parts = stem.split(".")
+        if last != "weight" or not dot:
+            unknown.append(name)
+        elif stem == "output":
+            out[name] = "lm_head.weight"
+        elif stem in _GLOBAL_NAMES:
+            out[name] = _GLOBAL_NAMES[stem] + ".weight"
+        elif len(parts) == 3 and parts[0] == "blk" and parts[1].isdigit() and parts[2] in _LAYER_NAMES \
+                and int(parts[1]) < num_layers:
+            out[name] = f"model.layers.{int(parts[1])}.{_LAYER_NAMES[parts[2]]}.weight"
+        else:
+            unknown.append(name)
+    if unknown:
+        raise GGUFError(f"{g.path}: tensors with no place in the model ({len(unknown)}): " + ", ".join(sorted(unknown)[:20]))
+    return out
+
+
+register_gguf_source(GGUF_ARCHITECTURE, gguf_config, gguf_tensor_names)

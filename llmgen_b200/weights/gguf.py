@@ -4,7 +4,9 @@ The reference loads one GGUF file (src/gguf.zig:361-480): a header (magic "GGUF"
 tensor count, metadata count), metadata as typed key/value pairs, tensor infos (name,
 dimensions innermost first, type, offset) and, from the next multiple of `general.alignment`
 (default 32), the tensor data.  This engine loads a folder with config.json and
-model.safetensors.  `convert_gguf` reads the former and writes the latter:
+model.safetensors.  `convert_gguf` reads the former and writes the latter; what depends on the
+architecture (metadata keys, tensor names) is registered by the architecture's module
+(`register_gguf_source`; for Qwen3 in models/qwen3.py):
 
   * sizes from the metadata keys the reference reads (src/models/qwen3.zig:100-140),
     `<arch>.block_count`, `.embedding_length`, `.attention.head_count[_kv]`,
@@ -29,7 +31,7 @@ from __future__ import annotations
 import mmap
 import struct
 from dataclasses import dataclass
-from typing import Any, Dict, List, Tuple
+from typing import Any, Callable, Dict, Tuple
 
 import torch
 
@@ -138,81 +140,29 @@ class GGUFFile:
         return torch.frombuffer(self._map, dtype=dtype, count=n, offset=begin).reshape(t.shape).clone()
 
 
-# the reference's names (left, `.weight` appended) and this engine's (right)
-_GLOBAL_NAMES = {"token_embd": "model.embed_tokens", "output_norm": "model.norm"}
-_LAYER_NAMES = {
-    "attn_norm": "input_layernorm", "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
-    "attn_output": "self_attn.o_proj", "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",
-    "ffn_norm": "post_attention_layernorm", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj",
-}
-ARCHITECTURES = {"qwen3": "Qwen3ForCausalLM"}
+@dataclass(frozen=True)
+class GGUFSource:
+    """How one architecture's GGUF files become a model folder: `config(file) -> dict` (config.json keys) and
+    `names(file, config) -> {name in the file: this engine's tensor name}`."""
+    config: Callable[["GGUFFile"], dict]
+    names: Callable[["GGUFFile", dict], Dict[str, str]]
 
 
-def config_from_metadata(g: GGUFFile) -> dict:
-    """config.json of the model a GGUF file describes; one error lists every key that is missing."""
+_SOURCES: Dict[str, GGUFSource] = {}
+
+
+def register_gguf_source(gguf_architecture: str, config: Callable, names: Callable) -> None:
+    """`gguf_architecture` is the file's `general.architecture` (src/gguf.zig:224-226)."""
+    _SOURCES[gguf_architecture] = GGUFSource(config, names)
+
+
+def gguf_source(g: "GGUFFile") -> GGUFSource:
+    from ..registry import _ensure_builtin
+    _ensure_builtin()                          # the built-in architectures register their sources when they are loaded
     arch = g.architecture()
-    if arch not in ARCHITECTURES:
-        raise GGUFError(f"{g.path}: general.architecture is {arch!r}; known: {', '.join(sorted(ARCHITECTURES))}")
-    meta, missing = g.metadata, []
-
-    def need(*names):
-        for name in names:
-            if f"{arch}.{name}" in meta:
-                return meta[f"{arch}.{name}"]
-        missing.append(" or ".join(f"{arch}.{n}" for n in names))
-        return 0
-
-    vocab = meta.get(f"{arch}.vocab_size") or len(meta.get("tokenizer.ggml.tokens") or ())
-    if not vocab and "token_embd.weight" in g.tensors:
-        vocab = g.tensors["token_embd.weight"].shape[0]
-    if not vocab:
-        missing.append(f"{arch}.vocab_size (or tokenizer.ggml.tokens)")
-    heads = need("attention.head_count")
-    hidden = need("embedding_length")
-    cfg = {
-        "architectures": [ARCHITECTURES[arch]], "model_type": arch,
-        "vocab_size": int(vocab), "hidden_size": int(hidden), "intermediate_size": int(need("feed_forward_length")),
-        "num_hidden_layers": int(need("block_count")), "num_attention_heads": int(heads),
-        "num_key_value_heads": int(meta.get(f"{arch}.attention.head_count_kv", heads)),
-        "rms_norm_eps": float(meta.get(f"{arch}.attention.layer_norm_rms_epsilon", 1e-6)),
-        "rope_theta": float(need("rope.freq_base", "rope.rope_freq_base")),
-        "max_position_embeddings": int(need("context_length")),
-        "tie_word_embeddings": "output.weight" not in g.tensors, "hidden_act": "silu",
-    }
-    if f"{arch}.attention.key_length" in meta:
-        cfg["head_dim"] = int(meta[f"{arch}.attention.key_length"])
-        value_length = meta.get(f"{arch}.attention.value_length", cfg["head_dim"])
-        if int(value_length) != cfg["head_dim"]:
-            raise GGUFError(f"{g.path}: key_length {cfg['head_dim']} and value_length {value_length} differ")
-    eos = meta.get("tokenizer.ggml.eos_token_id")
-    if isinstance(eos, int) and eos >= 0:
-        cfg["eos_token_id"] = eos
-    if missing:
-        raise GGUFError(f"{g.path}: metadata keys are missing: " + "; ".join(missing))
-    return cfg
-
-
-def tensor_names(g: GGUFFile, num_layers: int) -> Dict[str, str]:
-    """This engine's tensor name for every tensor of the file; unknown names are an error."""
-    out: Dict[str, str] = {}
-    unknown: List[str] = []
-    for name in g.tensors:
-        stem, dot, last = name.rpartition(".")
-        parts = stem.split(".")
-        if last != "weight" or not dot:
-            unknown.append(name)
-        elif stem == "output":
-            out[name] = "lm_head.weight"
-        elif stem in _GLOBAL_NAMES:
-            out[name] = _GLOBAL_NAMES[stem] + ".weight"
-        elif len(parts) == 3 and parts[0] == "blk" and parts[1].isdigit() and parts[2] in _LAYER_NAMES \
-                and int(parts[1]) < num_layers:
-            out[name] = f"model.layers.{int(parts[1])}.{_LAYER_NAMES[parts[2]]}.weight"
-        else:
-            unknown.append(name)
-    if unknown:
-        raise GGUFError(f"{g.path}: tensors with no place in the model ({len(unknown)}): " + ", ".join(sorted(unknown)[:20]))
-    return out
+    if arch not in _SOURCES:
+        raise GGUFError(f"{g.path}: general.architecture is {arch!r}; known: {', '.join(sorted(_SOURCES)) or 'none'}")
+    return _SOURCES[arch]
 
 
 def convert_gguf(path: str, out_dir: str) -> str:
@@ -223,8 +173,9 @@ def convert_gguf(path: str, out_dir: str) -> str:
     from .loader import open_weights
     from .random_init import write_model_folder
     g = GGUFFile(path)
-    cfg = config_from_metadata(g)
-    names = tensor_names(g, cfg["num_hidden_layers"])
+    source = gguf_source(g)
+    cfg = source.config(g)
+    names = source.names(g, cfg)
     tensors = {ours: g.tensor(theirs) for theirs, ours in names.items()}
     arch, typed = config_from_dict(cfg, where=path)
     write_model_folder(out_dir, typed.to_dict() if hasattr(typed, "to_dict") else cfg, tensors,
