@@ -6,12 +6,12 @@
 // of the visible keys [lo, ctx), where lo = max(0, ctx - window) for a windowed layer: the visible
 // range is cut evenly into `parts` pieces, so the launch shape does not depend on the context
 // lengths (a CUDA graph replays it).
-//   stream   every warp takes 8 of each 32 keys and brings their K and V rows into shared memory
-//            through a cp.async ring of its own (4 stages; keys past the part's end are zero-filled),
-//            so the loop has no block-wide barrier.  It keeps a running (m, l, acc): scores with 4
-//            lanes per key (float32 dot products against q, which sits in shared memory pre-multiplied
-//            by scale), maximum and sum over the 8 keys by shuffles, then P V with every lane owning
-//            head_dim / 32 output values for all GC heads.  The four warps' states are merged at the end.
+//   stream   every warp takes 16 of each 64 keys and brings their K and V rows into shared memory
+//            through a cp.async ring of its own (3 stages; keys past the part's end are zero-filled),
+//            so the loop has no block-wide barrier.  Both products of a step run on the tensor cores
+//            (`mma.sync.m16n8k16`: the chunk's heads are the rows of Q, which sits in registers
+//            pre-multiplied by scale; K through `ldmatrix`, V through `ldmatrix.trans`), with a running
+//            (m, l, acc) per head in float32.  The four warps' states are merged at the end.
 //   merge    with 2 to 8 parts the launch makes the parts of a (sequence, kv head) one thread-block
 //            cluster: the blocks leave their sums in shared memory and, after the cluster's barrier,
 //            each merges a share of the outputs reading the others' shared memory.  With more parts
@@ -70,6 +70,7 @@ struct DecodeParams {
     const float* q_gain;
     const float* k_gain;
     float eps, q_off, k_off;
+    int* error_flag;             // raised (2) when a sequence is longer than the bound the launch was sized for
 };
 
 // One head's row of the packed projection: lane holds the values lane, lane + 32, ... of the head
@@ -150,8 +151,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int HD, int GC, int KPW>
+template <int HD, int GC>
 struct DecodeSmem {
+    static constexpr int KPW = 16;                            // keys a warp takes per step
     static constexpr int STAGES = 3;
     static constexpr int ROW = HD * 2;                        // bytes of one key's K or V row
     static constexpr int STAGE = 2 * KPW * ROW;               // one warp's stage: KPW rows of K, then of V
@@ -162,7 +164,7 @@ struct DecodeSmem {
     static size_t bytes(int page_cap) { return (size_t)PAGES_OFF + (size_t)page_cap * 4; }
 };
 
-// Tensor-core helpers of the MMA variant (warp-level `mma.sync`, enough for a kernel bound by memory).
+// Tensor-core helpers (warp-level `mma.sync`, enough for a kernel bound by memory).
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem_addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr) : "memory");
@@ -182,17 +184,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// MMA = false: float32 arithmetic on the CUDA cores, 8 keys a warp per step.  MMA = true: the two
-// products of a step of 16 keys run on the tensor cores (`mma.sync.m16n8k16`, the chunk's heads are
-// the rows of a 16-row tile), which cuts the instructions per key about eightfold; with many heads per
-// kv head the CUDA-core variant is bound by its arithmetic, not by memory.
-template <int HD, int GC, bool MMA>
+// The two products of a step of 16 keys run on the tensor cores (`mma.sync.m16n8k16`, the chunk's heads
+// are the rows of a 16-row tile): float32 arithmetic on the CUDA cores took about eight times the
+// instructions per key and, with many heads per kv head, was bound by them and not by memory.
+template <int HD, int GC>
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeParams p) {
-    constexpr int KPW = MMA ? 16 : 8;   // keys a warp takes per step
-    constexpr int STAGES = 3;           // depth of each warp's cp.async ring
-    using L = DecodeSmem<HD, GC, KPW>;
-    constexpr int DPL = HD / 32;        // output values per lane
-    constexpr int CH = HD / 32;         // 16-byte chunks of a K row per lane (4 lanes per key)
+    using L = DecodeSmem<HD, GC>;
+    constexpr int KPW = L::KPW;         // keys a warp takes per step
+    constexpr int STAGES = L::STAGES;   // depth of each warp's cp.async ring
+    constexpr int DPL = HD / 32;        // values of a head per lane when a warp holds one row
     constexpr int CPR = HD / 8;         // 16-byte chunks per row
     constexpr int CPL = KPW * CPR / 32; // chunks of K (and of V) a lane copies per stage
     extern __shared__ __align__(16) unsigned char smem[];
@@ -233,6 +233,20 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     const int n_pages = n_keys > 0 ? ((k_end - 1) >> lps) - page_base + 1 : 0;
     const int* bt = p.block_tables + (size_t)s * p.max_blocks;
 
+    if (n_pages > p.page_cap) {
+        // ctx_len[s] exceeds the `max_ctx` this launch was sized for: the part's page ids would not fit the
+        // shared array.  Nothing is read or written for this block; the host sees the flag.
+        if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+        if (p.cluster_merge) {           // the other blocks of the cluster wait at both barriers
+            cluster_sync_all();
+            cluster_sync_all();
+        } else if (parts > 1 && tid == 0) {
+            // still draw the ticket, so that the counter is back at zero after the launch
+            int* counter = p.counters + (size_t)s * gridDim.y + blockIdx.y;
+            if (atomicAdd(counter, 1) == parts - 1) *counter = 0;
+        }
+        return;
+    }
     // The part's page ids first: the copies of keys need them.
     for (int i = tid; i < n_pages; i += THREADS) pages_s[i] = bt[page_base + i];
     __syncthreads();
@@ -248,11 +262,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
     // offset from the page's row: a handful of instructions per copy instead of a dozen.
     const bool one_page = ((k_beg & (KPW - 1)) == 0) && (((ps_mask + 1) & (KPW - 1)) == 0);
     const size_t lane_off = (size_t)(lane / CPR) * HD + (size_t)(lane % CPR) * 8;     // this lane's first copy inside the 8 rows
-    // where a 16-byte chunk of a row goes: the CUDA-core variant swizzles K by the key's parity (see
-    // above) and leaves V plain; the MMA variant XORs the chunk with the key's low 3 bits in both,
-    // which is what `ldmatrix` needs to read 8 rows without bank conflicts
-    auto k_chunk = [](int key, int l) { return MMA ? (l ^ (key & 7)) : (l ^ ((key & 1) << 2)); };
-    auto v_chunk = [](int key, int l) { return MMA ? (l ^ (key & 7)) : l; };
+    // where a 16-byte chunk of a row goes: XORed with the key's low 3 bits, which is what `ldmatrix`
+    // needs to read 8 rows without bank conflicts
+    auto k_chunk = [](int key, int l) { return l ^ (key & 7); };
+    auto v_chunk = [](int key, int l) { return l ^ (key & 7); };
     constexpr int KSTEP = 32 / CPR;       // keys between two copies of one lane
     auto issue = [&](int step, int stage) {
         unsigned char* dst = ring + stage * L::STAGE;
@@ -344,8 +357,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
 
     if (!early) first_copies();
 
-    if constexpr (MMA) {
-        // ---- tensor-core variant.  Lane (g = lane / 4, t = lane % 4) of a warp holds, of every
+    {
+        // Lane (g = lane / 4, t = lane % 4) of a warp holds, of every
         // 16 x 8 accumulator tile, row g columns 2t, 2t + 1 (and row g + 8, which no head uses: a
         // chunk has at most 8 heads).  Q's rows are the chunk's heads.
         const int g = lane >> 2, t4 = lane & 3;
@@ -448,121 +461,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
             if (t4 == 0) {
                 row[HD] = m_run;
                 row[HD + 1] = l_run;
-            }
-        }
-    } else {
-        const int grp = lane >> 2, j = lane & 3;
-        // the 32 (16) values of each q head that this lane multiplies: in registers for up to 2 heads
-        constexpr bool Q_IN_REGS = GC <= 2;
-        float qr[Q_IN_REGS ? GC : 1][Q_IN_REGS ? CH * 8 : 1];
-        if constexpr (Q_IN_REGS) {
-    #pragma unroll
-            for (int g = 0; g < GC; ++g)
-    #pragma unroll
-                for (int c = 0; c < CH; ++c)
-    #pragma unroll
-                    for (int e = 0; e < 8; ++e) qr[g][c * 8 + e] = q_s[g * HD + (c * 4 + j) * 8 + e];
-        }
-        float m[GC], l[GC], acc[GC][DPL];
-    #pragma unroll
-        for (int g = 0; g < GC; ++g) {
-            m[g] = -INFINITY;
-            l[g] = 0.f;
-    #pragma unroll
-            for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
-        }
-        for (int step = 0; step < n_steps; ++step) {
-            const int stage = step % STAGES;
-            // the ring slot freed by the previous step takes the load of step + STAGES - 1
-            if (step + STAGES - 1 < n_steps) issue(step + STAGES - 1, (step + STAGES - 1) % STAGES); else cp_async_commit();
-            cp_async_wait<STAGES - 1>();
-            __syncwarp();
-            const unsigned char* Ks = ring + stage * L::STAGE;
-            const unsigned char* Vs = Ks + KPW * L::ROW;
-            const int key = grp;
-            const bool valid = step * (WARPS * KPW) + warp * KPW + key < n_keys;
-            float dot[GC];
-    #pragma unroll
-            for (int g = 0; g < GC; ++g) dot[g] = 0.f;
-    #pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const int lc = c * 4 + j;
-                Vec16<bf16> v;
-                v.raw = *reinterpret_cast<const uint4*>(Ks + key * L::ROW + ((lc ^ ((key & 1) << 2)) << 4));
-                float kf[8];
-                v.unpack(kf);
-    #pragma unroll
-                for (int g = 0; g < GC; ++g) {
-                    if constexpr (Q_IN_REGS) {
-    #pragma unroll
-                        for (int e = 0; e < 8; ++e) dot[g] = fmaf(qr[g][c * 8 + e], kf[e], dot[g]);
-                    } else {
-                        const float4* qa = reinterpret_cast<const float4*>(q_s + g * HD + lc * 8);
-                        const float4 a = qa[0], b = qa[1];
-                        dot[g] = fmaf(a.x, kf[0], dot[g]); dot[g] = fmaf(a.y, kf[1], dot[g]);
-                        dot[g] = fmaf(a.z, kf[2], dot[g]); dot[g] = fmaf(a.w, kf[3], dot[g]);
-                        dot[g] = fmaf(b.x, kf[4], dot[g]); dot[g] = fmaf(b.y, kf[5], dot[g]);
-                        dot[g] = fmaf(b.z, kf[6], dot[g]); dot[g] = fmaf(b.w, kf[7], dot[g]);
-                    }
-                }
-            }
-            float pr[GC];
-    #pragma unroll
-            for (int g = 0; g < GC; ++g) {
-                float d = dot[g];
-                d += __shfl_xor_sync(0xffffffffu, d, 1);
-                d += __shfl_xor_sync(0xffffffffu, d, 2);
-                const float sv = valid ? d : -INFINITY;
-                float mx = sv;
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                const float m_new = fmaxf(m[g], mx);
-                const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
-                pr[g] = valid ? __expf(sv - m_new) : 0.f;
-                float sum = pr[g];
-                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-                l[g] = l[g] * alpha + sum;
-                m[g] = m_new;
-    #pragma unroll
-                for (int dd = 0; dd < DPL; ++dd) acc[g][dd] *= alpha;
-            }
-    #pragma unroll
-            for (int kk = 0; kk < KPW; ++kk) {
-                const unsigned char* vr = Vs + kk * L::ROW + lane * DPL * 2;
-                float vf[DPL];
-                if constexpr (DPL == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(vr);
-                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-                    vf[0] = a.x; vf[1] = a.y; vf[2] = b.x; vf[3] = b.y;
-                } else {
-                    const uint32_t raw = *reinterpret_cast<const uint32_t*>(vr);
-                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
-                    vf[0] = a.x; vf[1] = a.y;
-                }
-    #pragma unroll
-                for (int g = 0; g < GC; ++g) {
-                    const float pk = __shfl_sync(0xffffffffu, pr[g], kk * 4);
-    #pragma unroll
-                    for (int dd = 0; dd < DPL; ++dd) acc[g][dd] = fmaf(pk, vf[dd], acc[g][dd]);
-                }
-            }
-            __syncwarp();    // every lane has read the stage before it is refilled
-        }
-        cp_async_wait<0>();
-
-        // Merge the warps' states: M = max m_w, o = sum_w e^{m_w - M} acc_w, L = sum_w e^{m_w - M} l_w.
-    #pragma unroll
-        for (int g = 0; g < GC; ++g) {
-            float* row = mrg + (warp * GC + g) * (HD + 2);
-    #pragma unroll
-            for (int dd = 0; dd < DPL; ++dd) row[lane * DPL + dd] = acc[g][dd];
-            if (lane == 0) {
-                row[HD] = m[g];
-                row[HD + 1] = l[g];
             }
         }
     }
@@ -697,10 +595,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeP
 
 int g_cluster_merge = 1;      // 0: always merge through global memory and a ticket (for measurements)
 
-template <int HD, int GC, bool MMA>
+template <int HD, int GC>
 int launch(const DecodeParams& p, dim3 grid, cudaStream_t s) {
-    const size_t smem = DecodeSmem<HD, GC, MMA ? 16 : 8>::bytes(p.page_cap);
-    auto kernel = attention_decode_kernel<HD, GC, MMA>;
+    const size_t smem = DecodeSmem<HD, GC>::bytes(p.page_cap);
+    auto kernel = attention_decode_kernel<HD, GC>;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -714,24 +612,14 @@ int launch(const DecodeParams& p, dim3 grid, cudaStream_t s) {
     return LLMK_OK;
 }
 
-template <int HD, bool MMA>
+template <int HD>
 int dispatch_group(int gc, const DecodeParams& p, dim3 grid, cudaStream_t s) {
     switch (gc) {
-        case 1: return launch<HD, 1, MMA>(p, grid, s);
-        case 2: return launch<HD, 2, MMA>(p, grid, s);
-        case 4: return launch<HD, 4, MMA>(p, grid, s);
-        default: return launch<HD, 8, MMA>(p, grid, s);
+        case 1: return launch<HD, 1>(p, grid, s);
+        case 2: return launch<HD, 2>(p, grid, s);
+        case 4: return launch<HD, 4>(p, grid, s);
+        default: return launch<HD, 8>(p, grid, s);
     }
-}
-
-// Which variant runs: the tensor-core one unless LLMGEN_DECODE_MATH=simt asks for the other.
-bool use_mma() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("LLMGEN_DECODE_MATH");
-        v = (e && e[0] == 's') ? 0 : 1;
-    }
-    return v != 0;
 }
 
 int chunk_heads(int G) { return G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8; }
@@ -771,8 +659,11 @@ LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void*
                                       long long packed_stride, int splits, long long split_stride, int nk, int rot,
                                       const int* positions, const int* slots, const float* cos_tab,
                                       const float* sin_tab, const float* q_gain, const float* k_gain, float eps,
-                                      float q_off, float k_off, void* stream) {
+                                      float q_off, float k_off, int pairing, int head_norm, int* error_flag, void* stream) {
     if (n_seqs <= 0) return LLMK_OK;
+    if (packed && pairing != LLMK_PAIR_HALF_SPLIT)
+        LLMK_FAIL("attention_decode: rotary pairing %d is not built (0: half-split, pairs (i, i + rot / 2))", pairing);
+    if (packed && head_norm != LLMK_HEAD_NORM_RMS) LLMK_FAIL("attention_decode: per-head norm kind %d is not built (0: RMSNorm)", head_norm);
     if (!llmk_attention_decode_usable(nq, nkv, hd, page_size))
         LLMK_FAIL("attention_decode: not taken (heads %d/%d, head_dim %d must be 64 or 128, page size %d must be a power of two)", nq, nkv, hd, page_size);
     if (parts < 1 || parts > 128 || (parts > 1 && (!scratch || !counters)))
@@ -793,6 +684,7 @@ LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void*
     p.packed = packed; p.packed_stride = packed_stride; p.splits = splits; p.split_stride = split_stride;
     p.nk = nk; p.rot = rot; p.positions = positions; p.slots = slots; p.cos_tab = cos_tab; p.sin_tab = sin_tab;
     p.q_gain = q_gain; p.k_gain = k_gain; p.eps = eps; p.q_off = q_off; p.k_off = k_off;
+    p.error_flag = error_flag;
     const int G = nq / nkv;
     const int gc = chunk_heads(G);
     p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;
@@ -815,8 +707,7 @@ LLMK_EXPORT int llmk_attention_decode(void* out, long long o_stride, const void*
         LLMK_FAIL("attention_decode: %d keys per part in pages of %d need too much shared memory; use more parts", part_cap, page_size);
     dim3 grid(parts, nkv * p.chunks, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
-    if (use_mma()) return hd == 128 ? dispatch_group<128, true>(gc, p, grid, s) : dispatch_group<64, true>(gc, p, grid, s);
-    return hd == 128 ? dispatch_group<128, false>(gc, p, grid, s) : dispatch_group<64, false>(gc, p, grid, s);
+    return hd == 128 ? dispatch_group<128>(gc, p, grid, s) : dispatch_group<64>(gc, p, grid, s);
 }
 
 LLMK_EXPORT void llmk_attention_decode_set_cluster_merge(int on) { g_cluster_merge = on; }

@@ -59,20 +59,8 @@ struct Params {
     int max_blocks, nq, nkv, page_size, window, gc, bq, chunks;
     float scale_log2;
     unsigned v_lbo, v_sbo;
-#ifdef LLMK_ATTN_TIMELINE
-    long long* timeline;     // profiling builds only: clock64() stamps of block 0's first softmax warp
-#endif
 };
 
-#ifdef LLMK_ATTN_TIMELINE
-#define TL_STAMP(slot)                                                                                    \
-    do {                                                                                                  \
-        if (p.timeline && blockIdx.y == 0 && blockIdx.x == 0 && warp == 2 && lane == 0 && j < 16) \
-            p.timeline[j * 8 + (slot)] = clock64();                                                       \
-    } while (0)
-#else
-#define TL_STAMP(slot) do {} while (0)
-#endif
 
 template <int HD>
 struct Smem {
@@ -298,10 +286,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
             const int k0 = kt0 + j * BN + half * SC;      // first key of this thread's columns
-            TL_STAMP(0);
             if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag));
             tc::tc_fence_after_sync();
-            TL_STAMP(1);
             const uint32_t s_addr = tmem_base + lane_addr + (st ? S_COL1 : S_COL0) + half * SC;
             const bool need_mask = (k0 + SC - 1 > qpos) || (k0 <= lo);
             uint8_t* p_row = p_row0 + st * L::P_BYTES;       // P is double-buffered: P V of the tile before may still read the other
@@ -326,10 +312,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
             }
             const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            TL_STAMP(2);
             xchg[(st * 2 + half) * BM + r] = mx_own;
             asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight softmax warps
-            TL_STAMP(3);
             const float mx = fmaxf(mx_own, xchg[(st * 2 + (half ^ 1)) * BM + r]);
             // The row's reference maximum follows the true one lazily: only when that grew by more than 8 in
             // the exponent's scale (P then stays below 2^8, and the result is the same up to rounding, as
@@ -355,7 +339,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tc::tmem_st_wait();
                 }
             }
-            TL_STAMP(4);
             // pass 2: P into shared memory, row sum
             if (ok) {
                 const float mb = (m == -INFINITY) ? 0.f : m * sl2;
@@ -388,9 +371,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tc::fence_proxy_async();
                 tc::tc_fence_before_sync();
                 tc::mbar_arrive(tc::smem_u32(p_full));
-                TL_STAMP(5);
             }
-            TL_STAMP(7);
         }
         if (ok && n_tiles > 0) {
             ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&o_full[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1, abort_flag));
@@ -475,9 +456,6 @@ LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, 
                                   const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd,
                                   int page_size, int window, float scale, int* error_flag, unsigned v_lbo,
                                   unsigned v_sbo, void* stream
-#ifdef LLMK_ATTN_TIMELINE
-                                  , long long* timeline
-#endif
 ) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     const int bq = llmk_attention_tc_tile_queries(nq, nkv, hd, page_size);
@@ -509,9 +487,6 @@ LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, 
     p.scale_log2 = scale * 1.4426950408889634f;
     p.v_lbo = v_lbo ? v_lbo : (unsigned)(BN * 128);
     p.v_sbo = v_sbo ? v_sbo : 1024u;
-#ifdef LLMK_ATTN_TIMELINE
-    p.timeline = timeline;
-#endif
     CUtensorMap mq, mk, mv;
     if (!tc_host::make_map_bf16_3d(&mq, q, hd, nq, n_tokens, hd, q_stride, p.gc, p.bq))
         LLMK_FAIL("attention_tc: cuTensorMapEncodeTiled failed for q");

@@ -423,7 +423,7 @@ static bool launch_vec(const void* qkv, long long row_stride, void* q_out, long 
     do {                                                                                                                    \
         const int chunks = (nq + 2 * nk + U * rpw - 1) / (U * rpw);                                                         \
         long long tblocks = ((long long)n_tokens * chunks + 7) / 8;                                                         \
-        if (tblocks > 148 * 8) tblocks = 148 * 8;                                                                           \
+        if (tblocks > device_sm_count() * 8) tblocks = device_sm_count() * 8;                                                                           \
         *err = llmk_launch(attn_prep_token_kernel<T, L, U>, dim3((unsigned)tblocks), dim3(256), 0, s, true, (const T*)qkv,  \
                            row_stride, (T*)q_out, q_stride, (T*)kcache, (T*)vcache, positions, slots, cos_tab, sin_tab,     \
                            q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, page_size, eps, q_off, k_off);                  \
@@ -437,7 +437,7 @@ static bool launch_vec(const void* qkv, long long row_stride, void* q_out, long 
         return true;
     }
     long long blocks = (rows + 8 * rpw - 1) / (8 * rpw);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
 #define LAUNCH_VEC(L)                                                                                                   \
     *err = llmk_launch(attn_prep_vec_kernel<T, L>, dim3((unsigned)blocks), dim3(256), 0, s, true, (const T*)qkv, row_stride, \
                        (T*)q_out, q_stride, (T*)kcache, (T*)vcache, positions, slots, cos_tab, sin_tab, q_gain, k_gain,  \
@@ -455,8 +455,12 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
                                long long q_stride, void* kcache, void* vcache, const int* positions,
                                const int* slots, const float* cos_tab, const float* sin_tab, const float* q_gain,
                                const float* k_gain, int n_tokens, int nq, int nk, int nkv_cache, int hd, int rot,
-                               int page_size, float eps, float q_off, float k_off, int dtype, void* stream) {
+                               int page_size, float eps, float q_off, float k_off, int pairing, int head_norm, int dtype,
+                               void* stream) {
     if (n_tokens <= 0) return LLMK_OK;
+    if (pairing != LLMK_PAIR_HALF_SPLIT)
+        LLMK_FAIL("attn_prep: rotary pairing %d is not built (0: half-split, pairs (i, i + rot / 2))", pairing);
+    if (head_norm != LLMK_HEAD_NORM_RMS) LLMK_FAIL("attn_prep: per-head norm kind %d is not built (0: RMSNorm)", head_norm);
     if (hd <= 0 || hd % 2 != 0 || hd > 512) LLMK_FAIL("attn_prep: head_dim %d must be even and at most 512", hd);
     if (rot < 0 || rot > hd || rot % 2 != 0) LLMK_FAIL("attn_prep: rotary width %d must be even and at most head_dim %d", rot, hd);
     if (rot / 2 > 32 * MAX_PAIRS || hd - rot > 32 * MAX_TAIL) LLMK_FAIL("attn_prep: head_dim %d / rotary width %d too large", hd, rot);

@@ -21,6 +21,10 @@
 
 enum { LLMK_OK = 0, LLMK_BAD_ARG = 1, LLMK_CUDA_ERROR = 2 };
 enum { LLMK_F32 = 0, LLMK_BF16 = 1 };
+// How a rotary encoding pairs the values of a head, and which norm runs over a head of q and k before it:
+// kernels take the codes and refuse the ones they do not implement.
+enum { LLMK_PAIR_HALF_SPLIT = 0, LLMK_PAIR_INTERLEAVED = 1 };
+enum { LLMK_HEAD_NORM_RMS = 0 };
 
 typedef __nv_bfloat16 bf16;
 
@@ -81,6 +85,26 @@ template <> struct Vec16<bf16> {
 
 __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool host_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Streaming multiprocessors of the current device, asked once per device; launch plans (how many
+// slices, how many blocks) are made from it.  Without a device (a build check on a CPU box): a B200's 148.
+inline int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return 148;
+    }
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 148;
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

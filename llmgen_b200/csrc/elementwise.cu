@@ -393,7 +393,7 @@ static int launch_silu_mul(void* out, const void* in, int n, int F, int ld_in, i
     const size_t work = vec ? (size_t)n * (F / N) : (size_t)n * F;
     const int threads = 256;
     size_t blocks = (work + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     if (blocks == 0) return LLMK_OK;
     if (vec)
         silu_mul_vec_kernel<T><<<(int)blocks, threads, 0, s>>>((T*)out, (const T*)in, n, F, ld_in, group);
@@ -411,7 +411,7 @@ LLMK_EXPORT int llmk_silu_mul(void* out, const void* in, int n_rows, int F, int 
     if (splits > 0) {
         const size_t work = (size_t)n_rows * F;
         size_t blocks = (work + 255) / 256;
-        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
         cudaError_t e;
         if (dtype == LLMK_F32)
             e = llmk_launch(silu_mul_partials_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out,
@@ -447,7 +447,7 @@ LLMK_EXPORT int llmk_widen(float* out, const void* in, long long total, int dtyp
     if (total <= 0) return LLMK_OK;
     cudaStream_t s = (cudaStream_t)stream;
     long long blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     if (dtype == LLMK_F32)
         widen_kernel<float><<<(int)blocks, 256, 0, s>>>(out, (const float*)in, (size_t)total);
     else if (dtype == LLMK_BF16)

@@ -5,7 +5,7 @@
 // may not call cudaMalloc (or any allocating routine) at the point where they sample: a plugin
 // inside a host application whose own runtime owns all device memory, or code on a path where
 // allocation is forbidden.  They still pass the logits, temperatures, seed and the output ids; the
-// scratch for the first-stage candidates is a fixed array inside the library.
+// scratch for the blocks' candidates and the rows' ticket counters is a fixed array inside the library.
 //
 //   int llmk_sample_static(int* out, const float* logits, long long ld, const float* temps,
 //                          const unsigned long long* seed, int n_rows, int V, void* stream);
@@ -20,11 +20,12 @@
 //
 // Limits and rules:
 //   * at most LLMK_SAMPLE_STATIC_MAX_ROWS rows a call; more is refused with an error, nothing runs;
-//   * the array (64 KiB) stays on every GPU that loads the library until the process ends;
+//   * the array (65 KiB) stays on every GPU that loads the library until the process ends;
 //   * the first call on a device looks the array's address up (cudaGetSymbolAddress, that device
 //     current); make that first call outside any stream capture;
 //   * calls share the array: do not let two of them overlap on the GPU (one stream, or order
-//     them with events); nothing needs clearing between calls;
+//     them with events); nothing needs clearing between calls (the counters in it start at zero
+//     and every call leaves them at zero);
 //   * no cudaMalloc, cudaFree or other allocating call is made.
 #pragma once
 

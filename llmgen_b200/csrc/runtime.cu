@@ -618,13 +618,16 @@ LLMR_EXPORT int llmr_sched_request(void* sp, long long req, int* out4) {
 // single tokens changes: ids, positions, lengths, state slots, temperatures, and per group the slots
 // and the block-table rows whose table changed (`row_stamps[g * bucket + s]` remembers request and
 // stamp of what row s of group g holds; 0 = padding).  Offsets are in 4-byte words:
-// offs = [ids, positions, ctx_len, state_slots, temps, ids_from, then (slots_g, block_tables_g) per group].
+// offs = [ids, positions, ctx_len, state_slots, temps, ids_from, row_keys, then (slots_g, block_tables_g) per group].
+// row_keys (two words a row) is the sampler's key of the row: (seed_base + stride * (position + 1)) ^ (request << 40),
+// the reference's step_seed ^ (row << 40) (src/backend/cpu/sample.zig:28) with the position in the step's place
+// and the request in the row's, so that a draw depends on neither the batch nor the number of steps so far.
 // `from[s]` >= 0 names the row of the step before whose sampled token is row s's id (the host has
 // not read it yet; tokens[s] is then ignored), -1 takes tokens[s].
 // Returns 0, or 1 when a position has no page.
 LLMR_EXPORT int llmr_fill_decode(void* c, int* host, const int* offs, int n, int bucket, int max_blocks,
                                  const long long* reqs, const int* tokens, const int* from, const int* starts,
-                                 const float* temps, long long* row_stamps) {
+                                 const float* temps, unsigned long long seed_base, long long* row_stamps) {
     Cache* cache = static_cast<Cache*>(c);
     const int ps = cache->page_size;
     int* ids = host + offs[0];
@@ -633,8 +636,12 @@ LLMR_EXPORT int llmr_fill_decode(void* c, int* host, const int* offs, int n, int
     int* st = host + offs[3];
     float* tp = reinterpret_cast<float*>(host + offs[4]);
     int* fr = host + offs[5];
+    int* keys = host + offs[6];
     for (int s = 0; s < bucket; ++s) {
         const bool live = s < n;
+        const unsigned long long key =
+            live ? (seed_base + 0x9E3779B97F4A7C15ull * (unsigned long long)(starts[s] + 1)) ^ ((unsigned long long)reqs[s] << 40) : 0ull;
+        memcpy(keys + 2 * s, &key, sizeof(key));
         ids[s] = live && from[s] < 0 ? tokens[s] : 0;
         fr[s] = live ? from[s] : -1;
         pos[s] = live ? starts[s] : 0;
@@ -645,8 +652,8 @@ LLMR_EXPORT int llmr_fill_decode(void* c, int* host, const int* offs, int n, int
     const int n_groups = (int)cache->groups.size();
     for (int g = 0; g < n_groups; ++g) {
         Group* grp = cache->groups[g];
-        int* slots = host + offs[6 + 2 * g];
-        int* bt = host + offs[7 + 2 * g];
+        int* slots = host + offs[7 + 2 * g];
+        int* bt = host + offs[8 + 2 * g];
         long long* stamps = row_stamps + (size_t)g * bucket * 2;
         for (int s = 0; s < bucket; ++s) {
             int* row = bt + (size_t)s * max_blocks;

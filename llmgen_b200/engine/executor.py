@@ -42,9 +42,11 @@ class StepError(ValueError):
 
 @dataclass
 class PendingIds:
-    """The sampled ids of a launched decode step: a pinned host buffer that is valid once `event` has passed."""
+    """The sampled ids of a launched decode step: a pinned host buffer that is valid once `event` has passed,
+    and beside it the kernels' two status flags as they stood after the step."""
     host: torch.Tensor
     event: object
+    flags: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -87,7 +89,7 @@ class Executor:
         self.dtype = model.dtype
         self.eager = eager or sync_each
         self.sync_each = sync_each
-        self.step_seed = seed & MASK64
+        self.seed = seed & MASK64
         self.n_graph_steps = 0
         self.n_eager_steps = 0
         self.launch_count = 0
@@ -134,19 +136,22 @@ class Executor:
         self._static_step_arrays = all(getattr(m, "step_arrays_follow_shapes", False) for m in self._unique_mixers)
         self.workspace = Workspace(self.device, limits.max_step_tokens)
         Tm, Sm, G = limits.max_step_tokens, limits.max_num_seqs, len(self.group_specs)
-        words = 64 + 10 * Tm + 10 * Sm + G * (Tm + Sm * self.max_blocks + 8)
+        words = 64 + 12 * Tm + 12 * Sm + G * (Tm + Sm * self.max_blocks + 8)
         self.meta_host = [torch.empty(words, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.meta_events = [None, None]
         self.meta_dev = torch.zeros(words, dtype=torch.int32, device=self.device)
         self._meta_turn = 0
-        self.sample_scratch = torch.empty(ops.sample_scratch_bytes(max(Sm, 64)) // 4, dtype=torch.float32,
-                                          device=self.device)
+        self.sample_scratch = ops.sample_scratch(max(Sm, 64), self.device)
         self.ids_host = torch.empty(max(Tm, Sm), dtype=torch.int32).pin_memory()
         # decode steps replayed from a graph leave their sampled ids here; the next step may take its
         # input ids from it on the device (`decode_launch`), before the host has read them
         self.sampled_dev = torch.zeros(Sm, dtype=torch.int32, device=self.device)
         self._ids_hosts = [torch.empty(Sm, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._ids_events = [torch.cuda.Event(), torch.cuda.Event()]
+        # what the kernels report beside their results (a wait that ran out, a sequence beyond a launch's bound,
+        # a token id outside the vocabulary): read with every step's ids, never by a synchronisation of its own
+        self.status_dev = ops.status_flags(self.device)
+        self._status_hosts = [torch.zeros(2, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._ids_turn = 0
         self.graphs: Dict[Tuple[int, int], dict] = {}     # (batch-size bucket, context-length class) -> graph
         # decode steps rewrite only what changed in a host buffer that the same bucket filled last
@@ -184,14 +189,18 @@ class Executor:
         return [n] * len(self.group_specs)
 
     def _activation_reserve(self) -> int:
+        """Device memory to leave beside the cache pages for a step's activations: what the widest layer says it
+        keeps in the workspace (`workspace_bytes(tokens)`; a layer that does not say is counted by its hidden
+        width alone), the float32 residual, and the logits of a batch of decoded tokens."""
         spec = self.model.spec
+        tokens = self.limits.max_step_tokens
         elem = 2 if self.dtype == torch.bfloat16 else 4
         widest = 0
-        for ls in spec.layers:
-            ffn = getattr(ls, "ffn", None)
-            widest = max(widest, 3 * getattr(ffn, "intermediate_size", 0) + 6 * spec.hidden_size)
-        return self.limits.max_step_tokens * (widest * elem + spec.hidden_size * 4) \
-            + 2 * 64 * spec.vocab_size * 4 + (64 << 20)
+        for layer in self.model.layers:
+            ask = getattr(layer, "workspace_bytes", None)
+            widest = max(widest, ask(tokens) if ask is not None else 6 * tokens * spec.hidden_size * elem)
+        rows = max(64, self.limits.max_num_seqs)
+        return widest + tokens * spec.hidden_size * 4 + 2 * rows * spec.vocab_size * 4 + (64 << 20)
 
     # ------------------------------------------------------------------ cache front
     def admit(self, req: Hashable) -> bool:
@@ -334,7 +343,7 @@ class Executor:
     def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0, ctx_bound: int = 0,
                     ids_from: Optional[Sequence[int]] = None):
         """Fill and upload the step's metadata; returns (StepContext, want rows view, temps view,
-        seed view, number of wanted rows).  A batch padded to a graph's shape (`pad_to`) also gets
+        view of the sampler's row keys, number of wanted rows).  A batch padded to a graph's shape (`pad_to`) also gets
         `ids_from`: for each row the row of the step before whose sampled id is its token, or -1."""
         lim = self.limits
         ps = lim.page_size
@@ -345,15 +354,13 @@ class Executor:
         T = sum(q_lens)
         pure_decode = all(n == 1 for n in q_lens)
         b = StepMetaBuilder(q_lens, starts, pure_decode, lim.page_size)
-        self.step_seed = (self.step_seed + SEED_STRIDE) & MASK64
-        b.add("seed", np.array([self.step_seed], dtype=np.uint64).view(np.int32))
         ids = np.zeros(T, dtype=np.int32)
         pos = np.zeros(T, dtype=np.int32)
         seq_of = np.zeros(T, dtype=np.int32)
         cu_q = np.zeros(S + 1, dtype=np.int32)
         ctx_len = np.zeros(S, dtype=np.int32)
         state_slots = np.full(S, -1, dtype=np.int32)
-        want_rows, temps = [], []
+        want_rows, temps, keys = [], [], []
         t = 0
         for s, e in enumerate(entries):
             n = q_lens[s]
@@ -364,6 +371,7 @@ class Executor:
             state_slots[s] = self.cache.state.slot(e.req)
             want_rows += [t + w for w in e.want]
             temps += [e.temperature] * len(e.want)
+            keys += [self.row_key(e.req, e.start + w) for w in e.want]
             t += n
             cu_q[s + 1] = t
         for s in range(S_real, S):          # padding rows: one token, no keys, written nowhere
@@ -372,6 +380,7 @@ class Executor:
             cu_q[s + 1] = t
             want_rows.append(t - 1)
             temps.append(0.0)
+            keys.append(0)
         b.add("ids", ids)
         if pad_to > 0:
             src = np.full(T, -1, dtype=np.int32)
@@ -385,6 +394,7 @@ class Executor:
         b.add("state_slots", state_slots)
         b.add("want_rows", np.asarray(want_rows, dtype=np.int32))
         b.add("temps", np.asarray(temps, dtype=np.float32), dtype=np.float32)
+        b.add("row_keys", np.asarray(keys, dtype=np.uint64).view(np.int32))
         for gi, g in enumerate(self.cache.groups):
             slots = np.full(T, -1, dtype=np.int32)
             bt = np.zeros((S, self.max_blocks), dtype=np.int32)
@@ -433,7 +443,22 @@ class Executor:
             groups=[GroupView(views[f"slots_{gi}"], views[f"block_tables_{gi}"], self.max_blocks)
                     for gi in range(len(self.cache.groups))],
             extra=views)
-        return ctx, views["want_rows"], views["temps"], views["seed"], len(want_rows)
+        return ctx, views["want_rows"], views["temps"], views["row_keys"], len(want_rows)
+
+    def row_key(self, req: Hashable, position: int) -> int:
+        """The sampler's 64-bit key of the row that samples the token after `position` of `req`:
+        (seed + stride * (position + 1)) ^ (request << 40), the reference's step_seed ^ (row << 40)
+        (src/backend/cpu/sample.zig:28, seed stride src/executor.zig:717-753) with the position in the step's
+        place and the request's number in the row's.  A draw then depends on the request and the position
+        alone: not on what else is in the batch, on how many steps ran before, on whether steps are launched
+        ahead, nor on a preemption that computes the position a second time."""
+        return ((self.seed + SEED_STRIDE * (position + 1)) & MASK64) ^ ((self.cache.key(req) << 40) & MASK64)
+
+    def _raise_status(self, flags_host: torch.Tensor) -> None:
+        kernel_error, bad_token = int(flags_host[0]), int(flags_host[1])
+        if kernel_error or bad_token:
+            self.status_dev.zero_()
+            raise StepError(ops.status_message(kernel_error, bad_token))
 
     def _maybe_sync(self):
         if self.sync_each:
@@ -442,7 +467,7 @@ class Executor:
     def _eager_pass(self, entries: Sequence[StepEntry], sample: bool, return_logits: bool, pad_to: int = 0) -> StepOutput:
         if self.profiler is not None:
             self.profiler.begin_pass([e.start for e in entries], [len(e.tokens) for e in entries])
-        ctx, want_rows, temps, seed, n_want = self._build_meta(entries, pad_to=pad_to)
+        ctx, want_rows, temps, keys, n_want = self._build_meta(entries, pad_to=pad_to)
         ctx.fixed_shapes = pad_to > 0      # the launch shapes a captured graph of this step would have
         n_real = sum(len(e.want) for e in entries)
         out = StepOutput()
@@ -456,12 +481,14 @@ class Executor:
         logits = self.model.forward(ctx, self.layer_caches, want_rows, n_want)
         if sample:
             ids_dev = self.workspace.flat("sampled_ids", max(n_want, self.limits.max_num_seqs), torch.int32)[:n_want]
-            if n_want * ops.SAMPLE_SPLIT * 2 > self.sample_scratch.numel():
-                self.sample_scratch = torch.empty(n_want * ops.SAMPLE_SPLIT * 2, dtype=torch.float32, device=self.device)
-            ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
+            if ops.sample_scratch_bytes(n_want) > self.sample_scratch.numel() * 4:
+                self.sample_scratch = ops.sample_scratch(n_want, self.device)
+            ops.sample(ids_dev, logits, temps, None, self.sample_scratch, row_keys=keys)
             host = self.ids_host[:n_want] if n_want <= self.ids_host.numel() else torch.empty(n_want, dtype=torch.int32).pin_memory()
             host.copy_(ids_dev, non_blocking=True)
+            self._status_hosts[2].copy_(self.status_dev, non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            self._raise_status(self._status_hosts[2])
             out.token_ids = host.tolist()[:n_real]
         if return_logits:
             out.logits = logits[:n_real]
@@ -514,10 +541,10 @@ class Executor:
         ids_warm = torch.zeros(bucket, dtype=torch.int32, device=self.device)
 
         def run():
-            ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
+            ctx, want_rows, temps, keys, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
             ctx.fixed_shapes = True
             self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
-            ops.sample(ids_warm, logits, temps, seed, self.sample_scratch)
+            ops.sample(ids_warm, logits, temps, None, self.sample_scratch, row_keys=keys)
 
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -528,7 +555,7 @@ class Executor:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         # the metadata upload stays outside the graph: build it first, then capture the launches
-        ctx, want_rows, temps, seed, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
+        ctx, want_rows, temps, keys, n_want = self._build_meta([], pad_to=bucket, ctx_bound=ctx_bound)
         ctx.fixed_shapes = True
         torch.cuda.synchronize(self.device)
         self.workspace.frozen = True
@@ -536,7 +563,7 @@ class Executor:
         try:
             with torch.cuda.graph(graph, stream=stream):
                 self.model.forward(ctx, self.layer_caches, want_rows, n_want, out=logits)
-                ops.sample(ids_dev, logits, temps, seed, self.sample_scratch)
+                ops.sample(ids_dev, logits, temps, None, self.sample_scratch, row_keys=keys)
         finally:
             self.workspace.frozen = False
         entry = {"graph": graph, "ids": ids_dev, "logits": logits, "launches": ops.launches() - launches_before}
@@ -581,19 +608,23 @@ class Executor:
         self._ids_turn ^= 1
         host = self._ids_hosts[turn][:n]
         host.copy_(self.sampled_dev[:n], non_blocking=True)
+        flags = self._status_hosts[turn]
+        flags.copy_(self.status_dev, non_blocking=True)
         self._ids_events[turn].record()
         self.n_graph_steps += 1
-        return PendingIds(host, self._ids_events[turn])
+        return PendingIds(host, self._ids_events[turn], flags)
 
     def decode_collect(self, pending: "PendingIds") -> List[int]:
         """The sampled ids of a launched step, in the order of its entries."""
         pending.event.synchronize()
+        if pending.flags is not None:
+            self._raise_status(pending.flags)
         return pending.host.tolist()
 
     def _fill_decode_meta(self, entries: Sequence[StepEntry], bucket: int, prev_rows: Optional[Sequence[int]] = None) -> None:
         """The metadata of a step of single tokens.  The first fill of a pinned buffer for a bucket
         goes through `_build_meta`; later ones rewrite only what a decode step changes (tokens,
-        positions, lengths, slots, the seed, and block-table rows whose table grew), with the
+        positions, lengths, slots, the sampler's keys, and block-table rows whose table grew), with the
         layout of that first fill."""
         turn = self._meta_turn
         owner = self._host_owner[turn]
@@ -603,7 +634,7 @@ class Executor:
         if owner is None or owner[0] != bucket:
             self._build_meta(entries, pad_to=bucket, ids_from=prev_rows)
             t, layout, total = self._last_fill
-            names = ["ids", "positions", "ctx_len", "state_slots", "temps", "ids_from"]
+            names = ["ids", "positions", "ctx_len", "state_slots", "temps", "ids_from", "row_keys"]
             for gi in range(len(self.cache.groups)):
                 names += [f"slots_{gi}", f"block_tables_{gi}"]
             offs = (ctypes.c_int * len(names))(*[layout[name][0] for name in names])
@@ -620,9 +651,6 @@ class Executor:
             self.meta_events[turn].synchronize()
         host = self.meta_host[turn]
         n = len(entries)
-        self.step_seed = (self.step_seed + SEED_STRIDE) & MASK64
-        off, size, _ = layout["seed"]
-        host.numpy()[off:off + size] = np.array([self.step_seed], dtype=np.uint64).view(np.int32)
         a = self._decode_args
         key = self.cache.key
         a[0][:n] = [key(e.req) for e in entries]
@@ -636,7 +664,7 @@ class Executor:
         a[3][:n] = [e.temperature for e in entries]
         rc = self._runtime.llmr_fill_decode(self.cache.native_handle, ctypes.c_void_p(host.data_ptr()), offs,
                                             ctypes.c_int(n), ctypes.c_int(bucket), ctypes.c_int(self.max_blocks),
-                                            a[0], a[1], a[4], a[2], a[3], self._host_rows[turn])
+                                            a[0], a[1], a[4], a[2], a[3], ctypes.c_ulonglong(self.seed), self._host_rows[turn])
         if rc != 0:
             self._host_owner[turn] = None
             raise StepError(self._runtime.llmr_last_error().decode("utf-8", "replace"))

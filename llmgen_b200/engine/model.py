@@ -17,7 +17,6 @@ import torch
 from ..kernels import build as kernel_build
 from ..kernels import ops
 from ..parts.base import LayerCache
-from ..parts.linear import _FORCE as _FORCE_GEMM
 from ..parts.linear import linear
 from ..parts.registry import build_block, build_norm, model_kernel_modules
 from ..parts.spec import ModelSpec
@@ -41,7 +40,7 @@ class DecoderModel:
         for item in spec.run_order:
             if not 0 <= item.layer < len(self.layers):
                 raise ValueError(f"run list names layer {item.layer}, the model has {len(self.layers)}")
-        self.bad_token_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.bad_token_flag = ops.bad_token_flag(device)      # read by the engine with every step's results
 
     # -- what the engine needs to size caches and limits
     def mixers(self):
@@ -85,8 +84,6 @@ class DecoderModel:
         delta = None
         for item, cache in zip(self.spec.run_order, caches):
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)
-            if isinstance(delta, ops.Moved):        # the block left the residual stream in another array
-                resid, delta = delta.resid, delta.delta
         return resid, delta
 
     def logits(self, ctx: StepContext, resid: torch.Tensor, delta: Optional[torch.Tensor],
@@ -95,19 +92,10 @@ class DecoderModel:
         H, V = self.spec.hidden_size, self.spec.vocab_size
         ws = ctx.workspace
         normed = ws.buffer("final_normed", n_rows, H, self.dtype, capacity_rows=max(n_rows, 64))
-        if isinstance(delta, ops.RowSquares):
-            delta = None                # the last block added its output to the residual itself
         self.final_norm.add_norm(resid, delta, normed, rows=rows)
         if out is None:
             out = torch.empty((n_rows, V), dtype=torch.float32, device=self.device)
-        if self.dtype == torch.float32 or ops.gemv_usable(normed, self.lm_head) or _FORCE_GEMM != "lib":
-            linear(normed, self.lm_head, out)
-        else:
-            # the library product writes bfloat16; widen afterwards
-            narrow = ws.buffer("logits_bf16", n_rows, V, self.dtype, capacity_rows=max(n_rows, 64))
-            linear(normed, self.lm_head, narrow)
-            ops.widen(out, narrow)
-        return out
+        return linear(normed, self.lm_head, out)
 
     def forward(self, ctx: StepContext, caches: List[LayerCache], rows: torch.Tensor, n_rows: int,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -224,18 +224,14 @@ def efficiency_text(metrics: GenMetrics, cost: ModelCost, peak_tflops: Optional[
 
 # ------------------------------------------------------------------------------ OpProfiler
 def _nbytes(x) -> int:
-    """Bytes of an operand: an array, slices of a product cut along K, an operand that is not
-    computed yet (counted as its finished rows in 2-byte storage), or nothing."""
+    """Bytes of an operand: an array, the slices of a product cut along K, or nothing."""
     if x is None:
         return 0
-    tensor = getattr(x, "tensor", None)                    # ops.Partials, ops.RowSquares
+    tensor = getattr(x, "tensor", None)                    # ops.Partials
     if tensor is not None:
         return tensor.numel() * tensor.element_size()
     if hasattr(x, "numel") and hasattr(x, "element_size"):
         return x.numel() * x.element_size()
-    shape = getattr(x, "shape", None)                      # NormedRows, GatedRows, AddNormRows
-    if shape is not None:
-        return 2 * int(shape[0]) * int(shape[1])
     return 0
 
 
@@ -263,7 +259,7 @@ def _cost_product(a, info: PassInfo) -> Tuple[int, int]:
     x = a.get("a", a.get("x"))
     out = a.get("out", a.get("slices"))
     M, N, K = int(x.shape[0]), int(w.shape[0]), int(w.shape[1])
-    return 2 * M * N * K, _nbytes(w) + _nbytes(x) + _nbytes(out) + _nbytes(a.get("add_to"))
+    return 2 * M * N * K, _nbytes(w) + _nbytes(x) + _nbytes(out)
 
 
 def _cost_attention(a, info: PassInfo) -> Tuple[int, int]:
@@ -309,8 +305,7 @@ def _cost_all_operands(a, info: PassInfo) -> Tuple[int, int]:
 OP_COSTS: Dict[str, Callable] = {
     "embed_rows": _cost_embed, "add_rmsnorm": _cost_norm, "silu_mul": _cost_all_operands, "widen": _cost_all_operands,
     "attn_prep": _cost_attn_prep, "gemm_simt": _cost_product, "gemv_bf16": _cost_product, "gemm_tc": _cost_product,
-    "gemm_tc_sliced": _cost_product, "gemm_skinny": _cost_product, "gemm_skinny_fused": _cost_product,
-    "gemm_skinny_addnorm": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,
+    "gemm_skinny": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,
     "attention_tc": _cost_attention, "sample": _cost_all_operands,
 }
 

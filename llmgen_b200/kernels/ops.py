@@ -76,7 +76,7 @@ def _row_stride(t: torch.Tensor) -> int:
 class Partials:
     """The result of a matrix product cut along K: float32 slices [splits, rows, cols] whose sum, in
     slice order, is the product.  The kernels that consume a product (`add_rmsnorm`, `attn_prep`,
-    `silu_mul`) take a `Partials` in place of the finished array and do the sum themselves."""
+    `attention_decode`, `silu_mul`) take a `Partials` in place of the finished array and do the sum themselves."""
 
     def __init__(self, tensor: torch.Tensor):
         if tensor.dim() != 3 or tensor.dtype != torch.float32 or not tensor.is_contiguous():
@@ -91,48 +91,6 @@ class Partials:
     def sum(self) -> torch.Tensor:
         """The finished product (float32), for callers that have no kernel taking slices."""
         return self.tensor.sum(dim=0)
-
-
-class RowSquares:
-    """What a product leaves when it added its result to the float32 residual itself: for every row
-    the sum of squares of the updated residual, in `parts` parts ([parts, rows] float32, one per
-    128 columns), for the RMSNorm that follows."""
-
-    def __init__(self, tensor: torch.Tensor):
-        if tensor.dim() != 2 or tensor.dtype != torch.float32 or not tensor.is_contiguous():
-            raise KernelError("row sums of squares are a contiguous float32 [parts, rows] array")
-        self.tensor = tensor
-        self.parts, self.rows = tensor.shape
-
-
-class NormedRows:
-    """Rows of the float32 array `resid`, RMS-normalised, not yet computed: a product that can build
-    its operand itself takes this in place of the array (`gemm_skinny_fused`); `materialize` is the
-    same through the norm kernel.  y = resid / sqrt(sum of squares / width + eps) * (gain + offset)."""
-
-    def __init__(self, resid: torch.Tensor, squares: RowSquares, gain: torch.Tensor, eps: float, offset: float = 0.0):
-        if resid.dtype != torch.float32 or resid.dim() != 2 or squares.rows != resid.shape[0]:
-            raise KernelError("rows to normalise: a float32 [rows, width] array and one sum of squares per row")
-        self.resid, self.squares, self.gain, self.eps, self.offset = resid, squares, gain, float(eps), float(offset)
-        self.shape = resid.shape
-
-    def materialize(self, out: torch.Tensor) -> torch.Tensor:
-        add_rmsnorm(self.resid, None, self.gain, out, self.eps, self.offset)
-        return out
-
-
-class GatedRows:
-    """silu(gate) * up of a packed gate/up product that came back as slices, not yet computed."""
-
-    def __init__(self, gate_up: Partials, group: int):
-        if gate_up.cols % 2 != 0:
-            raise KernelError("a packed gate/up product has an even number of columns")
-        self.gate_up, self.group = gate_up, int(group)
-        self.shape = (gate_up.rows, gate_up.cols // 2)
-
-    def materialize(self, out: torch.Tensor) -> torch.Tensor:
-        silu_mul(out, self.gate_up, group=self.group)
-        return out
 
 
 # ---------------------------------------------------------------------------- elementwise
@@ -196,6 +154,27 @@ def widen(out: torch.Tensor, src: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------ attn_prep
+# Codes of the C ABI (csrc/common.cuh).  "half": pairs (i, i + rot / 2), the reference's pairing
+# (src/backend/cpu/rope.zig:13-45); "interleaved": pairs (2i, 2i + 1), which no kernel here implements yet:
+# a position encoding that names it is refused by the kernel with a message, not rotated wrongly.
+ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
+HEAD_NORMS = {"rmsnorm": 0}
+
+
+def pairing_code(pairing: str) -> int:
+    try:
+        return ROTARY_PAIRINGS[pairing]
+    except KeyError:
+        raise KernelError(f"unknown rotary pairing {pairing!r} (known: {', '.join(ROTARY_PAIRINGS)})") from None
+
+
+def head_norm_code(kind: str) -> int:
+    try:
+        return HEAD_NORMS[kind]
+    except KeyError:
+        raise KernelError(f"no kernel normalises heads with {kind!r} (known: {', '.join(HEAD_NORMS)})") from None
+
+
 def attn_prep_set_by_token(on: bool) -> None:
     """Which 16-byte variant `attn_prep` runs on prompts: a warp on several heads of one token at a
     time (the default) or a row at a time (for comparisons and tests)."""
@@ -206,10 +185,13 @@ def attn_prep(qkv, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor
               positions: Optional[torch.Tensor], slots: Optional[torch.Tensor], cos: Optional[torch.Tensor],
               sin: Optional[torch.Tensor], q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
               nq: int, nk: int, hd: int, rot: int, page_size: int, eps: float,
-              q_offset: float = 0.0, k_offset: float = 0.0, q_out: Optional[torch.Tensor] = None) -> None:
+              q_offset: float = 0.0, k_offset: float = 0.0, q_out: Optional[torch.Tensor] = None,
+              pairing: str = "half", head_norm: str = "rmsnorm") -> None:
     """Per-head norm and rotary encoding of q and k, and the cache write of k, v.  `qkv` holds the
     packed rows [n, (nq + 2 nk) hd] as an array (q is then rewritten in place unless `q_out` is
-    given) or as a `Partials` (q goes to `q_out`, which gives the storage dtype)."""
+    given) or as a `Partials` (q goes to `q_out`, which gives the storage dtype).  `pairing` says which
+    values of a head the rotary encoding turns together and `head_norm` which norm runs over a head
+    (see `ROTARY_PAIRINGS`, `HEAD_NORMS`); the kernel refuses the ones it does not implement."""
     lib = build.load("attn_prep")
     nkv_cache = kcache.shape[1] if kcache is not None else 0
     splits, split_stride = 0, 0
@@ -231,6 +213,7 @@ def attn_prep(qkv, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor
                                    _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(q_gain), _ptr(k_gain),
                                    c_int(n), c_int(nq), c_int(nk), c_int(nkv_cache), c_int(hd), c_int(rot),
                                    c_int(page_size), c_float(eps), c_float(q_offset), c_float(k_offset),
+                                   c_int(pairing_code(pairing)), c_int(head_norm_code(head_norm)),
                                    c_int(dtype_code(dtype)), _stream()))
 
 
@@ -271,34 +254,6 @@ def gemv_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-_tc_plans: Dict[Tuple[int, int, int], int] = {}
-
-
-def gemm_tc_splits(M: int, N: int, K: int) -> int:
-    """Into how many slices of K the tiled product of many rows is best cut (1: not cut)."""
-    key = (M, N, K)
-    v = _tc_plans.get(key)
-    if v is None:
-        v = int(build.load("gemm_tc").llmk_gemm_tc_splits(c_int(M), c_int(N), c_int(K)))
-        _tc_plans[key] = v
-    return v
-
-
-def gemm_tc_sliced(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
-    """The tiled tensor-core product cut along K: out is float32 [splits, M, N] and receives the sums
-    of `splits` slices of K, for a consumer that adds them up (`Partials`)."""
-    lib = build.load("gemm_tc")
-    M, K = a.shape
-    N = w.shape[0]
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
-        raise KernelError(f"gemm_tc: operands a{list(a.shape)} {a.dtype} w{list(w.shape)} {w.dtype} do not fit")
-    if out.dim() != 3 or out.shape[1] != M or out.shape[2] != N or out.dtype != torch.float32 or not out.is_contiguous():
-        raise KernelError("gemm_tc: the slices go to a contiguous float32 [splits, M, N] array")
-    _check(lib, lib.llmk_gemm_tc_sliced(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(a)),
-                                        c_longlong(_row_stride(w)), c_longlong(N), c_int(out.shape[0]),
-                                        _ptr(tc_error_flag(a.device)), c_int(1), _stream()))
-
-
 def gemm_tc_set_pair_mode(mode: int) -> None:
     """How `gemm_tc` uses pairs of blocks on 256-row tiles (`tcgen05.mma.cta_group::2`): 0 never,
     1 where the product has the rows for it (the default), 2 / 3 always, with tiles 256 / 128 columns
@@ -314,27 +269,68 @@ def gemm_tc_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-_tc_error_flags = {}
+_status = {}      # device (object or its string) -> (both flags, view of [0], view of [1])
+
+
+def _status_of(device):
+    entry = _status.get(device)
+    if entry is None:
+        entry = _status.get(str(device))
+        if entry is None:
+            flags = torch.zeros(2, dtype=torch.int32, device=device)
+            entry = (flags, flags[0:1], flags[1:2])
+            _status[str(device)] = entry
+        _status[device] = entry              # the device object itself as a second key: no string per launch
+    return entry
+
+
+def status_flags(device) -> torch.Tensor:
+    """Two device ints that kernels raise and the engine reads with a step's results: [0] a kernel's error
+    (1: a bounded wait ran out; 2: a sequence longer than its attention launch was sized for), [1] a token
+    id outside the vocabulary met by the embedding kernel."""
+    return _status_of(device)[0]
 
 
 def tc_error_flag(device) -> torch.Tensor:
-    """Device int that a tensor-core kernel raises when one of its bounded waits gave up."""
-    flag = _tc_error_flags.get(device)
-    if flag is None:
-        flag = _tc_error_flags.get(str(device))
-        if flag is None:
-            flag = torch.zeros(1, dtype=torch.int32, device=device)
-            _tc_error_flags[str(device)] = flag
-        _tc_error_flags[device] = flag          # the device object itself as a second key: no string per launch
-    return flag
+    """Device int that a kernel raises when one of its bounded waits gave up or an input broke its bounds."""
+    return _status_of(device)[1]
+
+
+def bad_token_flag(device) -> torch.Tensor:
+    """Device int that `embed_rows` raises when it meets an id outside the table."""
+    return _status_of(device)[2]
+
+
+def status_message(kernel_error: int, bad_token: int) -> Optional[str]:
+    """What the two flags say, or None when both are clear."""
+    if kernel_error == 2:
+        return "a sequence was longer than the bound its attention launch was sized for (results of that step are invalid)"
+    if kernel_error != 0:
+        return "a kernel gave up waiting on a barrier (results of that step are invalid)"
+    if bad_token != 0:
+        return "a token id outside the vocabulary reached the embedding (its row was read as zeros)"
+    return None
 
 
 def check_tc_errors(device) -> None:
-    """Raise if a tensor-core kernel reported a wait that ran out (synchronises)."""
-    flag = _tc_error_flags.get(str(device))
-    if flag is not None and int(flag.item()) != 0:
-        flag.zero_()
-        raise KernelError("a tensor-core kernel gave up waiting on a barrier (results of that step are invalid)")
+    """Raise if a kernel reported a wait that ran out or an input beyond its launch's bounds (synchronises)."""
+    entry = _status.get(str(device))
+    code = int(entry[1].item()) if entry is not None else 0
+    if code != 0:
+        entry[1].zero_()
+        raise KernelError(status_message(code, 0))
+
+
+_sm_counts: Dict[str, int] = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (launch plans are made from it, not from a constant)."""
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    key = str(dev)
+    if key not in _sm_counts:
+        _sm_counts[key] = int(torch.cuda.get_device_properties(dev).multi_processor_count)
+    return _sm_counts[key]
 
 
 def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pdl: bool = True) -> None:
@@ -358,18 +354,11 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
 
 
 SKINNY_MAX_ROWS = 256
-SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED, SKINNY_CLUSTER = 0, 1, 2, 3
+SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED = 0, 1, 2
 SKINNY_CLUSTER_GATED = 5     # slices of K added up inside a cluster (2 or 4), then silu(gate) * up: out[M, N/2]
 SKINNY_CLUSTER_MAX_ROWS = 64
 _cluster_plans = {}
 _skinny_plans = {}
-
-
-def gemm_skinny_set_half_tiles(on: bool) -> None:
-    """Whether the few-rows product cut along K takes tiles of 64 rows of W (`tcgen05.mma` with M = 64)
-    where tiles of 128 would leave half the SMs without a block.  Off by default (it was slower in a
-    decode step); LLMGEN_SKINNY_TILES=64 in the environment turns it on at load."""
-    build.load("gemm_skinny").llmk_gemm_skinny_set_half_tiles(c_int(1 if on else 0))
 
 
 def gemm_skinny_splits(M: int, N: int, K: int) -> int:
@@ -396,8 +385,9 @@ def gemm_skinny_cluster_splits(M: int, N: int, K: int) -> int:
 def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int = SKINNY_DIRECT, splits: int = 1) -> None:
     """The weight-streaming tensor-core product for M <= 256 rows (csrc/gemm_skinny.cu).
     SKINNY_DIRECT: out[M, N]; SKINNY_GATED: out[M, N/2] = silu(gate) * up; SKINNY_PARTIAL: out is
-    float32 [splits, M, N] and receives the partial sums of `splits` slices of K; SKINNY_CLUSTER:
-    out[M, N] from `splits` slices of K added up inside a thread-block cluster (M <= 64)."""
+    float32 [splits, M, N] and receives the partial sums of `splits` slices of K;
+    SKINNY_CLUSTER_GATED: out[M, N/2] = silu(gate) * up from `splits` slices of K (2 or 4) added up
+    inside a thread-block cluster (M <= 64)."""
     lib = build.load("gemm_skinny")
     M, K = a.shape
     N = w.shape[0]
@@ -411,162 +401,11 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, mode: int =
         n_out = N // 2 if mode in (SKINNY_GATED, SKINNY_CLUSTER_GATED) else N
         if out.shape[0] != M or out.shape[1] != n_out:
             raise KernelError(f"gemm_skinny: out{list(out.shape)} does not fit [{M}, {n_out}]")
-        splits, ldc = (splits if mode in (SKINNY_CLUSTER, SKINNY_CLUSTER_GATED) else 1), _row_stride(out)
+        splits, ldc = (splits if mode == SKINNY_CLUSTER_GATED else 1), _row_stride(out)
     _check(lib, lib.llmk_gemm_skinny(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
                                      c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), c_longlong(ldc),
                                      c_int(splits), c_int(mode), c_int(dtype_code(out.dtype)),
                                      _ptr(tc_error_flag(a.device)), _stream()))
-
-
-SKINNY_FUSED_MAX_ROWS = 64
-_fused_fits: Dict[Tuple[int, int, int], bool] = {}
-
-
-def gemm_skinny_fused_usable(x, w: torch.Tensor, splits: int, add_to: Optional[torch.Tensor] = None) -> bool:
-    """Can `gemm_skinny_fused` take this operand (an array, `NormedRows` or `GatedRows`) and, with
-    `add_to`, add the product to that float32 array?"""
-    M, K = x.shape
-    N = w.shape[0]
-    if not (0 < M <= SKINNY_FUSED_MAX_ROWS) or w.dtype != torch.bfloat16 or w.shape[1] != K or K % 8 != 0:
-        return False
-    if _row_stride(w) % 8 != 0 or w.data_ptr() % 16 != 0 or N % 4 != 0:
-        return False
-    if isinstance(x, NormedRows):
-        if x.resid.stride(1) != 1 or x.resid.stride(0) % 4 != 0 or x.resid.data_ptr() % 16 != 0 or x.gain.dtype != torch.float32:
-            return False
-    elif isinstance(x, GatedRows):
-        if x.group % 8 != 0 or K % x.group != 0:
-            return False
-    elif not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
-        return False
-    if not isinstance(x, torch.Tensor):
-        key = (M, K, splits)
-        fits = _fused_fits.get(key)
-        if fits is None:
-            fits = bool(build.load("gemm_skinny").llmk_gemm_skinny_fused_fits(c_int(M), c_int(K), c_int(splits)))
-            _fused_fits[key] = fits
-        if not fits:
-            return False
-    if add_to is not None:
-        if (add_to.dtype != torch.float32 or add_to.shape != (M, N) or add_to.stride(1) != 1 or add_to.stride(0) % 4 != 0
-                or add_to.data_ptr() % 16 != 0):
-            return False
-    return True
-
-
-def gemm_skinny_fused(slices: torch.Tensor, x, w: torch.Tensor, add_to: Optional[torch.Tensor] = None,
-                      squares_out: Optional[torch.Tensor] = None, tickets: Optional[torch.Tensor] = None) -> None:
-    """The few-rows product with its neighbours folded in (csrc/gemm_skinny.cu).  `slices` is float32
-    [splits, M, N]; `x` is a bfloat16 array [M, K], a `NormedRows` or a `GatedRows`, which the blocks
-    then compute themselves.  With `add_to` (float32 [M, N]) the sum of the slices is added to it by
-    the last block of each 128-column tile, and `squares_out` [ceil(N / 128), M] receives the parts of
-    each row's sum of squares; `tickets` is a zeroed int32 array with one entry per tile (left zeroed)."""
-    lib = build.load("gemm_skinny")
-    M, K = x.shape
-    N = w.shape[0]
-    if slices.dim() != 3 or slices.shape[1] != M or slices.shape[2] != N or slices.dtype != torch.float32 or not slices.is_contiguous():
-        raise KernelError("gemm_skinny_fused: the slices go to a contiguous float32 [splits, M, N] array")
-    tiles = (N + 127) // 128
-    null = c_void_p(None)
-    xs, xp, ldx = 0, null, 0
-    resid_p, x_ld, sq_p, n_sq, gain_p, eps, off = null, 0, null, 0, null, 0.0, 0.0
-    gu_p, gu_splits, gu_stride, gu_ld, group = null, 0, 0, 0, 0
-    if isinstance(x, NormedRows):
-        xs, resid_p, x_ld, sq_p, n_sq = 1, _ptr(x.resid), x.resid.stride(0), _ptr(x.squares.tensor), x.squares.parts
-        gain_p, eps, off = _ptr(x.gain), x.eps, x.offset
-    elif isinstance(x, GatedRows):
-        g = x.gate_up
-        xs, gu_p, gu_splits, gu_stride, gu_ld, group = 2, _ptr(g.tensor), g.splits, g.split_stride, g.cols, x.group
-    else:
-        xp, ldx = _ptr(x), _row_stride(x)
-    add_p, add_ld, sqo_p, tick_p = null, 0, null, null
-    if add_to is not None:
-        if squares_out is None or tickets is None or squares_out.numel() < tiles * M or tickets.numel() < tiles \
-                or squares_out.dtype != torch.float32 or tickets.dtype != torch.int32:
-            raise KernelError(f"gemm_skinny_fused: adding to the residual needs {tiles * M} float32 for the sums of "
-                              f"squares and {tiles} zeroed int32 tickets")
-        add_p, add_ld, sqo_p, tick_p = _ptr(add_to), add_to.stride(0), _ptr(squares_out), _ptr(tickets)
-    _check(lib, lib.llmk_gemm_skinny_fused(
-        _ptr(slices), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(w)), c_longlong(N),
-        c_int(slices.shape[0]), c_int(xs), xp, c_longlong(ldx), resid_p, c_longlong(x_ld), sq_p, c_int(n_sq), gain_p,
-        c_float(eps), c_float(off), gu_p, c_int(gu_splits), c_longlong(gu_stride), c_longlong(gu_ld), c_int(group),
-        add_p, c_longlong(add_ld), sqo_p, tick_p, _ptr(tc_error_flag(w.device)), _stream()))
-
-
-class AddNormRows:
-    """norm(resid_in + delta) as an operand that a few-rows product computes itself, delta being the
-    slices of the product before; the product also writes the sum to `resid_out`, another array than
-    the one it reads (the blocks of other tiles still read that one).  `materialize` is the same through
-    the norm kernel."""
-
-    def __init__(self, resid_in: torch.Tensor, delta: Partials, resid_out: torch.Tensor, gain: torch.Tensor, eps: float,
-                 offset: float = 0.0):
-        if resid_in.dtype != torch.float32 or resid_in.shape != resid_out.shape or resid_in.data_ptr() == resid_out.data_ptr():
-            raise KernelError("the residual is read from one float32 array and written to another of the same shape")
-        if delta.rows != resid_in.shape[0] or delta.cols != resid_in.shape[1]:
-            raise KernelError("the slices to add do not have the residual's shape")
-        self.resid_in, self.delta, self.resid_out, self.gain = resid_in, delta, resid_out, gain
-        self.eps, self.offset = float(eps), float(offset)
-        self.shape = resid_in.shape
-
-    def materialize(self, out: torch.Tensor) -> torch.Tensor:
-        self.resid_out.copy_(self.resid_in)
-        add_rmsnorm(self.resid_out, self.delta, self.gain, out, self.eps, self.offset)
-        return out
-
-
-class Moved:
-    """What a block returns in place of its pending output when the residual stream now lives in another
-    array than the one it was given: (`resid`, `delta`)."""
-
-    def __init__(self, resid: torch.Tensor, delta):
-        self.resid, self.delta = resid, delta
-
-
-ADDNORM_MAX_ROWS = 16
-
-
-def gemm_skinny_addnorm_splits(x: AddNormRows, w: torch.Tensor, gated: bool) -> int:
-    """Into how many slices of K `gemm_skinny_addnorm` would cut this product, 0 if it cannot take it."""
-    M, K = x.shape
-    N = w.shape[0]
-    if not (0 < M <= ADDNORM_MAX_ROWS) or w.dtype != torch.bfloat16 or w.shape[1] != K or K % 64 != 0:
-        return 0
-    if _row_stride(w) % 8 != 0 or w.data_ptr() % 16 != 0 or x.gain.dtype != torch.float32 or (gated and N % 32 != 0):
-        return 0
-    for t in (x.resid_in, x.resid_out):
-        if t.stride(1) != 1 or t.stride(0) != K or t.data_ptr() % 16 != 0:
-            return 0
-    num_kb = K // 64
-    splits = min(gemm_skinny_cluster_splits(M, N, K), 4 if gated else 8)
-    while splits >= 2:
-        per = num_kb // splits
-        if num_kb % splits == 0 and per % 4 == 0 and per <= 16 and M * per * 8 <= 1024:
-            return splits
-        splits //= 2
-    return 0
-
-
-def gemm_skinny_addnorm(out: torch.Tensor, x: AddNormRows, w: torch.Tensor, splits: int, gated: bool = False) -> None:
-    """The few-rows product that adds the slices before it to the residual and normalises its rows itself
-    (csrc/gemm_skinny.cu, X_ADDNORM).  gated: out is bfloat16 [M, N/2] = silu(gate) * up; else out is
-    float32 [splits, M, N], the slices of the product."""
-    lib = build.load("gemm_skinny")
-    M, K = x.shape
-    N = w.shape[0]
-    if gated:
-        if out.shape != (M, N // 2) or out.dtype != torch.bfloat16:
-            raise KernelError(f"gemm_skinny_addnorm: out{list(out.shape)} {out.dtype} does not fit bfloat16 [{M}, {N // 2}]")
-        ldc = _row_stride(out)
-    else:
-        if out.dim() != 3 or out.shape != (splits, M, N) or out.dtype != torch.float32 or not out.is_contiguous():
-            raise KernelError("gemm_skinny_addnorm: the slices go to a contiguous float32 [splits, M, N] array")
-        ldc = N
-    d = x.delta
-    _check(lib, lib.llmk_gemm_skinny_addnorm(
-        _ptr(out), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(w)), c_longlong(ldc), c_int(splits),
-        c_int(1 if gated else 0), _ptr(x.resid_in), _ptr(d.tensor), c_int(d.splits), c_longlong(d.split_stride), c_longlong(K),
-        _ptr(x.resid_out), _ptr(x.gain), c_float(x.eps), c_float(x.offset), _ptr(tc_error_flag(w.device)), _stream()))
 
 
 def gemm_skinny_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -636,11 +475,12 @@ def attention_decode(out: torch.Tensor, q: Optional[torch.Tensor], q_stride: int
                      slots: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
                      sin: Optional[torch.Tensor] = None, q_gain: Optional[torch.Tensor] = None,
                      k_gain: Optional[torch.Tensor] = None, eps: float = 0.0, q_offset: float = 0.0,
-                     k_offset: float = 0.0) -> None:
+                     k_offset: float = 0.0, pairing: str = "half", head_norm: str = "rmsnorm") -> None:
     """out[t] = attention of the single token of each sequence over the paged cache, bfloat16
     (csrc/attention_decode.cu).  `counters` (int32) must be zero before the first call.  With
     `packed` (the q/k/v projection rows as an array or a `Partials`) the kernel also normalises and
-    rotates q and k and writes k and v to the cache, and `q` is not read."""
+    rotates q and k and writes k and v to the cache, and `q` is not read.  `max_ctx` must bound every
+    sequence's length: a longer one is skipped and raises the device error flag (`check_tc_errors`)."""
     lib = build.load("attention_decode")
     if kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or (q is not None and q.dtype != torch.bfloat16):
         raise KernelError("attention_decode: bfloat16 only")
@@ -663,7 +503,9 @@ def attention_decode(out: torch.Tensor, q: Optional[torch.Tensor], q_stride: int
                                           _ptr(scratch), _ptr(counters), _ptr(src), c_longlong(packed_stride),
                                           c_int(splits), c_longlong(split_stride), c_int(nk), c_int(rot),
                                           _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(q_gain), _ptr(k_gain),
-                                          c_float(eps), c_float(q_offset), c_float(k_offset), _stream()))
+                                          c_float(eps), c_float(q_offset), c_float(k_offset),
+                                          c_int(pairing_code(pairing)), c_int(head_norm_code(head_norm)),
+                                          _ptr(tc_error_flag(out.device)), _stream()))
 
 
 def attention_tc_tile_queries(nq: int, nkv: int, hd: int, page_size: int) -> int:
@@ -690,20 +532,32 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torc
 
 # ------------------------------------------------------------------------------- sampling
 SAMPLE_SPLIT = 32
+_SAMPLE_ROW_BYTES = SAMPLE_SPLIT * 8 + 4        # a row's candidates and its ticket counter
 
 
 def sample_scratch_bytes(max_rows: int) -> int:
-    return max_rows * SAMPLE_SPLIT * 8
+    return max_rows * _SAMPLE_ROW_BYTES
 
 
-def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, seed: torch.Tensor,
-           scratch: torch.Tensor) -> None:
-    """out_ids[s] (int32) = argmax or Gumbel-max draw of logits[s] (float32 [n, V])."""
+def sample_scratch(max_rows: int, device) -> torch.Tensor:
+    """Scratch for `sample` with up to `max_rows` rows: zeroed, because the ticket counters in it must start
+    at zero (every launch leaves them at zero)."""
+    return torch.zeros(sample_scratch_bytes(max_rows) // 4, dtype=torch.int32, device=device)
+
+
+def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, seed: Optional[torch.Tensor],
+           scratch: torch.Tensor, row_keys: Optional[torch.Tensor] = None) -> None:
+    """out_ids[s] (int32) = argmax or Gumbel-max draw of logits[s] (float32 [n, V]); `scratch` from
+    `sample_scratch`.  The random numbers of row s come from `seed` (one 64-bit value) and s, or, with
+    `row_keys` (64 bits a row, as int64 or pairs of int32), from that row's key alone."""
     lib = build.load("sampling")
     n, V = logits.shape
     if logits.dtype != torch.float32:
         raise KernelError("sample: logits must be float32")
-    if scratch.numel() * scratch.element_size() < sample_scratch_bytes(n):
+    rows = scratch.numel() * scratch.element_size() // _SAMPLE_ROW_BYTES
+    if rows < n:
         raise KernelError("sample: scratch too small")
+    if row_keys is not None and row_keys.numel() * row_keys.element_size() < 8 * n:
+        raise KernelError("sample: one 64-bit key per row is required")
     _check(lib, lib.llmk_sample(_ptr(out_ids), _ptr(logits), c_longlong(_row_stride(logits)), _ptr(temps),
-                                _ptr(seed), c_int(n), c_int(V), _ptr(scratch), _stream()), 2)
+                                _ptr(seed), _ptr(row_keys), c_int(n), c_int(V), _ptr(scratch), c_int(rows), _stream()))

@@ -1,19 +1,14 @@
 """Causal grouped-query attention over the paged cache, as a mixer."""
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..cache.manager import FULL, WINDOW
 from ..kernels import ops
 from .base import KVRequest, LayerCache, Mixer
-from .linear import GEMM_MODULES, linear, linear_sliced
+from .linear import GEMM_MODULES, linear_sliced
 from .registry import build_position, norm_class, register_mixer
 from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
-
-NUM_SMS = 148
-_FORCE_ATTN = os.environ.get("LLMGEN_ATTN", "")      # "simt": the CUDA-core kernel everywhere
 
 
 class GQAAttention(Mixer):
@@ -54,8 +49,8 @@ class GQAAttention(Mixer):
         if spec.head_dim % 8 != 0 or spec.head_dim > 512:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 8, at most 512")
         for n in (spec.q_norm, spec.k_norm):
-            if n is not None and (n.kind != "rmsnorm" or n.dim != spec.head_dim):
-                raise ValueError("attention: per-head norms must be RMSNorm over head_dim")
+            if n is not None and (n.kind not in ops.HEAD_NORMS or n.dim != spec.head_dim):
+                raise ValueError(f"attention: per-head norms must run over head_dim and be one of {sorted(ops.HEAD_NORMS)}")
         self.spec = spec
         self.dtype = dtype
         self.nq, self.nkv, self.hd = spec.num_heads, spec.num_kv_heads, spec.head_dim
@@ -71,6 +66,11 @@ class GQAAttention(Mixer):
         self.q_off = float(spec.q_norm.weight_offset) if spec.q_norm else 0.0
         self.k_off = float(spec.k_norm.weight_offset) if spec.k_norm else 0.0
         self.position = build_position(spec.position, weights, dtype, device) if spec.position is not None else None
+        # which values of a head the position encoding turns together, and the kind of the per-head norms: the
+        # kernels are told and refuse what they do not implement
+        self.pairing = getattr(self.position, "pairing", "half") if self.position is not None else "half"
+        self.head_norm = (spec.q_norm or spec.k_norm).kind if (spec.q_norm or spec.k_norm) else "rmsnorm"
+        self.sm_count = ops.sm_count(device)
         self.window = int(spec.window or 0)
         self.bq = ops.attention_tile_queries(self.nq, self.nkv)
         self.tiles_name = f"attention_tiles_bq{self.bq}"
@@ -101,7 +101,7 @@ class GQAAttention(Mixer):
         builder.add(name + "_q0", [t[2] for t in tiles])
 
     def tc_tile_queries(self, page_size: int) -> int:
-        if self.dtype != torch.bfloat16 or _FORCE_ATTN == "simt":
+        if self.dtype != torch.bfloat16:
             return 0
         if page_size not in self._tc_bq:
             self._tc_bq[page_size] = ops.attention_tc_tile_queries(self.nq, self.nkv, self.hd, page_size)
@@ -131,7 +131,7 @@ class GQAAttention(Mixer):
         longest = ctx.max_ctx_bound if ctx.fixed_shapes else ctx.max_ctx
         if self.window:
             longest = min(longest, self.window)
-        by_sms = (2 * NUM_SMS + blocks - 1) // blocks
+        by_sms = (2 * self.sm_count + blocks - 1) // blocks
         by_len = max(1, longest // 128)
         parts = max(1, min(by_sms, by_len, 64))
         if self.window:
@@ -140,9 +140,15 @@ class GQAAttention(Mixer):
             return 1, 0
         return parts, 0
 
-    fuses_neighbours = True      # takes an operand that is not computed yet, adds to the residual when offered it
+    def workspace_bytes(self, tokens: int) -> int:
+        """Bytes of activations this part keeps in the step's workspace for `tokens` rows: the packed projection
+        (or its float32 slices at few rows), q, the attention's output and the output projection."""
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        packed = (self.nq + 2 * self.nkv) * self.hd
+        few = min(tokens, ops.SKINNY_MAX_ROWS) * 8 * max(packed, self.spec.hidden_size) * 4
+        return tokens * (packed + 2 * self.nq * self.hd + self.spec.hidden_size) * elem + few
 
-    def forward(self, ctx, x, cache: LayerCache, add_to: torch.Tensor = None):
+    def forward(self, ctx, x, cache: LayerCache):
         T = ctx.n_tokens
         ws = ctx.workspace
         group = ctx.groups[cache.group]
@@ -153,18 +159,20 @@ class GQAAttention(Mixer):
         rot = self.position.rotary_dim if self.position is not None else 0
         o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
         scale = float(self.spec.scale)
-        decode = (self.dtype == torch.bfloat16 and ctx.pure_decode and _FORCE_ATTN != "simt"
+        decode = (self.dtype == torch.bfloat16 and ctx.pure_decode
                   and ops.attention_decode_usable(self.nq, self.nkv, self.hd, cache.page_size))
         if decode and ops.attention_decode_fuses_prep(self.hd, rot):
             # single decoded tokens: the attention kernel normalises, rotates and stores q, k and v itself
             self._decode(ctx, o, None, cache, group, scale,
                          prep=dict(packed=packed, nk=nk, rot=rot, positions=ctx.positions, slots=group.slots, cos=cos,
                                    sin=sin, q_gain=self.q_gain, k_gain=self.k_gain, eps=self.norm_eps,
-                                   q_offset=self.q_off, k_offset=self.k_off))
-            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype, add_to=add_to)
+                                   q_offset=self.q_off, k_offset=self.k_off, pairing=self.pairing,
+                                   head_norm=self.head_norm))
+            return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         q = ws.buffer("attn_q", T, self.nq * self.hd, self.dtype) if isinstance(packed, ops.Partials) else packed
         ops.attn_prep(packed, cache.k, cache.v, ctx.positions, group.slots, cos, sin, self.q_gain, self.k_gain,
-                      self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q)
+                      self.nq, nk, self.hd, rot, cache.page_size, self.norm_eps, self.q_off, self.k_off, q_out=q,
+                      pairing=self.pairing, head_norm=self.head_norm)
         packed = q
         if decode:
             self._decode(ctx, o, packed, cache, group, scale)
@@ -188,7 +196,6 @@ class GQAAttention(Mixer):
                             self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch)
         return linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
 
-
     def _decode(self, ctx, o, q, cache, group, scale, prep=None) -> None:
         """Single decoded tokens: as many key parts as fill the SMs, at least 128 keys a part; the
         bound of the step's context class decides, not the lengths."""
@@ -202,7 +209,7 @@ class GQAAttention(Mixer):
         visible = min(bound, self.window) if self.window else bound
         blocks = max(1, S * self.nkv * chunks)
         # as many blocks as are resident at a time (2 per SM), at least 128 keys a part, at most 64 parts
-        parts = max(1, min((2 * NUM_SMS) // blocks, visible // 128, 64))
+        parts = max(1, min((2 * self.sm_count) // blocks, visible // 128, 64))
         scratch = counters = None
         if parts > 1:
             scratch = ws.flat("attn_decode_split", ops.attention_decode_scratch_floats(S, self.nq, self.hd, parts),

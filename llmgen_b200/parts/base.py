@@ -13,9 +13,6 @@ Norm:
                                               of the compute dtype, or a `kernels.ops.Partials`
                                               (float32 slices to be added up), whichever the
                                               part before it returned
-    deferred(resid, squares)                  optional: the norm as an operand that its consumer
-                                              computes itself (`kernels.ops.NormedRows`), given the
-                                              rows' sums of squares (`kernels.ops.RowSquares`)
 Position encoding:
     tables()                                  whatever its mixer's kernel needs (cos, sin)
 Mixer:
@@ -31,11 +28,10 @@ Mixer:
                                               `Partials` (see `parts.linear.linear_sliced`)
 Feed-forward:
     forward(ctx, x) -> [T, H]                 an array or a `Partials`
-Mixer and feed-forward, optional:
-    fuses_neighbours = True                   class attribute: `forward` also takes `add_to=resid`
-                                              and an `x` that is not computed yet (`NormedRows`);
-                                              if it added its output to `resid` itself it returns
-                                              a `RowSquares`, anything else has not been added
+Mixer, feed-forward and block, optional:
+    workspace_bytes(tokens) -> int            bytes of activations a step of `tokens` rows keeps in
+                                              the workspace for this part; the engine leaves that
+                                              much device memory beside the cache pages
 Block:
     mixer                                     the block's mixer (the engine asks it for cache)
     forward(ctx, resid, delta, cache) -> delta_out

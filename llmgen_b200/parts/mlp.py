@@ -1,19 +1,14 @@
 """Dense gated feed-forward (SwiGLU for Qwen3)."""
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..kernels import ops
 from .base import FeedForward
-from . import linear as linear_module
 from .linear import GEMM_MODULES, gated_product_usable, linear, linear_sliced
 from .registry import register_feed_forward
 from .spec import GatedMLPSpec, WeightDecl
 
-
-CLUSTER_GATED = os.environ.get("LLMGEN_GATED", "") != "separate"    # "separate": slices, then a kernel for the activation
 GATE_UP_GROUP = 16   # rows of gate, then rows of up, alternating: what the gated epilogue expects
 
 
@@ -62,45 +57,25 @@ class GatedMLP(FeedForward):
         self.w_gate_up = packed.to(device=device, dtype=dtype).contiguous()
         self.w_down = weights.device_tensor(spec.down_proj, dtype, device)
 
-    fuses_neighbours = True      # takes operands that are not computed yet, adds to the residual when offered it
+    def workspace_bytes(self, tokens: int) -> int:
+        """Bytes of activations this part keeps in the step's workspace for `tokens` rows: the packed gate/up
+        product or its float32 slices (few rows only), the activation and the output."""
+        F, H = self.spec.intermediate_size, self.spec.hidden_size
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        return tokens * (2 * F + F + H) * elem + min(tokens, ops.SKINNY_MAX_ROWS) * 8 * max(2 * F, H) * 4
 
-    def forward(self, ctx, x, add_to: torch.Tensor = None):
+    def forward(self, ctx, x):
         T = x.shape[0]
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
-        if isinstance(x, ops.AddNormRows):
-            # the residual add and the norm before, the sum of the slices and the activation after: one product
-            splits = 0
-            if self.group == GATE_UP_GROUP and CLUSTER_GATED and linear_module._FORCE == "" and linear_module._SPLITK == "":
-                splits = ops.gemm_skinny_addnorm_splits(x, self.w_gate_up, True)
-            if splits >= 2:
-                act = ws.buffer("ffn_act", T, F, self.dtype)
-                ops.gemm_skinny_addnorm(act, x, self.w_gate_up, splits, gated=True)
-                return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
-            x = x.materialize(ws.buffer("ffn_x", T, H, self.dtype))
-        few = self.dtype == torch.bfloat16 and T <= linear_module.FUSE_CHAIN_MAX_ROWS and linear_module.FUSE_CHAIN
-        if not isinstance(x, torch.Tensor) and not few:
-            x = x.materialize(ws.buffer("ffn_x", T, H, self.dtype))
-        lazy = not isinstance(x, torch.Tensor)
-        whole = (not lazy and self.group == GATE_UP_GROUP and gated_product_usable(x, self.w_gate_up)
-                 and ops.gemm_skinny_splits(T, 2 * F, H) == 1)          # one block column streams all of K: gated epilogue
-        if few and (lazy or add_to is not None) and not whole:
-            # few rows: the norm before, the activation between and the residual sum after are
-            # folded into the two products where the few-rows kernel can take them
-            gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
-            if isinstance(gate_up, ops.Partials) and self.group % 8 == 0:
-                return linear_sliced(ws, "ffn_out", ops.GatedRows(gate_up, self.group), self.w_down, self.dtype, add_to=add_to)
-            act = ws.buffer("ffn_act", T, F, self.dtype)
-            ops.silu_mul(act, gate_up, group=self.group)
-            return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
         act = ws.buffer("ffn_act", T, F, self.dtype)
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
-        if gated and CLUSTER_GATED and T <= ops.SKINNY_CLUSTER_MAX_ROWS and linear_module._SPLITK == "" \
-                and min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) >= 2:
+        cluster = min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) if gated and T <= ops.SKINNY_CLUSTER_MAX_ROWS else 1
+        if cluster >= 2:
             # few rows: K is cut, the slices are added up inside a thread-block cluster and the activation
             # follows there, so neither the packed product nor a kernel for the activation is needed
-            ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_CLUSTER_GATED,
-                            splits=min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4))
+            # (0.982 -> 0.967 ms a decode step at batch 8 against slices and an activation kernel)
+            ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_CLUSTER_GATED, splits=cluster)
         elif gated and T <= ops.SKINNY_MAX_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
             ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_GATED)
         elif gated and T > ops.SKINNY_MAX_ROWS:
@@ -108,7 +83,7 @@ class GatedMLP(FeedForward):
         else:
             gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
             ops.silu_mul(act, gate_up, group=self.group)
-        return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype, add_to=add_to)
+        return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

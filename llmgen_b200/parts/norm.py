@@ -36,15 +36,5 @@ class RMSNorm(Part):
         ops.add_rmsnorm(resid, delta, self.weight, out, self.eps, self.offset, rows=rows)
         return out
 
-    def deferred_add(self, resid_in: torch.Tensor, delta: "ops.Partials", resid_out: torch.Tensor) -> "ops.AddNormRows":
-        """norm(resid_in + delta) as an operand that the consuming product computes itself; the product
-        also leaves the sum in `resid_out`."""
-        return ops.AddNormRows(resid_in, delta, resid_out, self.weight, self.eps, self.offset)
-
-    def deferred(self, resid: torch.Tensor, squares: "ops.RowSquares") -> "ops.NormedRows":
-        """The norm of `resid` as an operand that the consuming product computes itself, given the
-        rows' sums of squares that the product before it left."""
-        return ops.NormedRows(resid, squares, self.weight, self.eps, self.offset)
-
 
 register_norm("rmsnorm", RMSNorm)

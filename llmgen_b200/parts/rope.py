@@ -31,6 +31,7 @@ class Rope(Part):
                             ang.sin().to(torch.float32).to(device).contiguous())
         self.cos, self.sin = _TABLES[key]
         self.rotary_dim = spec.rotary_dim
+        self.pairing = spec.pairing
         self.max_positions = spec.max_positions
 
     def tables(self):

@@ -51,14 +51,17 @@ class RMSNormSpec:
 # ----------------------------------------------------------------- position encodings
 @dataclass(frozen=True)
 class RopeSpec:
-    """Rotary position encoding in half-split (NEOX) pairing over the first `rotary_dim`
-    values of a head: pair (i, i + rotary_dim/2), angle = pos / theta^(2i/rotary_dim).
+    """Rotary position encoding over the first `rotary_dim` values of a head, angle =
+    pos / theta^(2i/rotary_dim).  `pairing` says which two values are turned together: "half" is the
+    half-split (NEOX) pairing (i, i + rotary_dim/2) of the reference; the attention kernels are told
+    the pairing and refuse one they do not implement.
 
     Reference: src/module/rope.zig:60-107, src/backend/cpu/rope.zig:13-75.
     """
     rotary_dim: int
     theta: float
     max_positions: int
+    pairing: str = "half"
     kind: str = "rope"
 
 

@@ -215,47 +215,6 @@ def test_layer_sizes_of_the_larger_models(tmp, hidden, heads, kv_heads, inter):
     assert outs[False] == outs[True]
 
 
-def test_chain_of_fused_products_when_switched_on(tmp, monkeypatch):
-    """LLMGEN_FUSE=chain: decoded tokens of a two-layer model at the benchmark's layer geometry go
-    through the few-rows products that build their operands themselves and add to the residual;
-    the logits still follow the plain implementation and graph replay still equals eager steps."""
-    from llmgen_b200 import LLM, SamplingParams
-    from llmgen_b200.engine.api import write_random_model
-    from llmgen_b200.kernels import ops
-    from llmgen_b200.parts import linear as linear_module
-    from tests.util import Driver, logits_close
-    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 700, "hidden_size": 1024,
-           "intermediate_size": 3072, "num_hidden_layers": 2, "num_attention_heads": 16, "num_key_value_heads": 8,
-           "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 1024,
-           "tie_word_embeddings": True, "hidden_act": "silu"}
-    path = os.path.join(tmp, "chain")
-    write_random_model(path, cfg, 12, 0.02, 0.1, "bfloat16")
-    monkeypatch.setattr(linear_module, "FUSE_CHAIN", True)
-    calls = {"n": 0}
-    plain_fused = ops.gemm_skinny_fused
-
-    def counted(*a, **k):
-        calls["n"] += 1
-        return plain_fused(*a, **k)
-
-    monkeypatch.setattr(ops, "gemm_skinny_fused", counted)
-    ids = random_ids(80, 700, 6)
-    ref = PlainQwen3(path).logits(ids)
-    d = Driver(path, "bfloat16", 256, 16)
-    logits_close(d.step([("a", ids[:60], range(60))]), ref[:60], "bfloat16")
-    assert calls["n"] == 0                                  # a prompt's portion is not few rows
-    for i in range(60, 80):
-        logits_close(d.step([("a", ids[i:i + 1], [0])]), ref[i:i + 1], "bfloat16")
-    other_switches = any(os.environ.get(k) for k in ("LLMGEN_GEMM", "LLMGEN_SPLITK", "LLMGEN_ATTN"))
-    if not other_switches:          # those take some or all of the products elsewhere
-        assert calls["n"] == 20 * (2 * 4 - 1)               # per layer o, gate_up, down and, after the first layer, qkv
-    outs = {}
-    for eager in (False, True):
-        llm = LLM(path, dtype="bfloat16", max_model_len=256, max_num_seqs=4, max_batched_tokens=1024, kv_blocks=64, eager=eager)
-        outs[eager] = [r["token_ids"] for r in llm.generate([ids[:50], ids[:7], ids[:33]], SamplingParams(0.0, 12, True))]
-    assert outs[False] == outs[True]
-
-
 def test_decode_steps_launched_one_ahead_give_what_steps_read_at_once_give(tmp):
     """The engine launches a decode step before it has read the ids of the step before (the GPU takes
     them from where that step left them).  Same ids as with `run_ahead` off: with requests that end at
@@ -327,46 +286,6 @@ def test_decode_launch_takes_ids_from_the_rows_of_the_step_before(tmp):
         runs[fed] = got
     # "a" sits out the third step: in the fed run its id for the fourth comes from the host (known by then)
     assert runs[True] == runs[False]
-
-
-def test_products_that_add_and_normalise_themselves_when_switched_on(tmp, monkeypatch):
-    """LLMGEN_ADDNORM=fused: decoded tokens at the benchmark's layer geometry go through products that add the
-    slices before them to the residual and normalise their rows themselves, the residual alternating between
-    two arrays; logits follow the plain implementation and graph replay equals eager steps."""
-    from llmgen_b200 import LLM, SamplingParams
-    from llmgen_b200.engine.api import write_random_model
-    from llmgen_b200.kernels import ops
-    from llmgen_b200.parts import linear as linear_module
-    from tests.util import Driver, logits_close
-    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 700, "hidden_size": 1024,
-           "intermediate_size": 3072, "num_hidden_layers": 3, "num_attention_heads": 16, "num_key_value_heads": 8,
-           "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 1024,
-           "tie_word_embeddings": True, "hidden_act": "silu"}
-    path = os.path.join(tmp, "addnorm")
-    write_random_model(path, cfg, 13, 0.02, 0.1, "bfloat16")
-    monkeypatch.setattr(linear_module, "ADDNORM", True)
-    calls = {"n": 0}
-    plain_fused = ops.gemm_skinny_addnorm
-
-    def counted(*a, **k):
-        calls["n"] += 1
-        return plain_fused(*a, **k)
-
-    monkeypatch.setattr(ops, "gemm_skinny_addnorm", counted)
-    ids = random_ids(80, 700, 7)
-    ref = PlainQwen3(path).logits(ids)
-    d = Driver(path, "bfloat16", 256, 16)
-    logits_close(d.step([("a", ids[:60], range(60))]), ref[:60], "bfloat16")
-    assert calls["n"] == 0
-    for i in range(60, 80):
-        logits_close(d.step([("a", ids[i:i + 1], [0])]), ref[i:i + 1], "bfloat16")
-    if not any(os.environ.get(k) for k in ("LLMGEN_GEMM", "LLMGEN_SPLITK", "LLMGEN_ATTN", "LLMGEN_FUSE", "LLMGEN_GATED")):
-        assert calls["n"] == 20 * (2 * 3 - 1)        # per layer gate_up and, after the first layer, qkv
-    outs = {}
-    for eager in (False, True):
-        llm = LLM(path, dtype="bfloat16", max_model_len=256, max_num_seqs=4, max_batched_tokens=1024, kv_blocks=64, eager=eager)
-        outs[eager] = [r["token_ids"] for r in llm.generate([ids[:50], ids[:7], ids[:33]], SamplingParams(0.0, 12, True))]
-    assert outs[False] == outs[True]
 
 
 @pytest.mark.parametrize("seed", [1, 2, 3])

@@ -250,13 +250,12 @@ def test_costs_of_the_small_kernels():
     assert nbytes == 2 * 7 * 80 * 4 + 7 * 80 * 2 + 7 * 80 * 2 + 80 * 4 and flops == 5 * 7 * 80
     flops, nbytes = pf._cost_norm({"resid": resid, "delta": None, "weight": gain, "out": y[:2], "rows": ids[:2], "write_resid": True}, info)
     assert nbytes == 2 * 80 * 4 + 2 * 80 * 2 + 80 * 4
-    # slices of a product cut along K count with all their bytes; an operand not computed yet as its rows
+    # slices of a product cut along K count with all their bytes
     slices = types.SimpleNamespace(tensor=torch.zeros(4, 7, 80, dtype=torch.float32))
-    assert pf._nbytes(slices) == 4 * 7 * 80 * 4
-    assert pf._nbytes(types.SimpleNamespace(shape=(7, 80))) == 7 * 80 * 2 and pf._nbytes(None) == 0
-    lazy = types.SimpleNamespace(shape=(7, 80))
+    assert pf._nbytes(slices) == 4 * 7 * 80 * 4 and pf._nbytes(None) == 0
+    x = torch.zeros(7, 80, dtype=torch.bfloat16)
     w = torch.zeros(48, 80, dtype=torch.bfloat16)
-    flops, nbytes = pf._cost_product({"slices": slices.tensor, "x": lazy, "w": w, "add_to": None}, info)
+    flops, nbytes = pf._cost_product({"out": slices.tensor, "a": x, "w": w}, info)
     assert flops == 2 * 7 * 48 * 80 and nbytes == 48 * 80 * 2 + 7 * 80 * 2 + 4 * 7 * 80 * 4
 
 

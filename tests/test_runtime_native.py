@@ -149,10 +149,10 @@ def test_decode_step_arrays_are_filled_natively_and_rows_rewritten_only_when_a_t
     lengths = {10: 9, 11: 4, 12: 17}
     for r, n in lengths.items():
         assert cache.admit(r) is not None and cache.reserve(r, 0, n + 1)
-    words = 6 * bucket + 2 * (bucket + bucket * max_blocks)
+    words = 8 * bucket + 2 * (bucket + bucket * max_blocks)
     host = (ctypes.c_int * words)()
     offs, at = [], 0
-    for size in [bucket] * 6 + [bucket, bucket * max_blocks] * 2:
+    for size in [bucket] * 6 + [2 * bucket] + [bucket, bucket * max_blocks] * 2:
         offs.append(at)
         at += size
     offs_c = (ctypes.c_int * len(offs))(*offs)
@@ -163,13 +163,17 @@ def test_decode_step_arrays_are_filled_natively_and_rows_rewritten_only_when_a_t
         rc = lib.llmr_fill_decode(cache.native_handle, host, offs_c, ctypes.c_int(n), ctypes.c_int(bucket),
                                   ctypes.c_int(max_blocks), (ctypes.c_longlong * n)(*[cache.key(r) for r in reqs]),
                                   (ctypes.c_int * n)(*tokens), (ctypes.c_int * n)(*(rows_before or [-1] * n)),
-                                  (ctypes.c_int * n)(*starts), (ctypes.c_float * n)(*temps), stamps)
+                                  (ctypes.c_int * n)(*starts), (ctypes.c_float * n)(*temps), ctypes.c_ulonglong(SEED), stamps)
         return rc, np.frombuffer(host, dtype=np.int32).copy()
 
+    SEED, STRIDE, M64 = 0x5EED5EED5EED, 0x9E3779B97F4A7C15, (1 << 64) - 1
     reqs = [10, 11, 12]
     starts = [lengths[r] for r in reqs]
     rc, a = fill(reqs, [5, 6, 7], starts, [0.0, 0.5, 1.0])
     assert rc == 0
+    # the sampler's key of a row: the request and the position, not the row or the number of steps
+    keys = a[offs[6]:offs[6] + 8].view(np.uint64).tolist()
+    assert keys == [((SEED + STRIDE * (p + 1)) & M64) ^ ((r << 40) & M64) for r, p in zip(reqs, starts)] + [0]
     assert a[offs[0]:offs[0] + 4].tolist() == [5, 6, 7, 0]
     assert a[offs[1]:offs[1] + 4].tolist() == starts + [0]
     assert a[offs[2]:offs[2] + 4].tolist() == [s + 1 for s in starts] + [0]
@@ -177,25 +181,25 @@ def test_decode_step_arrays_are_filled_natively_and_rows_rewritten_only_when_a_t
     assert a[offs[4]:offs[4] + 4].view(np.float32).tolist() == [0.0, 0.5, 1.0, 0.0]
     assert a[offs[5]:offs[5] + 4].tolist() == [-1, -1, -1, -1]
     for g, group in enumerate(cache.groups):
-        slots = a[offs[6 + 2 * g]:offs[6 + 2 * g] + 4].tolist()
+        slots = a[offs[7 + 2 * g]:offs[7 + 2 * g] + 4].tolist()
         assert slots == [group.slot_of(r, p) for r, p in zip(reqs, starts)] + [-1]
-        rows = a[offs[7 + 2 * g]:offs[7 + 2 * g] + bucket * max_blocks].reshape(bucket, max_blocks)
+        rows = a[offs[8 + 2 * g]:offs[8 + 2 * g] + bucket * max_blocks].reshape(bucket, max_blocks)
         for s, r in enumerate(reqs):
             t = group.table(r)
             assert rows[s, :len(t)].tolist() == t and not rows[s, len(t):].any()
         assert not rows[3].any()
     # a row that holds the same table at the same length is left alone (its stamp matches) ...
-    host[offs[7] + 0] = 999
+    host[offs[8] + 0] = 999
     rc, a = fill(reqs, [5, 6, 7], starts, [0.0, 0.5, 1.0])
-    assert rc == 0 and a[offs[7] + 0] == 999
+    assert rc == 0 and a[offs[8] + 0] == 999
     # ... and written again once the table has grown, or when another request takes the row
     assert cache.reserve(10, lengths[10] + 1, lengths[10] + 1 + page_size)
     rc, a = fill(reqs, [5, 6, 7], starts, [0.0, 0.5, 1.0])
-    assert rc == 0 and a[offs[7]:offs[7] + max_blocks].tolist()[:len(cache.groups[0].table(10))] == cache.groups[0].table(10)
+    assert rc == 0 and a[offs[8]:offs[8] + max_blocks].tolist()[:len(cache.groups[0].table(10))] == cache.groups[0].table(10)
     rc, a = fill([12, 11], [1, 2], [lengths[12], lengths[11]], [0.0, 0.0])
     t = cache.groups[0].table(12)
-    assert rc == 0 and a[offs[7]:offs[7] + len(t)].tolist() == t
-    assert not a[offs[7] + 2 * max_blocks:offs[7] + 3 * max_blocks].any()        # row 2 is padding now
+    assert rc == 0 and a[offs[8]:offs[8] + len(t)].tolist() == t
+    assert not a[offs[8] + 2 * max_blocks:offs[8] + 3 * max_blocks].any()        # row 2 is padding now
     # ids that are still on the device: the row of the step before is passed on, the id left at zero
     rc, a = fill(reqs, [5, 6, 7], starts, [0.0, 0.5, 1.0], rows_before=[2, -1, 0])
     assert rc == 0 and a[offs[0]:offs[0] + 4].tolist() == [0, 6, 0, 0] and a[offs[5]:offs[5] + 4].tolist() == [2, -1, 0, -1]

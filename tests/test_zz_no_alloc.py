@@ -45,7 +45,7 @@ def test_static_scratch_sampler_equals_the_ordinary_one_on_two_calls_in_a_row():
         temps = torch.tensor([0.0, 0.8, 1.3, 0.0, 0.5, 2.0, 0.0][:S]).cuda()
         seed = torch.tensor([977 + call], dtype=torch.int64, device="cuda")
         want = torch.zeros(S, dtype=torch.int32, device="cuda")
-        scratch = torch.empty(ops.sample_scratch_bytes(S) // 4, dtype=torch.float32, device="cuda")
+        scratch = ops.sample_scratch(S, "cuda")
         ops.sample(want, logits, temps, seed, scratch)
         got = torch.full((S,), -1, dtype=torch.int32, device="cuda")
         rc = _call_static(lib, got, logits, temps, seed)
