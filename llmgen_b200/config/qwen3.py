@@ -90,7 +90,7 @@ class Qwen3Config:
 
         # Which layers attend through a window.
         window = r.integer("sliding_window", default=None)
-        use_window = r.boolean("use_sliding_window", default=False)
+        use_window = r.boolean("use_sliding_window", default=None)
         layer_types = r.raw("layer_types")
         types: Tuple[str, ...] = ()
         if layers is not None:
@@ -99,6 +99,10 @@ class Qwen3Config:
                         or any(t not in (FULL_ATTENTION, SLIDING_ATTENTION) for t in layer_types)):
                     r.problem(f"'layer_types' must list {layers} entries of "
                               f"'{FULL_ATTENTION}' or '{SLIDING_ATTENTION}'")
+                elif use_window is False:
+                    # the switch is off: every layer attends to all keys whatever the list and
+                    # 'sliding_window' say (configurations are exported with the list left in place)
+                    types = tuple(FULL_ATTENTION for _ in range(layers))
                 else:
                     types = tuple(layer_types)
             elif use_window and window is not None:

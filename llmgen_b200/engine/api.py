@@ -56,7 +56,7 @@ def load_model(model_dir: str, dtype=torch.bfloat16, device="cuda:0") -> Decoder
     dev = require_cuda(device)
     arch, cfg = config_from_folder(model_dir)
     spec = arch.build_spec(cfg)
-    weights = open_weights(model_dir, model_weight_decls(spec))
+    weights = open_weights(model_dir, model_weight_decls(spec), spec.ignorable_tensors, spec.same_as)
     return DecoderModel(spec, weights, resolve_dtype(dtype), dev)
 
 

@@ -104,7 +104,7 @@ def describe(model_dir: Optional[str] = None, config: Optional[dict] = None, con
         has_file = any(name.endswith(".safetensors") for name in os.listdir(model_dir))
         if has_file:
             from .weights import open_weights
-            store = open_weights(model_dir, decls)
+            store = open_weights(model_dir, decls, spec.ignorable_tensors, spec.same_as)
             stored = Counter(str(store.directory.entry(d.name).dtype) for d in decls)
             lines.append("  model file: every declared tensor is there with its shape ("
                          + ", ".join(f"{n} stored as {k}" for k, n in sorted(stored.items())) + ")")

@@ -60,7 +60,11 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
         embedding=embedding, layers=tuple(layers), run_order=default_run_order(cfg.num_hidden_layers),
         final_norm=RMSNormSpec(cfg.hidden_size, cfg.rms_norm_eps, "model.norm.weight"),
         lm_head=embedding if cfg.tie_word_embeddings else "lm_head.weight",
-        max_positions=cfg.max_position_embeddings, eos_token_ids=cfg.eos_token_ids)
+        max_positions=cfg.max_position_embeddings, eos_token_ids=cfg.eos_token_ids,
+        # exports of tied models often still carry the output matrix (a copy of the table), and some carry the
+        # rotary inverse frequencies as a buffer: neither is read, the copy must be one
+        ignorable_tensors=(("lm_head.weight",) if cfg.tie_word_embeddings else ()) + ("*.rotary_emb.inv_freq",),
+        same_as=(("lm_head.weight", embedding),) if cfg.tie_word_embeddings else ())
 
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config, build_qwen3_spec, aliases=("qwen3",))

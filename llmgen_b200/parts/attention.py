@@ -54,8 +54,9 @@ class GQAAttention(Mixer):
         self.spec = spec
         self.dtype = dtype
         self.nq, self.nkv, self.hd = spec.num_heads, spec.num_kv_heads, spec.head_dim
-        self.w_qkv = torch.cat([weights.host_tensor(spec.q_proj), weights.host_tensor(spec.k_proj),
-                                weights.host_tensor(spec.v_proj)], dim=0).to(device=device, dtype=dtype).contiguous()
+        # packed on the device: each matrix goes up through the loader's pinned stage as the file holds it
+        self.w_qkv = torch.cat([weights.device_tensor(n, dtype, device, keep=False) for n in (spec.q_proj, spec.k_proj, spec.v_proj)],
+                               dim=0).contiguous()
         self.w_q = self.w_qkv[: self.nq * self.hd]
         self.w_o = weights.device_tensor(spec.o_proj, dtype, device)
         self.q_gain = weights.device_tensor(spec.q_norm.weight, dtype, device) if spec.q_norm else None

@@ -47,14 +47,16 @@ class GatedMLP(FeedForward):
         self.spec = spec
         self.dtype = dtype
         F = spec.intermediate_size
-        w_gate, w_up = weights.host_tensor(spec.gate_proj), weights.host_tensor(spec.up_proj)
+        # packed on the device: each matrix goes up through the loader's pinned stage as the file holds it
+        w_gate = weights.device_tensor(spec.gate_proj, dtype, device, keep=False)
+        w_up = weights.device_tensor(spec.up_proj, dtype, device, keep=False)
         if dtype == torch.bfloat16 and F % GATE_UP_GROUP == 0:
             self.group = GATE_UP_GROUP
             packed = interleave_gate_up(w_gate, w_up)
         else:
             self.group = F
             packed = torch.cat([w_gate, w_up], dim=0)
-        self.w_gate_up = packed.to(device=device, dtype=dtype).contiguous()
+        self.w_gate_up = packed.contiguous()
         self.w_down = weights.device_tensor(spec.down_proj, dtype, device)
 
     def workspace_bytes(self, tokens: int) -> int:

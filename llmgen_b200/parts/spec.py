@@ -152,6 +152,10 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     init_sigma: float = 0.02             # defaults of the random-weights mode
     init_sigma_norm: float = 0.1
+    # Tensors that a model folder of this architecture may carry although the model reads none of them
+    # (shell patterns), and (name, declared name) pairs of such tensors that must then hold the same values.
+    ignorable_tensors: Tuple[str, ...] = ()
+    same_as: Tuple[Tuple[str, str], ...] = ()
 
     @property
     def tied(self) -> bool:

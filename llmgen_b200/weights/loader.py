@@ -16,7 +16,8 @@ and shared (tied embeddings; src/memory/manager.zig:269-279).
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Sequence
+import fnmatch
+from typing import Dict, Iterable, List, Sequence, Tuple
 
 import torch
 
@@ -44,6 +45,54 @@ def check_declarations(decls: Sequence[WeightDecl]) -> Dict[str, WeightDecl]:
     return merged
 
 
+class PinnedStage:
+    """Host-to-device copies of tensors that live in a memory-mapped file: through two pinned buffers of
+    32 MiB used in turn, so that the copy engine reads page-locked memory while the host fills the other
+    buffer from the file (the reference stages its uploads the same way, src/memory/manager.zig:263-300).
+    A pageable `.to(device)` would have the driver stage every tensor through a small buffer of its own,
+    one synchronous piece at a time."""
+
+    CHUNK = 32 << 20
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._buffers = None
+        self._events = [None, None]
+        self._turn = 0
+        self.bytes_moved = 0
+
+    def upload(self, src: torch.Tensor) -> torch.Tensor:
+        """A device tensor with the values (and dtype) of the host tensor `src`."""
+        if self.device.type != "cuda" or src.numel() * src.element_size() < (1 << 20):
+            return src.to(self.device)
+        if self._buffers is None:
+            self._buffers = [torch.empty(self.CHUNK, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        src = src.contiguous()
+        out = torch.empty(src.shape, dtype=src.dtype, device=self.device)
+        from_bytes = src.reshape(-1).view(torch.uint8)
+        to_bytes = out.reshape(-1).view(torch.uint8)
+        total = from_bytes.numel()
+        for at in range(0, total, self.CHUNK):
+            turn = self._turn
+            self._turn ^= 1
+            if self._events[turn] is not None:
+                self._events[turn].synchronize()         # the copy that last read this buffer has finished
+            n = min(self.CHUNK, total - at)
+            self._buffers[turn][:n].copy_(from_bytes[at:at + n])
+            to_bytes[at:at + n].copy_(self._buffers[turn][:n], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[turn] = ev
+        self.bytes_moved += total
+        return out
+
+    def close(self) -> None:
+        for ev in self._events:
+            if ev is not None:
+                ev.synchronize()
+        self._buffers, self._events = None, [None, None]
+
+
 class WeightStore:
     """Checked access to a folder's tensors; uploads each name once."""
 
@@ -51,13 +100,22 @@ class WeightStore:
         self.directory = directory
         self.decls = decls
         self._device_cache: Dict[tuple, torch.Tensor] = {}
+        self._stages: Dict[str, PinnedStage] = {}
+
+    def _stage(self, device) -> PinnedStage:
+        key = str(device)
+        if key not in self._stages:
+            self._stages[key] = PinnedStage(device)
+        return self._stages[key]
 
     def host_tensor(self, name: str) -> torch.Tensor:
         if name not in self.decls:
             raise WeightError(f"tensor {name!r} was not declared by any part")
         return self.directory.tensor(name)
 
-    def device_tensor(self, name: str, compute_dtype: torch.dtype, device) -> torch.Tensor:
+    def device_tensor(self, name: str, compute_dtype: torch.dtype, device, keep: bool = True) -> torch.Tensor:
+        """The tensor on the device in the dtype its kind asks for.  `keep=False`: the caller packs it into a
+        tensor of its own and nobody else reads it, so the store does not hold on to the upload."""
         decl = self.decls.get(name)
         if decl is None:
             raise WeightError(f"tensor {name!r} was not declared by any part")
@@ -68,20 +126,36 @@ class WeightStore:
         else:
             dtype = torch.int32
         key = (name, dtype, str(device))
-        if key not in self._device_cache:
-            self._device_cache[key] = self.directory.tensor(name).to(device=device, dtype=dtype).contiguous()
-        return self._device_cache[key]
+        if key in self._device_cache:
+            return self._device_cache[key]
+        # the file's bytes go up as they are; a change of dtype (an exact widening) happens on the device
+        t = self._stage(device).upload(self.directory.tensor(name)).to(dtype).contiguous()
+        if keep:
+            self._device_cache[key] = t
+        return t
 
     def release(self) -> None:
-        """Drop the upload cache (the parts keep what they took)."""
+        """Drop the upload cache and the pinned buffers (the parts keep what they took)."""
         self._device_cache.clear()
+        for stage in self._stages.values():
+            stage.close()
+        self._stages.clear()
 
 
-def validate(directory, decls: Dict[str, WeightDecl], where: str) -> None:
+def validate(directory, decls: Dict[str, WeightDecl], where: str, ignorable: Sequence[str] = (),
+             same_as: Sequence[Tuple[str, str]] = ()) -> None:
+    """One `WeightError` for everything that does not fit.  `ignorable`: shell patterns of tensors the folder
+    may carry unread; `same_as`: (such a tensor, a declared one) whose values must then be equal, as for the
+    output matrix that exports of tied models carry beside the table it copies."""
     present = set(directory.names())
     missing = [n for n in decls if n not in present]
-    unexpected = sorted(present - set(decls))
+    unexpected = sorted(n for n in present - set(decls) if not any(fnmatch.fnmatchcase(n, pat) for pat in ignorable))
     wrong: List[str] = []
+    for extra, declared in same_as:
+        if extra in present and extra not in decls and declared in present:
+            a, b = directory.entry(extra), directory.entry(declared)
+            if tuple(a.shape) != tuple(b.shape) or a.dtype != b.dtype or not torch.equal(directory.tensor(extra), directory.tensor(declared)):
+                wrong.append(f"{extra}: the model reads {declared} in its place (tied), but the two differ")
     for name, d in decls.items():
         if name not in present:
             continue
@@ -102,13 +176,14 @@ def validate(directory, decls: Dict[str, WeightDecl], where: str) -> None:
         raise WeightError("\n".join(parts))
 
 
-def open_weights(model_dir: str, decls: Iterable[WeightDecl]) -> WeightStore:
+def open_weights(model_dir: str, decls: Iterable[WeightDecl], ignorable: Sequence[str] = (),
+                 same_as: Sequence[Tuple[str, str]] = ()) -> WeightStore:
     merged = check_declarations(list(decls))
     try:
         directory = TensorDirectory(model_dir)
     except SafetensorsError as e:
         raise WeightError(str(e)) from None
-    validate(directory, merged, model_dir)
+    validate(directory, merged, model_dir, ignorable, same_as)
     return WeightStore(directory, merged)
 
 

@@ -137,11 +137,17 @@ class PlainQwen3:
     """Reads config.json and model.safetensors of a folder and computes logits of whole
     sequences (src/models/qwen3.zig:224-236, 300-330)."""
 
-    def __init__(self, model_dir: str, dtype: torch.dtype = torch.float32):
+    def __init__(self, model_dir: str, dtype: torch.dtype = torch.float32, round_to: Optional[torch.dtype] = None):
+        """`round_to=torch.bfloat16`: weights and the output of every node are rounded to bfloat16 and widened
+        again, which is how the reference computes with bfloat16 activations (each node of its graph stores
+        its result in the activation dtype, src/models/qwen3.zig:153-162, src/backend/cpu/norm.zig:60-93).
+        The distance between such a run and the exact one is the scale of what bfloat16 arithmetic costs on
+        this model; tests bound the engine's bfloat16 error by a multiple of it."""
         with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
             c = json.load(f)
         self.c = c
         self.dtype = dtype
+        self.round_to = round_to
         self.L = c["num_hidden_layers"]
         self.H = c["hidden_size"]
         self.nq = c["num_attention_heads"]
@@ -163,25 +169,37 @@ class PlainQwen3:
         self.w: Dict[str, torch.Tensor] = {}
         with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
             for name in f.keys():
-                self.w[name] = f.get_tensor(name).to(dtype)
+                t = f.get_tensor(name)
+                if round_to is not None and t.dim() >= 2:           # matrices and tables; gains stay as stored
+                    t = t.to(round_to)
+                self.w[name] = t.to(dtype)
         self.cos, self.sin = rope_tables(c["max_position_embeddings"], self.hd, self.theta)
 
+    def rnd(self, x: torch.Tensor) -> torch.Tensor:
+        """A node's output as it is stored: rounded to the activation dtype when one is set."""
+        return x if self.round_to is None else x.to(self.round_to).to(x.dtype)
+
     def layer(self, i: int, x: torch.Tensor, positions: Sequence[int]) -> torch.Tensor:
-        w, p = self.w, f"model.layers.{i}."
+        w, p, r = self.w, f"model.layers.{i}.", self.rnd
         T = x.shape[0]
-        h = rmsnorm(x, w[p + "input_layernorm.weight"], self.eps)
-        q = linear(h, w[p + "self_attn.q_proj.weight"]).view(T, self.nq, self.hd)
-        k = linear(h, w[p + "self_attn.k_proj.weight"]).view(T, self.nkv, self.hd)
-        v = linear(h, w[p + "self_attn.v_proj.weight"]).view(T, self.nkv, self.hd)
-        q = rmsnorm(q, w[p + "self_attn.q_norm.weight"], self.eps)     # per head, before RoPE
-        k = rmsnorm(k, w[p + "self_attn.k_norm.weight"], self.eps)     # (src/models/qwen3.zig:200-201)
-        q = apply_rope(q, positions, self.cos, self.sin, self.hd)
-        k = apply_rope(k, positions, self.cos, self.sin, self.hd)
-        a = causal_attention(q, k, v, self.scale, self.windows[i]).reshape(T, self.nq * self.hd)
-        x1 = x + linear(a, w[p + "self_attn.o_proj.weight"])
-        h2 = rmsnorm(x1, w[p + "post_attention_layernorm.weight"], self.eps)
-        m = swiglu_mlp(h2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
-        return x1 + m
+        h = r(rmsnorm(x, w[p + "input_layernorm.weight"], self.eps))
+        q = r(linear(h, w[p + "self_attn.q_proj.weight"])).view(T, self.nq, self.hd)
+        k = r(linear(h, w[p + "self_attn.k_proj.weight"])).view(T, self.nkv, self.hd)
+        v = r(linear(h, w[p + "self_attn.v_proj.weight"])).view(T, self.nkv, self.hd)
+        q = r(rmsnorm(q, w[p + "self_attn.q_norm.weight"], self.eps))     # per head, before RoPE
+        k = r(rmsnorm(k, w[p + "self_attn.k_norm.weight"], self.eps))     # (src/models/qwen3.zig:200-201)
+        q = r(apply_rope(q, positions, self.cos, self.sin, self.hd))
+        k = r(apply_rope(k, positions, self.cos, self.sin, self.hd))
+        a = r(causal_attention(q, k, v, self.scale, self.windows[i])).reshape(T, self.nq * self.hd)
+        x1 = r(x + r(linear(a, w[p + "self_attn.o_proj.weight"])))
+        h2 = r(rmsnorm(x1, w[p + "post_attention_layernorm.weight"], self.eps))
+        if self.round_to is None:
+            m = swiglu_mlp(h2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        else:           # the same four nodes, each stored rounded
+            g = r(linear(h2, w[p + "mlp.gate_proj.weight"]))
+            u = r(linear(h2, w[p + "mlp.up_proj.weight"]))
+            m = r(linear(r(r(g / (1.0 + torch.exp(-g))) * u), w[p + "mlp.down_proj.weight"]))
+        return r(x1 + m)
 
     def logits(self, ids: Sequence[int]) -> torch.Tensor:
         """float logits [T, V] of one whole sequence starting at position 0."""
@@ -189,9 +207,9 @@ class PlainQwen3:
         positions = list(range(len(ids)))
         for i in range(self.L):
             x = self.layer(i, x, positions)
-        x = rmsnorm(x, self.w["model.norm.weight"], self.eps)
+        x = self.rnd(rmsnorm(x, self.w["model.norm.weight"], self.eps))
         head = self.w["model.embed_tokens.weight"] if self.tied else self.w["lm_head.weight"]
-        return linear(x, head)
+        return self.rnd(linear(x, head))
 
     def greedy(self, prompt: Sequence[int], n_new: int) -> List[int]:
         ids = list(prompt)

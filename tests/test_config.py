@@ -17,7 +17,7 @@ def test_reads_every_key_of_the_architecture():
     assert arch.name == "Qwen3ForCausalLM" and isinstance(cfg, Qwen3Config)
     assert (cfg.vocab_size, cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers) == (384, 96, 320, 3)
     assert (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim) == (8, 1, 32)
-    assert cfg.rms_norm_eps == 1e-5 and cfg.rope_theta == 1e6 and cfg.max_position_embeddings == 640
+    assert cfg.rms_norm_eps == 1e-5 and cfg.rope_theta == 1e6 and cfg.max_position_embeddings == 256
     assert cfg.tie_word_embeddings is False
     assert cfg.layer_types == ("full_attention",) * 3 and cfg.sliding_window is None
 
@@ -72,6 +72,13 @@ def test_window_layers():
     del d["sliding_window"]
     with pytest.raises(ConfigError, match="sliding_window"):
         config_from_dict(d)
+    # the list of layer types stays in exported configurations whose switch is off: then no layer has a window
+    off = dict(TINY_C, use_sliding_window=False)
+    _, cfg3 = config_from_dict(off)
+    assert cfg3.layer_types == ("full_attention",) * 4 and cfg3.sliding_window is None
+    # without the switch the list decides
+    unsaid = {k: v for k, v in TINY_C.items() if k != "use_sliding_window"}
+    assert config_from_dict(unsaid)[1].layer_types == cfg.layer_types
 
 
 def test_unknown_architecture():

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from tests.plain.qwen3_plain import PlainQwen3
-from tests.util import ROOT, TINY, make_folder, random_ids
+from tests.util import ROOT, TINY, make_folder, random_ids, reference
 
 pytestmark = pytest.mark.gpu
 
@@ -52,7 +52,11 @@ def test_bfloat16_generation_runs_and_agrees_mostly(tmp):
     llm = LLM(path, dtype="bfloat16", max_model_len=128, max_num_seqs=4, max_batched_tokens=128, kv_blocks=16)
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     for o, r in zip(outs, ref):
-        assert len(o["token_ids"]) == 8 and o["token_ids"][0] == r[0]
+        assert len(o["token_ids"]) == 8
+        same = 0
+        while same < 8 and o["token_ids"][same] == r[same]:
+            same += 1
+        assert same >= 7, f"bfloat16 ids {o['token_ids']} leave the plain ids {r} after {same} tokens"
 
 
 def test_preemption_recomputes_and_gives_the_same_ids(tmp):
@@ -194,20 +198,21 @@ def test_layer_sizes_of_the_larger_models(tmp, hidden, heads, kv_heads, inter):
     write_random_model(path, cfg, 11, 0.02, 0.1, "bfloat16")
     ids = random_ids(300, 1500, 5)
     ids_b = random_ids(60, 1500, 6)
-    plain_model = PlainQwen3(path)
-    ref, ref_b = plain_model.logits(ids), plain_model.logits(ids_b)
-    del plain_model
+    (ref, bound_a), (ref_b, bound_b) = reference(path, ids), reference(path, ids_b)
+    bound = max(bound_a, bound_b)
+    from tests.util import forget_plain_models
+    forget_plain_models()
     d = Driver(path, "bfloat16", 512, 16)
     got = d.step([("a", ids[:280], range(280))])
-    logits_close(got, ref[:280], "bfloat16")
+    logits_close(got, ref[:280], "bfloat16", bound)
     got = d.step([("b", ids_b[:40], range(40)), ("a", ids[280:281], [0])])       # 41 rows: a portion beside a decoded token
-    logits_close(got[:40], ref_b[:40], "bfloat16")
-    logits_close(got[40:], ref[280:281], "bfloat16")
+    logits_close(got[:40], ref_b[:40], "bfloat16", bound)
+    logits_close(got[40:], ref[280:281], "bfloat16", bound)
     for i in range(19):                                                          # then both decode
         got = d.step([("a", ids[281 + i:282 + i], [0])] + ([("b", ids_b[40 + i:41 + i], [0])] if 40 + i < 60 else []))
-        logits_close(got[:1], ref[281 + i:282 + i], "bfloat16")
+        logits_close(got[:1], ref[281 + i:282 + i], "bfloat16", bound)
         if got.shape[0] > 1:
-            logits_close(got[1:], ref_b[40 + i:41 + i], "bfloat16")
+            logits_close(got[1:], ref_b[40 + i:41 + i], "bfloat16", bound)
     outs = {}
     for eager in (False, True):
         llm = LLM(path, dtype="bfloat16", max_model_len=512, max_num_seqs=4, max_batched_tokens=2048, kv_blocks=128, eager=eager)
@@ -321,3 +326,93 @@ def test_random_requests_give_the_same_ids_one_step_ahead_and_not(tmp, seed, pol
         outs[ahead] = [o["token_ids"] for o in llm.generate(prompts, params)]
         assert llm.executor.cache.all_free()
     assert outs[True] == outs[False] == want
+
+
+def test_sampled_steps_cut_into_passes_give_the_ids_of_one_pass(tmp):
+    """`Executor.step(sample=True)` with more tokens than a pass holds: the step is cut into three passes, want
+    lists are out of order, some rows are greedy and some drawn at a temperature.  The ids are those of the same
+    step run as one pass (a draw depends on the request and the position, not on the pass or the row)."""
+    from llmgen_b200.engine.api import load_model
+    from llmgen_b200.engine.executor import EngineLimits, Executor, StepEntry
+    path = make_folder(tmp, "B")
+    prompts = {"x": random_ids(70, 384, 301), "y": random_ids(45, 384, 302), "z": random_ids(33, 384, 303)}
+    wants = {"x": [69, 3, 30], "y": [44, 0], "z": [32]}
+    temps = {"x": 0.8, "y": 0.0, "z": 1.3}
+    model = load_model(path, "float32")
+    got = {}
+    for cap in (256, 64):
+        ex = Executor(model, EngineLimits(max_num_seqs=4, max_model_len=128, max_step_tokens=cap, page_size=32,
+                                          num_pages=16), seed=77, eager=True)
+        entries = []
+        for r, ids in prompts.items():
+            assert ex.admit(r) and ex.reserve(r, 0, len(ids))
+            entries.append(StepEntry(r, ids, 0, wants[r], temps[r]))
+        assert len(ex._passes(entries)) == (1 if cap == 256 else 3)
+        out = ex.step(entries, sample=True, return_logits=True)
+        got[cap] = (out.token_ids, out.logits.cpu())
+    assert got[256][0] == got[64][0] and len(got[64][0]) == 6
+    assert float((got[256][1] - got[64][1]).abs().max()) < 1e-5
+    # greedy rows are the plain argmax
+    ref = PlainQwen3(path).logits(prompts["y"])
+    assert got[64][0][3:5] == [int(ref[44].argmax()), int(ref[0].argmax())]
+
+
+@pytest.mark.parametrize("n_live,bucket", [(40, 48), (100, 112)])
+def test_many_live_sequences_match_plain_greedy_ids(tmp, n_live, bucket):
+    """40 and 100 sequences decoding together (graph buckets 48 and 112, padded rows beside live ones, decode
+    attention with fewer blocks than sequences x heads would fill twice over) in float32 against plain greedy
+    ids; the sequences end at different lengths, so the batch shrinks through smaller buckets."""
+    from llmgen_b200 import LLM, SamplingParams
+    import random
+    path = make_folder(tmp, "A")
+    rng = random.Random(n_live)
+    prompts = [random_ids(rng.randint(1, 24), 256, 500 + i) for i in range(n_live)]
+    lengths = [rng.randint(3, 10) for _ in prompts]
+    plain = PlainQwen3(path)
+    ref = [plain.greedy(p, n) for p, n in zip(prompts, lengths)]
+    llm = LLM(path, dtype="float32", max_model_len=64, max_num_seqs=128, max_batched_tokens=4096, kv_blocks=512)
+    assert bucket in llm.executor.buckets()
+    outs = llm.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in lengths])
+    assert [o["token_ids"] for o in outs] == ref
+    assert llm.executor.n_graph_steps > 0 and bucket in {b for (b, c) in llm.executor.graphs}
+    assert llm.executor.cache.all_free()
+
+
+def test_temperature_ids_do_not_depend_on_steps_launched_ahead_nor_on_the_batch(tmp):
+    """A draw's random numbers come from (seed, request, position): the same ids with decode steps launched one
+    ahead and not (an end-of-sequence token and preemptions change which rows a step has and how many steps
+    run), with the requests submitted alone one after the other, and they are the plain sampler's ids."""
+    from llmgen_b200 import LLM, SamplingParams
+    from llmgen_b200.engine.executor import SEED_STRIDE
+    from tests.plain import qwen3_plain as plain
+    path = make_folder(tmp, "B")
+    prompts = [random_ids(n, 384, 600 + i) for i, n in enumerate((4, 19, 33, 8, 27))]
+    params = [SamplingParams(temperature=t, max_tokens=m, ignore_eos=False) for t, m in ((0.7, 30), (1.1, 40), (0.4, 35), (0.9, 45), (0.7, 38))]
+    seed = 4242
+
+    def run(ahead, eos=(), kv_blocks=5):
+        llm = LLM(path, dtype="float32", seed=seed, max_model_len=128, max_num_seqs=4, max_batched_tokens=128,
+                  block_size=32, kv_blocks=kv_blocks, policy="chunked", chunk=16)
+        llm.engine.run_ahead = ahead
+        llm.engine.scheduler.config.eos_token_ids = tuple(eos)
+        outs = llm.generate(prompts, params)
+        assert llm.executor.cache.all_free()
+        return [o["token_ids"] for o in outs], llm.engine.scheduler.num_preemptions
+
+    free, _ = run(True, kv_blocks=32)
+    eos = free[1][7]                                    # a token the second request draws: it ends there
+    a, pre_a = run(True, eos=[eos])
+    b, pre_b = run(False, eos=[eos])
+    assert a == b and pre_a > 0
+    assert a[1] == free[1][:free[1].index(eos) + 1]
+    # the plain sampler with the same keys: step seed = seed + stride * (position + 1), row = the request's number
+    model = PlainQwen3(path)
+    for rid, (prompt, p, ids) in enumerate(zip(prompts, params, a)):
+        seq = list(prompt)
+        for tok in ids:
+            logits = model.logits(seq)[-1]
+            step_seed = (seed + SEED_STRIDE * len(seq)) & ((1 << 64) - 1)
+            scores = plain.gumbel_scores(logits, p.temperature, step_seed, rid)
+            top = scores.topk(2)
+            assert tok == int(top.indices[0]) or float(top.values[0] - top.values[1]) < 1e-4
+            seq.append(tok)

@@ -179,6 +179,7 @@ def test_prenorm_block(dtype):
     # plain: the same layer on x + prev
     w = {k: v.float() for k, v in tensors.items()}
     m = object.__new__(plain.PlainQwen3)
+    m.round_to = None
     m.w, m.nq, m.nkv, m.hd, m.eps = w, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps
     m.scale, m.windows = 1 / math.sqrt(cfg.head_dim), [None, cfg.sliding_window]
     m.cos, m.sin = plain.rope_tables(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta)

@@ -77,7 +77,12 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert "dtype I32" in msg
 
 
-def test_untied_model_needs_lm_head_and_tied_refuses_it(tmp_path):
+def _spec(cfg):
+    arch, c = config_from_dict(cfg)
+    return arch.build_spec(c)
+
+
+def test_untied_model_needs_lm_head_and_tied_takes_only_a_true_copy(tmp_path):
     path = make_folder(str(tmp_path), "B")
     f = os.path.join(path, "model.safetensors")
     t = load_file(f)
@@ -87,11 +92,27 @@ def test_untied_model_needs_lm_head_and_tied_refuses_it(tmp_path):
         open_weights(path, _decls(TINY_B))
     path_a = make_folder(str(tmp_path), "A")
     fa = os.path.join(path_a, "model.safetensors")
-    ta = load_file(fa)
+    ta = {k: v.clone() for k, v in load_file(fa).items()}     # copies: the file these came from is written again below
     ta["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)
     save_file(ta, fa)
     with pytest.raises(WeightError, match="unexpected.*lm_head.weight"):
-        open_weights(path_a, _decls(TINY_A))
+        open_weights(path_a, _decls(TINY_A))               # nothing said that it may be there
+    # exports of tied models often carry the output matrix too: the architecture lets it pass if it is the
+    # table's copy (and rotary buffers whatever they hold), and still refuses anything else
+    spec = _spec(TINY_A)
+    with pytest.raises(WeightError, match="lm_head.weight.*differ"):
+        open_weights(path_a, _decls(TINY_A), spec.ignorable_tensors, spec.same_as)
+    ta["lm_head.weight"] = ta["model.embed_tokens.weight"].clone()
+    ta["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    save_file(ta, fa)
+    store = open_weights(path_a, _decls(TINY_A), spec.ignorable_tensors, spec.same_as)
+    assert torch.equal(store.host_tensor("model.embed_tokens.weight"), ta["model.embed_tokens.weight"])
+    with pytest.raises(WeightError, match="not declared"):
+        store.host_tensor("lm_head.weight")
+    ta["stray.weight"] = torch.ones(3)
+    save_file(ta, fa)
+    with pytest.raises(WeightError, match=r"unexpected \(1\): stray.weight"):
+        open_weights(path_a, _decls(TINY_A), spec.ignorable_tensors, spec.same_as)
 
 
 def test_broken_files(tmp_path):

@@ -42,8 +42,9 @@ def test_profiled_steps_give_the_same_logits_and_a_table(tmp, dtype):
         prof.disable()
         drv.executor.profiler = None
     assert not hasattr(ops.add_rmsnorm, "__wrapped__") and pf.OpProfiler._active is None
-    logits_close(got_prompt, ref_prompt, dtype)
-    logits_close(got_token, ref_token, dtype)
+    # the same kernels with marks between them: the same values
+    logits_close(got_prompt, ref_prompt, dtype, 1e-5)
+    logits_close(got_token, ref_token, dtype, 1e-5)
 
     assert prof.passes == {pf.PREFILL: 1, pf.DECODE: 1}
     for phase in (pf.PREFILL, pf.DECODE):
