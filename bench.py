@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
                     [--shape 0.6b|8b|32b --layers L]      (other layer sizes, beside the default run)
+    python bench.py --kernels [--kernels-out FILE.md]     (kernel by kernel beside the reference's own kernels)
 
 Prints ONE JSON line.  A "step" is one decode step of `--batch` sequences (default 8) whose
 prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
@@ -20,7 +21,10 @@ prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
 
 Inputs are larger than L2 (1.19 GB of weights per step against 126 MB), so nothing is flushed
 between timed iterations.  The reference (Zig + CUDA for sm_86) cannot be built or installed
-here, so `--impl reference` reports that it is unavailable.
+here, so `--impl reference` reports that it is unavailable.  Its CUDA kernels, however, are plain
+`extern "C"` functions: baseline/build_reference_kernels.py compiles them unmodified for sm_100a, and
+`--kernels` times them beside this engine's kernels on the same GPU, shapes and loop
+(baseline/kernel_compare.py); that mode prints one JSON line of its own and is no part of the default run.
 """
 import argparse
 import json
@@ -155,6 +159,34 @@ def prefill_flops(cfg, n_layers, P):
     return gemm + attn
 
 
+def kernels_table(args):
+    """Kernel by kernel beside the reference's own kernels recompiled for sm_100a; one JSON line."""
+    from baseline import reference_kernels as ref
+    if not ref.available():
+        print(json.dumps({"kernels": None, "unavailable": "baseline/_ref holds no library of the reference's kernels: run "
+                          "baseline/build_reference_kernels.py --src <checkout of the reference> first"}))
+        return 0
+    import torch
+    from llmgen_b200.engine.api import require_cuda
+    from llmgen_b200.kernels import build as kernel_build
+    from baseline import kernel_compare
+    require_cuda()
+    kernel_build.ensure_built(["elementwise", "attn_prep", "attention_decode", "attention_tc", "gemm_skinny", "gemm_tc"])
+    sampler = ClockSampler()
+    sampler.start()
+    w0 = sampler.mark()
+    rows = kernel_compare.run_all()
+    clocks = sampler.stop([(w0, sampler.mark())])
+    table = kernel_compare.as_markdown(rows)
+    if args.kernels_out:
+        os.makedirs(os.path.dirname(os.path.abspath(args.kernels_out)), exist_ok=True)
+        with open(args.kernels_out, "w") as f:
+            f.write(table + "\n")
+    print(table, file=sys.stderr)
+    print(json.dumps({"kernels": rows, "gpu": torch.cuda.get_device_name(0), "clocks": clocks}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -173,13 +205,19 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
+    ap.add_argument("--kernels", action="store_true",
+                    help="time this engine's kernels beside the reference's (baseline/_ref, built by baseline/build_reference_kernels.py)")
+    ap.add_argument("--kernels-out", default="", help="with --kernels: also write the table as markdown to this file")
     args = ap.parse_args()
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "AIxSpace/llmgen is a Zig 0.15 + CUDA (sm_86) program: no Zig "
                           "compiler is installed and pip reports 'Neither setup.py nor pyproject.toml found', so it "
-                          "cannot be installed or run here"}))
+                          "cannot be installed or run here; its CUDA kernels alone are compiled for sm_100a and timed "
+                          "beside this engine's by `bench.py --kernels` (profiles/reference_kernels_on_b200.md)"}))
         return 0
+    if args.kernels:
+        return kernels_table(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -8,6 +8,12 @@ cannot be imported or compiled.  Each function cites the lines it restates.  Two
 functions are pinned to the reference's own PyTorch-made fixtures
 (testdata/linear_case.*, testdata/norm_case.*; copies of the numbers in
 tests/golden/reference_fixtures.json, made by tests/golden/make_reference_fixtures.py).
+The reference's CUDA kernels, which are plain C entry points, do compile here (for sm_100a,
+unmodified): the per-head norm, the rotary pairing and angles, the place of a key in a page,
+the attention of a chunk's tail over shuffled pages with grouped heads (prompt and split decode
+kernels) and the sampler are pinned to their outputs on a B200
+(tests/golden/reference_kernel_fixtures.json, made by
+tests/golden/make_reference_kernel_fixtures.py; tests/test_plain.py).
 """
 from __future__ import annotations
 
