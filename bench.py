@@ -41,20 +41,13 @@ sys.path.insert(0, ROOT)
 
 # BASELINE.json configs[2]: "Qwen3-0.6B shape ... 28 layers, hidden 1024, 16 q heads, 8 kv heads,
 # head_dim 128, intermediate 3072 SwiGLU, vocab 151936, rope_theta 1,000,000, rms_eps 1e-6,
-# q/k RMSNorm, tied embeddings, full attention", benchmarked at max_model_len 4096.
-QWEN3_0_6B = {
-    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
-    "num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16, "num_key_value_heads": 8,
-    "head_dim": 128, "intermediate_size": 3072, "vocab_size": 151936, "rope_theta": 1000000.0,
-    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 40960, "hidden_act": "silu",
-}
-# BASELINE.json configs[3] and configs[4]: the layer sizes of Qwen3-8B and Qwen3-32B, for runs beside the
-# default one (`--shape 8b --layers 8`): the same kernels at wider layers.
-QWEN3_8B = dict(QWEN3_0_6B, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, intermediate_size=12288,
-                tie_word_embeddings=False)
-QWEN3_32B = dict(QWEN3_0_6B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600,
-                 tie_word_embeddings=False)
-SHAPES = {"0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "8b": ("Qwen3-8B shape", QWEN3_8B), "32b": ("Qwen3-32B shape", QWEN3_32B)}
+# q/k RMSNorm, tied embeddings, full attention", benchmarked at max_model_len 4096; configs[3] and [4]: the layer
+# sizes of Qwen3-8B and Qwen3-32B, for runs beside the default one (`--shape 8b --layers 8`).
+from llmgen_b200.models.shapes import QWEN3_SHAPES  # noqa: E402
+
+QWEN3_0_6B = QWEN3_SHAPES["qwen3-0.6b"]
+SHAPES = {"0.6b": ("Qwen3-0.6B shape", QWEN3_0_6B), "8b": ("Qwen3-8B shape", QWEN3_SHAPES["qwen3-8b"]),
+          "32b": ("Qwen3-32B shape", QWEN3_SHAPES["qwen3-32b"])}
 CONTEXT = 4096
 PROMPT_TOKENS = 512
 PREFILL_TOKENS = 2048

@@ -10,8 +10,8 @@ Options keep the reference's names and meanings:
     --model <dir>  --temp <f>  --max-model-len <n>  --max-num-seqs <n>  --max-batched-tokens <n>
     --pass-tokens <n>  --block-size <n>  --gpu-util <f>  --kv-blocks <n>
     --policy prefill_first|chunked  --chunk <n>  --out <path>  --dup <n>  --eager  --sync-each
-Added: --dtype bfloat16|float32, --seed <n>, --random <config.json> (random weights drawn from
---seed instead of a model folder).  The model is a folder with config.json and model.safetensors
+Added: --dtype bfloat16|float32, --seed <n>, --random <config.json | qwen3-0.6b | qwen3-8b | qwen3-32b> (random
+weights drawn from --seed instead of a model folder; --init-on-device draws them on the GPU).  The model is a folder with config.json and model.safetensors
 (default: environment variable LLMGEN_MODEL).
 Environment, for `chat` (the reference's names): LLMGEN_PROFILE prints the time, FLOP/s and bytes/s
 of every kernel by phase (eager steps); LLMGEN_METRICS prints TTFT, inter-token latencies and
@@ -51,7 +51,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("arg0", nargs="?", help="chat: prompt token ids; bench: workload.json; workload: the file to write")
     ap.add_argument("max_new", nargs="?", default=None, help="chat: most tokens to generate (default 2000); convert: the folder to write")
     ap.add_argument("--model", default=os.environ.get("LLMGEN_MODEL"))
-    ap.add_argument("--random", metavar="CONFIG_JSON", help="draw random weights for this config.json instead of --model")
+    ap.add_argument("--random", metavar="CONFIG_JSON|NAME", help="draw random weights for this config.json (or a named shape: "
+                    "qwen3-0.6b, qwen3-8b, qwen3-32b) instead of --model")
+    ap.add_argument("--init-on-device", action="store_true", help="with --random: draw the weights on the GPU (other values "
+                    "than the host's generator gives; for sizes that would take minutes on the host)")
     ap.add_argument("--seed", type=int, default=0x5EED)
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--temp", type=float, default=0.0)
@@ -86,11 +89,23 @@ def parse_prompt(text: str) -> List[int]:
     return [int(t) for t in text.replace(",", " ").split()]
 
 
+def random_config(text: str, max_model_len=None) -> dict:
+    """A config.json file, or the name of a shape (models/shapes.py)."""
+    if os.path.isfile(text):
+        with open(text, "r", encoding="utf-8") as f:
+            return json.load(f)
+    from .models.shapes import named_shape
+    try:
+        return named_shape(text)
+    except ValueError as e:
+        raise SystemExit(f"--random: {text!r} is no file, and {e}")
+
+
 def make_llm(args):
     from .engine.api import LLM, random_model
     if args.random:
-        with open(args.random, "r", encoding="utf-8") as f:
-            model = random_model(json.load(f), args.seed, args.dtype)
+        model = random_model(random_config(args.random, args.max_model_len), args.seed, args.dtype,
+                             init_on_device=args.init_on_device)
     elif args.model:
         model = args.model
     else:
@@ -239,7 +254,7 @@ def bench(args) -> int:
         "peak_rss_mb": resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 1024.0,
         "device_used_mb": (total - free) / 2 ** 20, "weights_mb": llm.model.weight_bytes() / 2 ** 20,
         "kv_cache_mb": ex.storage.bytes_held() / 2 ** 20, "kv_tokens": pages * ex.limits.page_size,
-        "load_s": llm.load_seconds, "preemptions": llm.engine.scheduler.num_preemptions - pre0, "steps": steps,
+        "load_s": llm.load_seconds, "graphs_captured": llm.graphs_captured, "preemptions": llm.engine.scheduler.num_preemptions - pre0, "steps": steps,
         "graph_steps": ex.n_graph_steps - graph0, "eager_steps": ex.n_eager_steps - eager0,
         "policy": args.policy, "dtype": args.dtype, "kv_leak": leak,
     }
@@ -276,8 +291,7 @@ def info(args) -> int:
     from .weights.loader import WeightError
     try:
         if args.random:
-            with open(args.random, "r", encoding="utf-8") as f:
-                text = describe(config=json.load(f), context=args.max_model_len or 4096)
+            text = describe(config=random_config(args.random), context=args.max_model_len or 4096)
         elif args.model:
             text = describe(model_dir=args.model, context=args.max_model_len or 4096)
         else:

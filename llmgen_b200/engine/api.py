@@ -76,15 +76,17 @@ def write_random_model(model_dir: str, config: dict, seed: int, sigma: Optional[
 
 
 def random_model(config: dict, seed: int, dtype=torch.bfloat16, device="cuda:0", sigma: Optional[float] = None,
-                 sigma_norm: Optional[float] = None, store_dtype=torch.bfloat16) -> DecoderModel:
-    """A model with random weights without touching the disk (same values as
-    `write_random_model` with the same arguments)."""
+                 sigma_norm: Optional[float] = None, store_dtype=torch.bfloat16, init_on_device: bool = False) -> DecoderModel:
+    """A model with random weights without touching the disk (same values as `write_random_model` with the
+    same arguments, unless `init_on_device`: the tensors are then drawn by the GPU's generator, which is what
+    benchmarks of models of tens of gigabytes use)."""
     dev = require_cuda(device)
     arch, cfg = config_from_dict(config)
     spec = arch.build_spec(cfg)
     decls = model_weight_decls(spec)
     tensors = random_tensors(decls, seed, spec.init_sigma if sigma is None else sigma,
-                             spec.init_sigma_norm if sigma_norm is None else sigma_norm, resolve_dtype(store_dtype))
+                             spec.init_sigma_norm if sigma_norm is None else sigma_norm, resolve_dtype(store_dtype),
+                             device=dev if init_on_device else "cpu")
     return DecoderModel(spec, weights_from_dict(tensors, decls), resolve_dtype(dtype), dev)
 
 
@@ -92,7 +94,11 @@ class LLM:
     def __init__(self, model: Union[str, DecoderModel], dtype="bfloat16", device="cuda:0", seed: int = DEFAULT_SEED,
                  max_num_seqs: int = 256, max_model_len: int = 4096, max_batched_tokens: int = 16384,
                  pass_tokens: int = 8192, block_size: int = 16, gpu_util: float = 0.9, kv_blocks: int = 0,
-                 policy: str = PREFILL_FIRST, chunk: int = 2048, eager: bool = False, sync_each: bool = False):
+                 policy: str = PREFILL_FIRST, chunk: int = 2048, eager: bool = False, sync_each: bool = False,
+                 capture_at_start: bool = True):
+        """`capture_at_start`: record the CUDA graph of every decode batch size and context class now (unless
+        `eager`), as the reference does when it starts; `load_seconds` then includes it.  False leaves each
+        graph to the first step that needs it."""
         t0 = time.perf_counter()
         self.model = model if isinstance(model, DecoderModel) else load_model(model, dtype, device)
         limits = EngineLimits(max_num_seqs=max_num_seqs, max_model_len=max_model_len, max_step_tokens=pass_tokens,
@@ -101,7 +107,11 @@ class LLM:
         self.engine = Engine(self.executor, SchedulerConfig(
             max_num_seqs=max_num_seqs, max_num_batched_tokens=max_batched_tokens, policy=policy,
             chunk_tokens=chunk, eos_token_ids=tuple(self.model.spec.eos_token_ids)))
-        self.load_seconds = time.perf_counter() - t0
+        self.graphs_captured = 0
+        if capture_at_start and not self.executor.eager:
+            self.graphs_captured = self.executor.capture_all()
+            torch.cuda.synchronize(self.executor.device)
+        self.load_seconds = time.perf_counter() - t0      # weights, cache, workspaces and graph capture
 
     @contextlib.contextmanager
     def profile(self):

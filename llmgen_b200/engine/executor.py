@@ -154,6 +154,7 @@ class Executor:
         self._status_hosts = [torch.zeros(2, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._ids_turn = 0
         self.graphs: Dict[Tuple[int, int], dict] = {}     # (batch-size bucket, context-length class) -> graph
+        self._graph_logits = None                         # float32 [max_num_seqs, vocab], shared by the graphs
         # decode steps rewrite only what changed in a host buffer that the same bucket filled last
         self._host_owner = [None, None]                   # per pinned buffer: (bucket, layout) of its last fill
         self._host_rows = [None, None]                    # per pinned buffer: per group and row, (request, table stamp)
@@ -534,7 +535,11 @@ class Executor:
         (src/executor.zig:609-660)."""
         ctx_bound = ctx_bound or self.limits.max_model_len
         V = self.model.spec.vocab_size
-        logits = torch.empty((bucket, V), dtype=torch.float32, device=self.device)
+        # one array of logits for all graphs (they never run at the same time): a graph of its own per bucket and
+        # class would hold gigabytes at a large vocabulary
+        if self._graph_logits is None:
+            self._graph_logits = torch.empty((self.limits.max_num_seqs, V), dtype=torch.float32, device=self.device)
+        logits = self._graph_logits[:bucket]
         ids_dev = self.sampled_dev[:bucket]
         # the warm-up runs sample elsewhere: a step in flight may have left ids in `sampled_dev` that the
         # step this graph is captured for takes its tokens from
@@ -570,11 +575,25 @@ class Executor:
         self.graphs[(bucket, ctx_bound)] = entry
         return entry
 
-    def capture_all(self) -> None:
-        """Capture every batch-size bucket at the largest context class."""
-        for b in self.buckets():
-            if (b, self.limits.max_model_len) not in self.graphs:
-                self._capture(b, self.limits.max_model_len)
+    def context_classes(self) -> List[int]:
+        """Every class of context length a decode graph is kept for, up to max_model_len."""
+        out, bound = [], 512
+        while bound < self.limits.max_model_len:
+            out.append(bound)
+            bound *= 2
+        return out + [self.limits.max_model_len]
+
+    def capture_all(self) -> int:
+        """Capture the decode graph of every batch-size bucket and context class, as the reference does for its
+        buckets when it starts (src/executor.zig:609-660), so that no step of a run pays for a capture.
+        Returns how many graphs were captured."""
+        made = 0
+        for bound in self.context_classes():
+            for b in self.buckets():
+                if (b, bound) not in self.graphs:
+                    self._capture(b, bound)
+                    made += 1
+        return made
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> StepOutput:
         return StepOutput(None, self.decode_collect(self._decode_launch(entries, None)))

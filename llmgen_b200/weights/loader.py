@@ -63,7 +63,7 @@ class PinnedStage:
 
     def upload(self, src: torch.Tensor) -> torch.Tensor:
         """A device tensor with the values (and dtype) of the host tensor `src`."""
-        if self.device.type != "cuda" or src.numel() * src.element_size() < (1 << 20):
+        if self.device.type != "cuda" or src.is_cuda or src.numel() * src.element_size() < (1 << 20):
             return src.to(self.device)
         if self._buffers is None:
             self._buffers = [torch.empty(self.CHUNK, dtype=torch.uint8).pin_memory() for _ in range(2)]

@@ -26,15 +26,18 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 
 def random_tensors(decls: Iterable[WeightDecl], seed: int, sigma: float, sigma_norm: float,
-                   dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+                   dtype: torch.dtype = torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
+    """`device`: where the tensors are drawn and left.  The host's generator and a GPU's give different values
+    for the same seed: model folders (and everything compared with the plain implementation) are drawn on the
+    host; drawing on the GPU is for benchmarks of sizes whose tens of gigabytes would take minutes on the host."""
     out: Dict[str, torch.Tensor] = {}
     for name, d in check_declarations(list(decls)).items():
-        g = torch.Generator(device="cpu")
+        g = torch.Generator(device=device)
         g.manual_seed(_tensor_seed(seed, name))
         if d.kind == INT_TABLE:
-            out[name] = torch.randint(0, 2 ** 15, tuple(d.shape), generator=g, dtype=torch.int32)
+            out[name] = torch.randint(0, 2 ** 15, tuple(d.shape), generator=g, dtype=torch.int32, device=device)
             continue
-        t = torch.empty(tuple(d.shape), dtype=torch.float32)
+        t = torch.empty(tuple(d.shape), dtype=torch.float32, device=device)
         if d.init == INIT_ONE_PLUS_NORMAL:
             t.normal_(0.0, sigma_norm, generator=g).add_(1.0)
         else:
