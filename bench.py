@@ -8,9 +8,10 @@
 Prints ONE JSON line.  A "step" is one decode step of `--batch` sequences (default 8) whose
 prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
 
-  value     decoded tokens per second, timed on the device with CUDA events over exactly K
-            graph-replayed decode steps (metadata upload + captured forward + sampling), after W
-            warm-up steps.  Contexts grow from 512 + W upward.
+  value     decoded tokens per second, timed on the device with CUDA events over exactly K decode
+            steps through the executor's launch interface (arrays filled and uploaded, graph
+            replayed, ids sampled and handed to the next step on the device, read one step late),
+            after W warm-up steps.  Contexts grow from 512 + W upward.
   e2e       the same through the Python entry point (`Engine.step`): every step copies its
             metadata from pinned host memory to the device and reads the sampled ids back.
   prefill   one 2,048-token prompt through one step: tokens/s, ms, and flops / time / the measured
@@ -18,6 +19,9 @@ prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
   roofline  the decode step against HBM: bytes it has to read (every weight once, the cache of the
             live requests) / its time / the measured copy bandwidth.
   points    decode tokens/s at batch 1 and 64.
+  mixed_step  8 decoded tokens beside a 64-token portion of a prompt in one step (launched kernel by kernel
+            from the host): wall ms and the ms between CUDA events.
+  load_s    engine construction with cache, workspaces and the capture of every decode graph.
 
 Inputs are larger than L2 (1.19 GB of weights per step against 126 MB), so nothing is flushed
 between timed iterations.  The reference (Zig + CUDA for sm_86) cannot be built or installed
@@ -245,7 +249,10 @@ def main():
     windows = []
 
     def device_decode(batch, warm, steps):
-        """K graph-replayed decode steps timed with CUDA events; returns (ms per step, mean context)."""
+        """K decode steps through the executor's launch interface, timed with CUDA events: every step fills and
+        uploads its arrays, replays its graph, samples, and hands its ids to the next step on the device (the
+        step after is launched before this one's ids are read, as the engine does).  Returns (ms per step, mean
+        context, launches per step)."""
         reqs = [f"dev{batch}_{i}" for i in range(batch)]
         P = args.prompt_tokens
         total = P + warm + steps + 1
@@ -253,35 +260,68 @@ def main():
         for r in reqs:
             assert ex.admit(r) and ex.reserve(r, 0, total)
         if P * batch <= 65536:
-            ex.step([StepEntry(r, p, 0, [P - 1], 0.6) for r, p in zip(reqs, prompts)], sample=True, return_logits=False)
+            first_ids = ex.step([StepEntry(r, p, 0, [P - 1], 0.6) for r, p in zip(reqs, prompts)], sample=True, return_logits=False).token_ids
         else:
-            for r, p in zip(reqs, prompts):
-                ex.step([StepEntry(r, p, 0, [P - 1], 0.6)], sample=True, return_logits=False)
-        toks = rng.integers(0, V, batch).tolist()
-        pos = P
-        bucket, g = ex.decode_graph(batch, total)     # one graph for the whole run: the class of the last context
+            first_ids = [ex.step([StepEntry(r, p, 0, [P - 1], 0.6)], sample=True, return_logits=False).token_ids[0]
+                         for r, p in zip(reqs, prompts)]
+        state = {"pos": P, "pending": None}
+        rows = list(range(batch))
+        launches_before, graph_steps_before = ex.launch_count, ex.n_graph_steps
 
-        def one(pos):
-            ex._build_meta([StepEntry(r, [t], pos, [0], 0.6) for r, t in zip(reqs, toks)], pad_to=bucket)
-            g["graph"].replay()
+        def one():
+            pos = state["pos"]
+            if state["pending"] is None:
+                entries = [StepEntry(r, [t], pos, [0], 0.6) for r, t in zip(reqs, first_ids)]
+                launched = ex.decode_launch(entries, None)
+            else:
+                entries = [StepEntry(r, [None], pos, [0], 0.6) for r in reqs]
+                launched = ex.decode_launch(entries, rows)
+                ex.decode_collect(state["pending"])          # the ids of the step before, read one step late
+            state["pending"], state["pos"] = launched, pos + 1
         for _ in range(warm):
-            one(pos)
-            pos += 1
+            one()
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = sampler.mark()
         start.record()
-        first = pos
+        first = state["pos"]
         for _ in range(steps):
-            one(pos)
-            pos += 1
+            one()
         end.record()
         torch.cuda.synchronize()
         windows.append((w0, sampler.mark()))
+        ex.decode_collect(state["pending"])
         ms = start.elapsed_time(end) / steps
+        # kernels of this package that every replayed step launches (counted when its graph was recorded)
+        per_step = (ex.launch_count - launches_before) // max(1, ex.n_graph_steps - graph_steps_before)
         for r in reqs:
             ex.release(r)
-        return ms, (first + 1 + pos) / 2.0, g["launches"]
+        return ms, (first + 1 + state["pos"]) / 2.0, per_step
+
+    def mixed_step(decoding=8, portion=64, repeats=20):
+        """A step of the kind the chunked policy makes: `decoding` single tokens beside one portion of a prompt.
+        Such steps are launched kernel by kernel from the host; wall time against device time shows what that costs."""
+        reqs = [f"mix{i}" for i in range(decoding)]
+        for r in reqs + ["mixp"]:
+            assert ex.admit(r) and ex.reserve(r, 0, 512 + repeats * portion + 8)
+        ex.step([StepEntry(r, rng.integers(0, V, 512).tolist(), 0, [511], 0.6) for r in reqs], sample=True, return_logits=False)
+        dev, wall = [], []
+        for i in range(repeats + 3):
+            entries = [StepEntry(r, [7], 512 + i, [0], 0.6) for r in reqs]
+            entries.append(StepEntry("mixp", rng.integers(0, V, portion).tolist(), i * portion, [], 0.6))
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            start.record()
+            ex.step(entries, sample=True, return_logits=False)
+            end.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                wall.append((time.perf_counter() - t0) * 1e3)
+                dev.append(start.elapsed_time(end))
+        for r in reqs + ["mixp"]:
+            ex.release(r)
+        return {"tokens": decoding + portion, "ms": statistics.median(wall), "ms_device_events": statistics.median(dev)}
 
     # ---- prefill: one 2,048-token prompt, one step
     def prefill_once():
@@ -307,7 +347,6 @@ def main():
                    "frac": pf / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
 
     # ---- the decode step on the device
-    launches0 = ops.launches()
     ms_step, mean_ctx, launches_per_step = device_decode(args.batch, warmup, K)
     value = args.batch / (ms_step / 1e3)
     step_bytes = nums["weight_bytes"] + args.batch * mean_ctx * nums["kv_bytes_per_token"]
@@ -340,21 +379,27 @@ def main():
         e2e_ms = max(start.elapsed_time(end), wall * 1e3)
         llm.engine.run_until_done()
         llm.engine.release_finished()
-        meta_words = 2 + 3 * args.batch + (args.batch + 1) + 4 * args.batch + 2 * args.batch + args.batch + args.batch * ex.max_blocks
-        e2e = {"value": emitted / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_words,
-               "d2h_bytes_per_step": 4 * args.batch}
+        # every step copies its packed arrays up (ids, positions, lengths, slots, block tables, sampler keys ...) and its
+        # sampled ids and the kernels' two status flags down
+        e2e = {"value": emitted / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": ex.last_upload_bytes,
+               "d2h_bytes_per_step": 4 * args.batch + 8}
 
     points = {}
+    mixed = None
     if not args.skip_points:
         for b in (1, 64):
             ms_b, _, _ = device_decode(b, warmup, K)
             points[f"decode_b{b}"] = b / (ms_b / 1e3)
+        mixed = mixed_step()
     clocks = sampler.stop(windows)
 
     line = {
         "metric": f"decode tok/s at batch {args.batch} ({shape_name}, bf16, random weights, {args.prompt_tokens}-token prompts)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8 if args.shape == "0.6b" else None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8 if args.shape == "0.6b" else None,
+        "vs_baseline_note": "BASELINE.md's numbers are the reference on an RTX 3090 (8 requests end to end: 1,666 tokens/s); "
+                            "another machine, not a same-hardware ratio",
+        "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random-init weights (seed 2)",
         "config": {"model": shape_name, "global_batch": args.batch, "seq_len": args.context, "parallelism": "single GPU",
                    "layers": n_layers, "layers_in_config": full_layers, "hidden": cfg["hidden_size"],
@@ -363,7 +408,7 @@ def main():
                    "prompt_tokens": args.prompt_tokens, "mean_context": mean_ctx, "page_size": args.block_size,
                    "l2": f"inputs larger than L2 ({nums['weight_bytes'] / 1e9:.2f} GB of weights per step), no flush", "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": launches_per_step * K, "prefill": prefill, "roofline": roofline, "points": points,
-        "clocks": clocks, "impl": "ours",
+        "mixed_step": mixed, "load_s": llm.load_seconds, "clocks": clocks, "impl": "ours",
     }
     print(json.dumps(line))
     return 0

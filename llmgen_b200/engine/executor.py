@@ -93,6 +93,7 @@ class Executor:
         self.n_graph_steps = 0
         self.n_eager_steps = 0
         self.launch_count = 0
+        self.last_upload_bytes = 0       # bytes of the last step's arrays copied to the device
         self.profiler = None             # an `engine.profiler.OpProfiler`: told of every eager pass
         if limits.max_model_len > model.max_positions():
             raise StepError(f"max_model_len {limits.max_model_len} exceeds the model's "
@@ -421,6 +422,7 @@ class Executor:
         self._host_owner[turn] = None
         self._last_fill = (turn, layout, total)
         self.meta_dev[:total].copy_(self.meta_host[turn][:total], non_blocking=True)
+        self.last_upload_bytes = 4 * total
         ev = torch.cuda.Event()
         ev.record()
         self.meta_events[turn] = ev
@@ -688,6 +690,7 @@ class Executor:
             self._host_owner[turn] = None
             raise StepError(self._runtime.llmr_last_error().decode("utf-8", "replace"))
         self.meta_dev[:total].copy_(self.meta_host[turn][:total], non_blocking=True)
+        self.last_upload_bytes = 4 * total
         ev = torch.cuda.Event()
         ev.record()
         self.meta_events[turn] = ev
