@@ -202,6 +202,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
+    ap.add_argument("--mixed", default="", metavar="DECODING,PORTION,REPEATS",
+                    help="for profiling runs: only steps of DECODING single tokens beside a portion of PORTION tokens")
     ap.add_argument("--kernels", action="store_true",
                     help="time this engine's kernels beside the reference's (baseline/_ref, built by baseline/build_reference_kernels.py)")
     ap.add_argument("--kernels-out", default="", help="with --kernels: also write the table as markdown to this file")
@@ -241,7 +243,8 @@ def main():
     rng = np.random.default_rng(SEED)
     model = random_model(cfg, SEED, "bfloat16")
     llm = LLM(model, max_num_seqs=64, max_model_len=args.context, max_batched_tokens=16384, pass_tokens=8192,
-              block_size=args.block_size, gpu_util=0.5, seed=SEED)
+              block_size=args.block_size, gpu_util=0.5, seed=SEED,
+              capture_at_start=not args.mixed)      # a profiling run of mixed steps replays no decode graph
     ex = llm.executor
     V = cfg["vocab_size"]
     sampler = ClockSampler()
@@ -300,7 +303,8 @@ def main():
 
     def mixed_step(decoding=8, portion=64, repeats=20):
         """A step of the kind the chunked policy makes: `decoding` single tokens beside one portion of a prompt.
-        Such steps are launched kernel by kernel from the host; wall time against device time shows what that costs."""
+        The layers of such a step are replayed from the CUDA graph of its shape; wall time against device time shows
+        what the host costs."""
         reqs = [f"mix{i}" for i in range(decoding)]
         for r in reqs + ["mixp"]:
             assert ex.admit(r) and ex.reserve(r, 0, 512 + repeats * portion + 8)
@@ -322,6 +326,11 @@ def main():
         for r in reqs + ["mixp"]:
             ex.release(r)
         return {"tokens": decoding + portion, "ms": statistics.median(wall), "ms_device_events": statistics.median(dev)}
+
+    if args.mixed:
+        d, p, r = (int(x) for x in args.mixed.split(","))
+        print(json.dumps({"mixed_step": mixed_step(d, p, r), "shaped_steps": ex.n_shaped_steps}))
+        return 0
 
     # ---- prefill: one 2,048-token prompt, one step
     def prefill_once():

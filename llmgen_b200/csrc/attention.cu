@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
     float* Vs = Ks + KT * (hd + 1);         // [KT][hd]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int s = p.tile_seq[blockIdx.x];
+    if (s < 0) return;                      // padding of a tile list of fixed length
     const int q0 = p.tile_q0[blockIdx.x];
     const int G = p.nq / p.nkv;
     const int kvh = blockIdx.y / p.chunks;

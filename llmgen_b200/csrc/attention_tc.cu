@@ -124,6 +124,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     constexpr uint32_t TMEM_COLS = 512;
     constexpr uint32_t S_COL0 = 0, S_COL1 = BN, O_COL0 = 2 * BN;
     extern __shared__ __align__(1024) uint8_t smem[];
+    // A tile whose sequence is -1 is padding of a list of fixed length (a launch shape kept for replay): the
+    // block leaves before it sets anything up.  The list is read ahead of `griddepcontrol.wait`: it belongs
+    // to the step's arrays, which a copy wrote before the step's first kernel started, never a kernel of the
+    // step itself.
+    if (p.tile_seq[blockIdx.y] < 0) return;
     if ((tc::smem_u32(smem) & 1023u) != 0) {      // uniform over the block: nothing has been set up yet
         if (threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 2);
         return;
@@ -449,7 +454,8 @@ LLMK_EXPORT int llmk_attention_tc_tile_queries(int nq, int nkv, int hd, int page
 
 // out[t, nq*hd] = attention of q[t] (bfloat16, row stride q_stride) over the paged cache
 // [num_pages, nkv, page_size, hd].  tile_seq / tile_q0 list tiles of `llmk_attention_tc_tile_queries`
-// queries each.  v_lbo / v_sbo: 0 for the defaults (descriptor strides of the V operand).
+// queries each; an entry with sequence -1 is skipped.  The two lists must not be written by a kernel of this
+// library launched just before (they are read before the wait on the kernel before).  v_lbo / v_sbo: 0 for the defaults (descriptor strides of the V operand).
 LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, long long q_stride, int n_tokens,
                                   const void* kcache, const void* vcache, long long num_pages,
                                   const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,

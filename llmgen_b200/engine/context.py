@@ -88,7 +88,7 @@ class StepMetaBuilder:
     ALIGN = 4  # words: every array starts on a 16-byte boundary
 
     def __init__(self, q_lens: Sequence[int] = (), starts: Sequence[int] = (), pure_decode: bool = False,
-                 page_size: int = 0):
+                 page_size: int = 0, token_bound: int = 0):
         self.names: List[str] = []
         self.arrays: Dict[str, np.ndarray] = {}
         # the batch, for parts that derive arrays of their own from it
@@ -98,6 +98,10 @@ class StepMetaBuilder:
         self.n_tokens = sum(self.q_lens)
         self.pure_decode = pure_decode
         self.page_size = page_size
+        # > 0: the step is laid out for replay with this many token rows (rows beyond `n_tokens` belong to no
+        # sequence, and `q_lens` ends in sequences of length 0): a part's arrays must then have sizes that follow
+        # from (token_bound, n_seqs) alone, whatever the lengths are
+        self.token_bound = token_bound
 
     def add(self, name: str, values, dtype=np.int32) -> None:
         if name in self.arrays:

@@ -155,6 +155,12 @@ class Executor:
         self._status_hosts = [torch.zeros(2, dtype=torch.int32).pin_memory() for _ in range(3)]
         self._ids_turn = 0
         self.graphs: Dict[Tuple[int, int], dict] = {}     # (batch-size bucket, context-length class) -> graph
+        # steps of any other kind (portions of prompts, with or without single tokens beside them) replay a graph
+        # captured for their shape, (token rows, sequences) rounded up: see `step_shape`
+        self.shape_graphs: Dict[Tuple[int, int], dict] = {}
+        self.shaped_steps = not self.eager and all(getattr(m, "replay_any_step", False) for m in self._unique_mixers)
+        self.n_shaped_steps = 0
+        self._token_shapes, self._seq_shapes = self.token_shapes(), self.seq_shapes()
         self._graph_logits = None                         # float32 [max_num_seqs, vocab], shared by the graphs
         # decode steps rewrite only what changed in a host buffer that the same bucket filled last
         self._host_owner = [None, None]                   # per pinned buffer: (bucket, layout) of its last fill
@@ -251,7 +257,11 @@ class Executor:
         passes = self._passes(entries)
         logits_parts, ids_parts, order = [], [], []
         for sub, keys in passes:
-            out = self._eager_pass(sub, sample, return_logits or len(passes) > 1)
+            shape = self.step_shape(sub) if self.shaped_steps and self.profiler is None else None
+            if shape is not None:
+                out = self._shaped_pass(sub, sample, return_logits or len(passes) > 1, shape)
+            else:
+                out = self._eager_pass(sub, sample, return_logits or len(passes) > 1)
             if return_logits or len(passes) > 1:
                 logits_parts.append(out.logits)
             if sample:
@@ -343,19 +353,22 @@ class Executor:
 
     # -- metadata
     def _build_meta(self, entries: Sequence[StepEntry], pad_to: int = 0, ctx_bound: int = 0,
-                    ids_from: Optional[Sequence[int]] = None):
+                    ids_from: Optional[Sequence[int]] = None, shape: Optional[Tuple[int, int]] = None):
         """Fill and upload the step's metadata; returns (StepContext, want rows view, temps view,
-        view of the sampler's row keys, number of wanted rows).  A batch padded to a graph's shape (`pad_to`) also gets
-        `ids_from`: for each row the row of the step before whose sampled id is its token, or -1."""
+        view of the sampler's row keys, number of wanted rows).  A batch of single tokens padded to a graph's
+        shape (`pad_to` sequences) also gets `ids_from`: for each row the row of the step before whose sampled id
+        is its token, or -1.  `shape` = (token rows, sequences) lays any other step out for the graph of that
+        shape: token rows beyond the step's own belong to no sequence and are written nowhere, and the sequences
+        beyond its own have no tokens."""
         lim = self.limits
         ps = lim.page_size
         S_real = len(entries)
-        S = max(S_real, pad_to)
-        q_lens = [len(e.tokens) for e in entries] + [1] * (S - S_real)
+        S = max(S_real, pad_to, shape[1] if shape else 0)
+        q_lens = [len(e.tokens) for e in entries] + [0 if shape else 1] * (S - S_real)
         starts = [e.start for e in entries] + [0] * (S - S_real)
-        T = sum(q_lens)
-        pure_decode = all(n == 1 for n in q_lens)
-        b = StepMetaBuilder(q_lens, starts, pure_decode, lim.page_size)
+        T = max(sum(q_lens), shape[0] if shape else 0)
+        pure_decode = all(n == 1 for n in q_lens) and not shape
+        b = StepMetaBuilder(q_lens, starts, pure_decode, lim.page_size, token_bound=shape[0] if shape else 0)
         ids = np.zeros(T, dtype=np.int32)
         pos = np.zeros(T, dtype=np.int32)
         seq_of = np.zeros(T, dtype=np.int32)
@@ -377,6 +390,9 @@ class Executor:
             t += n
             cu_q[s + 1] = t
         for s in range(S_real, S):          # padding rows: one token, no keys, written nowhere
+            if shape:
+                cu_q[s + 1] = t
+                continue
             seq_of[t] = s
             t += 1
             cu_q[s + 1] = t
@@ -394,9 +410,6 @@ class Executor:
         b.add("cu_q", cu_q)
         b.add("ctx_len", ctx_len)
         b.add("state_slots", state_slots)
-        b.add("want_rows", np.asarray(want_rows, dtype=np.int32))
-        b.add("temps", np.asarray(temps, dtype=np.float32), dtype=np.float32)
-        b.add("row_keys", np.asarray(keys, dtype=np.uint64).view(np.int32))
         for gi, g in enumerate(self.cache.groups):
             slots = np.full(T, -1, dtype=np.int32)
             bt = np.zeros((S, self.max_blocks), dtype=np.int32)
@@ -413,6 +426,11 @@ class Executor:
             b.add(f"block_tables_{gi}", bt)
         for m in self._unique_mixers:
             m.prepare_step(b)
+        # what only the sampler and the gather of the wanted rows read comes last: its size is the one thing that a
+        # step's shape does not fix, and nothing that a replayed graph reads lies behind it
+        b.add("want_rows", np.asarray(want_rows, dtype=np.int32))
+        b.add("temps", np.asarray(temps, dtype=np.float32), dtype=np.float32)
+        b.add("row_keys", np.asarray(keys, dtype=np.uint64).view(np.int32))
 
         turn = self._meta_turn
         self._meta_turn ^= 1
@@ -472,16 +490,34 @@ class Executor:
             self.profiler.begin_pass([e.start for e in entries], [len(e.tokens) for e in entries])
         ctx, want_rows, temps, keys, n_want = self._build_meta(entries, pad_to=pad_to)
         ctx.fixed_shapes = pad_to > 0      # the launch shapes a captured graph of this step would have
+        resid, delta = self.model.hidden_states(ctx, self.layer_caches)
+        return self._finish_pass(entries, ctx, resid, delta, want_rows, temps, keys, n_want, sample, return_logits)
+
+    def _shaped_pass(self, entries: Sequence[StepEntry], sample: bool, return_logits: bool, shape: Tuple[int, int]) -> StepOutput:
+        """What `_eager_pass` gives, with the layers replayed from the graph of the step's shape."""
+        g = self.shape_graphs.get(shape) or self._capture_shape(shape)
+        ctx, want_rows, temps, keys, n_want = self._build_meta(entries, shape=shape)
+        if self._shape_layout() != g["layout"]:
+            # a part laid its arrays out by the step's lengths, not by its shape: such a model's steps cannot be
+            # replayed; launch this one and all later ones kernel by kernel
+            self.shaped_steps = False
+            return self._eager_pass(entries, sample, return_logits)
+        g["graph"].replay()
+        self.launch_count += g["launches"]
+        self.n_shaped_steps += 1
+        return self._finish_pass(entries, ctx, g["resid"], g["delta"], want_rows, temps, keys, n_want, sample, return_logits)
+
+    def _finish_pass(self, entries, ctx, resid, delta, want_rows, temps, keys, n_want, sample, return_logits) -> StepOutput:
+        """Logits of the wanted rows of a pass whose layers have run (or are in the stream), and their sampled ids."""
         n_real = sum(len(e.want) for e in entries)
         out = StepOutput()
         if n_want == 0:
-            self.model.hidden_states(ctx, self.layer_caches)
             if return_logits:
                 out.logits = torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
             if sample:
                 out.token_ids = []
             return out
-        logits = self.model.forward(ctx, self.layer_caches, want_rows, n_want)
+        logits = self.model.logits(ctx, resid, delta, want_rows, n_want)
         if sample:
             ids_dev = self.workspace.flat("sampled_ids", max(n_want, self.limits.max_num_seqs), torch.int32)[:n_want]
             if ops.sample_scratch_bytes(n_want) > self.sample_scratch.numel() * 4:
@@ -596,6 +632,65 @@ class Executor:
                     self._capture(b, bound)
                     made += 1
         return made
+
+    # ------------------------------------------------------------------ graphs for steps of any kind
+    def token_shapes(self) -> List[int]:
+        """Token rows that a step which is not all single tokens is padded to before it replays a graph: 16 to 256
+        in the few-rows products' own steps, then multiples of 128 up to 1,024 (the tiled product's tile: padding
+        costs it nothing), of 256 up to 2,048 and of 512 beyond."""
+        top = self.limits.max_step_tokens
+        out = [16, 32, 48, 64, 96, 128, 192, 256] + list(range(384, 1025, 128)) + list(range(1280, 2049, 256))
+        out += list(range(2560, top + 512, 512))
+        out = [t for t in out if t < top]
+        return out + [top]
+
+    def seq_shapes(self) -> List[int]:
+        top = self.limits.max_num_seqs
+        return [b for b in (8, 64) if b < top] + [top]
+
+    def step_shape(self, entries: Sequence[StepEntry]) -> Optional[Tuple[int, int]]:
+        """(token rows, sequences) of the graph that this step replays."""
+        n_tokens = sum(len(e.tokens) for e in entries)
+        rows = next((t for t in self._token_shapes if t >= n_tokens), None)
+        seqs = next((b for b in self._seq_shapes if b >= len(entries)), None)
+        if rows is None or seqs is None:
+            return None
+        return rows, seqs
+
+    def _capture_shape(self, shape: Tuple[int, int]) -> dict:
+        """Record the launches of all layers for a step of `shape` into a graph.  They depend on the shape alone:
+        the step's arrays have fixed places and sizes in the uploaded block (lists of tiles are padded to the most
+        the shape can have) and every kernel runs over all token rows of the shape.  The gather of the wanted rows,
+        the output projection and the sampler stay outside: how many rows are wanted is not part of the shape."""
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            ctx = self._build_meta([], shape=shape)[0]      # loads kernels, creates the workspaces
+            ctx.fixed_shapes = True
+            self.model.hidden_states(ctx, self.layer_caches)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        self.workspace.frozen = True
+        launches_before = ops.launches()
+        try:
+            # the upload of the arrays stays outside the graph
+            ctx = self._build_meta([], shape=shape)[0]
+            ctx.fixed_shapes = True
+            layout = self._shape_layout()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph, stream=stream):
+                resid, delta = self.model.hidden_states(ctx, self.layer_caches)
+        finally:
+            self.workspace.frozen = False
+        entry = {"graph": graph, "resid": resid, "delta": delta, "layout": layout,
+                 "launches": ops.launches() - launches_before}
+        self.shape_graphs[shape] = entry
+        return entry
+
+    def _shape_layout(self) -> dict:
+        """Places and sizes of the arrays of the step just laid out, without those that no graph reads."""
+        return {k: v for k, v in self._last_fill[1].items() if k not in ("want_rows", "temps", "row_keys")}
 
     def _graph_step(self, entries: Sequence[StepEntry]) -> StepOutput:
         return StepOutput(None, self.decode_collect(self._decode_launch(entries, None)))

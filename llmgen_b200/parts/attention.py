@@ -28,6 +28,10 @@ class GQAAttention(Mixer):
     # what `prepare_step` adds depends on the lengths of the step's portions only, not on their
     # positions or requests: the engine may keep it across decode steps of one batch size
     step_arrays_follow_shapes = True
+    # its launches follow from a step's shape (token rows, sequences) alone, its lists of tiles have the length
+    # that the shape bounds, and token rows that belong to no sequence pass through untouched: any step may be
+    # replayed from the graph of its shape
+    replay_any_step = True
 
     @staticmethod
     def weight_decls(spec: AttentionSpec):
@@ -92,12 +96,20 @@ class GQAAttention(Mixer):
         if builder.has(name + "_seq"):
             return
         tiles = []
+        bound = getattr(builder, "token_bound", 0)
         for s, n in enumerate(builder.q_lens):
+            if bound and n == 0:
+                continue
             for start in range(0, max(n, 1), bq):
                 keys = builder.starts[s] + min(start + bq, max(n, 1))
                 tiles.append((min(keys, self.window + bq) if self.window else keys, s, start))
         if heaviest_first:
             tiles.sort(key=lambda t: -t[0])
+        if bound:
+            # a list of fixed length for the step's shape: no more tiles than this exist for `bound` tokens in
+            # `n_seqs` sequences; the rest is padding (sequence -1), which the kernels skip
+            most = bound // bq + builder.n_seqs
+            tiles += [(0, -1, 0)] * (most - len(tiles))
         builder.add(name + "_seq", [t[1] for t in tiles])
         builder.add(name + "_q0", [t[2] for t in tiles])
 

@@ -21,6 +21,16 @@ Mixer:
     prepare_step(builder)                     optional: add int32 arrays to the step's metadata
     step_arrays_follow_shapes = True          optional class attribute: those arrays depend on the
                                               portions' lengths only (lets decode steps reuse them)
+    replay_any_step = True                    optional class attribute: steps of every kind may be replayed from
+                                              a graph captured for their shape.  The mixer then promises that
+                                              `forward` launches the same kernels with the same arguments for
+                                              every step of one (token rows, sequences) pair: it reads lengths,
+                                              positions and tables from the step's device arrays only; arrays it
+                                              adds in `prepare_step` have sizes that follow from
+                                              `builder.token_bound` and `builder.n_seqs` (padded if need be);
+                                              token rows beyond the sequences' own (slot -1, in no sequence) and
+                                              sequences of length 0 are harmless to it.  Without it such steps
+                                              are launched kernel by kernel
     step_arrays_key()                         optional: mixers with equal keys add the same arrays,
                                               and only one of them is asked each step
     forward(ctx, x, cache) -> [T, H]          x is the normed input; `cache` is this run

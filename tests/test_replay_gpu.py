@@ -91,10 +91,11 @@ def test_last_32_one_by_one(tmp, name, dtype):
         logits_close(torch.cat(got), ref[head - 1:], dtype, bound)
 
 
+@pytest.mark.parametrize("eager", [True, False], ids=["launched", "replayed"])
 @pytest.mark.parametrize("name,dtype", CASES)
-def test_portions_of_changing_size(tmp, name, dtype):
+def test_portions_of_changing_size(tmp, name, dtype, eager):
     path, reqs, refs, bound = case(tmp, name)
-    d = Driver(path, dtype, 128, TINY[name][5])
+    d = Driver(path, dtype, 128, TINY[name][5], eager=eager)
     rng = random.Random(5)
     for ids, ref in zip(reqs, refs):
         n, p, got = len(ids), 0, []
@@ -107,6 +108,7 @@ def test_portions_of_changing_size(tmp, name, dtype):
             got.append(d.step([("r", ids[p:p + c], range(c))], end=["r"] if p + c == n else []))
             p += c
         logits_close(torch.cat(got), ref, dtype, bound)
+    assert eager or d.executor.n_shaped_steps > 0            # portions went through the graphs of their shapes
 
 
 def mixed_trace(reqs, seed, max_live=4):
@@ -142,14 +144,15 @@ def mixed_trace(reqs, seed, max_live=4):
     return steps, peak
 
 
+@pytest.mark.parametrize("eager", [True, False], ids=["launched", "replayed"])
 @pytest.mark.parametrize("name,dtype", CASES + [("C-sharp", "float32"), ("B-sharp", "float32"), ("A-sharp", "float32")])
-def test_mixed_with_pages_used_again(tmp, name, dtype):
+def test_mixed_with_pages_used_again(tmp, name, dtype, eager):
     sharp = name.endswith("-sharp")
     name = name[0]
     path, reqs, refs, bound = case(tmp, name, sharp)
     steps, pool = mixed_trace(reqs, seed=3)
     assert pool < sum((len(r) + 63) // 64 * 64 for r in reqs)          # so pages must be used again
-    d = Driver(path, dtype, pool, TINY[name][5])
+    d = Driver(path, dtype, pool, TINY[name][5], eager=eager)
     seen_pages = set()
     reused = False
     worst = 0.0
@@ -169,6 +172,7 @@ def test_mixed_with_pages_used_again(tmp, name, dtype):
     assert d.executor.cache.all_free()
     total_pages_taken = sum((len(r) + TINY[name][5] - 1) // TINY[name][5] for r in reqs)
     assert len(seen_pages) < total_pages_taken                           # some page served two requests
+    assert eager or (d.executor.n_shaped_steps > 0 and d.executor.shaped_steps)
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "float32"), ("C", "bfloat16"), ("B", "bfloat16")])
@@ -184,10 +188,11 @@ def test_long_decoding(tmp, name, dtype):
     logits_close(torch.cat(got), ref, dtype, bound)
 
 
+@pytest.mark.parametrize("eager", [True, False], ids=["launched", "replayed"])
 @pytest.mark.parametrize("name,dtype", CASES)
-def test_first_tokens(tmp, name, dtype):
+def test_first_tokens(tmp, name, dtype, eager):
     path, reqs, refs, bound = case(tmp, name)
-    d = Driver(path, dtype, 128, TINY[name][5])
+    d = Driver(path, dtype, 128, TINY[name][5], eager=eager)
     ids, ref = reqs[0], refs[0]
     # a prompt of one token, then single tokens; beside it a request cut 1 + 1 + 2
     got_a = [d.step([("a", ids[:1], [0])])]
@@ -202,9 +207,10 @@ def test_first_tokens(tmp, name, dtype):
     logits_close(torch.cat(got_b), refs[1][:4], dtype, bound)
 
 
+@pytest.mark.parametrize("eager", [True, False], ids=["launched", "replayed"])
 @pytest.mark.parametrize("name", ["D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_prompts_in_portions_beside_decoding(tmp, name, dtype):
+def test_long_prompts_in_portions_beside_decoding(tmp, name, dtype, eager):
     """517 and 330 tokens: several query and key tiles of the tensor-core kernel, portions that
     start inside a tile, a portion beside a decoded token, then both decoding (the flash-decoding
     kernel with several key parts), then a portion again."""
@@ -213,7 +219,7 @@ def test_long_prompts_in_portions_beside_decoding(tmp, name, dtype):
     a, b = random_ids(517, vocab, 41), random_ids(330, vocab, 42)
     (ref_a, bound_a), (ref_b, bound_b) = reference(path, a), reference(path, b)
     bound = max(bound_a, bound_b)
-    d = Driver(path, dtype, 1024, TINY[name][5])
+    d = Driver(path, dtype, 1024, TINY[name][5], eager=eager)
     worst = 0.0
 
     def check(got, *parts):
@@ -249,17 +255,18 @@ def needle_case(tmp, name, n, needle_at, seed=5, positions=0):
     return path, ids, ref, bound
 
 
+@pytest.mark.parametrize("eager", [True, False], ids=["launched", "replayed"])
 @pytest.mark.parametrize("name", ["D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n,needle_at", [(100, 3), (300, 15), (300, 16), (300, 160), (600, 127), (600, 128), (600, 31), (600, 597)])
-def test_one_key_that_matters_is_found_wherever_it_lies(tmp, name, dtype, n, needle_at):
+def test_one_key_that_matters_is_found_wherever_it_lies(tmp, name, dtype, n, needle_at, eager):
     """The needle model (tests.util.needle_folder): the probe token at the end reads mostly one key, which lies
     at a page's first or last place, at a key tile's edge, hundreds of keys back or next to the probe.  Its
     logits are compared when the probe comes with the whole prompt, as the last of a portion after portions of
     uneven size, and as a single decoded token after pages were given back and taken again."""
     path, ids, ref, bound = needle_case(tmp, name, n, needle_at)
     page = TINY[name][5]
-    d = Driver(path, dtype, 1024, page)
+    d = Driver(path, dtype, 1024, page, eager=eager)
     got = d.step([("w", ids, [n - 1])], end=["w"])
     logits_close(got, ref[n - 1:], dtype, bound)
     # pages of "w" are free again; another request takes some of them first, so that "p" gets them in another order

@@ -132,5 +132,12 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
         assert ex.admit("c") and ex.reserve("c", 0, len(ids_b))
         got_c = ex.step([StepEntry("c", ids_b, 0, list(range(5)))]).logits.cpu()
         assert float((got_c - ref_b).abs().max()) < 1e-4
+        # the toy reads the step's lengths on the host and does not say `replay_any_step`: an engine that replays
+        # graphs launches this model's steps of portions kernel by kernel all the same
+        ex2 = Executor(model, EngineLimits(max_num_seqs=3, max_model_len=64, max_step_tokens=64, page_size=16, num_pages=8))
+        assert not ex2.shaped_steps
+        assert ex2.admit("d") and ex2.reserve("d", 0, len(ids_b))
+        got_d = ex2.step([StepEntry("d", ids_b, 0, list(range(5)))]).logits.cpu()
+        assert float((got_d - ref_b).abs().max()) < 1e-4 and ex2.n_shaped_steps == 0
     finally:
         unregister_architecture("ToyForCausalLM")

@@ -139,13 +139,14 @@ class Driver:
     """Drives an `Executor` the way `bin/trace_run` does: keeps each request's position,
     reserves pages, runs steps, gives pages back."""
 
-    def __init__(self, model_dir: str, dtype: str, pool_tokens: int, page_size: int = 16, max_num_seqs: int = 8, model=None):
+    def __init__(self, model_dir: str, dtype: str, pool_tokens: int, page_size: int = 16, max_num_seqs: int = 8, model=None,
+                 eager: bool = True):
         from llmgen_b200.engine.api import load_model
         from llmgen_b200.engine.executor import EngineLimits, Executor
         self.model = model if model is not None else load_model(model_dir, dtype)
         limits = EngineLimits(max_num_seqs=max_num_seqs, max_model_len=min(self.model.max_positions(), pool_tokens),
                               max_step_tokens=pool_tokens, page_size=page_size, num_pages=pool_tokens // page_size)
-        self.executor = Executor(self.model, limits, eager=True)
+        self.executor = Executor(self.model, limits, eager=eager)
         self.positions: Dict[object, int] = {}
 
     def step(self, entries: Sequence[tuple], end: Sequence = ()) -> torch.Tensor:
