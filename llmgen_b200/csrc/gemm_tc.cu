@@ -142,6 +142,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             pdl_launch_dependents();
+            // W is a weight: no kernel of the stream writes it, so the first slices of it are asked for before the
+            // wait for the kernel that makes A, and arrive while that kernel ends.
+            uint32_t w_ahead = 0;
+            if constexpr (!PAIR) {
+                if (unit < total_tiles) {
+                    w_ahead = (uint32_t)(num_kb < STAGES ? num_kb : STAGES);
+                    const int n0 = (unit / m_tiles) * BN;
+                    for (uint32_t kb = 0; kb < w_ahead; ++kb) {
+                        const uint32_t bar = tc::smem_u32(&full[kb]);
+                        tc::mbar_expect_tx(bar, L::STAGE_BYTES);
+                        tc::tma_load_2d(tc::smem_u32(smem + kb * L::STAGE_BYTES) + MB * L::A_BYTES, &map_w, bar, (int)kb * BK, n0);
+                    }
+                }
+            }
             pdl_wait();   // A was written by the kernel before this one
             uint32_t it = 0;        // k-slices loaded so far, over all tiles of this block
             bool ok = true;
@@ -161,10 +175,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tc::tma_load_2d_pair(a_dst, &map_a, bar0, kb * BK, m0);
                         tc::tma_load_2d_pair(a_dst + L::A_BYTES, &map_w, bar0, kb * BK, n0);
                     } else {
-                        tc::mbar_expect_tx(bar, L::STAGE_BYTES);
+                        const bool w_here = it < w_ahead;       // its bytes are expected and W is on its way
+                        if (!w_here) tc::mbar_expect_tx(bar, L::STAGE_BYTES);
 #pragma unroll
                         for (int i = 0; i < MB; ++i) tc::tma_load_2d(a_dst + i * L::A_BYTES, &map_a, bar, kb * BK, m0 + i * BM);
-                        tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, kb * BK, n0);
+                        if (!w_here) tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, kb * BK, n0);
                     }
                 }
             }

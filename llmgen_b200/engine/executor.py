@@ -623,24 +623,32 @@ class Executor:
 
     def capture_all(self) -> int:
         """Capture the decode graph of every batch-size bucket and context class, as the reference does for its
-        buckets when it starts (src/executor.zig:609-660), so that no step of a run pays for a capture.
-        Returns how many graphs were captured."""
+        buckets when it starts (src/executor.zig:609-660), and the graph of every shape of the other steps, so that
+        no step of a run pays for a capture.  Returns how many graphs were captured."""
         made = 0
         for bound in self.context_classes():
             for b in self.buckets():
                 if (b, bound) not in self.graphs:
                     self._capture(b, bound)
                     made += 1
+        if self.shaped_steps:
+            for seqs in self._seq_shapes:
+                for rows in self._token_shapes:
+                    if (rows, seqs) not in self.shape_graphs:
+                        self._capture_shape((rows, seqs))
+                        made += 1
         return made
 
     # ------------------------------------------------------------------ graphs for steps of any kind
+    SHAPED_TOKENS_MAX = 2048      # steps of more tokens are launched kernel by kernel: the GPU then lags the host anyway
+
     def token_shapes(self) -> List[int]:
         """Token rows that a step which is not all single tokens is padded to before it replays a graph: 16 to 256
         in the few-rows products' own steps, then multiples of 128 up to 1,024 (the tiled product's tile: padding
-        costs it nothing), of 256 up to 2,048 and of 512 beyond."""
-        top = self.limits.max_step_tokens
+        costs it nothing) and of 256 up to 2,048.  Above that a step's kernels take longer than its launches, and
+        capturing a graph for it would cost more than it saves."""
+        top = min(self.limits.max_step_tokens, self.SHAPED_TOKENS_MAX)
         out = [16, 32, 48, 64, 96, 128, 192, 256] + list(range(384, 1025, 128)) + list(range(1280, 2049, 256))
-        out += list(range(2560, top + 512, 512))
         out = [t for t in out if t < top]
         return out + [top]
 
