@@ -306,8 +306,9 @@ def main():
         The layers of such a step are replayed from the CUDA graph of its shape; wall time against device time shows
         what the host costs."""
         reqs = [f"mix{i}" for i in range(decoding)]
-        for r in reqs + ["mixp"]:
-            assert ex.admit(r) and ex.reserve(r, 0, 512 + repeats * portion + 8)
+        for r in reqs:
+            assert ex.admit(r) and ex.reserve(r, 0, 512 + repeats + 3)
+        assert ex.admit("mixp") and ex.reserve("mixp", 0, (repeats + 3) * portion)
         ex.step([StepEntry(r, rng.integers(0, V, 512).tolist(), 0, [511], 0.6) for r in reqs], sample=True, return_logits=False)
         dev, wall = [], []
         for i in range(repeats + 3):

@@ -128,7 +128,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // block leaves before it sets anything up.  The list is read ahead of `griddepcontrol.wait`: it belongs
     // to the step's arrays, which a copy wrote before the step's first kernel started, never a kernel of the
     // step itself.
-    if (p.tile_seq[blockIdx.y] < 0) return;
+    if (p.tile_seq[blockIdx.y] < 0) {
+        // the block still waits for the kernel before: were all tiles padding, this grid would otherwise count as
+        // complete before that kernel is, and the kernel after this one could start too early
+        pdl_wait();
+        return;
+    }
     if ((tc::smem_u32(smem) & 1023u) != 0) {      // uniform over the block: nothing has been set up yet
         if (threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 2);
         return;

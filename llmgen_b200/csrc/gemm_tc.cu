@@ -80,7 +80,7 @@ __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __e
 template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_c, int store_by_tma,
+               const __grid_constant__ CUtensorMap map_c, int store_by_tma, int splits,
                TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag) {
     static_assert(!PAIR || MB == 1, "a pair of blocks takes one block of rows each");
     using L = Smem<BN, STAGES, MB, PAIR>;
@@ -102,6 +102,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int m_tiles = (M + ROWS - 1) / ROWS;
     const int n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
+    // K may be cut into `splits` slices (float32 results only): work item i is slice i / total_tiles of tile
+    // i % total_tiles and leaves its sum in slice `split` of C ([splits][M][ldc]) for the consumer to add up
+    const int total_items = total_tiles * splits;
+    const int kb_per_split = (num_kb + splits - 1) / splits;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // which block of the pair
     const int unit = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x; // this block's (or pair's) place in the grid
     const int units = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x;
@@ -146,23 +150,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // wait for the kernel that makes A, and arrive while that kernel ends.
             uint32_t w_ahead = 0;
             if constexpr (!PAIR) {
-                if (unit < total_tiles) {
-                    w_ahead = (uint32_t)(num_kb < STAGES ? num_kb : STAGES);
-                    const int n0 = (unit / m_tiles) * BN;
-                    for (uint32_t kb = 0; kb < w_ahead; ++kb) {
-                        const uint32_t bar = tc::smem_u32(&full[kb]);
+                if (unit < total_items) {
+                    const int tile = unit % total_tiles, kb0 = (unit / total_tiles) * kb_per_split;
+                    const int kbs = min(num_kb, kb0 + kb_per_split) - kb0;
+                    w_ahead = (uint32_t)(kbs < STAGES ? kbs : STAGES);
+                    const int n0 = (tile / m_tiles) * BN;
+                    for (uint32_t i = 0; i < w_ahead; ++i) {
+                        const uint32_t bar = tc::smem_u32(&full[i]);
                         tc::mbar_expect_tx(bar, L::STAGE_BYTES);
-                        tc::tma_load_2d(tc::smem_u32(smem + kb * L::STAGE_BYTES) + MB * L::A_BYTES, &map_w, bar, (int)kb * BK, n0);
+                        tc::tma_load_2d(tc::smem_u32(smem + i * L::STAGE_BYTES) + MB * L::A_BYTES, &map_w, bar, (kb0 + (int)i) * BK, n0);
                     }
                 }
             }
             pdl_wait();   // A was written by the kernel before this one
             uint32_t it = 0;        // k-slices loaded so far, over all tiles of this block
             bool ok = true;
-            for (int tile = unit; tile < total_tiles && ok; tile += units) {
+            for (int item = unit; item < total_items && ok; item += units) {
+                const int tile = item % total_tiles, split = item / total_tiles;
                 const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM;
                 const int n0 = (tile / m_tiles) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kb_end = min(num_kb, (split + 1) * kb_per_split);
+                for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (!tc::mbar_wait(tc::smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -200,14 +208,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
-            for (int tile = unit; tile < total_tiles && ok; tile += units, ++tile_iter) {
+            for (int item = unit; item < total_items && ok; item += units, ++tile_iter) {
+                const int split = item / total_tiles;
+                const int kb_begin = split * kb_per_split, kb_end = min(num_kb, (split + 1) * kb_per_split);
                 const int buf = tile_iter % ACC_SETS;
                 // the epilogue must have read this accumulator set before it is filled again
                 ok = tc::mbar_wait(tc::smem_u32(&acc_empty[buf]), ((tile_iter / ACC_SETS) & 1) ^ 1, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after_sync();
                 const uint32_t acc = tmem_base + (uint32_t)(buf * MB * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     ok = tc::mbar_wait(tc::smem_u32(&full[s]), round & 1, abort_flag);
@@ -219,12 +229,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
                         if constexpr (PAIR) {
-                            tc::mma_bf16_ss_pair(acc, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, (kb | k) != 0);
+                            tc::mma_bf16_ss_pair(acc, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, ((kb - kb_begin) | k) != 0);
                         } else {
 #pragma unroll
                             for (int i = 0; i < MB; ++i)
                                 tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
-                                                db, idesc, (kb | k) != 0);
+                                                db, idesc, ((kb - kb_begin) | k) != 0);
                         }
                     }
                     if constexpr (PAIR) tc::mma_commit_pair(tc::smem_u32(&empty[s]), (uint16_t)3);
@@ -244,7 +254,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int tile_iter = 0;
         uint32_t box_iter = 0;          // boxes this warp has handed to TMA
-        for (int tile = unit; tile < total_tiles && ok; tile += units, ++tile_iter) {
+        for (int item = unit; item < total_items && ok; item += units, ++tile_iter) {
+            const int tile = item % total_tiles, split = item / total_tiles;
             const int buf = tile_iter % ACC_SETS;
             const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM, n0 = (tile / m_tiles) * BN;
             ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&acc_full[buf]), (tile_iter / ACC_SETS) & 1, abort_flag));
@@ -312,6 +323,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     continue;
                 }
             }
+            if constexpr (sizeof(TC) == 4 && MB == 1 && !GATED) {
+                if (store_by_tma) {
+                    // float32 slices: slabs of 32 rows x 32 columns (128 bytes a row), handed to TMA the same way
+                    const uint32_t slabs = tc::smem_u32(smem + L::STAGING_OFFSET) + (uint32_t)quarter * 2 * L::SLAB_BYTES;
+                    const uint32_t acc0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+                    const bool rows_live = m0 + quarter * 32 < M;      // uniform over the warp
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        if (n0 + c0 >= N || !rows_live) break;
+                        const uint32_t slab = slabs + (uint32_t)(box_iter & 1) * L::SLAB_BYTES;
+                        if (lane == 0) tc::bulk_wait_read<1>();
+                        __syncwarp();
+                        uint32_t r[32];
+                        tc::tmem_ld_32x32_wait(acc0 + (uint32_t)c0, r);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            tc::st_shared_v4(slab + (uint32_t)lane * 128 + (uint32_t)((q ^ (lane & 7)) << 4),
+                                             make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]));
+                        tc::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tc::tma_store_3d(&map_c, slab, n0 + c0, m0 + quarter * 32, split);
+                            tc::bulk_commit();
+                        }
+                        ++box_iter;
+                    }
+                    tc::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (PAIR) tc::mbar_arrive_cluster(cluster_map_shared(tc::smem_u32(&acc_empty[buf]), 0));
+                        else tc::mbar_arrive(tc::smem_u32(&acc_empty[buf]));
+                    }
+                    continue;
+                }
+            }
 #pragma unroll 1
             for (int cc = 0; cc < MB * BN; cc += 32) {
                 const int mb = cc / BN, c0 = cc % BN;          // which block of rows, which columns of it
@@ -347,7 +393,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (j0 + i < n_out) dst[i] = from_float<TC>(o[i]);
                     }
                 } else {
-                    TC* dst = C + (size_t)row * ldc + n0 + c0;
+                    TC* dst = C + ((size_t)split * M + row) * ldc + n0 + c0;
                     if (vec_ok && n0 + c0 + 32 <= N) {
                         if constexpr (sizeof(TC) == 2) {
 #pragma unroll
@@ -434,9 +480,25 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
 
 int g_store_by_tma = 1;      // 0: the threads store their rows themselves (for measurements)
 
+// float32 slices of C ([splits][M][ldc]) for TMA stores of [32 x 32] boxes
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_slice_maps;
+bool get_slice_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t slices) {
+    MapKey key{base, rows, cols, ld, slices};
+    std::lock_guard<std::mutex> guard(g_map_lock);
+    auto it = g_slice_maps.find(key);
+    if (it != g_slice_maps.end()) {
+        *out = it->second;
+        return true;
+    }
+    if (!tc_host::make_map_f32_slices(out, base, rows, cols, ld, slices, 32)) return false;
+    if (g_slice_maps.size() > 1024) g_slice_maps.clear();
+    g_slice_maps.emplace(key, *out);
+    return true;
+}
+
 template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, long long ldc,
-           int* error_flag, int pdl, cudaStream_t s) {
+           int* error_flag, int pdl, cudaStream_t s, int splits = 1) {
     using L = Smem<BN, STAGES, MB, PAIR>;
     auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB, PAIR>;
     static bool configured = false;   // per instantiation
@@ -451,18 +513,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     int store_by_tma = 0;
     if (sizeof(TC) == 2 && MB == 1 && g_store_by_tma && host_aligned16(C) && ldc % 8 == 0)
         store_by_tma = get_map(&mc, C, M, GATED ? N / 2 : N, ldc, 32) ? 1 : 0;
+    if (sizeof(TC) == 4 && MB == 1 && !GATED && g_store_by_tma && host_aligned16(C) && ldc % 4 == 0)
+        store_by_tma = get_slice_map(&mc, C, M, N, ldc, splits) ? 1 : 0;
     const int NUM_SMS = device_sm_count();
     if constexpr (PAIR) {
         // clusters of two blocks, one pair of SMs each
-        const int tiles = ceil_div(N, BN) * ceil_div(M, 2 * BM);
+        const int tiles = ceil_div(N, BN) * ceil_div(M, 2 * BM) * splits;
         const int pairs = tiles < NUM_SMS / 2 ? tiles : NUM_SMS / 2;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch_clusters(kernel, dim3(2 * pairs), dim3(THREADS), L::TOTAL, s, pdl != 0,
-                                                             dim3(2, 1, 1), ma, mw, mc, store_by_tma, (TC*)C, M, N, K,
+                                                             dim3(2, 1, 1), ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K,
                                                              ldc, error_flag));
     } else {
-        const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM);
+        const int tiles = ceil_div(N, BN) * ceil_div(M, MB * BM) * splits;
         LLMK_CHECK_LAUNCH_RC("gemm_tc", llmk_launch(kernel, dim3(tiles < NUM_SMS ? tiles : NUM_SMS), dim3(THREADS), L::TOTAL, s,
-                                                    pdl != 0, ma, mw, mc, store_by_tma, (TC*)C, M, N, K, ldc,
+                                                    pdl != 0, ma, mw, mc, store_by_tma, splits, (TC*)C, M, N, K, ldc,
                                                     error_flag));
     }
     return LLMK_OK;
@@ -526,6 +590,39 @@ LLMK_EXPORT int llmk_gemm_tc_usable(const void* A, const void* W, int M, int N, 
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0) return 0;
     if (!host_aligned16(A) || !host_aligned16(W)) return 0;
     return 1;
+}
+
+// Into how many slices of K a product is best cut when its tiles of 128 x 128 are too few for the SMs: about
+// one work item per SM, at least 4 steps of 64 along K per item, at most 16 slices.  1: not cut.
+LLMK_EXPORT int llmk_gemm_tc_splits(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 1;
+    const int NUM_SMS = device_sm_count();
+    const long long tiles = (long long)ceil_div(M, BM) * ceil_div(N, 128);
+    if (tiles * 4 >= 3LL * NUM_SMS) return 1;           // the tiles alone keep three quarters of the SMs busy
+    const int num_kb = ceil_div(K, BK);
+    int splits = (int)(NUM_SMS / tiles);
+    if (splits > num_kb / 4) splits = num_kb / 4;
+    if (splits > 16) splits = 16;
+    if (splits < 2) return 1;
+    const int per = ceil_div(num_kb, splits);
+    return ceil_div(num_kb, per);                        // no slice is left empty
+}
+
+// C (float32, [splits][M][ldc]) receives the sums over `splits` slices of K of A[M, K] * W[N, K]^T, in tiles of
+// 128 x 128; the consumer adds the slices up in slice order.
+LLMK_EXPORT int llmk_gemm_tc_sliced(float* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                                    long long ldw, long long ldc, int splits, int* error_flag, int pdl, void* stream) {
+    if (M <= 0 || N <= 0) return LLMK_OK;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || !host_aligned16(A) || !host_aligned16(W))
+        LLMK_FAIL("gemm_tc: operands not usable (K=%d lda=%lld ldw=%lld must be multiples of 8, bases 16-byte aligned)", K, lda, ldw);
+    const int num_kb = ceil_div(K, BK);
+    if (splits < 1 || splits > num_kb) LLMK_FAIL("gemm_tc: %d slices for K=%d", splits, K);
+    if ((splits - 1) * ceil_div(num_kb, splits) >= num_kb) LLMK_FAIL("gemm_tc: %d slices of K=%d would leave one empty", splits, K);
+    if (ldc < N) LLMK_FAIL("gemm_tc: ldc=%lld too small", ldc);
+    CUtensorMap ma, mw;
+    if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, N, K, ldw, 128))
+        LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
+    return launch<float, 128, STAGES_128, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, (cudaStream_t)stream, splits);
 }
 
 LLMK_EXPORT void llmk_gemm_tc_set_pair_mode(int mode) { g_pair_mode = mode; }

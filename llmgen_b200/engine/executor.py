@@ -224,6 +224,8 @@ class Executor:
             self.cache.fresh_state.clear()
 
     def reserve(self, req: Hashable, start: int, end: int) -> bool:
+        if end > self.limits.max_model_len:
+            raise StepError(f"request {req!r}: positions up to {end} exceed max_model_len {self.limits.max_model_len}")
         return self.cache.reserve(req, start, end)
 
     def can_reserve(self, req: Hashable, start: int, end: int) -> bool:
@@ -455,7 +457,9 @@ class Executor:
         ctx = StepContext(
             n_tokens=T, n_seqs=S, dtype=self.dtype, device=self.device, workspace=self.workspace,
             requests=[e.req for e in entries], starts=starts, q_lens=q_lens, pure_decode=pure_decode,
-            max_ctx=longest, max_ctx_bound=ctx_bound or self.context_class(longest),
+            # a step laid out for the graph of its shape is bounded by the longest sequence the engine takes: the
+            # graph's launches must hold for every step of that shape
+            max_ctx=longest, max_ctx_bound=ctx_bound or (lim.max_model_len if shape else self.context_class(longest)),
             max_seqs_bound=lim.max_num_seqs,
             ids=views["ids"], ids_from=views.get("ids_from"),
             prev_sampled=self.sampled_dev if "ids_from" in layout else None,

@@ -254,6 +254,34 @@ def gemv_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+_tc_plans = {}
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    """Into how many slices of K the tiled product is best cut when its tiles are too few for the SMs (1: not cut)."""
+    key = (M, N, K)
+    v = _tc_plans.get(key)
+    if v is None:
+        v = int(build.load("gemm_tc").llmk_gemm_tc_splits(c_int(M), c_int(N), c_int(K)))
+        _tc_plans[key] = v
+    return v
+
+
+def gemm_tc_sliced(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """The tiled tensor-core product cut along K: out is float32 [splits, M, N] and receives the sums
+    of `splits` slices of K, for a consumer that adds them up (`Partials`)."""
+    lib = build.load("gemm_tc")
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError(f"gemm_tc: operands a{list(a.shape)} {a.dtype} w{list(w.shape)} {w.dtype} do not fit")
+    if out.dim() != 3 or out.shape[1] != M or out.shape[2] != N or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("gemm_tc: the slices go to a contiguous float32 [splits, M, N] array")
+    _check(lib, lib.llmk_gemm_tc_sliced(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(a)),
+                                        c_longlong(_row_stride(w)), c_longlong(N), c_int(out.shape[0]),
+                                        _ptr(tc_error_flag(a.device)), c_int(1), _stream()))
+
+
 def gemm_tc_set_pair_mode(mode: int) -> None:
     """How `gemm_tc` uses pairs of blocks on 256-row tiles (`tcgen05.mma.cta_group::2`): 0 never,
     1 where the product has the rows for it (the default), 2 / 3 always, with tiles 256 / 128 columns
@@ -353,7 +381,11 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
                                  c_int(1 if pdl else 0), _stream()))
 
 
-SKINNY_MAX_ROWS = 256
+SKINNY_MAX_ROWS = 256        # what the kernel takes
+SKINNY_BEST_ROWS = 32        # up to here it is the faster product (measured at 16, 32, 48 and 64 rows against the tiled product cut along K)
+# most bytes of float32 slices one cut product leaves: about one 128 x 128 item per SM for the tiled product,
+# 8 slices of 64 rows by the widest matrix for the few-rows one
+SLICED_PRODUCT_BYTES = 16 << 20
 SKINNY_DIRECT, SKINNY_PARTIAL, SKINNY_GATED = 0, 1, 2
 SKINNY_CLUSTER_GATED = 5     # slices of K added up inside a cluster (2 or 4), then silu(gate) * up: out[M, N/2]
 SKINNY_CLUSTER_MAX_ROWS = 64

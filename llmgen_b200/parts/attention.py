@@ -6,7 +6,7 @@ import torch
 from ..cache.manager import FULL, WINDOW
 from ..kernels import ops
 from .base import KVRequest, LayerCache, Mixer
-from .linear import GEMM_MODULES, linear_sliced
+from .linear import GEMM_MODULES, linear, linear_sliced
 from .registry import build_position, norm_class, register_mixer
 from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
 
@@ -155,26 +155,32 @@ class GQAAttention(Mixer):
 
     def workspace_bytes(self, tokens: int) -> int:
         """Bytes of activations this part keeps in the step's workspace for `tokens` rows: the packed projection
-        (or its float32 slices at few rows), q, the attention's output and the output projection."""
+        (and the float32 slices of two products cut along K), q, the attention's output and the output projection."""
         elem = 2 if self.dtype == torch.bfloat16 else 4
         packed = (self.nq + 2 * self.nkv) * self.hd
-        few = min(tokens, ops.SKINNY_MAX_ROWS) * 8 * max(packed, self.spec.hidden_size) * 4
-        return tokens * (packed + 2 * self.nq * self.hd + self.spec.hidden_size) * elem + few
+        return tokens * (packed + 2 * self.nq * self.hd + self.spec.hidden_size) * elem + 2 * ops.SLICED_PRODUCT_BYTES
 
     def forward(self, ctx, x, cache: LayerCache):
         T = ctx.n_tokens
         ws = ctx.workspace
         group = ctx.groups[cache.group]
         nk = self.nkv if cache.writes else 0
-        packed = linear_sliced(ws, "attn_qkv" if cache.writes else "attn_q_only", x,
-                               self.w_qkv if cache.writes else self.w_q, self.dtype)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rot = self.position.rotary_dim if self.position is not None else 0
-        o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
-        scale = float(self.spec.scale)
         decode = (self.dtype == torch.bfloat16 and ctx.pure_decode
                   and ops.attention_decode_usable(self.nq, self.nkv, self.hd, cache.page_size))
-        if decode and ops.attention_decode_fuses_prep(self.hd, rot):
+        fused = decode and ops.attention_decode_fuses_prep(self.hd, rot)
+        w = self.w_qkv if cache.writes else self.w_q
+        name = "attn_qkv" if cache.writes else "attn_q_only"
+        if fused or T <= ops.SKINNY_BEST_ROWS or self.dtype != torch.bfloat16:
+            packed = linear_sliced(ws, name, x, w, self.dtype)
+        else:
+            # the preparation kernel's fast path wants finished rows: with hundreds of them a product cut along K
+            # would save less than adding its slices up there costs
+            packed = linear(x, w, ws.buffer(name, T, w.shape[0], self.dtype))
+        o = ws.buffer("attn_o", T, self.nq * self.hd, self.dtype)
+        scale = float(self.spec.scale)
+        if fused:
             # single decoded tokens: the attention kernel normalises, rotates and stores q, k and v itself
             self._decode(ctx, o, None, cache, group, scale,
                          prep=dict(packed=packed, nk=nk, rot=rot, positions=ctx.positions, slots=group.slots, cos=cos,

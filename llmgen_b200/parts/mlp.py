@@ -61,10 +61,10 @@ class GatedMLP(FeedForward):
 
     def workspace_bytes(self, tokens: int) -> int:
         """Bytes of activations this part keeps in the step's workspace for `tokens` rows: the packed gate/up
-        product or its float32 slices (few rows only), the activation and the output."""
+        product, the activation and the output, and the float32 slices of two products cut along K."""
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         elem = 2 if self.dtype == torch.bfloat16 else 4
-        return tokens * (2 * F + F + H) * elem + min(tokens, ops.SKINNY_MAX_ROWS) * 8 * max(2 * F, H) * 4
+        return tokens * (2 * F + F + H) * elem + 2 * ops.SLICED_PRODUCT_BYTES
 
     def forward(self, ctx, x):
         T = x.shape[0]
@@ -78,9 +78,9 @@ class GatedMLP(FeedForward):
             # follows there, so neither the packed product nor a kernel for the activation is needed
             # (0.982 -> 0.967 ms a decode step at batch 8 against slices and an activation kernel)
             ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_CLUSTER_GATED, splits=cluster)
-        elif gated and T <= ops.SKINNY_MAX_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
+        elif gated and T <= ops.SKINNY_BEST_ROWS and ops.gemm_skinny_splits(T, 2 * F, H) == 1:
             ops.gemm_skinny(act, x, self.w_gate_up, ops.SKINNY_GATED)
-        elif gated and T > ops.SKINNY_MAX_ROWS:
+        elif gated and T > ops.SKINNY_BEST_ROWS:
             ops.gemm_tc(act, x, self.w_gate_up, gated=True)
         else:
             gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)

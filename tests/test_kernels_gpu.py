@@ -309,6 +309,48 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
     assert err < (2e-5 if out_dtype == torch.float32 else 6e-3) * scale, (err, scale)
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(96, 1024, 2048, 16), (128, 4096, 1024, 4), (300, 1000, 1032, 3), (512, 1024, 3072, 4),
+                                          (70, 130, 520, 9), (1024, 1024, 2048, 2), (257, 72, 136, 2)])
+def test_gemm_tc_cut_along_k(ops, M, N, K, splits):
+    """The tiled product cut along K: the float32 slices add up to the product (float64 reference of the same
+    bfloat16 operands), rows and columns beyond the matrix are not written, tails in M, N and K, and a last
+    slice shorter than the others."""
+    torch.manual_seed(60 + M)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    out = torch.full((splits + 1, M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_tc_sliced(out[:splits], dev(a), dev(w))
+    torch.cuda.synchronize()
+    ops.check_tc_errors(out.device)
+    ref = a.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    err = float((out[:splits].double().sum(0).cpu() - ref).abs().max())
+    assert err < 2e-5 * scale, (err, scale)
+    assert float((out[splits] - 7.0).abs().max()) == 0.0           # the array behind the slices is untouched
+    # each slice is the product over its own columns of K
+    per = ((K + 63) // 64 + splits - 1) // splits * 64
+    lo = (splits - 1) * per
+    last = a[:, lo:].double() @ w[:, lo:].double().t()
+    assert float((out[splits - 1].double().cpu() - last).abs().max()) < 2e-5 * scale
+
+
+def test_gemm_tc_splits_follow_the_tiles(ops):
+    """Few tiles: K is cut until about every SM has an item, no slice empty; many tiles: not cut."""
+    sms = ops.sm_count(torch.device("cuda"))
+    for M, N, K in [(96, 1024, 2048), (128, 4096, 1024), (512, 1024, 3072), (384, 6144, 1024), (2048, 1024, 2048), (65, 1024, 64)]:
+        s = ops.gemm_tc_splits(M, N, K)
+        tiles = ((M + 127) // 128) * ((N + 127) // 128)
+        kb = (K + 63) // 64
+        assert 1 <= s <= 16 and tiles * s <= max(sms, tiles)
+        if s > 1:
+            per = (kb + s - 1) // s
+            assert per >= 4 and (s - 1) * per < kb
+        if tiles * 4 >= 3 * sms:
+            assert s == 1
+
+
 @pytest.mark.parametrize("mode", [3, 2])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 200, 136), (2048, 1024, 3072), (100, 4096, 1024), (1000, 520, 2048)])
 def test_gemm_tc_pairs_of_blocks(ops, M, N, K, mode):
