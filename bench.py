@@ -202,6 +202,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
+    ap.add_argument("--lazy-graphs", action="store_true",
+                    help="for profiling runs: capture each CUDA graph when it is first used, not all of them at start")
     ap.add_argument("--mixed", default="", metavar="DECODING,PORTION,REPEATS",
                     help="for profiling runs: only steps of DECODING single tokens beside a portion of PORTION tokens")
     ap.add_argument("--kernels", action="store_true",
@@ -244,7 +246,7 @@ def main():
     model = random_model(cfg, SEED, "bfloat16")
     llm = LLM(model, max_num_seqs=64, max_model_len=args.context, max_batched_tokens=16384, pass_tokens=8192,
               block_size=args.block_size, gpu_util=0.5, seed=SEED,
-              capture_at_start=not args.mixed)      # a profiling run of mixed steps replays no decode graph
+              capture_at_start=not (args.mixed or args.lazy_graphs))
     ex = llm.executor
     V = cfg["vocab_size"]
     sampler = ClockSampler()

@@ -42,11 +42,12 @@ constexpr int BK = 64;           // one 128-byte swizzle row of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 
-template <int BN, int STAGES, int MB, bool PAIR = false>
+template <int BN, int STAGES, int MB, bool PAIR = false, int KS = 1>
 struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;        // one block of 128 rows of A
     static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;   // a pair's blocks hold half of the W rows each
-    static constexpr int STAGE_BYTES = MB * A_BYTES + B_BYTES;
+    static constexpr int SUB_BYTES = MB * A_BYTES + B_BYTES;        // one step of 64 along K: A blocks, then W
+    static constexpr int STAGE_BYTES = KS * SUB_BYTES;              // a stage of the ring holds KS such steps
     // the epilogue's staging: per epilogue warp two slabs of 32 rows x 64 bfloat16 columns (128-byte swizzle)
     static constexpr int SLAB_BYTES = 32 * 128;
     static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;
@@ -77,13 +78,13 @@ __device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __e
 // commits arrive on the `empty` and `acc_full` barriers of both blocks; the epilogue warps of both
 // release an accumulator set on rank 0's `acc_empty`.  Each block reads its own 128 rows of the
 // accumulator out of its own tensor memory.
-template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false>
+template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false, int KS = 1>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_c, int store_by_tma, int splits,
                TC* __restrict__ C, int M, int N, int K, long long ldc, int* error_flag) {
     static_assert(!PAIR || MB == 1, "a pair of blocks takes one block of rows each");
-    using L = Smem<BN, STAGES, MB, PAIR>;
+    using L = Smem<BN, STAGES, MB, PAIR, KS>;
     constexpr int ROWS = (PAIR ? 2 : MB) * BM;                     // rows of a tile
     constexpr int ACC_SETS = 2 * MB * BN <= 512 ? 2 : 1;
     constexpr uint32_t TMEM_COLS = ACC_SETS * MB * BN;             // 128, 256 or 512: a power of two
@@ -105,7 +106,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // K may be cut into `splits` slices (float32 results only): work item i is slice i / total_tiles of tile
     // i % total_tiles and leaves its sum in slice `split` of C ([splits][M][ldc]) for the consumer to add up
     const int total_items = total_tiles * splits;
-    const int kb_per_split = (num_kb + splits - 1) / splits;
+    // a stage of the ring holds KS steps of 64 along K under one barrier (the hand-over of a stage costs about as
+    // much as the copy of a narrow tile's step, so narrow tiles take two steps a stage); a slice begins on a stage
+    const int kb_per_split = ((num_kb + splits - 1) / splits + KS - 1) / KS * KS;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // which block of the pair
     const int unit = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x; // this block's (or pair's) place in the grid
     const int units = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x;
@@ -152,13 +155,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if constexpr (!PAIR) {
                 if (unit < total_items) {
                     const int tile = unit % total_tiles, kb0 = (unit / total_tiles) * kb_per_split;
-                    const int kbs = min(num_kb, kb0 + kb_per_split) - kb0;
-                    w_ahead = (uint32_t)(kbs < STAGES ? kbs : STAGES);
+                    const int sts = (min(num_kb, kb0 + kb_per_split) - kb0 + KS - 1) / KS;     // stages of the first item
+                    w_ahead = (uint32_t)(sts < STAGES ? sts : STAGES);
                     const int n0 = (tile / m_tiles) * BN;
                     for (uint32_t i = 0; i < w_ahead; ++i) {
                         const uint32_t bar = tc::smem_u32(&full[i]);
                         tc::mbar_expect_tx(bar, L::STAGE_BYTES);
-                        tc::tma_load_2d(tc::smem_u32(smem + i * L::STAGE_BYTES) + MB * L::A_BYTES, &map_w, bar, (kb0 + (int)i) * BK, n0);
+#pragma unroll
+                        for (int h = 0; h < KS; ++h)      // a step beyond K is filled with zeros and counts its bytes all the same
+                            tc::tma_load_2d(tc::smem_u32(smem + i * L::STAGE_BYTES + h * L::SUB_BYTES) + MB * L::A_BYTES, &map_w, bar,
+                                            (kb0 + (int)i * KS + h) * BK, n0);
                     }
                 }
             }
@@ -170,24 +176,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int m0 = (tile % m_tiles) * ROWS + (int)rank * BM;
                 const int n0 = (tile / m_tiles) * BN + (PAIR ? (int)rank * (BN / 2) : 0);
                 const int kb_end = min(num_kb, (split + 1) * kb_per_split);
-                for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
+                for (int kb = split * kb_per_split; kb < kb_end; kb += KS, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (!tc::mbar_wait(tc::smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t bar = tc::smem_u32(&full[s]);
-                    const uint32_t a_dst = tc::smem_u32(smem + s * L::STAGE_BYTES);
                     if constexpr (PAIR) {
                         // both blocks' bytes are counted on rank 0's barrier
                         if (rank == 0) tc::mbar_expect_tx(bar, 2 * L::STAGE_BYTES);
                         const uint32_t bar0 = cluster_map_shared(bar, 0);
-                        tc::tma_load_2d_pair(a_dst, &map_a, bar0, kb * BK, m0);
-                        tc::tma_load_2d_pair(a_dst + L::A_BYTES, &map_w, bar0, kb * BK, n0);
+#pragma unroll
+                        for (int h = 0; h < KS; ++h) {
+                            const uint32_t a_dst = tc::smem_u32(smem + s * L::STAGE_BYTES + h * L::SUB_BYTES);
+                            tc::tma_load_2d_pair(a_dst, &map_a, bar0, (kb + h) * BK, m0);
+                            tc::tma_load_2d_pair(a_dst + L::A_BYTES, &map_w, bar0, (kb + h) * BK, n0);
+                        }
                     } else {
                         const bool w_here = it < w_ahead;       // its bytes are expected and W is on its way
                         if (!w_here) tc::mbar_expect_tx(bar, L::STAGE_BYTES);
 #pragma unroll
-                        for (int i = 0; i < MB; ++i) tc::tma_load_2d(a_dst + i * L::A_BYTES, &map_a, bar, kb * BK, m0 + i * BM);
-                        if (!w_here) tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, kb * BK, n0);
+                        for (int h = 0; h < KS; ++h) {
+                            const uint32_t a_dst = tc::smem_u32(smem + s * L::STAGE_BYTES + h * L::SUB_BYTES);
+#pragma unroll
+                            for (int i = 0; i < MB; ++i) tc::tma_load_2d(a_dst + i * L::A_BYTES, &map_a, bar, (kb + h) * BK, m0 + i * BM);
+                            if (!w_here) tc::tma_load_2d(a_dst + MB * L::A_BYTES, &map_w, bar, (kb + h) * BK, n0);
+                        }
                     }
                 }
             }
@@ -217,24 +230,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!ok) break;
                 tc::tc_fence_after_sync();
                 const uint32_t acc = tmem_base + (uint32_t)(buf * MB * BN);
-                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                for (int kb = kb_begin; kb < kb_end; kb += KS, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     ok = tc::mbar_wait(tc::smem_u32(&full[s]), round & 1, abort_flag);
                     if (!ok) break;
                     tc::tc_fence_after_sync();
-                    const uint32_t a_addr = tc::smem_u32(smem + s * L::STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + MB * L::A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
-                        if constexpr (PAIR) {
-                            tc::mma_bf16_ss_pair(acc, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, ((kb - kb_begin) | k) != 0);
-                        } else {
+                    for (int h = 0; h < KS; ++h) {
+                        if (kb + h >= kb_end) break;            // a step beyond K holds zeros: nothing to add
+                        const uint32_t a_addr = tc::smem_u32(smem + s * L::STAGE_BYTES + h * L::SUB_BYTES);
+                        const uint32_t b_addr = a_addr + MB * L::A_BYTES;
 #pragma unroll
-                            for (int i = 0; i < MB; ++i)
-                                tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
-                                                db, idesc, ((kb - kb_begin) | k) != 0);
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
+                            const bool add = ((kb + h - kb_begin) | k) != 0;
+                            if constexpr (PAIR) {
+                                tc::mma_bf16_ss_pair(acc, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, add);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < MB; ++i)
+                                    tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
+                                                    db, idesc, add);
+                            }
                         }
                     }
                     if constexpr (PAIR) tc::mma_commit_pair(tc::smem_u32(&empty[s]), (uint16_t)3);
@@ -496,11 +514,11 @@ bool get_slice_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t c
     return true;
 }
 
-template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false>
+template <typename TC, int BN, int STAGES, bool GATED, int MB, bool PAIR = false, int KS = 1>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, long long ldc,
            int* error_flag, int pdl, cudaStream_t s, int splits = 1) {
-    using L = Smem<BN, STAGES, MB, PAIR>;
-    auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB, PAIR>;
+    using L = Smem<BN, STAGES, MB, PAIR, KS>;
+    auto kernel = gemm_tc_kernel<TC, BN, STAGES, GATED, MB, PAIR, KS>;
     static bool configured = false;   // per instantiation
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -538,7 +556,7 @@ int g_pair_mode = 1;
 
 // ring depth of the narrower tiles (3, 4 and 6 were measured on a prompt's products: no difference
 // beyond 4, the MMA instructions set the pace)
-constexpr int STAGES_128 = 4, STAGES_64 = 4;
+constexpr int STAGES_128 = 3, KS_128 = 2, STAGES_64 = 4;      // 128-wide tiles: three stages of two steps along K
 
 template <typename TC, bool GATED>
 int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
@@ -570,14 +588,14 @@ int dispatch_tile(const void* A, const void* W, void* C, int M, int N, int K, lo
         if (!get_map(&pa, A, M, K, lda, BM) || !get_map(&pw, W, N, K, ldw, pair_bn / 2))
             LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
         if (pair_bn == 256) return launch<TC, 256, 6, GATED, 1, true>(pa, pw, C, M, N, K, ldc, error_flag, pdl, s);
-        return launch<TC, 128, 6, GATED, 1, true>(pa, pw, C, M, N, K, ldc, error_flag, pdl, s);
+        return launch<TC, 128, 4, GATED, 1, true, 2>(pa, pw, C, M, N, K, ldc, error_flag, pdl, s);
     }
     CUtensorMap ma, mw;
     if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, N, K, ldw, bn))
         LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
     switch (bn) {
         case 256: return launch<TC, 256, 4, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
-        case 128: return launch<TC, 128, STAGES_128, GATED, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
+        case 128: return launch<TC, 128, STAGES_128, GATED, 1, false, KS_128>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
         default: return launch<TC, 64, STAGES_64, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, s);
     }
 }
@@ -604,7 +622,7 @@ LLMK_EXPORT int llmk_gemm_tc_splits(int M, int N, int K) {
     if (splits > num_kb / 4) splits = num_kb / 4;
     if (splits > 16) splits = 16;
     if (splits < 2) return 1;
-    const int per = ceil_div(num_kb, splits);
+    const int per = ceil_div(ceil_div(num_kb, splits), KS_128) * KS_128;      // a slice begins on a stage of the ring
     return ceil_div(num_kb, per);                        // no slice is left empty
 }
 
@@ -617,12 +635,13 @@ LLMK_EXPORT int llmk_gemm_tc_sliced(float* C, const void* A, const void* W, int 
         LLMK_FAIL("gemm_tc: operands not usable (K=%d lda=%lld ldw=%lld must be multiples of 8, bases 16-byte aligned)", K, lda, ldw);
     const int num_kb = ceil_div(K, BK);
     if (splits < 1 || splits > num_kb) LLMK_FAIL("gemm_tc: %d slices for K=%d", splits, K);
-    if ((splits - 1) * ceil_div(num_kb, splits) >= num_kb) LLMK_FAIL("gemm_tc: %d slices of K=%d would leave one empty", splits, K);
+    if ((splits - 1) * (ceil_div(ceil_div(num_kb, splits), KS_128) * KS_128) >= num_kb)
+        LLMK_FAIL("gemm_tc: %d slices of K=%d would leave one empty (slices are multiples of %d columns)", splits, K, KS_128 * BK);
     if (ldc < N) LLMK_FAIL("gemm_tc: ldc=%lld too small", ldc);
     CUtensorMap ma, mw;
     if (!get_map(&ma, A, M, K, lda, BM) || !get_map(&mw, W, N, K, ldw, 128))
         LLMK_FAIL("gemm_tc: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
-    return launch<float, 128, STAGES_128, false, 1>(ma, mw, C, M, N, K, ldc, error_flag, pdl, (cudaStream_t)stream, splits);
+    return launch<float, 128, STAGES_128, false, 1, false, KS_128>(ma, mw, C, M, N, K, ldc, error_flag, pdl, (cudaStream_t)stream, splits);
 }
 
 LLMK_EXPORT void llmk_gemm_tc_set_pair_mode(int mode) { g_pair_mode = mode; }
