@@ -59,7 +59,7 @@ def _bf(*shape, scale=1.0):
 
 
 # ------------------------------------------------------------------------------ products
-def products(rows=(1, 8, 64, 2048)):
+def products(rows=(1, 8, 64, 256, 512, 2048)):
     out = []
     shapes = [("qkv", (NQ + 2 * NKV) * HD, H), ("o_proj", H, NQ * HD), ("down", H, F), ("lm_head", V, H)]
     for name, N, K in shapes:
@@ -71,20 +71,26 @@ def products(rows=(1, 8, 64, 2048)):
             x = _bf(M, K)
             y_ref = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
             t_ref = time_us(lambda i: ref.linear(y_ref, x, ws[i]), n)
-            if M <= ops.SKINNY_MAX_ROWS:
-                splits = ops.gemm_skinny_splits(M, N, K)
-                if splits > 1:
-                    part = torch.empty(splits, M, N, dtype=torch.float32, device="cuda")
+            # the choice parts/linear.py makes: the few-rows product up to SKINNY_BEST_ROWS, the tiled one above,
+            # either of them cut along K (float32 slices for the consumer) where that fills the SMs
+            few = M <= ops.SKINNY_BEST_ROWS
+            splits = ops.gemm_skinny_splits(M, N, K) if few else ops.gemm_tc_splits(M, N, K)
+            if name == "lm_head":
+                splits = 1                                   # float32 logits, never cut
+            if splits > 1:
+                part = torch.empty(splits, M, N, dtype=torch.float32, device="cuda")
+                if few:
                     ours = lambda i: ops.gemm_skinny(part, x, ws[i], ops.SKINNY_PARTIAL)
-                    what = f"gemm_skinny, {splits} slices of K"
                 else:
-                    y = torch.empty(M, N, dtype=torch.float32 if name == "lm_head" else torch.bfloat16, device="cuda")
-                    ours = lambda i: ops.gemm_skinny(y, x, ws[i])
-                    what = "gemm_skinny"
+                    ours = lambda i: ops.gemm_tc_sliced(part, x, ws[i])
+                what = f"{'gemm_skinny' if few else 'gemm_tc'}, {splits} slices of K"
             else:
-                y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-                ours = lambda i: ops.gemm_tc(y, x, ws[i])
-                what = "gemm_tc"
+                y = torch.empty(M, N, dtype=torch.float32 if name == "lm_head" else torch.bfloat16, device="cuda")
+                if few:
+                    ours = lambda i: ops.gemm_skinny(y, x, ws[i])
+                else:
+                    ours = lambda i: ops.gemm_tc(y, x, ws[i])
+                what = "gemm_skinny" if few else "gemm_tc"
             t_ours = time_us(ours, n)
             out.append({"kernel": f"{name} [{N} x {K}]", "case": f"M = {M}", "ours": what,
                         "reference": "gemv_kernel" if M <= 2 else "cublasGemmEx", "ours_us": t_ours, "ref_us": t_ref,

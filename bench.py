@@ -202,6 +202,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
+    ap.add_argument("--rates", action="store_true",
+                    help="print the device's tcgen05.mma and TMA rates (baseline/device_rates.py) and exit")
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="for profiling runs: capture each CUDA graph when it is first used, not all of them at start")
     ap.add_argument("--mixed", default="", metavar="DECODING,PORTION,REPEATS",
@@ -219,6 +221,10 @@ def main():
         return 0
     if args.kernels:
         return kernels_table(args)
+    if args.rates:
+        from baseline import device_rates
+        sys.stdout.write(device_rates.run())
+        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
