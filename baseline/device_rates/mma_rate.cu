@@ -7,17 +7,21 @@
 #include <cuda_runtime.h>
 #include "tcgen05.cuh"
 
-template <int N, int NACC>
+// BMN: B is read MN-major (its rows contiguous, as a [K, N] tile: the V operand of attention's P V).
+// NOISE: what the block's other three warps do meanwhile: 0 nothing, 1 load tensor memory, 2 store to shared memory.
+template <int N, int NACC, bool BMN = false, int NOISE = 0>
 __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned long long* ns, int iters, int* err) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ uint64_t bar;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ volatile int done;
     const int warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < (16384 + N * 128) / 4; i += 128) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        done = 0;
         tc::mbar_init(tc::smem_u32(&bar), 1);
         tc::fence_barrier_init();
     }
@@ -32,14 +36,15 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
     const uint32_t tmem = tmem_slot;
     if (threadIdx.x == 0) {
         const uint64_t adesc = tc::smem_desc_sw128(tc::smem_u32(smem));
-        const uint64_t bdesc = tc::smem_desc_sw128(tc::smem_u32(smem + 16384));
-        constexpr uint32_t idesc = tc::idesc_bf16_f32(128, N);
+        const uint64_t bdesc = BMN ? tc::smem_desc_sw128_mn(tc::smem_u32(smem + 16384), 128 * 128, 1024)
+                                   : tc::smem_desc_sw128(tc::smem_u32(smem + 16384));
+        constexpr uint32_t idesc = BMN ? tc::idesc_bf16_f32_b_mn(128, N) : tc::idesc_bf16_f32(128, N);
         const long long c0 = clock64();
         const unsigned long long t0 = tc::global_timer();
         for (int it = 0; it < iters; ++it) {
             const uint32_t d = tmem + (uint32_t)((it % NACC) * N);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) tc::mma_bf16_ss(d, adesc + 2 * k, bdesc + 2 * k, idesc, true);
+            for (int k = 0; k < 4; ++k) tc::mma_bf16_ss(d, adesc + 2 * k, bdesc + (BMN ? 128 * k : 2 * k), idesc, true);
         }
         tc::mma_commit(tc::smem_u32(&bar));
         const bool ok = tc::mbar_wait(tc::smem_u32(&bar), 0, &abort_flag);
@@ -48,19 +53,35 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
         if (!ok) atomicExch(err, 1);
         cycles[blockIdx.x] = c1 - c0;
         ns[blockIdx.x] = t1 - t0;
+        done = 1;
+    } else if (NOISE != 0 && warp >= 1 && warp < 4) {
+        // bounded by the issuing thread's own end (its wait is bounded) and by a count of its own
+        uint32_t r[32];
+        for (int i = 0; i < 32; ++i) r[i] = threadIdx.x + i;
+        for (int it = 0; it < 400000 && !done; ++it) {
+            if (NOISE == 1) {
+                tc::tmem_ld_32x32_wait(tmem + ((uint32_t)(warp * 32) << 16) + 256u + (uint32_t)((it & 3) * 32), r);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    tc::st_shared_v4(tc::smem_u32(smem) + 16384 + N * 128 + 1024 + (uint32_t)(((threadIdx.x * 8 + q + it) & 1023) << 4),
+                                     make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]));
+            }
+        }
+        if (r[0] == 0xdeadbeefu) atomicExch(err, 7);     // keeps the loads alive
     }
     tc::tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tc::tmem_dealloc(tmem, 512);
 }
 
-template <int N, int NACC>
+template <int N, int NACC, bool BMN = false, int NOISE = 0>
 void run(int blocks, int iters) {
     long long* cyc; unsigned long long* ns; int* err;
     cudaMalloc(&cyc, blocks * 8); cudaMalloc(&ns, blocks * 8); cudaMalloc(&err, 4); cudaMemset(err, 0, 4);
-    const int smem = 16384 + N * 128 + 1024;
-    cudaFuncSetAttribute(rate_kernel<N, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    for (int rep = 0; rep < 2; ++rep) rate_kernel<N, NACC><<<blocks, 128, smem>>>(cyc, ns, iters, err);
+    const int smem = 16384 + N * 128 + 1024 + 1024 + 16384;     // A, B, alignment slack, and 16 KB that the noise stores hit
+    cudaFuncSetAttribute(rate_kernel<N, NACC, BMN, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    for (int rep = 0; rep < 2; ++rep) rate_kernel<N, NACC, BMN, NOISE><<<blocks, 128, smem>>>(cyc, ns, iters, err);
     cudaError_t e = cudaDeviceSynchronize();
     long long hc[148]; unsigned long long hn[148]; int herr;
     cudaMemcpy(hc, cyc, blocks * 8, cudaMemcpyDeviceToHost); cudaMemcpy(hn, ns, blocks * 8, cudaMemcpyDeviceToHost);
@@ -69,7 +90,8 @@ void run(int blocks, int iters) {
     for (int i = 0; i < blocks; ++i) { mc += hc[i]; mn += hn[i]; }
     mc /= blocks; mn /= blocks;
     const double per = 4.0 * iters;
-    printf("M=128 N=%3d acc=%d blocks=%3d: %7.1f cycles / mma, %6.1f ns / mma, %6.0f TFLOP/s all blocks (%s, err %d)\n", N, NACC, blocks,
+    printf("M=128 N=%3d acc=%d %s %s blocks=%3d: %7.1f cycles / mma, %6.1f ns / mma, %6.0f TFLOP/s all blocks (%s, err %d)\n", N, NACC, BMN ? "B MN-major" : "B K-major ",
+           NOISE == 0 ? "alone            " : NOISE == 1 ? "beside tmem loads" : "beside smem stores", blocks,
            mc / per, mn / per, 2.0 * 128 * N * 16 * blocks / (mn / per) / 1e3, cudaGetErrorString(e), herr);
     cudaFree(cyc); cudaFree(ns); cudaFree(err);
 }
@@ -82,6 +104,10 @@ int main() {
         run<128, 2>(blocks, iters);
         run<256, 1>(blocks, iters);
         run<256, 2>(blocks, iters);
+        run<128, 1, true>(blocks, iters);
+        run<128, 1, false, 1>(blocks, iters);
+        run<128, 1, false, 2>(blocks, iters);
+        run<128, 1, true, 1>(blocks, iters);
     }
     return 0;
 }

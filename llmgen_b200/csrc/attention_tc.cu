@@ -45,7 +45,6 @@ namespace {
 constexpr int BM = 128;     // rows of a tile
 constexpr int BN = 128;     // keys per tile
 constexpr int THREADS = 352;    // K producer, MMA, eight softmax warps, V producer
-constexpr int MAX_PAGES_PER_TILE = 8;   // page size >= 16
 
 struct Params {
     bf16* out;
@@ -85,37 +84,37 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// First cache row of each page of the tile of keys starting at `k0` (pages past the sequence's last
-// one, or already given back by a window, are replaced by the last page: their keys are masked).
-__device__ __forceinline__ void page_rows(int (&rows)[MAX_PAGES_PER_TILE], const int* bt, int k0, int ctx, int ps,
-                                          int nkv, int kvh) {
-    const int pages_per_tile = BN / ps;
-    const int last_page = (ctx - 1) / ps;
-    const int page0 = k0 / ps;
+// The page ids of the tile of keys starting at `k0`, as the block table has them (pages past the sequence's last
+// one are replaced by the last page: their keys are masked).  Only the loads are issued here: the caller asks for
+// the next tile's ids before it waits for a free stage and issues the copies of this tile, so that the table's
+// latency (1,300 to 1,900 cycles a tile when it was looked up in turn, half of a tile's time) is not waited for.
+// PS (the page size) is a template parameter throughout: the producers are single threads whose instruction count
+// per tile is what bounds them, and constant trip counts and strides halve it.
+template <int PS>
+__device__ __forceinline__ void page_ids(int (&ids)[BN / PS], const int* bt, int k0, int last_page) {
+    const int page0 = k0 / PS;
 #pragma unroll
-    for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg) {
-        if (pg < pages_per_tile) {
-            int page = __ldg(bt + min(page0 + pg, last_page));
-            if (page < 0) page = __ldg(bt + last_page);
-            rows[pg] = (page * nkv + kvh) * ps;
-        }
+    for (int pg = 0; pg < BN / PS; ++pg) ids[pg] = __ldg(bt + min(page0 + pg, last_page));
+}
+
+// One tile of BN keys, page by page: per page and 64-wide block of the head a box [PS, 64] whose first cache row
+// is (page * nkv + kvh) * PS (a page already given back by a window, id -1, is replaced by the last page: its keys
+// are masked).
+template <int HB, int PS>
+__device__ __forceinline__ void load_pages(uint32_t dst, const CUtensorMap* map, uint32_t bar, const int (&ids)[BN / PS],
+                                           const int* bt, int last_page, int nkv, int kvh) {
+    tc::mbar_expect_tx(bar, BN * HB * 128);
+#pragma unroll
+    for (int pg = 0; pg < BN / PS; ++pg) {
+        int page = ids[pg];
+        if (page < 0) page = __ldg(bt + last_page);
+        const int row = (page * nkv + kvh) * PS;
+#pragma unroll
+        for (int h = 0; h < HB; ++h) tc::tma_load_2d(dst + h * BN * 128 + pg * PS * 128, map, bar, h * 64, row);
     }
 }
 
-// One tile of BN keys, page by page: per page and 64-wide block of the head a box [page_size, 64].
-template <int HB>
-__device__ __forceinline__ void load_pages(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                           const int (&rows)[MAX_PAGES_PER_TILE], int ps, int bytes) {
-    const int pages_per_tile = BN / ps;
-    tc::mbar_expect_tx(bar, bytes);
-#pragma unroll
-    for (int pg = 0; pg < MAX_PAGES_PER_TILE; ++pg)
-        if (pg < pages_per_tile)
-#pragma unroll
-            for (int h = 0; h < HB; ++h) tc::tma_load_2d(dst + h * BN * 128 + pg * ps * 128, map, bar, h * 64, rows[pg]);
-}
-
-template <int HD>
+template <int HD, int PS>
 __global__ void __launch_bounds__(THREADS)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -201,46 +200,59 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int h = 0; h < HB; ++h)
                 tc::tma_load_3d(tc::smem_u32(smem + L::Q_OFF + h * BM * 128), &map_q, qbar, h * 64, head0, q_beg + q0);
             const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+            const int last_page = (ctx - 1) / PS;
+            int ids[BN / PS], next_ids[BN / PS];
+            page_ids<PS>(next_ids, bt, kt0, last_page);
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j & 1;
                 const uint32_t round = j >> 1;
-                int rows[MAX_PAGES_PER_TILE];
-                page_rows(rows, bt, kt0 + j * BN, ctx, p.page_size, p.nkv, kvh);
+#pragma unroll
+                for (int pg = 0; pg < BN / PS; ++pg) ids[pg] = next_ids[pg];
+                if (j + 1 < n_tiles) page_ids<PS>(next_ids, bt, kt0 + (j + 1) * BN, last_page);
                 if (!tc::mbar_wait(tc::smem_u32(&k_empty[st]), (round & 1) ^ 1, abort_flag)) break;
-                load_pages<HB>(tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES), &map_k, tc::smem_u32(&k_full[st]), rows,
-                               p.page_size, L::KV_BYTES);
+                load_pages<HB, PS>(tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES), &map_k, tc::smem_u32(&k_full[st]), ids, bt,
+                                   last_page, p.nkv, kvh);
             }
         }
     } else if (warp == 10) {
         // V producer: a ring of its own, so that K of the next tiles never waits for a V slot.
         if (lane == 0 && n_tiles > 0) {
             const int* bt = p.block_tables + (size_t)s * p.max_blocks;
+            const int last_page = (ctx - 1) / PS;
+            int ids[BN / PS], next_ids[BN / PS];
+            page_ids<PS>(next_ids, bt, kt0, last_page);
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j & 1;
                 const uint32_t round = j >> 1;
-                int rows[MAX_PAGES_PER_TILE];
-                page_rows(rows, bt, kt0 + j * BN, ctx, p.page_size, p.nkv, kvh);
+#pragma unroll
+                for (int pg = 0; pg < BN / PS; ++pg) ids[pg] = next_ids[pg];
+                if (j + 1 < n_tiles) page_ids<PS>(next_ids, bt, kt0 + (j + 1) * BN, last_page);
                 if (!tc::mbar_wait(tc::smem_u32(&v_empty[st]), (round & 1) ^ 1, abort_flag)) break;
-                load_pages<HB>(tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES), &map_v, tc::smem_u32(&v_full[st]), rows,
-                               p.page_size, L::KV_BYTES);
+                load_pages<HB, PS>(tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES), &map_v, tc::smem_u32(&v_full[st]), ids, bt,
+                                   last_page, p.nkv, kvh);
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_s = tc::idesc_bf16_f32(BM, BN);
             constexpr uint32_t idesc_o = tc::idesc_bf16_f32_b_mn(BM, HD);
-            const uint32_t q_addr = tc::smem_u32(smem + L::Q_OFF);
-            const uint32_t p_base = tc::smem_u32(smem + L::P_OFF);
+            // descriptors of the four operands, built once: a step along K (or along the keys) adds to the start
+            // address, which is the descriptor's lowest field in units of 16 bytes
+            const uint64_t q_desc = tc::smem_desc_sw128(tc::smem_u32(smem + L::Q_OFF));
+            const uint64_t k_desc[2] = {tc::smem_desc_sw128(tc::smem_u32(smem + L::K_OFF)),
+                                        tc::smem_desc_sw128(tc::smem_u32(smem + L::K_OFF + L::KV_BYTES))};
+            const uint64_t p_desc[2] = {tc::smem_desc_sw128(tc::smem_u32(smem + L::P_OFF)),
+                                        tc::smem_desc_sw128(tc::smem_u32(smem + L::P_OFF + L::P_BYTES))};
+            const uint64_t v_desc[2] = {tc::smem_desc_sw128_mn(tc::smem_u32(smem + L::V_OFF), p.v_lbo, p.v_sbo),
+                                        tc::smem_desc_sw128_mn(tc::smem_u32(smem + L::V_OFF + L::KV_BYTES), p.v_lbo, p.v_sbo)};
             auto issue_qk = [&](int j) -> bool {
                 const int st = j & 1;
                 if (!tc::mbar_wait(tc::smem_u32(&k_full[st]), (j >> 1) & 1, abort_flag)) return false;
                 tc::tc_fence_after_sync();
-                const uint32_t k_addr = tc::smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k / 4) * (BM * 128) + (k % 4) * 32;
-                    tc::mma_bf16_ss(tmem_base + (st ? S_COL1 : S_COL0), tc::smem_desc_sw128(q_addr + off),
-                                    tc::smem_desc_sw128(k_addr + off), idesc_s, k != 0);
+                    const uint64_t off = (uint64_t)(((k / 4) * (BM * 128) + (k % 4) * 32) >> 4);
+                    tc::mma_bf16_ss(tmem_base + (st ? S_COL1 : S_COL0), q_desc + off, k_desc[st] + off, idesc_s, k != 0);
                 }
                 tc::mma_commit(tc::smem_u32(&s_full[st]));
                 tc::mma_commit(tc::smem_u32(&k_empty[st]));
@@ -256,12 +268,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                      tc::mbar_wait(tc::smem_u32(&v_full[st]), (j >> 1) & 1, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after_sync();
-                const uint32_t v_addr = tc::smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
-                const uint32_t p_addr = p_base + st * L::P_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t da = tc::smem_desc_sw128(p_addr + (kk / 4) * (BM * 128) + (kk % 4) * 32);
-                    const uint64_t db = tc::smem_desc_sw128_mn(v_addr + kk * 16 * 128, p.v_lbo, p.v_sbo);
+                    const uint64_t da = p_desc[st] + (uint64_t)(((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4);
+                    const uint64_t db = v_desc[st] + (uint64_t)((kk * 16 * 128) >> 4);
                     tc::mma_bf16_ss(tmem_base + O_COL0, da, db, idesc_o, (j | kk) != 0);   // O adds up in tensor memory over the tiles
                 }
                 tc::mma_commit(tc::smem_u32(&o_full[st]));
@@ -293,19 +303,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
         const uint32_t o_addr = tmem_base + lane_addr + O_COL0 + half * OC;     // this thread's columns of O
 
+        // This thread's scores of a tile: read from tensor memory once and kept for both passes.  (Asking for the
+        // next tile's scores in the middle of pass 2, into the registers just used up, was measured: 41.1 against
+        // 35.4 us on a 2,048-token prompt.)
+        uint32_t v[SC / 32][32];
+        static_assert(SC == 64, "two loads of 32 columns");
+        const uint32_t s_col = lane_addr + half * SC;
+        const int pair_barrier = 1 + quarter;       // the two warps of a row exchange its maxima: a barrier of their own
+
         for (int j = 0; j < n_tiles; ++j) {
             const int st = j & 1;
             const int k0 = kt0 + j * BN + half * SC;      // first key of this thread's columns
-            if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag));
-            tc::tc_fence_after_sync();
-            const uint32_t s_addr = tmem_base + lane_addr + (st ? S_COL1 : S_COL0) + half * SC;
             const bool need_mask = (k0 + SC - 1 > qpos) || (k0 <= lo);
             uint8_t* p_row = p_row0 + st * L::P_BYTES;       // P is double-buffered: P V of the tile before may still read the other
             // pass 1: the maximum of this thread's half of the row (four independent chains)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            uint32_t v[SC / 32][32];      // this thread's scores of the tile: read once, kept for both passes
-            static_assert(SC == 64, "two loads of 32 columns");
+            if (ok) ok = __all_sync(0xffffffffu, tc::mbar_wait(tc::smem_u32(&s_full[st]), (j >> 1) & 1, abort_flag));
+            tc::tc_fence_after_sync();
             if (ok) {
+                const uint32_t s_addr = tmem_base + s_col + (st ? S_COL1 : S_COL0);
                 tc::tmem_ld_32x32_x2_wait(s_addr, s_addr + 32, v[0], v[1]);
 #pragma unroll
                 for (int c = 0; c < SC / 32; ++c) {
@@ -323,7 +339,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             xchg[(st * 2 + half) * BM + r] = mx_own;
-            asm volatile("bar.sync 1, 256;" ::: "memory");       // the eight softmax warps
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");       // the row's two warps
             const float mx = fmaxf(mx_own, xchg[(st * 2 + (half ^ 1)) * BM + r]);
             // The row's reference maximum follows the true one lazily: only when that grew by more than 8 in
             // the exponent's scale (P then stays below 2^8, and the result is the same up to rounding, as
@@ -388,9 +404,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc::tc_fence_after_sync();
         }
         // the row's sum is the two halves' sums (both were kept against the same maxima)
-        asm volatile("bar.sync 1, 256;" ::: "memory");       // every read of the last tile's maxima is done
+        const int pair_barrier_end = 1 + quarter;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier_end) : "memory");       // every read of the last tile's maxima is done
         xchg[half * BM + r] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier_end) : "memory");
         const float l_row = l + xchg[(half ^ 1) * BM + r];
         const bool writes = ok && qi < max(nq_tile, 0) && (chunk * p.gc + r % p.gc) < G;
         const float inv = (row_valid && l_row > 0.f) ? 1.0f / l_row : 0.f;
@@ -432,11 +449,11 @@ int group_chunk(int G) {
     return gc;
 }
 
-template <int HD>
+template <int HD, int PS>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, dim3 grid,
            cudaStream_t s) {
     using L = Smem<HD>;
-    auto kernel = attention_tc_kernel<HD>;
+    auto kernel = attention_tc_kernel<HD, PS>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -508,6 +525,10 @@ LLMK_EXPORT int llmk_attention_tc(void* out, long long o_stride, const void* q, 
     if (n_tiles > 65535) LLMK_FAIL("attention_tc: %d tiles of queries in one launch (limit 65535)", n_tiles);
     dim3 grid(nkv * p.chunks, n_tiles);
     cudaStream_t s = (cudaStream_t)stream;
-    if (hd == 128) return launch<128>(mq, mk, mv, p, grid, s);
-    return launch<64>(mq, mk, mv, p, grid, s);
+    switch (page_size) {
+        case 16: return hd == 128 ? launch<128, 16>(mq, mk, mv, p, grid, s) : launch<64, 16>(mq, mk, mv, p, grid, s);
+        case 32: return hd == 128 ? launch<128, 32>(mq, mk, mv, p, grid, s) : launch<64, 32>(mq, mk, mv, p, grid, s);
+        case 64: return hd == 128 ? launch<128, 64>(mq, mk, mv, p, grid, s) : launch<64, 64>(mq, mk, mv, p, grid, s);
+        default: return hd == 128 ? launch<128, 128>(mq, mk, mv, p, grid, s) : launch<64, 128>(mq, mk, mv, p, grid, s);
+    }
 }
