@@ -416,3 +416,37 @@ def test_temperature_ids_do_not_depend_on_steps_launched_ahead_nor_on_the_batch(
             top = scores.topk(2)
             assert tok == int(top.indices[0]) or float(top.values[0] - top.values[1]) < 1e-4
             seq.append(tok)
+
+
+def test_steps_of_prompts_replay_the_graphs_of_their_shapes(tmp):
+    """Every step that is not all single tokens is rounded up to a shape (token rows, sequences) and replays that
+    shape's graph: the shapes cover every step up to the limit, all graphs exist once the engine is built (a run
+    captures none), chunked prompts beside decoding requests give the ids of the engine that launches kernel by
+    kernel, and a reservation beyond max_model_len is refused before it can widen a block table."""
+    from llmgen_b200 import LLM, SamplingParams
+    from llmgen_b200.engine.executor import StepEntry, StepError
+    path = make_folder(tmp, "E")
+    prompts = [random_ids(n, 290, 300 + i) for i, n in enumerate((150, 9, 77, 230, 31))]
+    params = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    outs = {}
+    for eager in (False, True):
+        llm = LLM(path, dtype="bfloat16", max_model_len=512, max_num_seqs=4, max_batched_tokens=96, kv_blocks=64, block_size=32,
+                  policy="chunked", chunk=40, eager=eager)
+        ex = llm.executor
+        if not eager:
+            shapes = ex.token_shapes()
+            assert shapes == sorted(set(shapes)) and shapes[-1] == min(ex.limits.max_step_tokens, ex.SHAPED_TOKENS_MAX)
+            assert ex.step_shape([StepEntry("x", [1] * 17, 0)]) == (32, 4)
+            assert ex.step_shape([StepEntry("x", [1] * shapes[-1], 0)]) == (shapes[-1], 4)
+            assert ex.step_shape([StepEntry("x", [1] * (shapes[-1] + 1), 0)]) is None
+            captured = len(ex.shape_graphs)
+            assert ex.shaped_steps and captured == len(shapes) * len(ex.seq_shapes()) and llm.graphs_captured >= captured
+        outs[eager] = [r["token_ids"] for r in llm.generate(prompts, params)]
+        if not eager:
+            assert ex.n_shaped_steps > 0 and len(ex.shape_graphs) == captured
+            with pytest.raises(StepError, match="max_model_len"):
+                ex.admit("far") and ex.reserve("far", 0, 513)
+            ex.release("far")
+        assert ex.cache.all_free()
+    agree = sum(sum(x == y for x, y in zip(a, b)) for a, b in zip(outs[False], outs[True]))
+    assert agree >= 0.9 * sum(len(a) for a in outs[True]), (agree, outs)
