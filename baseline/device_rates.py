@@ -1,8 +1,10 @@
-"""Two rates of the device that the kernels' rooflines rest on, measured by small programs of their own:
+"""Three rates of the device that the kernels' rooflines rest on, measured by small programs of their own:
 
     mma_rate   cycles per `tcgen05.mma` of 128 x N x 16 issued back to back (N = 64, 128, 256)
     tma_rate   bytes per clock and SM that TMA tile loads bring from L2 into shared memory, against the bytes and
                the number of boxes per stage of the ring, on one SM and on all
+    exp_rate   cycles per exponential and thread in the second pass of a softmax (fma, ex2, sum, pack, store) with 4, 8
+               and 16 warps an SM, and with part of the exponentials computed by a cubic on the FMA pipe
 
     python baseline/device_rates.py [--out FOLDER]        (needs nvcc and a B200; `bench.py --rates` calls it)
 
@@ -17,7 +19,7 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.normpath(os.path.join(HERE, "..", "llmgen_b200", "csrc"))
-PROGRAMS = ("mma_rate", "tma_rate")
+PROGRAMS = ("mma_rate", "tma_rate", "exp_rate")
 
 
 def build(out: str, nvcc: str = "nvcc"):
@@ -42,7 +44,7 @@ def run(out: str = "") -> str:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="", help="keep the two programs in this folder")
+    ap.add_argument("--out", default="", help="keep the programs in this folder")
     args = ap.parse_args()
     sys.stdout.write(run(args.out))
     return 0

@@ -203,7 +203,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true", help="for profiling runs: leave the prefill measurement out")
     ap.add_argument("--skip-e2e", action="store_true", help="for profiling runs: leave the end-to-end measurement out")
     ap.add_argument("--rates", action="store_true",
-                    help="print the device's tcgen05.mma and TMA rates (baseline/device_rates.py) and exit")
+                    help="print the device's tcgen05.mma, TMA and exponential rates (baseline/device_rates.py) and exit")
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="for profiling runs: capture each CUDA graph when it is first used, not all of them at start")
     ap.add_argument("--mixed", default="", metavar="DECODING,PORTION,REPEATS",
