@@ -529,9 +529,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, 
     // where TMA can address C (16-byte aligned base and rows); otherwise the threads store their rows
     CUtensorMap mc{};
     int store_by_tma = 0;
-    if (sizeof(TC) == 2 && MB == 1 && g_store_by_tma && host_aligned16(C) && ldc % 8 == 0)
+    // (a TMA store clips at the tensor's last column in units of 16 bytes, measured: with a width that is no
+    // multiple of 16 bytes it writes up to 7 bfloat16 columns beyond it, so such results are stored by the threads)
+    if (sizeof(TC) == 2 && MB == 1 && g_store_by_tma && host_aligned16(C) && ldc % 8 == 0 && (GATED ? N / 2 : N) % 8 == 0)
         store_by_tma = get_map(&mc, C, M, GATED ? N / 2 : N, ldc, 32) ? 1 : 0;
-    if (sizeof(TC) == 4 && MB == 1 && !GATED && g_store_by_tma && host_aligned16(C) && ldc % 4 == 0)
+    if (sizeof(TC) == 4 && MB == 1 && !GATED && g_store_by_tma && host_aligned16(C) && ldc % 4 == 0 && N % 4 == 0)
         store_by_tma = get_slice_map(&mc, C, M, N, ldc, splits) ? 1 : 0;
     const int NUM_SMS = device_sm_count();
     if constexpr (PAIR) {

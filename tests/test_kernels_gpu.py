@@ -307,6 +307,13 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
     scale = float(ref.abs().max())
     err = float((out.double().cpu() - ref).abs().max())
     assert err < (2e-5 if out_dtype == torch.float32 else 6e-3) * scale, (err, scale)
+    # the same result inside a wider array with 16-byte aligned rows (where TMA stores are possible): what lies
+    # around it is left alone, whatever N (a TMA store clips in units of 16 bytes, so other widths must not take it)
+    buf = torch.full((M + 1, N + 24 - N % 8), 7.0, dtype=out_dtype, device="cuda")
+    ops.gemm_tc(buf[:M, :N], dev(a), dev(w))
+    torch.cuda.synchronize()
+    assert torch.equal(buf[:M, :N], out)
+    assert bool((buf[M] == 7.0).all()) and bool((buf[:, N:] == 7.0).all())
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(96, 1024, 2048, 16), (128, 4096, 1024, 4), (300, 1000, 1032, 3), (512, 1024, 3072, 4),
