@@ -20,7 +20,7 @@ LLMK_DEFINE_LAST_ERROR()
 template <typename T>
 __global__ void embed_rows_kernel(float* __restrict__ out, const T* __restrict__ table,
                                   const int* __restrict__ ids, const int* __restrict__ ids_from,
-                                  const int* __restrict__ sampled, int H, int V, int* bad) {
+                                  const int* __restrict__ sampled, int H, int V, int* bad, float scale) {
     const int t = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
@@ -30,11 +30,11 @@ __global__ void embed_rows_kernel(float* __restrict__ out, const T* __restrict__
     if (!ok && threadIdx.x == 0 && bad) atomicAdd(bad, 1);
     const T* row = table + (size_t)(ok ? id : 0) * H;
     float* dst = out + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_float(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? to_float(row[i]) * scale : 0.f;
 }
 
 LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, const int* ids_from, const int* sampled,
-                                int n_tokens, int H, int V, int* bad_flag, int dtype, void* stream) {
+                                int n_tokens, int H, int V, int* bad_flag, int dtype, float scale, void* stream) {
     if (n_tokens <= 0) return LLMK_OK;
     if (H <= 0 || V <= 0) LLMK_FAIL("embed_rows: bad sizes H=%d V=%d", H, V);
     if ((ids_from != nullptr) != (sampled != nullptr)) LLMK_FAIL("embed_rows: ids_from and sampled come together");
@@ -42,12 +42,31 @@ LLMK_EXPORT int llmk_embed_rows(float* out, const void* table, const int* ids, c
     const int threads = H >= 1024 ? 256 : 128;
     cudaError_t e;
     if (dtype == LLMK_F32)
-        e = llmk_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const float*)table, ids, ids_from, sampled, H, V, bad_flag);
+        e = llmk_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const float*)table, ids, ids_from, sampled, H, V, bad_flag, scale);
     else if (dtype == LLMK_BF16)
-        e = llmk_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const bf16*)table, ids, ids_from, sampled, H, V, bad_flag);
+        e = llmk_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, true, out, (const bf16*)table, ids, ids_from, sampled, H, V, bad_flag, scale);
     else
         LLMK_FAIL("embed_rows: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("embed_rows", e);
+    return LLMK_OK;
+}
+
+// x = cap * tanh(x / cap) on float32 logits, in place: an architecture's bound on its logits (none here has one;
+// `ModelSpec.logit_cap` is the slot).
+__global__ void logit_cap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float inv = 1.0f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+LLMK_EXPORT int llmk_logit_cap(float* x, long long n, float cap, void* stream) {
+    if (n <= 0) return LLMK_OK;
+    if (!(cap > 0.f)) LLMK_FAIL("logit_cap: the cap must be positive, got %g", (double)cap);
+    long long blocks = (n + 255) / 256;
+    if (blocks > device_sm_count() * 8) blocks = device_sm_count() * 8;
+    LLMK_CHECK_LAUNCH_RC("logit_cap", llmk_launch(logit_cap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, true, x, n, cap));
     return LLMK_OK;
 }
 

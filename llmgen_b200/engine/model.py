@@ -80,7 +80,8 @@ class DecoderModel:
         """Run embedding and all run items; returns (residual float32 [T, H], pending delta)."""
         T, H = ctx.n_tokens, self.spec.hidden_size
         resid = ctx.workspace.buffer("residual", T, H, torch.float32)
-        ops.embed_rows(resid, self.embedding, ctx.ids, self.bad_token_flag, ids_from=ctx.ids_from, sampled=ctx.prev_sampled)
+        ops.embed_rows(resid, self.embedding, ctx.ids, self.bad_token_flag, ids_from=ctx.ids_from, sampled=ctx.prev_sampled,
+                       scale=float(self.spec.embedding_scale))
         delta = None
         for item, cache in zip(self.spec.run_order, caches):
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)
@@ -95,7 +96,10 @@ class DecoderModel:
         self.final_norm.add_norm(resid, delta, normed, rows=rows)
         if out is None:
             out = torch.empty((n_rows, V), dtype=torch.float32, device=self.device)
-        return linear(normed, self.lm_head, out)
+        out = linear(normed, self.lm_head, out)
+        if self.spec.logit_cap > 0:
+            ops.logit_cap(out, float(self.spec.logit_cap))
+        return out
 
     def forward(self, ctx: StepContext, caches: List[LayerCache], rows: torch.Tensor, n_rows: int,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -95,13 +95,22 @@ class Partials:
 
 # ---------------------------------------------------------------------------- elementwise
 def embed_rows(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, bad_flag: Optional[torch.Tensor] = None,
-               ids_from: Optional[torch.Tensor] = None, sampled: Optional[torch.Tensor] = None) -> None:
-    """out[t] (float32 [n, H]) = table[ids[t]]; ids int32 on the device.  With `ids_from` and
+               ids_from: Optional[torch.Tensor] = None, sampled: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out[t] (float32 [n, H]) = table[ids[t]] * scale; ids int32 on the device.  With `ids_from` and
     `sampled` (int32, device) a row whose ids_from[t] >= 0 takes the id sampled[ids_from[t]]."""
     lib = build.load("elementwise")
     n, H = out.shape
     _check(lib, lib.llmk_embed_rows(_ptr(out), _ptr(table), _ptr(ids), _ptr(ids_from), _ptr(sampled), c_int(n), c_int(H),
-                                    c_int(table.shape[0]), _ptr(bad_flag), c_int(dtype_code(table.dtype)), _stream()))
+                                    c_int(table.shape[0]), _ptr(bad_flag), c_int(dtype_code(table.dtype)), c_float(scale),
+                                    _stream()))
+
+
+def logit_cap(logits: torch.Tensor, cap: float) -> None:
+    """logits (float32, contiguous) = cap * tanh(logits / cap), in place."""
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("logit_cap: logits must be contiguous float32")
+    lib = build.load("elementwise")
+    _check(lib, lib.llmk_logit_cap(_ptr(logits), c_longlong(logits.numel()), c_float(cap), _stream()))
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, out: torch.Tensor,

@@ -152,6 +152,8 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     init_sigma: float = 0.02             # defaults of the random-weights mode
     init_sigma_norm: float = 0.1
+    embedding_scale: float = 1.0         # rows of the table are multiplied by this as they enter the residual
+    logit_cap: float = 0.0               # > 0: logits = cap * tanh(logits / cap)
     # Tensors that a model folder of this architecture may carry although the model reads none of them
     # (shell patterns), and (name, declared name) pairs of such tensors that must then hold the same values.
     ignorable_tensors: Tuple[str, ...] = ()

@@ -1,8 +1,9 @@
-"""The order in which layers run is data: an architecture defined here, from the framework's own parts, whose run
-list names one layer twice (each pass with a cache of its own) and lets a later layer attend over the keys and values
-that an earlier item stored (it projects q only).  Registered, built and stepped through the engine without a change
-to the framework's files, and compared with a plain composition of the parts' plain functions: whole prompts, portions
-of changing size beside another request, and single tokens, in float32 and bfloat16, launched and replayed."""
+"""The order in which layers run is data, and so are two numbers around the layers (a scale on the embedding's rows, a
+bound on the logits).  An architecture defined here, from the framework's own parts, has a run list that names one
+layer twice (each pass with a cache of its own) and lets a later layer attend over the keys and values that an earlier
+item stored (it projects q only).  It is registered, built and stepped through the engine without a change to the
+framework's files, and compared with a plain composition of the parts' plain functions: whole prompts, portions of
+changing size beside another request, and single tokens, in float32 and bfloat16, launched and replayed."""
 import dataclasses
 import math
 
@@ -132,3 +133,38 @@ def test_a_layer_run_twice_and_a_layer_reading_an_earlier_items_cache(looped, dt
     assert ex.cache.all_free()
     if not eager:
         assert ex.n_shaped_steps > 0 or not ex.shaped_steps
+
+
+def test_an_embedding_scale_and_a_bound_on_the_logits_are_data_too(looped):
+    """`ModelSpec.embedding_scale` and `ModelSpec.logit_cap`: rows enter the residual multiplied by the scale, logits
+    leave as cap * tanh(logits / cap); the default values change nothing (every other test runs with them)."""
+    from llmgen_b200.engine.api import require_cuda
+    from llmgen_b200.engine.executor import EngineLimits, Executor, StepEntry
+    from llmgen_b200.engine.model import DecoderModel
+    from llmgen_b200.parts.spec import default_run_order
+    from llmgen_b200.weights import weights_from_dict
+
+    spec, decls, tensors = looped
+    scale, cap = 2.5, 0.75
+    spec = dataclasses.replace(spec, run_order=default_run_order(len(spec.layers)), embedding_scale=scale, logit_cap=cap)
+    model = DecoderModel(spec, weights_from_dict(tensors, decls), torch.float32, require_cuda())
+    ex = Executor(model, EngineLimits(max_num_seqs=2, max_model_len=64, max_step_tokens=64, page_size=16, num_pages=6), eager=True)
+    ids = torch.randint(0, CFG["vocab_size"], (29,), generator=torch.Generator().manual_seed(8)).tolist()
+    # plain: the default order, the table scaled, the logits bounded
+    w = {k: v.float() for k, v in tensors.items()}
+    w_scaled = dict(w)
+    w_scaled["model.embed_tokens.weight"] = w["model.embed_tokens.weight"] * scale
+    global RUN
+    saved, RUN = RUN, [(i, i, True) for i in range(CFG["num_hidden_layers"])]
+    try:
+        hidden_ref = plain_logits(w_scaled, ids)            # its last product used the scaled table: undo that below
+    finally:
+        RUN = saved
+    ref = cap * torch.tanh(hidden_ref / scale / cap)
+    assert ex.admit("a") and ex.reserve("a", 0, len(ids))
+    got = [ex.step([StepEntry("a", ids[:20], 0, list(range(20)))]).logits.cpu()]
+    for t in range(20, len(ids)):
+        got.append(ex.step([StepEntry("a", [ids[t]], t, [0])]).logits.cpu())
+    got = torch.cat(got)
+    assert float(got.abs().max()) <= cap and float(hidden_ref.abs().max()) / scale > cap        # the bound bites
+    assert float((got - ref).abs().max()) < FP32_TOL
