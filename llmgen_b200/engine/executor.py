@@ -80,6 +80,15 @@ class StepOutput:
     token_ids: Optional[List[int]] = None   # one per wanted row, host
 
 
+def _model_parts(model):
+    """Every part object of a model: its blocks, what they hold (norms, mixer, feed-forward) and the final norm."""
+    parts = [model.final_norm]
+    for layer in model.layers:
+        parts.append(layer)
+        parts += [v for v in vars(layer).values() if hasattr(v, "forward") or hasattr(v, "add_norm")]
+    return parts
+
+
 class Executor:
     def __init__(self, model: DecoderModel, limits: EngineLimits, seed: int = DEFAULT_SEED,
                  eager: bool = False, sync_each: bool = False):
@@ -87,7 +96,11 @@ class Executor:
         self.limits = limits
         self.device = model.device
         self.dtype = model.dtype
-        self.eager = eager or sync_each
+        # a part whose `forward` cannot be recorded into a CUDA graph (it reads a result back on the host, or its
+        # launches depend on the data) says so with a class attribute `capturable = False`; every step of a model
+        # with such a part is launched kernel by kernel
+        self.uncapturable = sorted({type(p).__name__ for p in _model_parts(model) if getattr(p, "capturable", True) is False})
+        self.eager = eager or sync_each or bool(self.uncapturable)
         self.sync_each = sync_each
         self.seed = seed & MASK64
         self.n_graph_steps = 0

@@ -38,6 +38,11 @@ Mixer:
                                               `Partials` (see `parts.linear.linear_sliced`)
 Feed-forward:
     forward(ctx, x) -> [T, H]                 an array or a `Partials`
+Any part, optional:
+    capturable = False                        class attribute of a part whose `forward` (or `add_norm`) cannot be
+                                              recorded into a CUDA graph: it reads a result back on the host, or
+                                              what it launches depends on the data.  A model with such a part
+                                              runs every step kernel by kernel
 Mixer, feed-forward and block, optional:
     workspace_bytes(tokens) -> int            bytes of activations a step of `tokens` rows keeps in
                                               the workspace for this part; the engine leaves that

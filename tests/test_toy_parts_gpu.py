@@ -48,6 +48,8 @@ def make_parts():
     from llmgen_b200.parts.spec import WeightDecl
 
     class RoutedFeedForward(FeedForward):
+        capturable = False          # `forward` asks which rows chose an expert (a read-back): no graph can hold it
+
         @staticmethod
         def weight_decls(spec):
             decls = [WeightDecl(spec.router, (spec.num_experts, spec.hidden_size))]
@@ -171,8 +173,9 @@ def test_routed_feed_forward_and_another_position_encoding_register_build_and_st
         assert sum(1 for x in decls if ".e" in x.name) == 2 * 2 * 5          # two routed layers, five experts, two matrices
         tensors = random_tensors(decls, 23, 0.15, 0.1, torch.float32)
         model = DecoderModel(spec, weights_from_dict(tensors, decls), torch.float32, require_cuda())
-        ex = Executor(model, EngineLimits(max_num_seqs=2, max_model_len=64, max_step_tokens=64, page_size=16, num_pages=6),
-                      eager=True)
+        # graphs are asked for; the routed feed-forward says it cannot be recorded, so every step is launched
+        ex = Executor(model, EngineLimits(max_num_seqs=2, max_model_len=64, max_step_tokens=64, page_size=16, num_pages=6))
+        assert ex.eager and ex.uncapturable == ["RoutedFeedForward"] and not ex.shaped_steps
         gen = torch.Generator().manual_seed(4)
         ids_a = torch.randint(0, d["vocab"], (37,), generator=gen).tolist()
         ids_b = torch.randint(0, d["vocab"], (21,), generator=gen).tolist()
