@@ -1,7 +1,7 @@
 """Device arrays behind the cache manager's pages and state slots.
 
 Per cache number (a run item's `cache`): K and V arrays [pages, kv_heads, page_size, head_dim]
-in the engine's storage dtype (the reference's layout, src/memory/page_atten.zig:2,
+(V with its own width where a mixer asks for one) in the engine's storage dtype (the reference's layout, src/memory/page_atten.zig:2,
 src/backend/cuda/attention/attention.cu:12), and/or one state array [slots, *shape].  Cache
 numbers that share a group share its page ids; each keeps its own arrays.
 """
@@ -37,7 +37,7 @@ def bytes_per_page(kv_requests: Dict[int, KVRequest], group_index: Dict[int, int
                    dtype: torch.dtype) -> int:
     """Bytes one page id of `group` occupies over all cache numbers of that group."""
     elem = torch.empty((), dtype=dtype).element_size()
-    return sum(2 * r.num_kv_heads * page_size * r.head_dim * elem
+    return sum(r.num_kv_heads * page_size * (r.head_dim + r.value_dim) * elem
                for c, r in kv_requests.items() if group_index[c] == group)
 
 
@@ -50,8 +50,9 @@ class CacheStorage:
         self.kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self.state: Dict[int, torch.Tensor] = {}
         for c, r in kv_requests.items():
-            shape = (pages_per_group[group_index[c]], r.num_kv_heads, page_size, r.head_dim)
-            self.kv[c] = (torch.zeros(shape, dtype=dtype, device=device), torch.zeros(shape, dtype=dtype, device=device))
+            shape = (pages_per_group[group_index[c]], r.num_kv_heads, page_size)
+            self.kv[c] = (torch.zeros(shape + (r.head_dim,), dtype=dtype, device=device),
+                          torch.zeros(shape + (r.value_dim,), dtype=dtype, device=device))
         for c, r in state_requests.items():
             self.state[c] = torch.zeros((num_state_slots, *r.shape), dtype=r.dtype, device=device)
 
@@ -71,5 +72,5 @@ class CacheStorage:
             t.index_fill_(0, idx, 0)
 
     def bytes_held(self) -> int:
-        n = sum(k.numel() * k.element_size() * 2 for k, _ in self.kv.values())
+        n = sum(k.numel() * k.element_size() + v.numel() * v.element_size() for k, v in self.kv.values())
         return n + sum(t.numel() * t.element_size() for t in self.state.values())

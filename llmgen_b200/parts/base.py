@@ -69,6 +69,11 @@ class KVRequest:
     window: int              # 0 for FULL
     num_kv_heads: int
     head_dim: int
+    v_head_dim: int = 0      # width of a value where it differs from a key's (0: the same)
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -82,7 +87,7 @@ class StateRequest:
 class LayerCache:
     """What a run item hands to its mixer."""
     k: Optional[torch.Tensor] = None        # [pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None        # the same with the values' width (KVRequest.v_head_dim)
     group: int = 0                          # index into ctx.groups
     page_size: int = 0
     writes: bool = True                     # False: read what another run item wrote

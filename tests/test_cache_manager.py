@@ -124,3 +124,22 @@ def test_random_orders_keep_the_books(seed):
     assert m.all_free()
     with pytest.raises(KeyError):
         m.groups[0].slot_of("nobody", 0)
+
+
+def test_storage_gives_values_their_own_width_where_a_mixer_asks_for_one():
+    """A mixer's `KVRequest` may name another width for values than for keys: the arrays, and the bytes a page
+    costs (which the engine's page budget divides by), follow it."""
+    import torch
+    from llmgen_b200.cache.storage import CacheStorage, bytes_per_page, plan_groups
+    from llmgen_b200.parts.base import KVRequest
+    reqs = {0: KVRequest(FULL, 0, 2, 48), 1: KVRequest(FULL, 0, 3, 64, v_head_dim=16)}
+    groups, index = plan_groups(reqs)
+    assert len(groups) == 1 and index == {0: 0, 1: 0}
+    page = 8
+    assert bytes_per_page(reqs, index, 0, page, torch.bfloat16) == (2 * page * (48 + 48) + 3 * page * (64 + 16)) * 2
+    st = CacheStorage(reqs, {}, index, [5], page, 2, torch.float32, "cpu")
+    assert st.kv[0][0].shape == (5, 2, page, 48) and st.kv[0][1].shape == (5, 2, page, 48)
+    assert st.kv[1][0].shape == (5, 3, page, 64) and st.kv[1][1].shape == (5, 3, page, 16)
+    assert st.bytes_held() == 5 * bytes_per_page(reqs, index, 0, page, torch.float32)
+    lc = st.layer_cache(1, writes=True)
+    assert lc.k.shape[-1] == 64 and lc.v.shape[-1] == 16 and lc.page_size == page
