@@ -314,6 +314,9 @@ def main():
         The layers of such a step are replayed from the CUDA graph of its shape; wall time against device time shows
         what the host costs."""
         reqs = [f"mix{i}" for i in range(decoding)]
+        if decoding + 1 > ex.limits.max_num_seqs:
+            raise SystemExit(f"--mixed: {decoding} single tokens and a portion are {decoding + 1} sequences; "
+                             f"--batch {ex.limits.max_num_seqs} admits no more than that many")
         for r in reqs:
             assert ex.admit(r) and ex.reserve(r, 0, 512 + repeats + 3)
         assert ex.admit("mixp") and ex.reserve("mixp", 0, (repeats + 3) * portion)
