@@ -12,7 +12,9 @@
 // 3 one thread has TMA write boxes of [128, 64] (16 KB) from L2 into eight other buffers of the block's shared memory,
 // two boxes per barrier, four barriers in flight, each pair asked for again as soon as it has landed: shared memory then
 // serves the MMA's operand reads and TMA's writes.
-template <int N, int NACC, bool BMN = false, int NOISE = 0>
+// SETS: how many different operand sets (A and B tiles, 16 KB + N * 128 bytes each) the instructions walk through in
+// turn, a set per four instructions (one step of 64 along K), as a kernel's ring of stages does; 1: the same tiles again.
+template <int N, int NACC, bool BMN = false, int NOISE = 0, int SETS = 1>
 __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned long long* ns, int iters, int* err,
                                                    const __grid_constant__ CUtensorMap map, long long* tma_bytes) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -24,7 +26,8 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
     constexpr int TB = 4;                  // pairs of boxes in flight
     __shared__ uint64_t tma_bar[TB];
     const int warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < (16384 + N * 128) / 4; i += 128) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;
+    constexpr int SET_BYTES = 16384 + N * 128;
+    for (int i = threadIdx.x; i < SETS * SET_BYTES / 4; i += 128) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;
     if (threadIdx.x == 0) {
         abort_flag = 0;
         done = 0;
@@ -50,8 +53,9 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
         const unsigned long long t0 = tc::global_timer();
         for (int it = 0; it < iters; ++it) {
             const uint32_t d = tmem + (uint32_t)((it % NACC) * N);
+            const uint64_t off = (uint64_t)(((it % SETS) * SET_BYTES) >> 4);      // the start address is the descriptor's lowest field, in units of 16 bytes
 #pragma unroll
-            for (int k = 0; k < 4; ++k) tc::mma_bf16_ss(d, adesc + 2 * k, bdesc + (BMN ? 128 * k : 2 * k), idesc, true);
+            for (int k = 0; k < 4; ++k) tc::mma_bf16_ss(d, adesc + off + 2 * k, bdesc + off + (BMN ? 128 * k : 2 * k), idesc, true);
         }
         tc::mma_commit(tc::smem_u32(&bar));
         const bool ok = tc::mbar_wait(tc::smem_u32(&bar), 0, &abort_flag);
@@ -65,7 +69,7 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
         if (threadIdx.x == 32) {
             // a pair is asked for again as soon as it has landed.  Bounded by the issuing thread's end and by a count;
             // what is in flight at the end is waited for (bounded) before the block leaves.
-            const uint32_t ring = tc::smem_u32(smem) + 16384 + N * 128 + 1024;
+            const uint32_t ring = tc::smem_u32(smem) + SETS * SET_BYTES + 1024;
             const int row0 = (blockIdx.x % 32) * 256;
             long long boxes = 0;
             uint32_t phase[TB];
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
-                    tc::st_shared_v4(tc::smem_u32(smem) + 16384 + N * 128 + 1024 + (uint32_t)(((threadIdx.x * 8 + q + it) & 1023) << 4),
+                    tc::st_shared_v4(tc::smem_u32(smem) + SETS * SET_BYTES + 1024 + (uint32_t)(((threadIdx.x * 8 + q + it) & 1023) << 4),
                                      make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]));
             }
         }
@@ -118,15 +122,15 @@ __global__ void __launch_bounds__(128) rate_kernel(long long* cycles, unsigned l
 
 CUtensorMap g_map;        // [8192, 1024] bfloat16 in boxes of [128, 64], for the TMA writes of NOISE 3
 
-template <int N, int NACC, bool BMN = false, int NOISE = 0>
+template <int N, int NACC, bool BMN = false, int NOISE = 0, int SETS = 1>
 void run(int blocks, int iters) {
     long long* cyc; unsigned long long* ns; int* err; long long* tb;
     cudaMalloc(&cyc, blocks * 8); cudaMalloc(&ns, blocks * 8); cudaMalloc(&err, 4); cudaMemset(err, 0, 4);
     cudaMalloc(&tb, blocks * 8); cudaMemset(tb, 0, blocks * 8);
     // A, B, alignment slack, and what the noise writes: 16 KB for the stores, 128 KB for the TMA boxes
-    const int smem = 16384 + N * 128 + 1024 + 1024 + (NOISE == 3 ? 131072 : 16384);
-    cudaFuncSetAttribute(rate_kernel<N, NACC, BMN, NOISE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    for (int rep = 0; rep < 2; ++rep) rate_kernel<N, NACC, BMN, NOISE><<<blocks, 128, smem>>>(cyc, ns, iters, err, g_map, tb);
+    const int smem = SETS * (16384 + N * 128) + 1024 + 1024 + (NOISE == 3 ? 131072 : 16384);
+    cudaFuncSetAttribute(rate_kernel<N, NACC, BMN, NOISE, SETS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    for (int rep = 0; rep < 2; ++rep) rate_kernel<N, NACC, BMN, NOISE, SETS><<<blocks, 128, smem>>>(cyc, ns, iters, err, g_map, tb);
     cudaError_t e = cudaDeviceSynchronize();
     long long hc[148], hb[148]; unsigned long long hn[148]; int herr;
     cudaMemcpy(hc, cyc, blocks * 8, cudaMemcpyDeviceToHost); cudaMemcpy(hn, ns, blocks * 8, cudaMemcpyDeviceToHost);
@@ -137,7 +141,8 @@ void run(int blocks, int iters) {
     mc /= blocks; mn /= blocks; mb /= blocks;
     const double per = 4.0 * iters;
     printf("M=128 N=%3d acc=%d %s %s blocks=%3d: %7.1f cycles / mma, %6.1f ns / mma, %6.0f TFLOP/s all blocks", N, NACC, BMN ? "B MN-major" : "B K-major ",
-           NOISE == 0 ? "alone            " : NOISE == 1 ? "beside tmem loads" : NOISE == 2 ? "beside smem stores" : "beside TMA writes ", blocks,
+           NOISE == 0 ? (SETS > 1 ? "alone, 4 operand sets" : "alone            ") : NOISE == 1 ? "beside tmem loads" : NOISE == 2 ? "beside smem stores"
+                      : (SETS > 1 ? "beside TMA writes, 2 operand sets" : "beside TMA writes "), blocks,
            mc / per, mn / per, 2.0 * 128 * N * 16 * blocks / (mn / per) / 1e3);
     if (NOISE == 3) printf(", TMA wrote %.1f B/clk, the MMAs read %.1f B/clk", mb / mc, (128 + N) * 32.0 / (mc / per));
     printf(" (%s, err %d)\n", cudaGetErrorString(e), herr);
@@ -163,6 +168,9 @@ int main() {
         run<128, 1, false, 3>(blocks, iters);
         run<256, 1, false, 3>(blocks, iters);
         run<64, 1, false, 3>(blocks, iters);
+        run<128, 1, false, 0, 4>(blocks, iters);
+        run<256, 1, false, 0, 4>(blocks, iters);
+        run<128, 1, false, 3, 2>(blocks, iters);
     }
     return 0;
 }

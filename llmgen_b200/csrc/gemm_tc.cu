@@ -218,6 +218,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = tc::idesc_bf16_f32(PAIR ? 2 * BM : BM, BN);
+            // The descriptor of the ring's first byte, built once: every operand tile's descriptor is this one plus
+            // its byte offset in units of 16 (the start address is the descriptor's lowest field); built per
+            // instruction they cost the one issuing thread a few per cent (11.1 -> 10.9 us, 15.2 -> 14.9 us on the
+            // N = 1,024 products of a 2,048-token prompt).
+            const uint64_t ring_desc = tc::smem_desc_sw128(tc::smem_u32(smem));
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
@@ -239,18 +244,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int h = 0; h < KS; ++h) {
                         if (kb + h >= kb_end) break;            // a step beyond K holds zeros: nothing to add
-                        const uint32_t a_addr = tc::smem_u32(smem + s * L::STAGE_BYTES + h * L::SUB_BYTES);
-                        const uint32_t b_addr = a_addr + MB * L::A_BYTES;
+                        const uint64_t a_desc = ring_desc + (uint64_t)((s * L::STAGE_BYTES + h * L::SUB_BYTES) >> 4);
+                        const uint64_t b_desc = a_desc + (uint64_t)((MB * L::A_BYTES) >> 4);
+                        const bool first = kb + h == kb_begin;
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
-                            const uint64_t db = tc::smem_desc_sw128(b_addr + k * UMMA_K * 2);
-                            const bool add = ((kb + h - kb_begin) | k) != 0;
+                            const uint64_t db = b_desc + (uint64_t)((k * UMMA_K * 2) >> 4);
+                            const bool add = !first || k != 0;
                             if constexpr (PAIR) {
-                                tc::mma_bf16_ss_pair(acc, tc::smem_desc_sw128(a_addr + k * UMMA_K * 2), db, idesc, add);
+                                tc::mma_bf16_ss_pair(acc, a_desc + (uint64_t)((k * UMMA_K * 2) >> 4), db, idesc, add);
                             } else {
 #pragma unroll
                                 for (int i = 0; i < MB; ++i)
-                                    tc::mma_bf16_ss(acc + (uint32_t)(i * BN), tc::smem_desc_sw128(a_addr + i * L::A_BYTES + k * UMMA_K * 2),
+                                    tc::mma_bf16_ss(acc + (uint32_t)(i * BN), a_desc + (uint64_t)((i * L::A_BYTES + k * UMMA_K * 2) >> 4),
                                                     db, idesc, add);
                             }
                         }
