@@ -44,6 +44,7 @@ MODULES: Dict[str, List[str]] = {
     "gemv": [],
     "gemm_tc": [],
     "gemm_skinny": [],
+    "gemm_rows8": [],
     "attention": [],
     "attention_decode": [],
     "attention_tc": [],

@@ -390,6 +390,44 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
                                  c_int(1 if pdl else 0), _stream()))
 
 
+ROWS8_MAX_ROWS = 8           # what the kernel takes
+ROWS8_BEST_ROWS = 4          # up to here the engine uses it (decode steps of 1 / 2 / 4 / 8 sequences: +2.3 / +5.5 / +0.7 / -1.0 %)
+_rows8_plans = {}
+
+
+def gemm_rows8_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the product for up to 8 rows that loads W straight from global memory into `mma.sync`
+    (csrc/gemm_rows8.cu) takes these operands."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[0] > ROWS8_MAX_ROWS:
+        return False
+    lib = build.load("gemm_rows8")
+    M, K = a.shape
+    return bool(lib.llmk_gemm_rows8_usable(_ptr(a), _ptr(w), c_int(M), c_int(w.shape[0]), c_int(K), c_longlong(_row_stride(a)),
+                                           c_longlong(_row_stride(w))))
+
+
+def gemm_rows8_slices(N: int, K: int) -> int:
+    """Into how many slices of K that product cuts [M, K] x [N, K]^T."""
+    v = _rows8_plans.get((N, K))
+    if v is None:
+        v = int(build.load("gemm_rows8").llmk_gemm_rows8_slices(c_int(N), c_int(K)))
+        _rows8_plans[(N, K)] = v
+    return v
+
+
+def gemm_rows8(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[slices, M, N] (float32, contiguous; slices = gemm_rows8_slices(N, K)) = the partial sums of a[M, K] @ w[N, K]^T
+    over the slices of K, M <= 8."""
+    lib = build.load("gemm_rows8")
+    M, K = a.shape
+    N = w.shape[0]
+    if out.dtype != torch.float32 or not out.is_contiguous() or tuple(out.shape) != (gemm_rows8_slices(N, K), M, N) or w.shape[1] != K:
+        raise KernelError(f"gemm_rows8: a{list(a.shape)} w{list(w.shape)} need contiguous float32 slices "
+                          f"[{gemm_rows8_slices(N, K)}, {M}, {N}], got {list(out.shape)} {out.dtype}")
+    _check(lib, lib.llmk_gemm_rows8(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(a)),
+                                    c_longlong(_row_stride(w)), _stream()))
+
+
 SKINNY_MAX_ROWS = 256        # what the kernel takes
 SKINNY_BEST_ROWS = 32        # up to here it is the faster product (measured at 16, 32, 48 and 64 rows against the tiled product cut along K)
 # most bytes of float32 slices one cut product leaves: about one 128 x 128 item per SM for the tiled product,

@@ -1,7 +1,10 @@
 """y = x W^T: the one place that chooses a matrix-product kernel.
 
     float32 engine   CUDA-core kernel with a fixed summation order (csrc/gemm_simt.cu)
-    bfloat16 engine  up to 64 rows: the weight-streaming tensor-core kernel with swapped operands
+    bfloat16 engine  up to 8 rows, products that leave slices (qkv, o_proj, down_proj of a decode step): W straight
+                     from global memory into `mma.sync`, all of it asked for before the wait for the kernel that
+                     makes x (csrc/gemm_rows8.cu);
+                     up to 64 rows: the weight-streaming tensor-core kernel with swapped operands
                      (csrc/gemm_skinny.cu), cut along K so that every SM streams a share of W; more rows: the
                      tiled tensor-core kernel (csrc/gemm_tc.cu: TMA, tcgen05.mma, tensor memory), cut along K
                      too while its tiles are too few for the SMs (a few hundred rows).  Either way the float32
@@ -20,7 +23,7 @@ import torch
 
 from ..kernels import ops
 
-GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny")
+GEMM_MODULES = ("gemm_simt", "gemv", "gemm_tc", "gemm_skinny", "gemm_rows8")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -44,6 +47,12 @@ def linear_sliced(ws, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: to
     """x W^T into the workspace buffer `name`: the finished [M, N] array, or, when the product is cut
     along K, an `ops.Partials` for a consumer that adds the slices."""
     M, N, K = x.shape[0], w.shape[0], x.shape[1]
+    if 0 < M <= ops.ROWS8_BEST_ROWS and ops.gemm_rows8_usable(x, w):
+        # up to 8 rows: W straight from global memory into mma.sync, the fewest dependent steps (csrc/gemm_rows8.cu)
+        slices = ops.gemm_rows8_slices(N, K)
+        part = ws.flat(name + "_slices", slices * M * N, torch.float32).view(slices, M, N)
+        ops.gemm_rows8(part, x, w)
+        return ops.Partials(part)
     if M > 0 and x.dtype == torch.bfloat16 and ops.gemm_tc_usable(x, w):
         few = M <= ops.SKINNY_BEST_ROWS
         splits = ops.gemm_skinny_splits(M, N, K) if few else ops.gemm_tc_splits(M, N, K)

@@ -316,6 +316,42 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
     assert bool((buf[M] == 7.0).all()) and bool((buf[:, N:] == 7.0).all())
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 1024), (8, 1024, 2048), (8, 1024, 3072), (1, 6144, 1024), (3, 72, 136), (7, 1000, 1032),
+                                   (5, 16, 8), (8, 130, 3072), (2, 48, 40), (4, 100, 520)])
+def test_gemm_rows8(ops, M, N, K):
+    """The product for up to 8 rows (W straight from global memory into mma.sync): its float32 slices add up to the
+    product (float64 reference of the same bfloat16 operands); tails in N (no multiple of 16), in K (no multiple of
+    32, slices that do not divide it), every M from 1 to 8; values that only the last k, the last row of W and each
+    half of an MMA's 16 rows see; strided operands; refusals."""
+    torch.manual_seed(80 + M + N)
+    a = torch.randn(M, K + 8).to(torch.bfloat16)[:, :K]              # rows 16-byte aligned, not contiguous
+    w = (torch.randn(N, K) * 0.5).to(torch.bfloat16)
+    a[M - 1, K - 1] = 8.0
+    w[N - 1, K - 1] = 8.0
+    w[min(N - 1, 9), 0] = -6.0
+    ad, wd = dev(a.contiguous())[:, :], dev(w)
+    big = torch.zeros(M, K + 8, dtype=torch.bfloat16, device="cuda")
+    big[:, :K] = ad
+    ad = big[:, :K]
+    assert ops.gemm_rows8_usable(ad, wd)
+    slices = ops.gemm_rows8_slices(N, K)
+    assert 1 <= slices <= 8
+    out = torch.full((slices + 1, M, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_rows8(out[:slices], ad, wd)
+    torch.cuda.synchronize()
+    assert bool((out[slices] == 7.0).all())
+    ref = a.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    err = float((out[:slices].double().sum(0).cpu() - ref).abs().max())
+    assert err < 2e-5 * scale, (err, scale)
+    if K > 32 * 12:          # more than one slice: each holds its own columns of K only
+        assert slices > 1 and float(out[0].abs().max()) > 0 and float((out[0] - out[:slices].sum(0)).abs().max()) > 0
+    # 9 rows, a K of no whole 16-byte pieces, a K beyond 8 slices: refused
+    assert not ops.gemm_rows8_usable(torch.zeros(9, K, dtype=torch.bfloat16, device="cuda"), wd)
+    assert not ops.gemm_rows8_usable(torch.zeros(2, 3080, dtype=torch.bfloat16, device="cuda"), torch.zeros(16, 3080, dtype=torch.bfloat16, device="cuda"))
+    assert not ops.gemm_rows8_usable(torch.zeros(2, 36, dtype=torch.bfloat16, device="cuda")[:, :34], torch.zeros(16, 34, dtype=torch.bfloat16, device="cuda"))
+
+
 @pytest.mark.parametrize("M,N,K,splits", [(96, 1024, 2048, 16), (128, 4096, 1024, 4), (300, 1000, 1032, 3), (512, 1024, 3072, 4),
                                           (70, 130, 520, 3), (1024, 1024, 2048, 2), (257, 72, 136, 2)])
 def test_gemm_tc_cut_along_k(ops, M, N, K, splits):
