@@ -12,10 +12,10 @@
 // Measured against the tcgen05 few-rows product (csrc/gemm_skinny.cu: TMA ring, mbarriers, tensor-memory accumulator)
 // on the decode products of the 0.6B shape at 8 rows, graph of 40 launches of one product, weights streamed from HBM:
 // qkv 3.57 -> 3.0 us, o_proj 3.02 -> 2.03, down_proj 3.55 -> 2.32.  Inside a decode step the gain is smaller, because
-// there a product's time is mostly the wait for the kernel before: 0.913 against 0.911 ms a step at 8 sequences,
-// 1,286 against 1,253 tokens/s at one.  What the loads before the wait are worth shows when they are held back:
-// with 6, 3 and 0 of a warp's 12 blocks of W asked for before the wait the step takes 1.03, 1.11 and 1.22 ms.
-// Above 8 rows the tcgen05 product keeps its place.
+// there a product's time is mostly the wait for the kernel before: steps of 1 / 2 / 4 / 8 sequences take 0.780 / 0.773 /
+// 0.898 / 0.918 ms with this kernel against 0.798 / 0.816 / 0.905 / 0.910 ms with the tcgen05 one, so the engine uses it
+// up to 4 rows (`ops.ROWS8_BEST_ROWS`).  What the loads before the wait are worth shows when they are held back: with
+// 6, 3 and 0 of a warp's 12 blocks of W asked for before the wait a step of 8 sequences takes 1.03, 1.11 and 1.22 ms.
 //
 // The reference streams weights with a GEMV kernel for one row and calls cublasGemmEx for more
 // (src/backend/cuda/linear/linear.cu:22-96).

@@ -1,7 +1,7 @@
 """y = x W^T: the one place that chooses a matrix-product kernel.
 
     float32 engine   CUDA-core kernel with a fixed summation order (csrc/gemm_simt.cu)
-    bfloat16 engine  up to 8 rows, products that leave slices (qkv, o_proj, down_proj of a decode step): W straight
+    bfloat16 engine  up to 4 rows, products that leave slices (qkv, o_proj, down_proj of a decode step): W straight
                      from global memory into `mma.sync`, all of it asked for before the wait for the kernel that
                      makes x (csrc/gemm_rows8.cu);
                      up to 64 rows: the weight-streaming tensor-core kernel with swapped operands
@@ -48,7 +48,7 @@ def linear_sliced(ws, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: to
     along K, an `ops.Partials` for a consumer that adds the slices."""
     M, N, K = x.shape[0], w.shape[0], x.shape[1]
     if 0 < M <= ops.ROWS8_BEST_ROWS and ops.gemm_rows8_usable(x, w):
-        # up to 8 rows: W straight from global memory into mma.sync, the fewest dependent steps (csrc/gemm_rows8.cu)
+        # a few rows: W straight from global memory into mma.sync, the fewest dependent steps (csrc/gemm_rows8.cu)
         slices = ops.gemm_rows8_slices(N, K)
         part = ws.flat(name + "_slices", slices * M * N, torch.float32).view(slices, M, N)
         ops.gemm_rows8(part, x, w)
