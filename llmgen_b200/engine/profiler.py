@@ -305,7 +305,7 @@ def _cost_all_operands(a, info: PassInfo) -> Tuple[int, int]:
 OP_COSTS: Dict[str, Callable] = {
     "embed_rows": _cost_embed, "add_rmsnorm": _cost_norm, "silu_mul": _cost_all_operands, "widen": _cost_all_operands,
     "attn_prep": _cost_attn_prep, "gemm_simt": _cost_product, "gemv_bf16": _cost_product, "gemm_tc": _cost_product,
-    "gemm_skinny": _cost_product, "gemm_rows8": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,
+    "gemm_skinny": _cost_product, "gemm_rows8": _cost_product, "gemm_rows8_gated": _cost_product, "paged_attention": _cost_attention, "attention_decode": _cost_attention,
     "attention_tc": _cost_attention, "sample": _cost_all_operands,
 }
 

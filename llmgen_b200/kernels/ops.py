@@ -392,6 +392,7 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
 
 ROWS8_MAX_ROWS = 8           # what the kernel takes
 ROWS8_BEST_ROWS = 4          # up to here the engine uses it (decode steps of 1 / 2 / 4 / 8 sequences: +2.3 / +5.5 / +0.7 / -1.0 %)
+ROWS8_GATED_BEST_ROWS = 1    # and its gated form (a step of one sequence 0.780 -> 0.767 ms; of 2 and 4: 0.773 -> 0.817, 0.898 -> 1.015)
 _rows8_plans = {}
 
 
@@ -426,6 +427,27 @@ def gemm_rows8(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
                           f"[{gemm_rows8_slices(N, K)}, {M}, {N}], got {list(out.shape)} {out.dtype}")
     _check(lib, lib.llmk_gemm_rows8(_ptr(out), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_longlong(_row_stride(a)),
                                     c_longlong(_row_stride(w)), _stream()))
+
+
+def gemm_rows8_gated_usable(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the gated form of that product (w interleaving 16 gate and 16 up rows) takes these operands."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[0] > ROWS8_MAX_ROWS:
+        return False
+    lib = build.load("gemm_rows8")
+    M, K = a.shape
+    return bool(lib.llmk_gemm_rows8_gated_usable(_ptr(a), _ptr(w), c_int(M), c_int(w.shape[0]), c_int(K), c_longlong(_row_stride(a)),
+                                                 c_longlong(_row_stride(w))))
+
+
+def gemm_rows8_gated(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[M, N/2] (bfloat16) = silu(gate) * up of a[M, K] @ w[N, K]^T, w interleaving gate and up rows in groups of 16, M <= 8."""
+    lib = build.load("gemm_rows8")
+    M, K = a.shape
+    N = w.shape[0]
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N // 2) or w.shape[1] != K:
+        raise KernelError(f"gemm_rows8_gated: a{list(a.shape)} w{list(w.shape)} need a bfloat16 result [{M}, {N // 2}], got {list(out.shape)} {out.dtype}")
+    _check(lib, lib.llmk_gemm_rows8_gated(_ptr(out), c_longlong(_row_stride(out)), _ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K),
+                                          c_longlong(_row_stride(a)), c_longlong(_row_stride(w)), _stream()))
 
 
 SKINNY_MAX_ROWS = 256        # what the kernel takes

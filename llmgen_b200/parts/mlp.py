@@ -73,7 +73,10 @@ class GatedMLP(FeedForward):
         act = ws.buffer("ffn_act", T, F, self.dtype)
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
         cluster = min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) if gated and T <= ops.SKINNY_CLUSTER_MAX_ROWS else 1
-        if cluster >= 2:
+        if gated and T <= ops.ROWS8_GATED_BEST_ROWS and ops.gemm_rows8_gated_usable(x, self.w_gate_up):
+            # a few rows: W straight from global memory into mma.sync, the activation in the same kernel (csrc/gemm_rows8.cu)
+            ops.gemm_rows8_gated(act, x, self.w_gate_up)
+        elif cluster >= 2:
             # few rows: K is cut, the slices are added up inside a thread-block cluster and the activation
             # follows there, so neither the packed product nor a kernel for the activation is needed
             # (0.982 -> 0.967 ms a decode step at batch 8 against slices and an activation kernel)

@@ -352,6 +352,32 @@ def test_gemm_rows8(ops, M, N, K):
     assert not ops.gemm_rows8_usable(torch.zeros(2, 36, dtype=torch.bfloat16, device="cuda")[:, :34], torch.zeros(16, 34, dtype=torch.bfloat16, device="cuda"))
 
 
+@pytest.mark.parametrize("M,F,K", [(8, 3072, 1024), (1, 3072, 1024), (4, 48, 128), (3, 176, 264), (7, 16, 8), (5, 1024, 1536), (2, 80, 1000)])
+def test_gemm_rows8_gated(ops, M, F, K):
+    """The gated form: silu(gate) * up of up to 8 rows against a float64 reference, W's rows interleaved in groups of
+    16, every share of K that four warps take (also none for the last warps), F no multiple of the block's 16 columns
+    beyond it; the surroundings of the result are left alone; a K that the warps' registers cannot hold is refused."""
+    from llmgen_b200.parts.mlp import interleave_gate_up
+    torch.manual_seed(190 + M + F)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    wg = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+    a[M - 1, K - 1] = 4.0
+    wg[F - 1, K - 1] = 2.0
+    wu[min(F - 1, 9), 0] = -3.0
+    w = dev(interleave_gate_up(wg, wu))
+    assert ops.gemm_rows8_gated_usable(dev(a), w)
+    buf = torch.full((M + 1, F + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_rows8_gated(buf[:M, :F], dev(a), w)
+    torch.cuda.synchronize()
+    g = a.double() @ wg.double().t()
+    u = a.double() @ wu.double().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((buf[:M, :F].double().cpu() - ref).abs().max()) < 8e-3 * max(1.0, float(ref.abs().max()))
+    assert bool((buf[M] == 7.0).all()) and bool((buf[:, F:] == 7.0).all())
+    assert not ops.gemm_rows8_gated_usable(torch.zeros(2, 2048, dtype=torch.bfloat16, device="cuda"), torch.zeros(64, 2048, dtype=torch.bfloat16, device="cuda"))
+
+
 @pytest.mark.parametrize("M,N,K,splits", [(96, 1024, 2048, 16), (128, 4096, 1024, 4), (300, 1000, 1032, 3), (512, 1024, 3072, 4),
                                           (70, 130, 520, 3), (1024, 1024, 2048, 2), (257, 72, 136, 2)])
 def test_gemm_tc_cut_along_k(ops, M, N, K, splits):
