@@ -71,13 +71,19 @@ def products(rows=(1, 8, 64, 256, 512, 2048)):
             x = _bf(M, K)
             y_ref = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
             t_ref = time_us(lambda i: ref.linear(y_ref, x, ws[i]), n)
-            # the choice parts/linear.py makes: the few-rows product up to SKINNY_BEST_ROWS, the tiled one above,
-            # either of them cut along K (float32 slices for the consumer) where that fills the SMs
+            # the choice parts/linear.py makes: W straight into mma.sync up to ROWS8_BEST_ROWS, the few-rows tcgen05
+            # product up to SKINNY_BEST_ROWS, the tiled one above, each cut along K (float32 slices for the consumer)
+            # where that fills the SMs
             few = M <= ops.SKINNY_BEST_ROWS
             splits = ops.gemm_skinny_splits(M, N, K) if few else ops.gemm_tc_splits(M, N, K)
             if name == "lm_head":
                 splits = 1                                   # float32 logits, never cut
-            if splits > 1:
+            if name != "lm_head" and M <= ops.ROWS8_BEST_ROWS and ops.gemm_rows8_usable(x, ws[0]):
+                slices = ops.gemm_rows8_slices(N, K)
+                part8 = torch.empty(slices, M, N, dtype=torch.float32, device="cuda")
+                ours = lambda i: ops.gemm_rows8(part8, x, ws[i])
+                what = f"gemm_rows8 (mma.sync from global memory), {slices} slices of K"
+            elif splits > 1:
                 part = torch.empty(splits, M, N, dtype=torch.float32, device="cuda")
                 if few:
                     ours = lambda i: ops.gemm_skinny(part, x, ws[i], ops.SKINNY_PARTIAL)
@@ -112,7 +118,10 @@ def products(rows=(1, 8, 64, 256, 512, 2048)):
             lib.cuda_silu(c_void_p(g.data_ptr()), c_void_p(g.data_ptr()), c_size_t(g.numel()))
             lib.cuda_mul(c_void_p(a.data_ptr()), c_void_p(g.data_ptr()), c_void_p(u.data_ptr()), c_size_t(g.numel()))
         act = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
-        if M <= ops.SKINNY_CLUSTER_MAX_ROWS:
+        if M <= ops.ROWS8_GATED_BEST_ROWS and ops.gemm_rows8_gated_usable(x, packed[0]):
+            ours = lambda i: ops.gemm_rows8_gated(act, x, packed[i])
+            what = "gemm_rows8 (mma.sync from global memory), gated"
+        elif M <= ops.SKINNY_CLUSTER_MAX_ROWS:
             cl = min(ops.gemm_skinny_cluster_splits(M, 2 * F, H), 4)
             ours = lambda i: ops.gemm_skinny(act, x, packed[i], ops.SKINNY_CLUSTER_GATED, splits=cl)
             what = f"gemm_skinny, cluster of {cl}, gated"
