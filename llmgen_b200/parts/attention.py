@@ -227,12 +227,15 @@ class GQAAttention(Mixer):
         bound = max(ctx.max_ctx_bound, ctx.max_ctx, 1)
         visible = min(bound, self.window) if self.window else bound
         blocks = max(1, S * self.nkv * chunks)
-        # as many blocks as are resident at a time (2 per SM), at least 128 keys a part, at most 64 parts
-        parts = max(1, min(int(DECODE_BLOCKS_PER_SM * self.sm_count) // blocks, visible // 128, 64))
-        if 4 < parts <= 8 and parts * blocks > self.sm_count:
-            # clusters of 5 to 8 blocks that fill every place of every SM leave the kernels after this one no room to
-            # start under it (a step of 4 sequences: 0.898 ms with 8 parts, 0.801 with 4); a block an SM then
-            parts = max(4, min(parts, self.sm_count // blocks))
+        # Key parts: at least 128 keys each, at most 64.  A block an SM where that still cuts every sequence's keys
+        # into 4 parts or more (up to 4 sequences on 8 kv heads): two blocks an SM (the most that are resident) leave
+        # the kernels after this one no room to start, and to ask for their weights, under it (a step of 4 sequences
+        # of 640 keys: 0.898 ms with 8 parts, 0.798 with 4; of 1,500 keys: 0.994 with 9, 0.888 with 4).  Two blocks
+        # an SM otherwise: with 8 sequences 2 parts are too few (0.935 against 0.907 ms with 4; at 1,500 keys 1.095
+        # against 1.022).
+        one_each = self.sm_count // blocks
+        target = one_each if one_each >= 4 else (2 * self.sm_count) // blocks
+        parts = max(1, min(target, visible // 128, 64))
         scratch = counters = None
         if parts > 1:
             scratch = ws.flat("attn_decode_split", ops.attention_decode_scratch_floats(S, self.nq, self.hd, parts),
@@ -242,9 +245,6 @@ class GQAAttention(Mixer):
         ops.attention_decode(o, q, q.stride(0) if q is not None else 0, cache.k, cache.v, group.block_tables,
                              group.max_blocks, ctx.ctx_len, ctx.cu_q, S, self.nq, self.nkv, self.hd, cache.page_size,
                              self.window, scale, parts, bound, scratch, counters, **(prep or {}))
-
-
-DECODE_BLOCKS_PER_SM = 2      # blocks of the decode attention that an SM holds at a time: the key parts fill them
 
 
 register_mixer("attention", GQAAttention)
