@@ -418,7 +418,7 @@ def main():
         "metric": f"decode tok/s at batch {args.batch} ({shape_name}, bf16, random weights, {args.prompt_tokens}-token prompts)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": value / PUBLISHED_B8 if args.shape == "0.6b" else None,
-        "vs_baseline_note": "BASELINE.md's numbers are the reference on an RTX 3090 (8 requests end to end: 1,666 tokens/s); "
+        "vs_baseline_note": "the published numbers are the reference's on an RTX 3090 (8 requests end to end: 1,666 tokens/s); "
                             "another machine, not a same-hardware ratio",
         "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random-init weights (seed 2)",
